@@ -1,0 +1,111 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions,
+// the C ABI's error reporting.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+#include <cstring>
+
+// Element-type codes of the C ABI.
+enum : int { OI_F32 = 0, OI_BF16 = 1 };
+
+// Error codes returned by every entry point (0 = success). CUDA runtime errors
+// are returned as 1000 + cudaError_t.
+enum : int {
+  OI_OK = 0,
+  OI_ERR_BAD_ARGUMENT = 1,   // a size or dtype the kernel refuses
+  OI_ERR_UNSUPPORTED = 2,
+  OI_ERR_TOO_LARGE = 3,
+  OI_ERR_CUDA = 1000,
+};
+
+#define OI_API extern "C" __attribute__((visibility("default")))
+
+void oi_set_error(const char* fmt, ...);
+
+#define OI_REQUIRE(cond, ...)            \
+  do {                                   \
+    if (!(cond)) {                       \
+      oi_set_error(__VA_ARGS__);         \
+      return OI_ERR_BAD_ARGUMENT;        \
+    }                                    \
+  } while (0)
+
+#define OI_CHECK_LAUNCH()                                                     \
+  do {                                                                        \
+    cudaError_t e__ = cudaGetLastError();                                     \
+    if (e__ != cudaSuccess) {                                                 \
+      oi_set_error("%s:%d: launch failed: %s", __FILE__, __LINE__,            \
+                   cudaGetErrorString(e__));                                  \
+      return OI_ERR_CUDA + (int)e__;                                          \
+    }                                                                         \
+  } while (0)
+
+#define OI_CHECK_CUDA(expr)                                                   \
+  do {                                                                        \
+    cudaError_t e__ = (expr);                                                 \
+    if (e__ != cudaSuccess) {                                                 \
+      oi_set_error("%s:%d: %s failed: %s", __FILE__, __LINE__, #expr,         \
+                   cudaGetErrorString(e__));                                  \
+      return OI_ERR_CUDA + (int)e__;                                          \
+    }                                                                         \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+// Load element i of an array whose element type is only known at run time.
+__device__ __forceinline__ float load_as_f32(const void* p, int dtype, size_t i) {
+  return dtype == OI_F32 ? reinterpret_cast<const float*>(p)[i]
+                         : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum with a fixed tree (same order whatever else runs): every thread
+// gets the result. `scratch` holds at least 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }

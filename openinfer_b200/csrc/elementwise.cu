@@ -1,0 +1,202 @@
+// Embedding gather, RMSNorm (with fused residual add or row gather), SiLU*mul.
+//
+// What each computes follows the reference's ops (embedding:
+// pegainfer-kernels/csrc/shared/elementwise.cu:368-384; RMSNorm and fused add+RMSNorm:
+// csrc/shared/flashinfer_norm.cu:39-132, 204-210; SiLU*mul: elementwise.cu:259-273), with all
+// arithmetic in float32 and ONE rounding to the storage type at the output.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]
+// ---------------------------------------------------------------------------
+template <typename TO, typename TW>
+__global__ void embedding_kernel(TO* __restrict__ out, const TW* __restrict__ table,
+                                 const int* __restrict__ ids, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host validates ids; never read outside
+  const TW* src = table + (size_t)id * hidden;
+  TO* dst = out + (size_t)t * hidden;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) dst[d] = from_f32<TO>(to_f32(src[d]));
+}
+
+// same element type on both sides and rows that are whole 16-byte vectors: a plain copy
+__global__ void embedding_vec_kernel(uint4* __restrict__ out, const uint4* __restrict__ table,
+                                     const int* __restrict__ ids, int vecs_per_row, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const uint4* src = table + (size_t)id * vecs_per_row;
+  uint4* dst = out + (size_t)t * vecs_per_row;
+  for (int d = threadIdx.x; d < vecs_per_row; d += blockDim.x) dst[d] = src[d];
+}
+
+OI_API int oi_embedding(void* out, int out_dtype, const void* table, int table_dtype,
+                        const int* ids, int tokens, int hidden, int vocab, void* stream) {
+  OI_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes tokens=%d hidden=%d vocab=%d",
+             tokens, hidden, vocab);
+  if (tokens == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t esize = out_dtype == OI_F32 ? 4 : 2;
+  if (out_dtype == table_dtype && (hidden * esize) % 16 == 0 &&
+      ((uintptr_t)out % 16 == 0) && ((uintptr_t)table % 16 == 0)) {
+    const int vecs = (int)(hidden * esize / 16);
+    embedding_vec_kernel<<<tokens, vecs < 256 ? ((vecs + 31) / 32) * 32 : 256, 0, s>>>(
+        (uint4*)out, (const uint4*)table, ids, vecs, vocab);
+  } else if (out_dtype == OI_F32 && table_dtype == OI_F32) {
+    embedding_kernel<float, float><<<tokens, 256, 0, s>>>((float*)out, (const float*)table, ids, hidden, vocab);
+  } else if (out_dtype == OI_BF16 && table_dtype == OI_BF16) {
+    embedding_kernel<bf16, bf16><<<tokens, 256, 0, s>>>((bf16*)out, (const bf16*)table, ids, hidden, vocab);
+  } else if (out_dtype == OI_F32 && table_dtype == OI_BF16) {
+    embedding_kernel<float, bf16><<<tokens, 256, 0, s>>>((float*)out, (const bf16*)table, ids, hidden, vocab);
+  } else if (out_dtype == OI_BF16 && table_dtype == OI_F32) {
+    embedding_kernel<bf16, float><<<tokens, 256, 0, s>>>((bf16*)out, (const float*)table, ids, hidden, vocab);
+  } else {
+    OI_REQUIRE(false, "embedding: unknown dtype codes %d/%d", out_dtype, table_dtype);
+  }
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm. One block per output row.
+//   delta != null : x[row] <- round(x[row] + delta[row]) first (the residual sum, stored), and the
+//                   norm is taken of the ROUNDED sum (flashinfer_norm.cu:76-83, 107-124).
+//   row_idx != null : output row r reads x[row_idx[r]] (+ delta[row_idx[r]], not stored): the rows
+//                   whose logits are wanted.
+//   out[r] = round( x * rsqrt(mean(x^2) + eps) * (w_offset + w) )
+// ---------------------------------------------------------------------------
+template <typename T, bool kCache>
+__global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* __restrict__ delta,
+                               const void* __restrict__ w, int w_dtype, const int* __restrict__ row_idx,
+                               int hidden, float eps, float w_offset) {
+  extern __shared__ float row_cache[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
+  T* xr = x + src * hidden;
+  const T* dr = delta ? delta + src * hidden : nullptr;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    float v = to_f32(xr[d]);
+    if (dr) {
+      v = to_f32(from_f32<T>(v + to_f32(dr[d])));
+      if (!row_idx) xr[d] = from_f32<T>(v);  // gathered rows may repeat: the sum is not stored
+    }
+    if (kCache) row_cache[d] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  T* orow = out + (size_t)r * hidden;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    float v;
+    if (kCache) v = row_cache[d];
+    else if (dr && row_idx) v = to_f32(from_f32<T>(to_f32(xr[d]) + to_f32(dr[d])));
+    else v = to_f32(xr[d]);
+    orow[d] = from_f32<T>(v * inv * (w_offset + load_as_f32(w, w_dtype, d)));
+  }
+}
+
+template <typename T>
+static int launch_rmsnorm(void* out, void* x, const void* delta, const void* w, int w_dtype,
+                          const int* row_idx, int rows, int hidden, float eps, float w_offset,
+                          cudaStream_t s) {
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem <= 48 * 1024) {
+    rmsnorm_kernel<T, true><<<rows, threads, smem, s>>>((T*)out, (T*)x, (const T*)delta, w, w_dtype,
+                                                        row_idx, hidden, eps, w_offset);
+  } else {
+    rmsnorm_kernel<T, false><<<rows, threads, 0, s>>>((T*)out, (T*)x, (const T*)delta, w, w_dtype,
+                                                      row_idx, hidden, eps, w_offset);
+  }
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+OI_API int oi_rmsnorm(void* out, void* x, const void* delta, int dtype, const void* w, int w_dtype,
+                      const int* row_idx, int rows, int hidden, float eps, float w_offset,
+                      void* stream) {
+  OI_REQUIRE(rows >= 0 && hidden > 0, "rmsnorm: bad sizes rows=%d hidden=%d", rows, hidden);
+  OI_REQUIRE(!(delta && out == x), "rmsnorm: with a residual add, out must not alias x");
+  if (rows == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == OI_F32) return launch_rmsnorm<float>(out, x, delta, w, w_dtype, row_idx, rows, hidden, eps, w_offset, s);
+  if (dtype == OI_BF16) return launch_rmsnorm<bf16>(out, x, delta, w, w_dtype, row_idx, rows, hidden, eps, w_offset, s);
+  OI_REQUIRE(false, "rmsnorm: unknown dtype code %d", dtype);
+}
+
+// ---------------------------------------------------------------------------
+// residual add without a norm: x <- round(x + delta)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_inplace_kernel(T* __restrict__ x, const T* __restrict__ delta, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = from_f32<T>(to_f32(x[i]) + to_f32(delta[i]));
+}
+
+OI_API int oi_add_inplace(void* x, const void* delta, int dtype, long long n, void* stream) {
+  OI_REQUIRE(n >= 0, "add: bad size %lld", n);
+  if (n == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  if (dtype == OI_F32) add_inplace_kernel<float><<<blocks, 256, 0, s>>>((float*)x, (const float*)delta, (size_t)n);
+  else if (dtype == OI_BF16) add_inplace_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)x, (const bf16*)delta, (size_t)n);
+  else OI_REQUIRE(false, "add: unknown dtype code %d", dtype);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// SiLU * mul on a fused [rows, 2*inter] gate|up buffer: out[r, i] = silu(g) * u
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / inter, c = i - r * inter;
+    const float g = to_f32(gate_up[r * 2 * inter + c]);
+    const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+// 8 bf16 per thread when inter is a multiple of 8
+__global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up,
+                                       int inter8, size_t n8) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / inter8, c = i - r * inter8;
+    uint4 gv = gate_up[r * 2 * inter8 + c];
+    uint4 uv = gate_up[r * 2 * inter8 + inter8 + c];
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]);
+      const float2 u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+    }
+    out[i] = ov;
+  }
+}
+
+OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, void* stream) {
+  OI_REQUIRE(rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
+  if (rows == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t n = (size_t)rows * inter;
+  if (dtype == OI_BF16 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
+    const size_t n8 = n / 8;
+    const int blocks = (int)((n8 + 255) / 256 > 148 * 16 ? 148 * 16 : (n8 + 255) / 256);
+    silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((uint4*)out, (const uint4*)gate_up, inter / 8, n8);
+  } else {
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    if (dtype == OI_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gate_up, inter, n);
+    else if (dtype == OI_BF16) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, n);
+    else OI_REQUIRE(false, "silu_mul: unknown dtype code %d", dtype);
+  }
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}

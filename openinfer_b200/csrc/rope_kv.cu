@@ -1,0 +1,108 @@
+// Fused per-head q/k norm + rotate-half position rotation + write of K and V into the paged cache.
+//
+// One warp per (token, head) over the fused projection output [tokens, (nq + 2*nkv) * hd]:
+//   q heads: norm, rotate, written back in place (attention reads q from this buffer);
+//   k heads: norm, rotate, written to the K page of (request, position);
+//   v heads: copied to the V page.
+// Formulas: per-head RMSNorm before the rotation with the layer's eps, v untouched
+// (pegainfer-kernels/csrc/shared/prefill_attention.cu:84-99); rotate-half over the pair
+// (d, d + half) (prefill_attention.cu:101-122); cache address page*page_stride + (pos % P)*nkv*hd
+// + head*hd (pegainfer-kv-cache/src/layout.rs:5-33). The reference replaces three kernels' worth
+// of traffic (norm+rope, then a separate scatter: csrc/shared/paged_attention.cu:309-348) — here
+// K and V go from the projection output straight to their page. Arithmetic is float32 with one
+// rounding at the store; cos/sin come from float32 tables [max_pos, rot_half].
+#include "common.cuh"
+
+template <typename T>
+__global__ void qk_norm_rope_kv_kernel(
+    T* __restrict__ qkv, int row_stride, int nq, int nkv, int hd,
+    const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_dtype, float eps,
+    float w_offset, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+    int rot_half, int max_pos, const int* __restrict__ positions, const int* __restrict__ slots,
+    T* __restrict__ k_cache, T* __restrict__ v_cache, long long page_stride, int page_size,
+    int heads_total, int tokens) {
+  const int lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)tokens * heads_total) return;
+  const int token = (int)(gw / heads_total);
+  const int head = (int)(gw - (long long)token * heads_total);
+  T* src = qkv + (size_t)token * row_stride + (size_t)head * hd;
+
+  const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
+  T* dst = src;  // q: in place
+  if (kind != 0) {
+    const int slot = slots[token];
+    if (slot < 0) return;  // a padding row: nothing to store
+    const int kvh = kind == 1 ? head - nq : head - nq - nkv;
+    T* base = kind == 1 ? k_cache : v_cache;
+    dst = base + (size_t)(slot / page_size) * page_stride +
+          (size_t)(slot % page_size) * nkv * hd + (size_t)kvh * hd;
+  }
+  if (kind == 2) {
+    for (int d = lane; d < hd; d += 32) dst[d] = src[d];
+    return;
+  }
+  const void* w = kind == 0 ? q_norm_w : k_norm_w;
+  float inv = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      const float v = to_f32(src[d]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)hd + eps);
+  }
+  int pos = positions[token];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // admission bounds positions
+  for (int i = lane; i < rot_half; i += 32) {
+    float a = to_f32(src[i]), b = to_f32(src[i + rot_half]);
+    if (w) {
+      a = a * inv * (w_offset + load_as_f32(w, norm_dtype, i));
+      b = b * inv * (w_offset + load_as_f32(w, norm_dtype, i + rot_half));
+    }
+    const float c = cos_tab[(size_t)pos * rot_half + i];
+    const float s = sin_tab[(size_t)pos * rot_half + i];
+    dst[i] = from_f32<T>(a * c - b * s);
+    dst[i + rot_half] = from_f32<T>(a * s + b * c);
+  }
+  for (int d = 2 * rot_half + lane; d < hd; d += 32) {  // dims beyond the rotary part
+    float a = to_f32(src[d]);
+    if (w) a = a * inv * (w_offset + load_as_f32(w, norm_dtype, d));
+    dst[d] = from_f32<T>(a);
+  }
+}
+
+// write_kv = 0: only the nq query heads are processed (a mixer that reads another layer's cache).
+OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, int nq, int nkv, int hd,
+                              const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
+                              float w_offset, const float* cos_tab, const float* sin_tab, int rot_half,
+                              int max_pos, const int* positions, const int* slots, void* k_cache,
+                              void* v_cache, long long page_stride, int page_size, int write_kv,
+                              void* stream) {
+  OI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && hd > 0, "qk_norm_rope_kv: bad sizes");
+  OI_REQUIRE(rot_half >= 0 && 2 * rot_half <= hd, "qk_norm_rope_kv: rotary_dim %d exceeds head_dim %d",
+             2 * rot_half, hd);
+  OI_REQUIRE(rot_half == 0 || (cos_tab && sin_tab && max_pos > 0), "qk_norm_rope_kv: rotation without tables");
+  OI_REQUIRE(!write_kv || (k_cache && v_cache && slots && page_size > 0), "qk_norm_rope_kv: cache write without a cache");
+  if (tokens == 0) return OI_OK;
+  const int heads_total = write_kv ? nq + 2 * nkv : nq;
+  const long long warps = (long long)tokens * heads_total;
+  const int blocks = (int)((warps + 3) / 4);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == OI_F32) {
+    qk_norm_rope_kv_kernel<float><<<blocks, 128, 0, s>>>(
+        (float*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
+        sin_tab, rot_half, max_pos, positions, slots, (float*)k_cache, (float*)v_cache, page_stride,
+        page_size, heads_total, tokens);
+  } else if (dtype == OI_BF16) {
+    qk_norm_rope_kv_kernel<bf16><<<blocks, 128, 0, s>>>(
+        (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
+        sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride,
+        page_size, heads_total, tokens);
+  } else {
+    OI_REQUIRE(false, "qk_norm_rope_kv: unknown dtype code %d", dtype);
+  }
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}

@@ -1,0 +1,29 @@
+// Error reporting of the C ABI and a few device queries.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void oi_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+// Message of the last failed call on this thread.
+OI_API const char* oi_last_error() { return g_error; }
+
+// ABI version: bumped when an entry point's signature changes.
+OI_API int oi_abi_version() { return 1; }
+
+OI_API int oi_device_info(int device, int* sm_major, int* sm_minor, int* sm_count, long long* l2_bytes) {
+  cudaDeviceProp prop;
+  OI_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));
+  *sm_major = prop.major;
+  *sm_minor = prop.minor;
+  *sm_count = prop.multiProcessorCount;
+  *l2_bytes = prop.l2CacheSize;
+  return OI_OK;
+}

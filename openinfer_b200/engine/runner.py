@@ -1,0 +1,274 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step`` takes portions of prompts and single decoded tokens side by side,
+cut anywhere, runs only the rows it is given against what earlier steps left in the
+cache, and returns float32 logits at the wanted rows. It is the one path by which
+tokens reach the model: generation, the scheduler and trace replay all call it. The
+reference's three entry points (execute_prefill / execute_decode / execute_unified,
+pegainfer-qwen3/src/executor.rs:2549-2857) are special cases of this one.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import RELEASED, CacheManager
+from ..cache.pool import OutOfPages
+from ..config.base import load_config, resolve_architecture
+from ..kernels import lib as kernel_lib
+from ..parts.model import Model
+from ..weights.loader import load_tensors
+from ..weights.random import random_tensors
+from .context import GroupStep, StepContext
+
+
+class StepError(ValueError):
+    """A step that cannot run as given (bad token id, position beyond the model's range, ...)."""
+
+
+@dataclasses.dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()   # places among ``tokens`` whose logits are asked for
+
+
+def _dtype_of(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    table = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+    if name not in table:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}")
+    return table[name]
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, device: torch.device) -> None:
+        self.model = model
+        self.cache = cache
+        self.device = torch.device(device)
+        self.spec = model.spec
+        self._staging: Optional[torch.Tensor] = None
+        self._staging_event: Optional[torch.cuda.Event] = None
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def build(cls, config, tensors_or_seed, dtype="bfloat16", device="cuda:0", *, page_size: int = 16,
+              num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
+              max_requests: int = 256, folder: Optional[str] = None) -> "ModelRunner":
+        """Assemble model + cache on the device.
+
+        ``tensors_or_seed``: None to load ``folder``'s safetensors, or an int seed for
+        random weights drawn on the device. The pool holds ``num_pages`` pages per group,
+        or enough for ``max_tokens`` positions (rounded up to whole pages)."""
+        dtype = _dtype_of(dtype)
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise kernel_lib.KernelError(
+                f"device {device} is not a CUDA device; this engine has no CPU path")
+        if not torch.cuda.is_available():
+            raise kernel_lib.KernelError("no CUDA device is available; this engine has no CPU path")
+        kernel_lib.load()  # build / load now: a missing extension fails here, loudly
+        torch.cuda.set_device(device)
+        # the true 32-bit path must not use a reduced-precision matrix mode anywhere
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        entry = resolve_architecture(config.to_dict())
+        spec = entry.build_spec(config)
+        model = Model(spec, dtype)
+        expected = model.expected_tensors()
+        if tensors_or_seed is None:
+            if folder is None:
+                raise ValueError("either a folder or a seed is needed")
+            tensors = load_tensors(folder, expected, dtype, device)
+        else:
+            tensors = random_tensors(expected, int(tensors_or_seed), dtype=dtype, device=device)
+        model.load(tensors, device)
+        del tensors
+        cache = CacheManager(page_size=page_size)
+        model.bind_cache(cache)
+        if num_pages is None:
+            if max_tokens is None:
+                raise ValueError("give num_pages or max_tokens")
+            num_pages = max(1, -(-int(max_tokens) // page_size))
+        cache.allocate(num_pages, max_requests, device=device, dtype=dtype)
+        return cls(model, cache, device)
+
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **kw) -> "ModelRunner":
+        config = load_config(folder)
+        return cls.build(config, None, dtype=dtype, device=device, folder=folder, **kw)
+
+    # ------------------------------------------------------------------ helpers
+    def _stage(self, host: np.ndarray) -> torch.Tensor:
+        """Host int32 array -> device tensor through a pinned staging buffer, one copy."""
+        n = host.size
+        if self._staging is None or self._staging.numel() < n:
+            self._staging = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
+            self._staging_event = None
+        if self._staging_event is not None:
+            self._staging_event.synchronize()  # the previous step's copy has left the buffer
+        self._staging[:n].numpy()[:] = host
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        dev.copy_(self._staging[:n], non_blocking=True)
+        self._staging_event = torch.cuda.Event()
+        self._staging_event.record()
+        return dev
+
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        vocab, max_pos = self.spec.vocab_size, self.spec.max_positions
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < vocab):
+                    raise StepError(f"request {e.request_id!r}: token id {t} outside [0, {vocab})")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
+            held = self.cache.num_tokens(e.request_id) if self.cache.has(e.request_id) else 0
+            if max_pos and held + n > max_pos:
+                raise StepError(
+                    f"request {e.request_id!r}: {held + n} positions exceed max_position_embeddings {max_pos}")
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch. Returns float32 logits [wanted rows, vocab] on the device, rows in
+        the order of the entries and of each entry's ``want`` (None when nothing is wanted).
+
+        Raises ``OutOfPages`` with nothing changed if the cache cannot hold the new rows."""
+        entries = list(entries)
+        if not entries:
+            return None
+        self.validate(entries)
+        cache = self.cache
+        opened, reserved = [], []
+        try:
+            starts = []
+            for e in entries:
+                if not cache.has(e.request_id):
+                    cache.open(e.request_id)
+                    opened.append(e.request_id)
+                starts.append(cache.reserve(e.request_id, len(e.tokens)))
+                reserved.append(e.request_id)
+        except OutOfPages:
+            for rid in reserved:
+                cache.rollback(rid)
+            for rid in opened:
+                cache.close(rid)
+            raise
+        try:
+            ctx, row_idx = self._build_context(entries, starts)
+            h, pending = self.model.forward(ctx)
+            logits = self.model.logits(h, pending, row_idx) if row_idx is not None else None
+        except Exception:
+            for rid in reserved:
+                cache.rollback(rid)
+            for rid in opened:
+                cache.close(rid)
+            raise
+        for rid in reserved:
+            cache.commit(rid)
+        self.steps_run += 1
+        return logits
+
+    def end(self, request_id: Hashable) -> None:
+        """The request is finished: its pages and state slot go back to the pools."""
+        if self.cache.has(request_id):
+            self.cache.close(request_id)
+
+    # ------------------------------------------------------------------ metadata
+    def _build_context(self, entries: List[StepEntry], starts: List[int]):
+        cache = self.cache
+        P = cache.page_size
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        G = len(cache.groups)
+        max_pages = max(1, max(-(-kv // P) for kv in kv_lens))
+        want_rows: List[int] = []
+
+        # layout of the packed int32 buffer (every section starts on a 16-byte boundary)
+        sections: Dict[str, int] = {}
+        off = 0
+        for name, size in (("token_ids", T), ("positions", T), ("token_req", T), ("cu_seqlens", B + 1),
+                           ("state_slots", B)):
+            sections[name] = off
+            off += _align4(size)
+        for g in range(G):
+            for name, size in ((f"slots{g}", T), (f"table{g}", B * max_pages), (f"kv_lens{g}", B)):
+                sections[name] = off
+                off += _align4(size)
+        n_want = sum(len(e.want) for e in entries)
+        sections["want"] = off
+        off += _align4(max(n_want, 1))
+        host = np.zeros(off, dtype=np.int32)
+
+        def view(name, size):
+            return host[sections[name]: sections[name] + size]
+
+        tok, pos, req = view("token_ids", T), view("positions", T), view("token_req", T)
+        cu = view("cu_seqlens", B + 1)
+        slots_host = view("state_slots", B)
+        row = 0
+        for b, e in enumerate(entries):
+            n = q_lens[b]
+            tok[row: row + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos[row: row + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
+            req[row: row + n] = b
+            cu[b] = row
+            slots_host[b] = cache.state_slot(e.request_id)
+            want_rows.extend(row + int(w) for w in e.want)
+            row += n
+        cu[B] = T
+        for g in range(G):
+            sl = view(f"slots{g}", T)
+            tb = view(f"table{g}", B * max_pages).reshape(B, max_pages)
+            kl = view(f"kv_lens{g}", B)
+            row = 0
+            for b, e in enumerate(entries):
+                table = np.asarray(cache.block_table(e.request_id, g), dtype=np.int32)
+                n = q_lens[b]
+                p = np.arange(starts[b], starts[b] + n)
+                sl[row: row + n] = table[p // P] * P + (p % P)
+                shown = np.where(table == RELEASED, 0, table)  # never read: behind the window
+                tb[b, : len(shown)] = shown[:max_pages]
+                kl[b] = kv_lens[b]
+                row += n
+        if n_want:
+            view("want", n_want)[:] = np.asarray(want_rows, dtype=np.int32)
+
+        dev = self._stage(host)
+
+        def dview(name, size):
+            return dev[sections[name]: sections[name] + size]
+
+        groups = [
+            GroupStep(slot_mapping=dview(f"slots{g}", T),
+                      block_table=dview(f"table{g}", B * max_pages).view(B, max_pages),
+                      kv_lens=dview(f"kv_lens{g}", B), window=cache.groups[g].window)
+            for g in range(G)
+        ]
+        ctx = StepContext(
+            num_tokens=T, num_requests=B, token_ids=dview("token_ids", T), positions=dview("positions", T),
+            token_req=dview("token_req", T), cu_seqlens=dview("cu_seqlens", B + 1),
+            state_slots=dview("state_slots", B), groups=groups, cache=cache,
+            q_lens_host=q_lens, starts_host=list(starts), kv_lens_host=kv_lens,
+            state_slots_host=[int(s) for s in slots_host], decode_only=all(n == 1 for n in q_lens),
+            max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+        row_idx = dview("want", n_want) if n_want else None
+        return ctx, row_idx

@@ -1,0 +1,92 @@
+"""Loads the CUDA library and declares its C entry points.
+
+There is no fallback: if the library cannot be built or loaded, or an entry point
+reports an error, a ``KernelError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+# name -> argument types (all return int)
+_SIGNATURES = {
+    "oi_embedding": [P, I, P, I, P, I, I, I, P],
+    "oi_rmsnorm": [P, P, P, I, P, I, P, I, I, F, F, P],
+    "oi_add_inplace": [P, P, I, L, P],
+    "oi_silu_mul": [P, P, I, I, I, P],
+    "oi_qk_norm_rope_kv": [P, I, I, I, I, I, I, P, P, I, F, F, P, P, I, I, P, P, P, P, L, I, I, P],
+    "oi_attention_generic": [P, I, P, I, I, P, P, L, I, P, I, P, P, I, I, I, I, F, I, P],
+    "oi_gemm_generic": [P, I, P, I, P, I, I, I, I, L, L, L, P],
+    "oi_argmax": [P, P, I, I, L, P],
+    "oi_sample": [P, P, L, P, I, I, P, P, P, P, P, P],
+}
+
+
+def load(verbose: bool = True) -> ctypes.CDLL:
+    """The loaded library (built on first use)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        from ..csrc.build import BuildError, ensure_built
+
+        try:
+            path = ensure_built(verbose=verbose)
+        except BuildError as e:
+            raise KernelError(f"the CUDA kernels could not be built: {e}") from e
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"the CUDA kernel library {path} could not be loaded: {e}") from e
+        lib.oi_last_error.restype = c_char_p
+        lib.oi_last_error.argtypes = []
+        lib.oi_abi_version.restype = c_int
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name, None)
+            if fn is None:
+                raise KernelError(f"{path} lacks entry point {name}")
+            fn.argtypes = args
+            fn.restype = c_int
+        _declare_optional(lib)
+        _lib = lib
+        return lib
+
+
+# entry points added by later source files; declared when present
+_OPTIONAL = {}
+
+
+def declare(name: str, argtypes) -> None:
+    """Register the signature of a further entry point (used by the wrappers of
+    kernels that live in their own source files)."""
+    _OPTIONAL[name] = argtypes
+    if _lib is not None:
+        _declare_optional(_lib)
+
+
+def _declare_optional(lib) -> None:
+    for name, args in _OPTIONAL.items():
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = args
+            fn.restype = c_int
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().oi_last_error().decode(errors="replace")
+        raise KernelError(f"{what} failed (code {code}): {msg}")

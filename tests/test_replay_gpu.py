@@ -1,0 +1,99 @@
+"""The engine against the plain implementation under every way of cutting the work,
+in float32 and in bfloat16, for both tiny configurations."""
+import random
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import (TINY, assert_close, make_model_folder, random_tokens, replay_in_process,
+                     replay_trace_run, round64, trace_mixed, trace_portions, trace_tail, trace_whole)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 47, 130, 200, 77, 33], "B": [1, 9, 70, 150, 261, 40]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (cfg, seed) in TINY.items():
+        out[name] = make_model_folder(str(tmp_path_factory.mktemp(f"tiny{name}")), cfg, seed)
+    return out
+
+
+@pytest.fixture(scope="module")
+def workloads(folders):
+    """Per config: the requests and the plain implementation's logits at every position."""
+    out = {}
+    for name, folder in folders.items():
+        cfg, w = plain.read_model_folder(folder)
+        rng = random.Random(100 + len(name))
+        reqs = {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(LENGTHS[name])}
+        ref = {rid: plain.forward_logits(cfg, w, toks) for rid, toks in reqs.items()}
+        out[name] = (cfg, reqs, ref)
+    return out
+
+
+def _runner(folder, dtype, max_tokens, page_size=16):
+    from openinfer_b200.engine.runner import ModelRunner
+    return ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_size=page_size,
+                                   max_tokens=max_tokens, max_requests=8)
+
+
+def _check(got, ref, dtype, what):
+    assert set(got) == set(ref)
+    for rid in ref:
+        assert_close(got[rid], ref[rid], dtype, f"{what} request {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cuttings_match_plain(folders, workloads, name, dtype, mode):
+    cfg, reqs, ref = workloads[name]
+    biggest = max(round64(len(t)) for t in reqs.values())
+    if mode == "whole":
+        steps, max_tokens = trace_whole(reqs), biggest
+    elif mode == "tail":
+        steps, max_tokens = trace_tail(reqs), biggest
+    elif mode == "portions":
+        steps, max_tokens = trace_portions(reqs), biggest
+    else:
+        # room for the largest request plus two more blocks of 64: pages must be reused
+        max_tokens = biggest + 128
+        steps = trace_mixed(reqs, max_tokens, seed=7)
+        assert max(len(s["entries"]) for s in steps) >= 2
+    page = 8 if name == "A" else 16
+    runner = _runner(folders[name], dtype, max_tokens, page_size=page)
+    got = replay_in_process(runner, steps)
+    _check(got, ref, dtype, f"{name}/{dtype}/{mode}")
+    runner.cache.check()
+    assert runner.cache.min_free_pages() == runner.cache.num_pages, "pages were not all given back"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folders, workloads, tmp_path, dtype):
+    """The bin/trace_run program itself, fed line by line, mixed trace with page reuse."""
+    name = "B"
+    cfg, reqs, ref = workloads[name]
+    max_tokens = max(round64(len(t)) for t in reqs.values()) + 128
+    steps = trace_mixed(reqs, max_tokens, seed=3)
+    got = replay_trace_run(folders[name], dtype, steps, str(tmp_path / "out"), max_tokens, cfg["vocab_size"])
+    _check(got, ref, dtype, f"trace_run/{dtype}")
+
+
+def test_first_tokens_and_long_decode(folders, workloads):
+    """The first tokens of a sequence one by one from an empty cache, then a long decode."""
+    name = "A"
+    cfg, w = plain.read_model_folder(folders[name])
+    rng = random.Random(5)
+    toks = random_tokens(rng, 300, cfg["vocab_size"])
+    ref = plain.forward_logits(cfg, w, toks)
+    for dtype in ("float32", "bfloat16"):
+        runner = _runner(folders[name], dtype, round64(len(toks)), page_size=8)
+        steps = [{"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []}
+                 for i, t in enumerate(toks)]
+        steps[-1]["end"] = ["x"]
+        got = replay_in_process(runner, steps)
+        assert_close(got["x"], ref, dtype, f"token by token {dtype}")
