@@ -1,0 +1,286 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens per second of the engine at Qwen3-8B sizes with random weights.
+
+    python bench.py --gpus 1 --steps K --warmup W
+
+A "step" is one decode step of a batch of 8 requests, each with a 2,048-token context
+(16-token pages). ``value`` is device-timed (CUDA events around exactly K steps of the
+engine's step function plus on-device argmax); ``e2e`` is the same through the Python
+entry point ``LLM.step()`` with host token ids in and out every step. The line also
+reports a 2,048-token prefill, the decode step's fraction of the HBM roofline, and decode
+at batch 1 and 64. Prints ONE JSON line. The engine runs on one GPU: for --gpus > 1 it
+says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE configs[2]: Qwen3-8B sizes
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+    vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+    max_position_embeddings=4096)
+CONTEXT = 2048
+PAGE = 16
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as fh:
+                raw = json.load(fh)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            return out, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0) -> None:
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points and the prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust + CUDA workspace (no setup.py/pyproject.toml: pip reports "
+                          "'not installable'); no Rust toolchain in this image"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from openinfer_b200.config.base import resolve_architecture
+    from openinfer_b200.engine.engine import LLM
+    from openinfer_b200.engine.runner import ModelRunner, StepEntry
+    from openinfer_b200.kernels import lib as klib
+    from openinfer_b200.kernels import ops
+    from openinfer_b200.sampling.params import SamplingParams
+
+    peaks, peaks_src = read_peaks()
+    cfg_dict = dict(QWEN3_8B)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    config = resolve_architecture(cfg_dict).config_cls.from_dict(cfg_dict)
+    K, W, B = args.steps, args.warmup, args.batch
+    max_batch = B if args.skip_points else max(B, 64)
+    per_req = CONTEXT + K + W + max(B, 8) + 16 + 2 * PAGE
+    pool_tokens = max_batch * per_req + PREFILL_TOKENS + 64
+    dev = torch.device("cuda:0")
+    runner = ModelRunner.build(config, 0, dtype=args.dtype, device=dev, page_size=PAGE,
+                               max_tokens=pool_tokens, max_requests=max_batch + 8)
+    runner.cuda_graph = True
+    cache = runner.cache
+    esize = 2 if args.dtype == "bfloat16" else 4
+    for g in cache.groups:  # contexts are not computed but filled: decode reads the same bytes
+        g.tensor.normal_(0.0, 0.5)
+    rng = random.Random(0)
+    vocab = config.vocab_size
+
+    def fake_context(rid, n):
+        cache.open(rid)
+        cache.reserve(rid, n)
+        cache.commit(rid)
+
+    def decode_run(batch, steps, warmup):
+        """Device-timed decode: `steps` steps of `batch` requests at context CONTEXT."""
+        ids = [f"b{batch}_{i}" for i in range(batch)]
+        for rid in ids:
+            fake_context(rid, CONTEXT)
+        toks = [[rng.randrange(vocab)] for _ in ids]
+        out = torch.empty(batch, dtype=torch.int32, device=dev)
+
+        def one():
+            logits = runner.step([StepEntry(rid, t, [0]) for rid, t in zip(ids, toks)])
+            ops.argmax(out, logits)
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        l0 = klib.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = klib.launches - l0
+        for rid in ids:
+            runner.end(rid)
+        return ms, launches
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_step, launches = decode_run(B, K, W)
+    clocks = sampler.stop()
+    value = B * 1000.0 / ms_step
+
+    # roofline of the decode step: every weight once + the cache of the live requests
+    kv_tokens = B * (CONTEXT + W + K // 2)
+    step_bytes = runner.model.weight_bytes() + kv_tokens * cache.bytes_per_token(esize)
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks_src}
+
+    # end to end through the Python entry point: host token ids in and out every step
+    llm = LLM(config=config, runner=runner, max_prefill_tokens=2048, max_decode_batch=max_batch)
+    for i in range(B):
+        llm.submit([rng.randrange(vocab) for _ in range(CONTEXT)], SamplingParams(ignore_eos=True), W + K + B + 8)
+    while len(llm.scheduler.active) < B:
+        llm.step()
+    for _ in range(W):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_tok = 0
+    for _ in range(K - 1):  # the prompt's last step produced the first token; K - 1 more decode steps are left
+        n_tok += sum(1 for ev in llm.step() if ev.kind == "token")
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    while llm.has_work():
+        llm.step()
+    e2e = {"value": round(n_tok / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": B * 4,
+           "ms_per_step": round(e2e_s * 1000 / max(K - 1, 1), 4)}
+    # bytes of step metadata copied host->device each step (token ids, positions, block tables, ...)
+    e2e["h2d_bytes_per_step"] = int(runner._staging_last_bytes) if hasattr(runner, "_staging_last_bytes") else None
+
+    out = {
+        "metric": "decode tokens/s (Qwen3-8B sizes, random weights, batch 8, context 2048)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B sizes", "layers": config.num_hidden_layers, "layers_full": full_layers,
+            "hidden": config.hidden_size, "q_heads": config.num_attention_heads,
+            "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+            "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+            "rope_theta": config.rope_theta, "rms_norm_eps": config.rms_norm_eps, "tied": config.tie_word_embeddings,
+            "global_batch": B, "seq_len": CONTEXT, "kv_page": PAGE, "new_tokens": K,
+            "parallelism": "single GPU", "l2": "weights (>15 GB) exceed L2; no flush needed",
+        },
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+    }
+
+    if not args.skip_points:
+        points = {}
+        for b in (1, 64):
+            steps = max(16, K // 2)
+            ms_b, _ = decode_run(b, steps, max(3, W // 2))
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+        out["points"] = points
+
+        # prefill of one 2,048-token prompt in one step
+        toks = [rng.randrange(vocab) for _ in range(PREFILL_TOKENS)]
+        times = []
+        for i in range(3 + 3):
+            rid = f"pf{i}"
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step([StepEntry(rid, toks, [PREFILL_TOKENS - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.end(rid)
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        pf_ms = statistics.median(times)
+        L, H, I = config.num_hidden_layers, config.hidden_size, config.intermediate_size
+        dq, dkv = config.q_dim, config.kv_dim
+        T = PREFILL_TOKENS
+        flops = L * (2 * T * H * (dq + 2 * dkv) + 2 * T * dq * H + 2 * T * H * 2 * I + 2 * T * I * H
+                     + 4 * config.num_attention_heads * config.head_dim * T * T / 2) + 2 * vocab * H
+        peak_tf = peaks["bf16_tflops"] if args.dtype == "bfloat16" else 75.0
+        out["prefill"] = {"value": round(T * 1000.0 / pf_ms, 1), "tokens": T, "ms": round(pf_ms, 3),
+                          "frac": round(flops / (pf_ms * 1e-3) / (peak_tf * 1e12), 4), "peaks": peaks_src}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

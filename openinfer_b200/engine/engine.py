@@ -1,0 +1,173 @@
+"""The generation engine: model runner + sampler as the scheduler's executor, and the
+Python entry point ``LLM.generate`` (token ids in, token ids out; tokenizers live outside).
+
+The reference has no Python API (it serves HTTP); its programmatic surface is the
+executor plus ``EngineHandle::submit`` (pegainfer-qwen3/src/lib.rs:199-213,
+pegainfer-frontend/src/engine.rs:67-95). Option names and defaults follow its command
+line (pegainfer-frontend/src/model_line.rs:85-187, pegainfer-qwen3/src/model_line.rs:32-118).
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..config.base import ModelConfig, load_config
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .runner import ModelRunner, StepEntry
+from .scheduler import (DEFAULT_ENGINE_SEED, DEFAULT_MAX_DECODE_BATCH, DEFAULT_MAX_PREFILL_TOKENS, DecodeItem,
+                        Event, Executor, PrefillItem, Request, Scheduler)
+
+DEFAULT_GPU_MEMORY_UTILIZATION = 0.90   # pegainfer-qwen3/src/weights.rs:31-36
+DEFAULT_KV_MARGIN_MIB = 150
+DEFAULT_KV_PAGE_SIZE = 16
+
+
+class RunnerExecutor(Executor):
+    """Executes the scheduler's batches on the model runner and samples the wanted rows."""
+
+    def __init__(self, runner: ModelRunner) -> None:
+        self.runner = runner
+        self.page_size = runner.cache.page_size
+        self.total_pages = runner.cache.num_pages
+        self.sampler = Sampler(runner.spec.vocab_size, runner.device)
+
+    def free_pages(self) -> int:
+        return self.runner.cache.min_free_pages()
+
+    def execute(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int) -> Dict[Hashable, int]:
+        entries, rows = [], []
+        for p in prefill:
+            entries.append(StepEntry(p.request_id, p.tokens, [len(p.tokens) - 1] if p.is_last else []))
+            if p.is_last:
+                rows.append(p)
+        for d in decode:
+            entries.append(StepEntry(d.request_id, [d.token], [0]))
+            rows.append(d)
+        logits = self.runner.step(entries)
+        if not rows:
+            return {}
+        tokens = self.sampler.select(logits, [r.sampling for r in rows], [r.step_index for r in rows], step_seed)
+        return {r.request_id: t for r, t in zip(rows, tokens)}
+
+    def drop(self, request_id: Hashable) -> None:
+        self.runner.end(request_id)
+
+
+@dataclasses.dataclass
+class GenerationResult:
+    request_id: Hashable
+    token_ids: List[int]
+    finish_reason: str   # "stop" | "length" | "rejected:<why>" | "error:<message>"
+
+
+class LLM:
+    """Load a model folder (or build a random model from a config and a seed) and generate.
+
+    >>> llm = LLM("/path/to/model")                        # config.json + safetensors
+    >>> llm.generate([[1, 2, 3]], max_tokens=8)            # greedy
+    [[...8 token ids...]]
+    """
+
+    def __init__(self, model_path: Optional[str] = None, *, config: Optional[ModelConfig] = None,
+                 seed: Optional[int] = None, dtype: str = "bfloat16", device_ordinal: int = 0,
+                 kv_page_size: int = DEFAULT_KV_PAGE_SIZE, num_pages: Optional[int] = None,
+                 max_cache_tokens: Optional[int] = None,
+                 gpu_memory_utilization: float = DEFAULT_GPU_MEMORY_UTILIZATION,
+                 kv_cache_memory_margin_mib: int = DEFAULT_KV_MARGIN_MIB,
+                 max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
+                 max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
+                 cuda_graph: bool = True, runner: Optional[ModelRunner] = None) -> None:
+        device = f"cuda:{device_ordinal}"
+        weights_seed = None
+        if runner is not None:
+            pass  # model, weights and cache already stand
+        elif model_path is not None:
+            config = load_config(model_path)
+            weights_seed = None
+        elif config is not None and seed is not None:
+            weights_seed = seed
+        else:
+            raise ValueError("give model_path, or config and seed for random weights")
+        if runner is not None:
+            self.runner = runner
+        elif num_pages is None and max_cache_tokens is None:
+            from .memory import pages_from_memory_budget
+
+            self.runner, _ = pages_from_memory_budget(
+                config, weights_seed, model_path, dtype, device, kv_page_size, gpu_memory_utilization,
+                kv_cache_memory_margin_mib, max_prefill_tokens)
+        else:
+            self.runner = ModelRunner.build(
+                config, weights_seed, dtype=dtype, device=device, page_size=kv_page_size, num_pages=num_pages,
+                max_tokens=max_cache_tokens, max_requests=max_decode_batch, folder=model_path)
+        self.runner.cuda_graph = cuda_graph
+        self.config = config
+        self.executor = RunnerExecutor(self.runner)
+        max_context = self.runner.spec.max_positions or (1 << 30)
+        self.scheduler = Scheduler(
+            self.executor, max_context_tokens=max_context, stop_token_ids=self.runner.spec.stop_token_ids,
+            max_prefill_tokens=max_prefill_tokens, max_decode_batch=max_decode_batch, seed=engine_seed)
+        self._next_id = 0
+
+    # ---- step-wise use: submit requests, then call step() until has_work() is false
+    def submit(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None,
+               max_tokens: int = 16) -> Hashable:
+        rid = self._next_id
+        self._next_id += 1
+        self.scheduler.submit(Request(rid, list(prompt_token_ids), int(max_tokens), sampling_params or SamplingParams()))
+        return rid
+
+    def step(self) -> List[Event]:
+        """One scheduler iteration: host tokens in, one batch on the GPU, sampled tokens out."""
+        return self.scheduler.step()
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def generate_detailed(self, prompt_token_ids: Sequence[Sequence[int]],
+                          sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                          max_tokens: Union[int, Sequence[int]] = 16) -> List[GenerationResult]:
+        n = len(prompt_token_ids)
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        sp = [sampling_params] * n if isinstance(sampling_params, SamplingParams) else list(sampling_params)
+        mt = [max_tokens] * n if isinstance(max_tokens, int) else list(max_tokens)
+        if len(sp) != n or len(mt) != n:
+            raise ValueError("sampling_params / max_tokens must be single values or one per prompt")
+        ids = []
+        for i in range(n):
+            rid = self._next_id
+            self._next_id += 1
+            ids.append(rid)
+            self.scheduler.submit(Request(rid, list(prompt_token_ids[i]), int(mt[i]), sp[i]))
+        out: Dict[Hashable, GenerationResult] = {rid: GenerationResult(rid, [], "") for rid in ids}
+        for ev in self.scheduler.run():
+            r = out.get(ev.request_id)
+            if r is None:
+                continue
+            if ev.kind == "token":
+                r.token_ids.append(ev.token)
+            elif ev.kind == "finished":
+                r.finish_reason = ev.reason
+            elif ev.kind in ("rejected", "error"):
+                r.finish_reason = f"{ev.kind}:{ev.reason}"
+        return [out[rid] for rid in ids]
+
+    def generate(self, prompt_token_ids: Sequence[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 max_tokens: Union[int, Sequence[int]] = 16) -> List[List[int]]:
+        """Generated token ids per prompt (host lists in, host lists out)."""
+        results = self.generate_detailed(prompt_token_ids, sampling_params, max_tokens)
+        for r in results:
+            if r.finish_reason.startswith(("rejected", "error")):
+                raise RuntimeError(f"request {r.request_id} did not run: {r.finish_reason}")
+        return [r.token_ids for r in results]
+
+
+def generate(model_path: str, prompt_token_ids: Sequence[Sequence[int]], max_tokens: int = 16,
+             sampling_params: Optional[SamplingParams] = None, **engine_options) -> List[List[int]]:
+    """One-call form: load ``model_path``, generate, return token ids per prompt."""
+    return LLM(model_path, **engine_options).generate(prompt_token_ids, sampling_params, max_tokens)

@@ -117,6 +117,7 @@ class ModelRunner:
         if self._staging_event is not None:
             self._staging_event.synchronize()  # the previous step's copy has left the buffer
         self._staging[:n].numpy()[:] = host
+        self._staging_last_bytes = n * 4
         dev = torch.empty(n, dtype=torch.int32, device=self.device)
         dev.copy_(self._staging[:n], non_blocking=True)
         self._staging_event = torch.cuda.Event()

@@ -1,0 +1,271 @@
+"""Continuous-batching scheduler: admits requests, cuts prompts into portions under a
+token budget, decodes, finishes and frees.
+
+Decisions follow the reference's scheduler (pegainfer-qwen3/src/scheduler.rs):
+
+* three queues, ``deferred`` (waiting for room) -> ``prefilling`` (admitted, prompt not
+  done, first come first served) -> ``active`` (decoding) (scheduler.rs:540-555);
+* admission reserves a request's WHOLE lifetime in pages, ceil((prompt + max_tokens) / P)
+  (or ceil(prompt / P) when max_tokens <= 1), against the free pages minus what admitted
+  requests will still draw, and needs a free decode slot (scheduler.rs:1094-1119,
+  1172-1258). So an admitted request never runs out of pages; there is no preemption and
+  no swapping. A request that cannot fit now stays deferred (later, smaller requests may
+  pass it); one that could never fit, or whose prompt + max_tokens exceeds the context
+  limit, is rejected at once;
+* every step forwards at most ``max_prefill_tokens`` prompt tokens in total, taken from the
+  front of ``prefilling`` (scheduler.rs:145-179), beside one token of every active request
+  (plan.rs:56-87): prompt portions always ride along with decoding;
+* a stop token ends a request without being emitted (unless ignore_eos); reaching
+  max_tokens emits the token and ends it (scheduler/resolve.rs:148-170, 203-230);
+* if a step fails all the same (the executor raises, e.g. pages ran out because the pool is
+  smaller than reported), every request the step touched ends with an error and is
+  dropped, and the scheduler goes on with the rest (scheduler.rs:1354-1378).
+
+The scheduler is host code only: it talks to an *executor* (the model runner plus
+sampler, or a fake in tests).
+"""
+from __future__ import annotations
+
+import dataclasses
+import random
+from typing import Dict, Hashable, List, Optional, Sequence
+
+from ..sampling.params import SamplingParams
+
+DEFAULT_MAX_PREFILL_TOKENS = 1024   # scheduler.rs:1170
+DEFAULT_MAX_DECODE_BATCH = 256      # batch_decode_buffers.rs:25-28
+DEFAULT_ENGINE_SEED = 42            # lib.rs:292
+
+
+@dataclasses.dataclass
+class Request:
+    request_id: Hashable
+    prompt_tokens: Sequence[int]
+    max_tokens: int = 16
+    sampling: SamplingParams = SamplingParams()
+
+
+@dataclasses.dataclass
+class Event:
+    """What the scheduler reports: kind is "token", "finished", "rejected" or "error"."""
+
+    request_id: Hashable
+    kind: str
+    token: Optional[int] = None
+    reason: str = ""   # finished: "stop" | "length"; rejected: "context_length" | "kv_budget" | "empty_prompt"; error: message
+
+
+@dataclasses.dataclass
+class PrefillItem:
+    request_id: Hashable
+    tokens: Sequence[int]     # this step's portion of the prompt
+    is_last: bool             # the portion ends the prompt: its last row is sampled
+    sampling: SamplingParams = SamplingParams()
+    step_index: int = 0       # request-local count of tokens drawn so far
+
+
+@dataclasses.dataclass
+class DecodeItem:
+    request_id: Hashable
+    token: int                # the last generated token, fed back
+    sampling: SamplingParams = SamplingParams()
+    step_index: int = 0
+
+
+class Executor:
+    """What the scheduler needs from below (the reference's ModelExecutor trait,
+    pegainfer-qwen3/src/executor.rs:838-974)."""
+
+    page_size: int
+    total_pages: int
+
+    def free_pages(self) -> int:
+        raise NotImplementedError
+
+    def execute(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int) -> Dict[Hashable, int]:
+        """Run one batch; returns the sampled token of every last portion and every decode item."""
+        raise NotImplementedError
+
+    def drop(self, request_id: Hashable) -> None:
+        raise NotImplementedError
+
+
+@dataclasses.dataclass
+class _Pending:
+    req: Request
+    done: int = 0        # prompt tokens already in the cache
+    step_chunk: int = 0
+
+
+@dataclasses.dataclass
+class _Active:
+    req: Request
+    generated: List[int]
+    last_token: int
+
+
+def lifetime_pages(prompt_len: int, max_tokens: int, page_size: int) -> int:
+    """Pages a request can draw over its life (scheduler.rs:1094-1101)."""
+    tokens = prompt_len if max_tokens <= 1 else prompt_len + max_tokens
+    return max(1, -(-tokens // page_size))
+
+
+def pages_for(tokens: int, page_size: int) -> int:
+    return -(-tokens // page_size)
+
+
+class Scheduler:
+    def __init__(self, executor: Executor, *, max_context_tokens: int, stop_token_ids: Sequence[int] = (),
+                 max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
+                 max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, seed: int = DEFAULT_ENGINE_SEED) -> None:
+        if max_prefill_tokens <= 0 or max_decode_batch <= 0:
+            raise ValueError("max_prefill_tokens and max_decode_batch must be positive")
+        self.executor = executor
+        self.page_size = executor.page_size
+        self.max_context_tokens = max_context_tokens
+        self.stop_token_ids = set(int(t) for t in stop_token_ids)
+        self.max_prefill_tokens = max_prefill_tokens
+        self.max_decode_batch = max_decode_batch
+        self.rng = random.Random(seed)
+        self.deferred: List[Request] = []
+        self.prefilling: List[_Pending] = []
+        self.active: List[_Active] = []
+        self.steps = 0
+
+    # ------------------------------------------------------------------ public
+    def submit(self, req: Request) -> None:
+        self.deferred.append(req)
+
+    def has_work(self) -> bool:
+        return bool(self.deferred or self.prefilling or self.active)
+
+    def load(self) -> Dict[str, int]:
+        """Snapshot like the reference's LoadSnapshot (scheduler.rs:513-526)."""
+        return {"kv_used_pages": self.executor.total_pages - self.executor.free_pages(),
+                "kv_total_pages": self.executor.total_pages,
+                "running": len(self.active) + len(self.prefilling), "waiting": len(self.deferred)}
+
+    # ------------------------------------------------------------------ admission
+    def _future_pages(self) -> int:
+        P = self.page_size
+        fut = 0
+        for a in self.active:
+            held = len(a.req.prompt_tokens) + len(a.generated) - 1  # the last token has no keys yet
+            fut += max(0, lifetime_pages(len(a.req.prompt_tokens), a.req.max_tokens, P) - pages_for(held, P))
+        for p in self.prefilling:
+            fut += max(0, lifetime_pages(len(p.req.prompt_tokens), p.req.max_tokens, P) - pages_for(p.done, P))
+        return fut
+
+    def _admit(self) -> List[Event]:
+        events: List[Event] = []
+        budget = max(0, self.executor.free_pages() - self._future_pages())
+        slots = max(0, self.max_decode_batch - len(self.active) - len(self.prefilling))
+        still: List[Request] = []
+        for req in self.deferred:
+            n = len(req.prompt_tokens)
+            if n == 0:
+                events.append(Event(req.request_id, "rejected", reason="empty_prompt"))
+                continue
+            if n + req.max_tokens > self.max_context_tokens:
+                events.append(Event(req.request_id, "rejected", reason="context_length"))
+                continue
+            need = lifetime_pages(n, req.max_tokens, self.page_size)
+            if need > self.executor.total_pages:
+                events.append(Event(req.request_id, "rejected", reason="kv_budget"))
+                continue
+            if need <= budget and slots > 0:
+                budget -= need
+                slots -= 1
+                self.prefilling.append(_Pending(req))
+            else:
+                still.append(req)
+        self.deferred = still
+        return events
+
+    # ------------------------------------------------------------------ portions
+    def _take_prefill(self) -> List[_Pending]:
+        budget = self.max_prefill_tokens
+        taken: List[_Pending] = []
+        i = 0
+        while i < len(self.prefilling) and budget > 0:
+            p = self.prefilling[i]
+            chunk = min(len(p.req.prompt_tokens) - p.done, budget)
+            p.step_chunk = chunk
+            budget -= chunk
+            taken.append(self.prefilling.pop(i))
+        return taken
+
+    # ------------------------------------------------------------------ one iteration
+    def step(self) -> List[Event]:
+        """Admit, build one batch, run it, resolve. Returns this iteration's events."""
+        events = self._admit()
+        taken = self._take_prefill()
+        decoding = list(self.active)
+        if not taken and not decoding:
+            return events
+        prefill_items = [
+            PrefillItem(p.req.request_id, p.req.prompt_tokens[p.done: p.done + p.step_chunk],
+                        is_last=p.done + p.step_chunk == len(p.req.prompt_tokens),
+                        sampling=p.req.sampling, step_index=0)
+            for p in taken]
+        decode_items = [DecodeItem(a.req.request_id, a.last_token, a.req.sampling, len(a.generated))
+                        for a in decoding]
+        step_seed = self.rng.getrandbits(64)
+        self.steps += 1
+        try:
+            tokens = self.executor.execute(prefill_items, decode_items, step_seed)
+        except Exception as e:  # the step failed: everyone it touched fails, the rest goes on
+            for p in taken:
+                events.append(Event(p.req.request_id, "error", reason=f"{type(e).__name__}: {e}"))
+                self.executor.drop(p.req.request_id)
+            for a in decoding:
+                events.append(Event(a.req.request_id, "error", reason=f"{type(e).__name__}: {e}"))
+                self.executor.drop(a.req.request_id)
+            self.active = []
+            return events
+
+        # decode rows first (they are older), then the requests whose prompt just ended
+        for a in decoding:
+            self._resolve(a, tokens[a.req.request_id], events)
+        unfinished: List[_Pending] = []
+        for p in taken:
+            p.done += p.step_chunk
+            if p.done < len(p.req.prompt_tokens):
+                unfinished.append(p)
+                continue
+            a = _Active(p.req, [], -1)
+            self.active.append(a)
+            self._resolve(a, tokens[p.req.request_id], events)
+        self.prefilling = unfinished + self.prefilling  # back to the front (effects.rs:318-406)
+        return events
+
+    def _resolve(self, a: _Active, token: int, events: List[Event]) -> None:
+        req = a.req
+        if token in self.stop_token_ids and not req.sampling.ignore_eos:
+            self._finish(a, events, "stop")
+            return
+        a.generated.append(token)
+        a.last_token = token
+        events.append(Event(req.request_id, "token", token=token))
+        if len(a.generated) >= max(1, req.max_tokens):
+            self._finish(a, events, "length")
+
+    def _finish(self, a: _Active, events: List[Event], reason: str) -> None:
+        events.append(Event(a.req.request_id, "finished", reason=reason))
+        self.executor.drop(a.req.request_id)
+        self.active = [x for x in self.active if x is not a]
+
+    def run(self) -> List[Event]:
+        """Iterate until every submitted request has ended."""
+        events: List[Event] = []
+        idle = 0
+        while self.has_work():
+            got = self.step()
+            events.extend(got)
+            idle = idle + 1 if not got else 0
+            if idle > 3 and not self.prefilling and not self.active:
+                # nothing runs and nothing was admitted: the deferred requests can never fit
+                for req in self.deferred:
+                    events.append(Event(req.request_id, "rejected", reason="kv_budget"))
+                self.deferred = []
+        return events

@@ -86,7 +86,13 @@ def _declare_optional(lib) -> None:
             fn.restype = c_int
 
 
+# number of entry-point calls that launched work (read by the benchmark)
+launches = 0
+
+
 def check(code: int, what: str) -> None:
+    global launches
+    launches += 1
     if code != 0:
         msg = load().oi_last_error().decode(errors="replace")
         raise KernelError(f"{what} failed (code {code}): {msg}")

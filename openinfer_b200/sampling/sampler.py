@@ -1,0 +1,63 @@
+"""Token selection for a batch of logits rows: greedy rows through the argmax kernel,
+the others through the sampling kernel; one device-to-host copy of the chosen ids.
+
+The split follows the reference's ``select_batch`` (pegainfer-sample/src/lib.rs:148-276):
+rows that are effectively greedy take the argmax path; a seeded row's draw is a function
+of (its seed, its own step) only, so it does not depend on what else is in the batch; an
+unseeded row draws from the engine's per-step seed and its row number.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .params import SamplingParams, mix_seed, uniform_from
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, device: torch.device) -> None:
+        self.vocab_size = vocab_size
+        self.device = torch.device(device)
+        self._probs: Optional[torch.Tensor] = None
+
+    def select(self, logits: torch.Tensor, params: Sequence[SamplingParams], steps: Sequence[int],
+               step_seed: int) -> List[int]:
+        """``logits`` float32 [rows, vocab]; ``steps[i]`` is row i's request-local step
+        (how many tokens that request has drawn so far). Returns one token id per row."""
+        n = len(params)
+        if n == 0:
+            return []
+        if logits.shape[0] != n or logits.shape[1] != self.vocab_size:
+            raise ValueError(f"logits {tuple(logits.shape)} do not match {n} rows of vocab {self.vocab_size}")
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        sampled = [i for i, p in enumerate(params) if not p.effectively_greedy(self.vocab_size)]
+        if len(sampled) < n:
+            ops.argmax(out, logits)  # every row; sampled rows are overwritten below
+        if sampled:
+            k = len(sampled)
+            host = np.zeros((5, k), dtype=np.float32)
+            topk = np.zeros(k, dtype=np.int32)
+            for j, i in enumerate(sampled):
+                p = params[i]
+                host[0, j] = p.temperature
+                host[1, j] = p.top_p
+                host[2, j] = p.min_p
+                host[3, j] = (uniform_from(p.seed, steps[i]) if p.seed is not None
+                              else uniform_from(mix_seed(step_seed, i), steps[i]))
+                topk[j] = p.top_k if 0 < p.top_k < self.vocab_size else 0
+            fl = torch.from_numpy(host).to(self.device)
+            tk = torch.from_numpy(topk).to(self.device)
+            rows = logits if k == n else logits[torch.tensor(sampled, device=self.device)]
+            if self._probs is None or self._probs.numel() < k * self.vocab_size:
+                self._probs = torch.empty(k * self.vocab_size, dtype=torch.float32, device=self.device)
+            picked = torch.empty(k, dtype=torch.int32, device=self.device)
+            ops.sample(picked, rows.contiguous(), self._probs, fl[0].contiguous(), tk, fl[1].contiguous(),
+                       fl[2].contiguous(), fl[3].contiguous())
+            if k == n:
+                out = picked
+            else:
+                out[torch.tensor(sampled, device=self.device)] = picked
+        return [int(t) for t in out.cpu().tolist()]
