@@ -54,10 +54,13 @@ class IdPool:
 
     def release(self, ids: Iterable[int]) -> None:
         ids = list(ids)
-        for i in ids:
-            if not (0 <= i < self.count) or not self._held[i]:
+        seen = set()
+        for i in ids:  # all or nothing: check everything before anything changes
+            if not (0 <= i < self.count) or not self._held[i] or i in seen:
                 raise DoubleFree(f"{self.what} {i} is not held")
-            self._held[i] = False  # a repeated id in `ids` trips the check above
+            seen.add(i)
+        for i in ids:
+            self._held[i] = False
             self._free.append(i)
 
     def is_held(self, i: int) -> bool:

@@ -60,11 +60,11 @@ class ModelConfig:
             return tuple(value)
         try:
             if t == "int":
-                if isinstance(value, bool) or (isinstance(value, float) and value != int(value)):
+                if isinstance(value, bool) or not isinstance(value, (int, float)) or value != int(value):
                     raise TypeError
                 return int(value)
             if t == "float":
-                if isinstance(value, bool):
+                if isinstance(value, bool) or not isinstance(value, (int, float)):
                     raise TypeError
                 return float(value)
             if t == "bool":

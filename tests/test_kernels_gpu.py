@@ -1,0 +1,310 @@
+"""Each CUDA kernel alone against a plain float32 statement of the same operation, at sizes
+other than the engine's (widths that are no power of two, odd row counts, every head size)."""
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib():
+    from openinfer_b200.kernels import lib
+    lib.load()
+    torch.manual_seed(0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [24, 100, 1000])
+def test_embedding(dtype, hidden):
+    from openinfer_b200.kernels import ops
+    vocab, n = 77, 13
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    ids = torch.randint(0, vocab, (n,), device=DEV, dtype=torch.int32)
+    out = torch.empty(n, hidden, device=DEV, dtype=dtype)
+    ops.embedding(out, table, ids)
+    assert torch.equal(out, table[ids.long()])  # a bit-exact copy
+    if dtype == torch.bfloat16:  # a table stored in 32-bit feeding a bfloat16 model
+        t32 = table.float() * 1.001
+        ops.embedding(out, t32, ids)
+        assert torch.equal(out, t32[ids.long()].to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [20, 96, 1000, 5120, 13000])
+def test_rmsnorm_plain_add_and_gather(dtype, hidden):
+    from openinfer_b200.kernels import ops
+    rows, eps = 7, 3e-5
+    x = (torch.randn(rows, hidden, device=DEV) * 3).to(dtype)
+    w32 = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    for w in ([w32.to(dtype), w32] if dtype == torch.bfloat16 else [w32]):  # weight may be stored in 32-bit
+        ref = plain.rms_norm(x.float().cpu(), w.float().cpu(), eps)
+        out = torch.empty_like(x)
+        ops.rmsnorm(out, x.clone(), w, eps)
+        assert torch.allclose(out.float().cpu(), ref, **tol(dtype))
+    w = w32.to(dtype)
+    # weight offset: scale is (1 + w)
+    out = torch.empty_like(x)
+    ops.rmsnorm(out, x.clone(), w, eps, weight_offset=1.0)
+    assert torch.allclose(out.float().cpu(), plain.rms_norm(x.float().cpu(), 1.0 + w.float().cpu(), eps), **tol(dtype))
+    # fused residual add: x <- x + delta (stored), norm of the rounded sum
+    delta = torch.randn(rows, hidden, device=DEV).to(dtype)
+    xs = x.clone()
+    ops.rmsnorm(out, xs, w, eps, delta=delta)
+    summed = (x.float() + delta.float()).to(dtype)
+    assert torch.equal(xs, summed)
+    assert torch.allclose(out.float().cpu(), plain.rms_norm(summed.float().cpu(), w.float().cpu(), eps), **tol(dtype))
+    # gathered rows (with repeats), with and without a pending delta; x is left alone
+    idx = torch.tensor([6, 0, 0, 3], device=DEV, dtype=torch.int32)
+    g = torch.empty(4, hidden, device=DEV, dtype=dtype)
+    xs = x.clone()
+    ops.rmsnorm(g, xs, w, eps, row_idx=idx)
+    assert torch.allclose(g.float().cpu(), plain.rms_norm(x.float().cpu()[idx.long().cpu()], w.float().cpu(), eps), **tol(dtype))
+    ops.rmsnorm(g, xs, w, eps, delta=delta, row_idx=idx)
+    assert torch.equal(xs, x)
+    assert torch.allclose(g.float().cpu(), plain.rms_norm(summed.float().cpu()[idx.long().cpu()], w.float().cpu(), eps), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [24, 100, 1111])
+def test_silu_mul(dtype, inter):
+    from openinfer_b200.kernels import ops
+    rows = 5
+    gu = (torch.randn(rows, 2 * inter, device=DEV) * 2).to(dtype)
+    out = torch.empty(rows, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(out, gu)
+    g, u = gu.float()[:, :inter], gu.float()[:, inter:]
+    assert torch.allclose(out.float(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 100, 33), (65, 129, 17), (130, 64, 300)])
+def test_gemm_generic(dtype, M, N, K):
+    from openinfer_b200.kernels import ops
+    a = torch.randn(M, K, device=DEV).to(dtype)
+    w = torch.randn(N, K, device=DEV).to(dtype)
+    out = torch.empty(M, N, device=DEV, dtype=dtype)
+    ops.gemm_generic(out, a, w)
+    ref = a.double() @ w.double().t()
+    assert torch.allclose(out.double(), ref, atol=1e-4 if dtype == torch.float32 else 0.15, rtol=1e-5 if dtype == torch.float32 else 2e-2)
+    # float32 output from bfloat16 operands, strided input rows, mixed operand types
+    big = torch.randn(M, K + 8, device=DEV).to(dtype)
+    o32 = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    ops.gemm_generic(o32, big[:, :K], w.float())
+    assert torch.allclose(o32.double(), big[:, :K].double() @ w.float().double().t(), atol=1e-4, rtol=1e-5)
+    # a row's result does not depend on the other rows (batch invariance, bit for bit)
+    one = torch.empty(1, N, device=DEV, dtype=dtype)
+    ops.gemm_generic(one, a[M - 1:], w)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def _rope_ref(x, positions, rot, theta, w, eps, offset):
+    """plain: per-head norm then rotate-half over the first `rot` dims; x [T, heads, hd] float32 cpu"""
+    if w is not None:
+        x = plain.rms_norm(x, offset + w, eps)
+    if rot:
+        cos, sin = plain.rope_tables(rot, theta, positions)
+        x = torch.cat([plain.apply_rope(x[..., :rot], cos, sin), x[..., rot:]], dim=-1)
+    return x
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (6, 2, 32, 32, True), (5, 1, 64, 32, True),
+                                                (3, 3, 128, 128, False), (2, 1, 256, 0, True), (7, 7, 48, 48, True)])
+def test_qk_norm_rope_kv_write(dtype, nq, nkv, hd, rot, norm):
+    from openinfer_b200.kernels import ops
+    from openinfer_b200.parts.position import RotaryEncoding
+    from openinfer_b200.parts.spec import PositionSpec
+    T, P, pages, theta, eps, max_pos = 11, 4, 9, 5000.0, 1e-5, 64
+    width = (nq + 2 * nkv) * hd
+    qkv = torch.randn(T, width + 8, device=DEV).to(dtype)[:, :width]  # a row stride wider than the row
+    src = qkv.clone().float().cpu()
+    positions = torch.tensor([0, 1, 2, 3, 4, 5, 6, 40, 41, 63, 17], dtype=torch.int32)
+    slots = torch.tensor([4, 5, 6, 7, 12, 13, 14, 0, 1, 35, -1], dtype=torch.int32)  # -1: a padding row
+    qw = (1 + 0.1 * torch.randn(hd)).to(dtype) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd)).to(dtype) if norm else None
+    cos = sin = None
+    if rot:
+        cos, sin = RotaryEncoding(PositionSpec("rope", rot, theta, max_pos)).rotation_tables(torch.device(DEV))
+    cache = torch.zeros(pages, 2, 2, P, nkv, hd, device=DEV, dtype=dtype)  # [pages, layers, k/v, P, nkv, hd]
+    layer = 1
+    ops.qk_norm_rope_kv(qkv, nq, nkv, hd, q_norm_w=qw.to(DEV) if norm else None, k_norm_w=kw.to(DEV) if norm else None,
+                        eps=eps, weight_offset=0.0, cos=cos, sin=sin, positions=positions.to(DEV), slots=slots.to(DEV),
+                        k_cache=cache[:, layer, 0], v_cache=cache[:, layer, 1], page_stride=cache.stride(0), page_size=P)
+    q_ref = _rope_ref(src[:, : nq * hd].view(T, nq, hd), positions, rot, theta, qw.float() if norm else None, eps, 0.0)
+    k_ref = _rope_ref(src[:, nq * hd: (nq + nkv) * hd].view(T, nkv, hd), positions, rot, theta, kw.float() if norm else None, eps, 0.0)
+    v_ref = src[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    t = tol(dtype)
+    assert torch.allclose(qkv[:, : nq * hd].float().cpu().view(T, nq, hd), q_ref, **t)
+    assert torch.equal(qkv[:, nq * hd:].float().cpu(), src[:, nq * hd:])  # k, v inputs are not touched
+    flat = cache[:, layer].float().cpu()  # [pages, 2, P, nkv, hd]
+    for i in range(T):
+        s = int(slots[i])
+        if s < 0:
+            continue
+        assert torch.allclose(flat[s // P, 0, s % P], k_ref[i], **t), f"k row {i}"
+        assert torch.allclose(flat[s // P, 1, s % P], v_ref[i].to(dtype).float(), atol=0, rtol=0), f"v row {i}"
+    written = {int(s) for s in slots if s >= 0}
+    for s in range(pages * P):
+        if s not in written:
+            assert flat[s // P, :, s % P].abs().sum() == 0, f"slot {s} was written"
+    assert cache[:, 0].abs().sum() == 0  # the other layer of the page is untouched
+
+
+def _paged(k, v, P, order, dtype, pages_total):
+    """Put [S, nkv, hd] keys/values into pages in the given page order. Returns cache, block table row."""
+    S, nkv, hd = k.shape
+    cache = torch.zeros(pages_total, 1, 2, P, nkv, hd, dtype=dtype)
+    for j in range(S):
+        cache[order[j // P], 0, 0, j % P] = k[j].to(dtype)
+        cache[order[j // P], 0, 1, j % P] = v[j].to(dtype)
+    return cache
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,P,window", [
+    (4, 2, 16, 8, None), (6, 2, 32, 16, None), (3, 1, 64, 4, 7), (8, 8, 128, 16, None), (5, 5, 256, 2, 33),
+    (12, 4, 48, 16, None), (32, 8, 128, 16, 100), (2, 1, 8, 1, None)])
+def test_attention_generic(dtype, nq, nkv, hd, P, window):
+    """Two requests in one batch: a prompt portion over a cached prefix, and a single decoded token."""
+    from openinfer_b200.kernels import ops
+    torch.manual_seed(nq * 100 + hd)
+    S0, new0, S1 = 70, 9, 131          # request 0: 61 cached + 9 new rows; request 1: 130 cached + 1 new
+    scale = 1.0 / math.sqrt(hd)
+    pages_total = 80
+    perm = torch.randperm(pages_total).tolist()
+    n0, n1 = -(-S0 // P), -(-S1 // P)
+    if n0 + n1 > pages_total:
+        pages_total = n0 + n1 + 3
+        perm = torch.randperm(pages_total).tolist()
+    order0, order1 = perm[:n0], perm[n0: n0 + n1]
+    ks = [torch.randn(S, nkv, hd) for S in (S0, S1)]
+    vs = [torch.randn(S, nkv, hd) for S in (S0, S1)]
+    qs = [torch.randn(S, nq, hd) for S in (S0, S1)]
+    cache = _paged(ks[0], vs[0], P, order0, dtype, pages_total)
+    c1 = _paged(ks[1], vs[1], P, order1, dtype, pages_total)
+    cache = (cache + c1).to(DEV)
+    bt = torch.zeros(2, max(n0, n1), dtype=torch.int32)
+    bt[0, :n0] = torch.tensor(order0)
+    bt[1, :n1] = torch.tensor(order1)
+    rows = [(0, p) for p in range(S0 - new0, S0)] + [(1, S1 - 1)]
+    q = torch.stack([qs[r][p] for r, p in rows]).to(dtype)              # [T, nq, hd]
+    wide = torch.zeros(len(rows), nq * hd + 2 * nkv * hd, dtype=dtype)  # q lives in a wider buffer
+    wide[:, : nq * hd] = q.view(len(rows), -1)
+    wide = wide.to(DEV)
+    out = torch.empty(len(rows), nq * hd, device=DEV, dtype=dtype)
+    ops.attention_generic(wide[:, : nq * hd], out, cache[:, 0, 0], cache[:, 0, 1], cache.stride(0), P, bt.to(DEV),
+                          torch.tensor([r for r, _ in rows], dtype=torch.int32, device=DEV),
+                          torch.tensor([p for _, p in rows], dtype=torch.int32, device=DEV), nq, nkv, hd, scale, window)
+    for i, (r, p) in enumerate(rows):
+        kk, vv = ks[r].to(dtype).float(), vs[r].to(dtype).float()
+        qq = torch.zeros(p + 1, nq, hd)
+        qq[p] = q[i].float()
+        ref = plain.causal_attention(qq, kk[: p + 1], vv[: p + 1], scale, window)[p]
+        assert torch.allclose(out[i].float().cpu().view(nq, hd), ref, **tol(dtype)), f"row {i} (request {r}, position {p})"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """One key among hundreds is made to stand out (scaled query and key): the output must be
+    that key's value, wherever in the cache it lies: first position, a page's edge, mid-page."""
+    from openinfer_b200.kernels import ops
+    nq, nkv, hd, P, S = 2, 1, 32, 16, 600
+    for far in (0, 15, 16, 17, 255, 256, 300, 598, 599):
+        k = torch.randn(S, nkv, hd) * 0.1
+        v = torch.randn(S, nkv, hd)
+        q = torch.randn(1, nq, hd) * 0.1
+        direction = torch.randn(hd)
+        direction /= direction.norm()
+        k[far, 0] = direction * 12.0
+        q[0, :] = direction * 12.0 * math.sqrt(hd) / 2       # score = 72 * ... far above the rest
+        order = torch.randperm(40).tolist()
+        cache = _paged(k, v, P, order, dtype, 40).to(DEV)
+        bt = torch.tensor([order[: -(-S // P)]], dtype=torch.int32, device=DEV)
+        out = torch.empty(1, nq * hd, device=DEV, dtype=dtype)
+        ops.attention_generic(q.view(1, -1).to(dtype).to(DEV), out, cache[:, 0, 0], cache[:, 0, 1], cache.stride(0), P, bt,
+                              torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([S - 1], dtype=torch.int32, device=DEV),
+                              nq, nkv, hd, 1.0 / math.sqrt(hd), None)
+        want = v[far, 0].to(dtype).float()
+        for h in range(nq):
+            assert torch.allclose(out[0].float().cpu().view(nq, hd)[h], want, atol=2e-2), f"far key at {far}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(dtype):
+    """The key just outside the window is made huge: it must not be seen; the one just inside must."""
+    from openinfer_b200.kernels import ops
+    nq, nkv, hd, P, S, W = 1, 1, 16, 4, 50, 9
+    for inside in (False, True):
+        k = torch.randn(S, nkv, hd) * 0.1
+        v = torch.randn(S, nkv, hd)
+        d = torch.zeros(hd)
+        d[0] = 1.0
+        pos = S - 1
+        edge = pos - W + (1 if inside else 0)   # pos - W + 1 is the oldest visible key
+        k[edge, 0] = d * 20
+        q = (d * 20).view(1, 1, hd)
+        order = list(range(13))
+        cache = _paged(k, v, P, order, dtype, 13).to(DEV)
+        bt = torch.tensor([order], dtype=torch.int32, device=DEV)
+        out = torch.empty(1, hd, device=DEV, dtype=dtype)
+        ops.attention_generic(q.view(1, -1).to(dtype).to(DEV), out, cache[:, 0, 0], cache[:, 0, 1], cache.stride(0), P, bt,
+                              torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([pos], dtype=torch.int32, device=DEV),
+                              nq, nkv, hd, 1.0, W)
+        close = torch.allclose(out[0].float().cpu(), v[edge, 0].to(dtype).float(), atol=2e-2)
+        assert close == inside
+
+
+def test_argmax_ties_and_odd_vocab():
+    from openinfer_b200.kernels import ops
+    for vocab in (5, 1000, 151936 // 7):
+        logits = torch.randn(6, vocab, device=DEV)
+        logits[1, vocab // 2] = 50.0
+        logits[2, :] = 1.0                       # all tied: lowest index
+        logits[3, [vocab - 1, 2]] = 60.0         # tie between two: lowest index
+        logits[4, vocab - 1] = 70.0
+        out = torch.empty(6, dtype=torch.int32, device=DEV)
+        ops.argmax(out, logits)
+        ref = [int(torch.argmax(logits[0])), vocab // 2, 0, 2, vocab - 1, int(torch.argmax(logits[5]))]
+        assert out.tolist() == ref
+        wide = torch.randn(3, vocab + 5, device=DEV)[:, :vocab]  # strided rows
+        out3 = torch.empty(3, dtype=torch.int32, device=DEV)
+        ops.argmax(out3, wide)
+        assert out3.tolist() == torch.argmax(wide, dim=-1).tolist()
+
+
+@pytest.mark.parametrize("vocab", [50, 384, 5000])
+def test_sample_matches_plain_distribution(vocab):
+    """The kept set and the drawn token follow the plain statement of temperature / top-k /
+    top-p / min-p, for uniform numbers across [0, 1)."""
+    from openinfer_b200.kernels import ops
+    torch.manual_seed(vocab)
+    settings = [(0.8, -1, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (0.7, -1, 0.9, 0.0), (1.3, 20, 0.8, 0.0),
+                (1.0, -1, 1.0, 0.1), (0.9, 10, 0.95, 0.05), (1.0, -1, 0.01, 0.0)]
+    us = [0.0, 0.001, 0.25, 0.5, 0.75, 0.999, 0.9999999]
+    logits = torch.randn(len(settings), vocab) * 2.0
+    for u in us:
+        rows = len(settings)
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        scratch = torch.empty(rows * vocab, device=DEV)
+        ops.sample(out, logits.to(DEV), scratch,
+                   torch.tensor([s[0] for s in settings], device=DEV), torch.tensor([max(s[1], 0) for s in settings], dtype=torch.int32, device=DEV),
+                   torch.tensor([s[2] for s in settings], device=DEV), torch.tensor([s[3] for s in settings], device=DEV),
+                   torch.full((rows,), u, device=DEV))
+        for r, (t, k, p, mp) in enumerate(settings):
+            dist = plain.sampling_distribution(logits[r], t, k, p, mp)
+            tok = int(out[r])
+            assert dist[tok] > 0, f"setting {settings[r]} u={u}: token {tok} is outside the kept set"
+            cdf = torch.cumsum(dist, 0)
+            lo = float(cdf[tok] - dist[tok])
+            assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, f"setting {settings[r]} u={u}: token {tok} covers [{lo}, {float(cdf[tok])}]"

@@ -1,0 +1,215 @@
+"""The scheduler's decisions with a fake executor (no GPU)."""
+from typing import Dict, List
+
+import pytest
+
+from openinfer_b200.engine.scheduler import (DecodeItem, Event, Executor, PrefillItem, Request, Scheduler,
+                                             lifetime_pages)
+from openinfer_b200.sampling.params import SamplingParams
+
+
+class FakeExecutor(Executor):
+    """Counts pages like the real cache does and 'generates' token = (last input token + 1) % 100."""
+
+    def __init__(self, total_pages=64, page_size=4, fail_on_step=None, real_pages=None):
+        self.page_size, self.total_pages = page_size, total_pages
+        self.real_pages = total_pages if real_pages is None else real_pages  # what there really is
+        self.tokens: Dict[object, int] = {}
+        self.batches: List[tuple] = []
+        self.dropped: List[object] = []
+        self.fail_on_step = fail_on_step
+
+    def used(self):
+        return sum(-(-n // self.page_size) for n in self.tokens.values())
+
+    def free_pages(self):
+        return self.total_pages - self.used()
+
+    def execute(self, prefill, decode, step_seed):
+        self.batches.append(([(p.request_id, len(p.tokens), p.is_last) for p in prefill],
+                             [d.request_id for d in decode]))
+        if self.fail_on_step is not None and len(self.batches) - 1 == self.fail_on_step:
+            raise RuntimeError("injected failure")
+        out = {}
+        grow = {p.request_id: len(p.tokens) for p in prefill}
+        grow.update({d.request_id: 1 for d in decode})
+        need = sum(-(-(self.tokens.get(r, 0) + n) // self.page_size) - -(-self.tokens.get(r, 0) // self.page_size)
+                   for r, n in grow.items())
+        if need > self.real_pages - self.used():
+            raise RuntimeError("OutOfPages")
+        for p in prefill:
+            self.tokens[p.request_id] = self.tokens.get(p.request_id, 0) + len(p.tokens)
+            if p.is_last:
+                out[p.request_id] = (p.tokens[-1] + 1) % 100
+        for d in decode:
+            self.tokens[d.request_id] += 1
+            out[d.request_id] = (d.token + 1) % 100
+        return out
+
+    def drop(self, rid):
+        self.dropped.append(rid)
+        self.tokens.pop(rid, None)
+
+
+def sched(ex, **kw):
+    kw.setdefault("max_context_tokens", 1000)
+    return Scheduler(ex, **kw)
+
+
+def collect(events):
+    toks, fin = {}, {}
+    for e in events:
+        if e.kind == "token":
+            toks.setdefault(e.request_id, []).append(e.token)
+        else:
+            fin[e.request_id] = (e.kind, e.reason)
+    return toks, fin
+
+
+def test_lifetime_pages():
+    assert lifetime_pages(5, 3, 4) == 2 and lifetime_pages(5, 1, 4) == 2 and lifetime_pages(8, 1, 4) == 2
+    assert lifetime_pages(8, 2, 4) == 3 and lifetime_pages(1, 0, 4) == 1
+
+
+def test_generates_and_frees():
+    ex = FakeExecutor()
+    s = sched(ex)
+    s.submit(Request("a", [1, 2, 3], max_tokens=4))
+    toks, fin = collect(s.run())
+    assert toks["a"] == [4, 5, 6, 7] and fin["a"] == ("finished", "length")
+    assert ex.dropped == ["a"] and ex.used() == 0
+    # the first token comes from the prompt's last step; three decode steps follow
+    assert ex.batches[0] == ([("a", 3, True)], []) and all(b == ([], ["a"]) for b in ex.batches[1:]) and len(ex.batches) == 4
+
+
+def test_prompt_cut_under_token_budget_fifo_and_mixed_with_decode():
+    ex = FakeExecutor(total_pages=200)
+    s = sched(ex, max_prefill_tokens=10)
+    s.submit(Request("a", list(range(4)), max_tokens=8))
+    s.submit(Request("b", list(range(23)), max_tokens=2))
+    s.submit(Request("c", list(range(5)), max_tokens=2))
+    s.run()
+    pre = [b[0] for b in ex.batches]
+    assert pre[0] == [("a", 4, True), ("b", 6, False)]          # budget 10: a whole, b's first 6
+    assert pre[1] == [("b", 10, False)]                          # b stays at the front
+    assert pre[2] == [("b", 7, True), ("c", 3, False)]
+    assert pre[3] == [("c", 2, True)]
+    assert ex.batches[1][1] == ["a"] and ex.batches[2][1] == ["a"]  # a decodes beside b's portions
+    assert sum(n for step in pre for _, n, _ in step) == 4 + 23 + 5
+
+
+def test_stop_token_not_emitted_and_ignore_eos():
+    ex = FakeExecutor()
+    s = sched(ex, stop_token_ids=[6])
+    s.submit(Request("a", [3], max_tokens=10))                                   # 4, 5, then 6 = stop
+    s.submit(Request("b", [3], max_tokens=5, sampling=SamplingParams(ignore_eos=True)))
+    s.submit(Request("c", [5], max_tokens=5))                                    # first token is the stop token
+    toks, fin = collect(s.run())
+    assert toks["a"] == [4, 5] and fin["a"] == ("finished", "stop")
+    assert toks["b"] == [4, 5, 6, 7, 8] and fin["b"] == ("finished", "length")
+    assert "c" not in toks and fin["c"] == ("finished", "stop")
+    assert sorted(ex.dropped) == ["a", "b", "c"]
+
+
+def test_max_tokens_one_finishes_after_prompt():
+    ex = FakeExecutor()
+    s = sched(ex)
+    s.submit(Request("a", [1, 2], max_tokens=1))
+    toks, fin = collect(s.run())
+    assert toks["a"] == [3] and fin["a"] == ("finished", "length") and len(ex.batches) == 1
+
+
+def test_rejections():
+    ex = FakeExecutor(total_pages=4, page_size=4)
+    s = sched(ex, max_context_tokens=50)
+    s.submit(Request("long", list(range(45)), max_tokens=10))   # 55 > 50
+    s.submit(Request("big", list(range(20)), max_tokens=4))     # 6 pages > 4 in total
+    s.submit(Request("empty", [], max_tokens=4))
+    s.submit(Request("ok", [1, 2, 3], max_tokens=4))
+    toks, fin = collect(s.run())
+    assert fin["long"] == ("rejected", "context_length") and fin["big"] == ("rejected", "kv_budget")
+    assert fin["empty"] == ("rejected", "empty_prompt") and fin["ok"] == ("finished", "length")
+    assert all(rid == "ok" for b in ex.batches for rid, _, _ in b[0])
+
+
+def test_admission_reserves_whole_lifetime_so_pages_never_run_out():
+    """Three requests of 3 pages each in a pool of 7: two run, the third waits until one ends."""
+    ex = FakeExecutor(total_pages=7, page_size=4)
+    s = sched(ex)
+    for rid in "abc":
+        s.submit(Request(rid, list(range(6)), max_tokens=6))     # ceil(12 / 4) = 3 pages
+    events = []
+    seen_c_start = None
+    while s.has_work():
+        events += s.step()
+        assert ex.used() <= 7
+        if seen_c_start is None and any(rid == "c" for rid, _, _ in ex.batches[-1][0]):
+            seen_c_start = len(ex.batches)
+            assert ex.dropped, "c was admitted before anyone finished"
+    toks, fin = collect(events)
+    assert all(len(toks[r]) == 6 and fin[r] == ("finished", "length") for r in "abc")
+    assert ex.used() == 0 and seen_c_start is not None
+
+
+def test_later_smaller_request_may_pass_a_deferred_one():
+    ex = FakeExecutor(total_pages=5, page_size=4)
+    s = sched(ex)
+    s.submit(Request("a", list(range(8)), max_tokens=4))    # 3 pages
+    s.submit(Request("b", list(range(8)), max_tokens=4))    # 3 pages: does not fit beside a
+    s.submit(Request("c", list(range(2)), max_tokens=2))    # 1 page: fits
+    s.step()
+    assert {rid for rid, _, _ in ex.batches[0][0]} == {"a", "c"}
+    assert [r.request_id for r in s.deferred] == ["b"]
+    toks, fin = collect(s.run())
+    assert fin["b"] == ("finished", "length")
+
+
+def test_decode_slots_limit():
+    ex = FakeExecutor(total_pages=100)
+    s = sched(ex, max_decode_batch=2)
+    for rid in "abc":
+        s.submit(Request(rid, [1], max_tokens=3))
+    s.step()
+    assert len(ex.batches[0][0]) == 2 and len(s.deferred) == 1
+    s.run()
+    assert max(len(b[1]) for b in ex.batches) <= 2
+
+
+def test_failed_step_fails_everyone_it_touched_and_the_rest_goes_on():
+    ex = FakeExecutor(fail_on_step=2)
+    s = sched(ex)
+    s.submit(Request("a", [1, 2], max_tokens=5))
+    s.submit(Request("b", [1, 2], max_tokens=5))
+    ev = s.step() + s.step() + s.step()
+    toks, fin = collect(ev)
+    assert fin["a"][0] == "error" and fin["b"][0] == "error" and "injected" in fin["a"][1]
+    assert sorted(ex.dropped) == ["a", "b"] and not s.active and ex.used() == 0
+    s.submit(Request("c", [7], max_tokens=2))
+    toks, fin = collect(s.run())
+    assert toks["c"] == [8, 9] and fin["c"] == ("finished", "length")
+
+
+def test_pages_run_out_when_the_pool_is_smaller_than_reported():
+    """The decided behaviour when a step cannot get its pages: the step's requests fail with an
+    error and are dropped; nothing hangs, the scheduler stays usable."""
+    ex = FakeExecutor(total_pages=12, page_size=4, real_pages=2)
+    s = Scheduler(ex, max_context_tokens=1000)
+    s.submit(Request("a", list(range(12)), max_tokens=4))
+    toks, fin = collect(s.run())
+    assert fin["a"][0] == "error" and "OutOfPages" in fin["a"][1]
+    assert ex.dropped == ["a"] and not s.has_work()
+
+
+def test_per_step_seed_is_reproducible():
+    seeds = []
+
+    class Rec(FakeExecutor):
+        def execute(self, prefill, decode, step_seed):
+            seeds.append(step_seed)
+            return super().execute(prefill, decode, step_seed)
+
+    for _ in range(2):
+        s = sched(Rec(), seed=42)
+        s.submit(Request("a", [1], max_tokens=3))
+        s.run()
+    assert seeds[:3] == seeds[3:] and len(set(seeds[:3])) == 3
