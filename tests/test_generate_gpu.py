@@ -1,0 +1,119 @@
+"""Generation through the Python entry point and the command line."""
+import json
+import os
+import random
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import ROOT, TINY, make_model_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {n: make_model_folder(str(tmp_path_factory.mktemp(f"g{n}")), cfg, seed) for n, (cfg, seed) in TINY.items()}
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain(folders, name):
+    """Config A: prompts of 5/11/17 tokens, 8 greedy tokens; B: 1/9/33/70 in portions of 13."""
+    from openinfer_b200 import LLM
+    cfg, w = plain.read_model_folder(folders[name])
+    rng = random.Random(11)
+    lens = [5, 11, 17] if name == "A" else [1, 9, 33, 70]
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in lens]
+    n_new = 8 if name == "A" else 12
+    want = [plain.greedy_generate(cfg, w, p, n_new) for p in prompts]
+    llm = LLM(folders[name], dtype="float32", max_cache_tokens=1024, max_prefill_tokens=13,
+              kv_page_size=8 if name == "A" else 16)
+    assert llm.generate(prompts, max_tokens=n_new) == want
+    assert llm.runner.cache.min_free_pages() == llm.runner.cache.num_pages
+    # the same requests one at a time give the same tokens (batching does not change results)
+    assert [llm.generate([p], max_tokens=n_new)[0] for p in prompts] == want
+
+
+def test_bf16_greedy_follows_plain_where_the_margin_is_clear(folders):
+    from openinfer_b200 import LLM
+    cfg, w = plain.read_model_folder(folders["B"])
+    rng = random.Random(4)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (9, 33)]
+    got = LLM(folders["B"], dtype="bfloat16", max_cache_tokens=512).generate(prompts, max_tokens=6)
+    for p, g in zip(prompts, got):
+        seq = list(p)
+        for tok in g:
+            logits = plain.forward_logits(cfg, w, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if float(top2[0] - top2[1]) > 0.05 * float(logits.abs().max()):
+                assert tok == int(logits.argmax())
+            seq.append(tok)
+
+
+def test_sampled_generation_is_reproducible_and_seed_dependent(folders):
+    from openinfer_b200 import LLM, SamplingParams
+    llm = LLM(folders["B"], dtype="bfloat16", max_cache_tokens=1024, max_prefill_tokens=13)
+    rng = random.Random(8)
+    prompts = [random_tokens(rng, n, 384) for n in (1, 9, 33, 70)]
+    sp = SamplingParams(temperature=0.8, seed=1234)
+    a = llm.generate(prompts, sp, max_tokens=12)
+    b = llm.generate(prompts, sp, max_tokens=12)
+    assert a == b and all(len(x) == 12 for x in a)
+    # a seeded request's tokens do not depend on what else is in the batch
+    assert llm.generate([prompts[2]], sp, max_tokens=12)[0] == a[2]
+    c = llm.generate(prompts, SamplingParams(temperature=0.8, seed=99), max_tokens=12)
+    assert c != a
+    # top_k = 1 and a tiny top_p collapse to greedy (pegainfer-qwen3/tests/sampling_behavior.rs:1-15)
+    g = llm.generate(prompts, max_tokens=6)
+    assert llm.generate(prompts, SamplingParams(temperature=1.0, top_k=1), max_tokens=6) == g
+    assert llm.generate(prompts, SamplingParams(temperature=1.0, top_p=1e-6, seed=5), max_tokens=6) == g
+    # temperature gives diversity across seeds
+    outs = {tuple(llm.generate([prompts[1]], SamplingParams(temperature=1.5, seed=s), max_tokens=8)[0]) for s in range(6)}
+    assert len(outs) > 1
+
+
+def test_stop_tokens_and_rejection(folders, tmp_path):
+    from openinfer_b200 import LLM
+    import shutil
+    f = str(tmp_path / "m")
+    shutil.copytree(folders["A"], f)
+    cfg, w = plain.read_model_folder(f)
+    prompt = [3, 1, 4, 1, 5]
+    free = plain.greedy_generate(cfg, w, prompt, 8)
+    stop = free[3]
+    first = free.index(stop)
+    raw = json.load(open(os.path.join(f, "config.json")))
+    raw["eos_token_id"] = stop
+    json.dump(raw, open(os.path.join(f, "config.json"), "w"))
+    llm = LLM(f, dtype="float32", max_cache_tokens=512)
+    res = llm.generate_detailed([prompt, list(range(600))], max_tokens=8)
+    assert res[0].token_ids == free[:first] and res[0].finish_reason == "stop"   # the stop token is not emitted
+    assert res[1].finish_reason == "rejected:context_length" and res[1].token_ids == []
+
+
+def test_command_line(folders):
+    cfg, w = plain.read_model_folder(folders["A"])
+    want = plain.greedy_generate(cfg, w, [7, 8, 9], 5)
+    out = subprocess.run([sys.executable, "-m", "openinfer_b200", "--model-path", folders["A"], "--dtype", "float32",
+                          "--prompt-ids", "7,8,9", "--max-tokens", "5", "--num-pages", "32", "--kv-page-size", "8"],
+                         cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["token_ids"] == want and line["finish_reason"] == "length"
+
+
+def test_memory_budget_sizes_the_pool(folders):
+    from openinfer_b200 import LLM
+    llm = LLM(folders["A"], dtype="bfloat16", gpu_memory_utilization=0.05)
+    assert llm.runner.cache.num_pages > 100
+    assert len(llm.generate([[1, 2, 3]], max_tokens=4)[0]) == 4
+
+
+def test_no_cpu_path(folders):
+    from openinfer_b200.engine.runner import ModelRunner
+    from openinfer_b200.kernels import KernelError
+    with pytest.raises(KernelError, match="no CPU path"):
+        ModelRunner.from_folder(folders["A"], device="cpu", max_tokens=64)

@@ -1,0 +1,275 @@
+"""Each part alone against its plain statement, and the generality of the assembly: a
+window, a layer that reads another layer's cache, a layer named twice in the run order, and
+a toy mixer with state of its own that is defined here, registered, built and stepped
+without touching the package."""
+import dataclasses
+import math
+import random
+from typing import Dict, List, Optional
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _runner(spec, dtype, tensors, page=4, pages=64):
+    from openinfer_b200.cache import CacheManager
+    from openinfer_b200.engine.runner import ModelRunner
+    from openinfer_b200.parts.model import Model
+    model = Model(spec, dtype)
+    model.load({k: v.to(DEV).to(dtype) for k, v in tensors.items()}, torch.device(DEV))
+    cache = CacheManager(page_size=page)
+    model.bind_cache(cache)
+    cache.allocate(pages, 8, device=torch.device(DEV), dtype=dtype)
+    return ModelRunner(model, cache, torch.device(DEV))
+
+
+def _random_tensors(spec, seed):
+    from openinfer_b200.parts.model import Model
+    from openinfer_b200.weights import random_tensors
+    return random_tensors(Model(spec, torch.bfloat16).expected_tensors(), seed)
+
+
+def _mini_spec(window=None, order=None, layers=2, nq=4, nkv=2, hd=16, hidden=40, inter=72, vocab=50,
+               rotary_dim=None, qk_norm=True, offset=0.0):
+    from openinfer_b200.parts.spec import (AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NormSpec, PositionSpec)
+    norm = NormSpec("rms", hidden, 1e-5, offset)
+    pos = PositionSpec("rope", rotary_dim or hd, 777.0, 256)
+    mixer = AttentionSpec(hidden_size=hidden, num_heads=nq, num_kv_heads=nkv, head_dim=hd,
+                          softmax_scale=1 / math.sqrt(hd), position=pos,
+                          qk_norm=NormSpec("rms", hd, 1e-5, offset) if qk_norm else None, window=window)
+    blocks = tuple(BlockSpec(name=f"L{i}.", mixer=mixer, feed_forward=GatedMlpSpec(hidden_size=hidden, intermediate_size=inter),
+                             input_norm=norm, post_norm=norm) for i in range(layers))
+    return ModelSpec(vocab_size=vocab, hidden_size=hidden, blocks=blocks, order=tuple(order or range(layers)),
+                     final_norm=norm, embedding_name="emb", final_norm_name="fn.", head_name="head", max_positions=256)
+
+
+def _plain_forward(spec, w, toks, window=None, order=None, cache_of=None, rotary_dim=None, qk_norm=True, offset=0.0):
+    """Whole-sequence float32 forward of a mini spec, from the plain part functions."""
+    w = {k: v.float() for k, v in w.items()}
+    m = spec.blocks[0].mixer
+    T = len(toks)
+    positions = torch.arange(T)
+    h = plain.embedding(torch.tensor(toks), w["emb"])
+    kv_of_call = {}
+    calls = spec.calls()
+    for ci, c in enumerate(calls):
+        p = f"L{c.layer}."
+        x = plain.rms_norm(h, offset + w[p + "input_layernorm.weight"], 1e-5)
+        a = p + "self_attn."
+        q = plain.linear(x, w[a + "q_proj.weight"]).view(T, m.num_heads, m.head_dim)
+        if qk_norm:
+            q = plain.rms_norm(q, offset + w[a + "q_norm.weight"], 1e-5)
+        rot = rotary_dim or m.head_dim
+        cos, sin = plain.rope_tables(rot, 777.0, positions)
+        q = torch.cat([plain.apply_rope(q[..., :rot], cos, sin), q[..., rot:]], -1)
+        if c.read_cache_of is None:
+            k = plain.linear(x, w[a + "k_proj.weight"]).view(T, m.num_kv_heads, m.head_dim)
+            if qk_norm:
+                k = plain.rms_norm(k, offset + w[a + "k_norm.weight"], 1e-5)
+            k = torch.cat([plain.apply_rope(k[..., :rot], cos, sin), k[..., rot:]], -1)
+            v = plain.linear(x, w[a + "v_proj.weight"]).view(T, m.num_kv_heads, m.head_dim)
+            kv_of_call[ci] = (k, v)
+        else:
+            k, v = kv_of_call[c.read_cache_of]
+        o = plain.causal_attention(q, k, v, m.softmax_scale, window)
+        h = h + plain.linear(o.reshape(T, -1), w[a + "o_proj.weight"])
+        x = plain.rms_norm(h, offset + w[p + "post_attention_layernorm.weight"], 1e-5)
+        h = h + plain.swiglu(x, w, p + "mlp.")
+    h = plain.rms_norm(h, offset + w["fn.weight"], 1e-5)
+    return plain.linear(h, w["head"])
+
+
+def _step_all(runner, toks, cuts):
+    from openinfer_b200.engine.runner import StepEntry
+    out, at = [], 0
+    for n in cuts:
+        out.append(runner.step([StepEntry("r", toks[at: at + n], list(range(n)))]).float().cpu())
+        at += n
+    assert at == len(toks)
+    runner.end("r")
+    return torch.cat(out)
+
+
+def _cuts(n, rng):
+    cuts = []
+    while n:
+        c = min(n, rng.choice([1, 2, 3, 7, 11]))
+        cuts.append(c)
+        n -= c
+    return cuts
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ["plain", "window", "partial_rotary", "no_qk_norm", "one_plus_w",
+                                  "shared_cache", "layer_twice"])
+def test_assemblies(dtype, case):
+    from openinfer_b200.parts.spec import LayerCall
+    kw, pkw = {}, {}
+    if case == "window":
+        kw = dict(window=6)
+        pkw = dict(window=6)
+    elif case == "partial_rotary":
+        kw = dict(rotary_dim=8)
+        pkw = dict(rotary_dim=8)
+    elif case == "no_qk_norm":
+        kw = dict(qk_norm=False)
+        pkw = dict(qk_norm=False)
+    elif case == "one_plus_w":
+        kw = dict(offset=1.0)
+        pkw = dict(offset=1.0)
+    elif case == "shared_cache":      # the second call reads the keys and values of the first
+        kw = dict(order=(0, LayerCall(1, read_cache_of=0)))
+    elif case == "layer_twice":       # layer 0 runs twice (with a cache of its own each time), then layer 1
+        kw = dict(order=(0, 0, 1))
+    spec = _mini_spec(**kw)
+    w = _random_tensors(spec, 3)
+    rng = random.Random(1)
+    toks = [rng.randrange(50) for _ in range(37)]
+    ref = _plain_forward(spec, w, toks, **pkw)
+    runner = _runner(spec, dtype, w)
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    assert_close(_step_all(runner, toks, [len(toks)]), ref, name, f"{case} whole")
+    assert_close(_step_all(runner, toks, _cuts(len(toks), rng)), ref, name, f"{case} in portions")
+    runner.cache.check()
+    assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
+    if case == "window":
+        # pages behind the window went back while the request was live
+        from openinfer_b200.engine.runner import StepEntry
+        for t in toks:
+            runner.step([StepEntry("w", [t], [])])
+        assert runner.cache.groups[0].pool.used_count <= -(-6 // 4) + 1
+        runner.end("w")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_each_part_alone(dtype):
+    """Norm, feed-forward and attention parts, each called by itself."""
+    from openinfer_b200.parts import build_feed_forward, build_norm
+    from openinfer_b200.parts.spec import GatedMlpSpec, NormSpec
+    torch.manual_seed(0)
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    x = torch.randn(9, 56).to(dtype)
+    norm = build_norm(NormSpec("rms", 56, 1e-4))
+    wn = (1 + 0.1 * torch.randn(56)).to(dtype)
+    norm.load({"weight": wn.to(DEV)})
+    got = norm(x.to(DEV))
+    assert torch.allclose(got.float().cpu(), plain.rms_norm(x.float(), wn.float(), 1e-4), atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
+    ffn = build_feed_forward(GatedMlpSpec(hidden_size=56, intermediate_size=88))
+    wf = {k: (torch.randn(s) * 0.1).to(dtype) for k, s in
+          {"gate_proj.weight": (88, 56), "up_proj.weight": (88, 56), "down_proj.weight": (56, 88)}.items()}
+    ffn.load({k: v.to(DEV) for k, v in wf.items()})
+    got = ffn.forward(x.to(DEV), None)
+    ref = plain.swiglu(x.float(), {k: v.float() for k, v in wf.items()}, "")
+    assert_close(got, ref, name, "gated mlp")
+
+
+# ---------------------------------------------------------------------------
+# a toy mixer with state of its own: a running mean of the inputs of a request
+# ---------------------------------------------------------------------------
+@dataclasses.dataclass(frozen=True)
+class RunningMeanSpec:
+    kind: str = "toy_running_mean"
+    hidden_size: int = 0
+
+
+def _register_toy():
+    from openinfer_b200.cache import StateNeed
+    from openinfer_b200.parts import Mixer, ParamInfo, register_mixer
+
+    @register_mixer("toy_running_mean")
+    class RunningMean(Mixer):
+        """y_t = w * mean(x_0..x_t) of the request; the state is (sum, count). Written with
+        torch ops: it is a test double, not a product kernel."""
+
+        def parameters(self):
+            return {"scale.weight": ParamInfo((self.spec.hidden_size,), ("one_plus_normal", 0.02))}
+
+        def load(self, tensors):
+            self.w = tensors["scale.weight"]
+
+        def state_needs(self):
+            return [StateNeed((self.spec.hidden_size + 1,), "float32")]
+
+        def forward(self, x, ctx, binding):
+            state = ctx.cache.state_tensor(binding.states[0])
+            out = torch.empty_like(x)
+            row = 0
+            for b, n in enumerate(ctx.q_lens_host):
+                slot = ctx.state_slots_host[b]
+                s = state[slot]
+                xs = x[row: row + n].float()
+                csum = torch.cumsum(xs, 0) + s[:-1]
+                cnt = torch.arange(1, n + 1, device=x.device, dtype=torch.float32) + s[-1]
+                out[row: row + n] = (csum / cnt[:, None] * self.w.float()).to(x.dtype)
+                s[:-1] = csum[-1]
+                s[-1] = cnt[-1]
+                row += n
+            return out
+
+    return RunningMean
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps():
+    from openinfer_b200.engine.runner import StepEntry
+    from openinfer_b200.parts.spec import BlockSpec, GatedMlpSpec, ModelSpec, NormSpec
+    _register_toy()
+    hidden, vocab = 24, 31
+    norm = NormSpec("rms", hidden, 1e-5)
+    attn_block = _mini_spec(layers=1, hidden=hidden, nq=2, nkv=1, hd=8, inter=40, vocab=vocab).blocks[0]
+    toy_block = BlockSpec(name="T.", mixer=RunningMeanSpec(hidden_size=hidden), mixer_name="mix.",
+                          feed_forward=GatedMlpSpec(hidden_size=hidden, intermediate_size=40),
+                          input_norm=norm, post_norm=norm)
+    # one model with different mixers in different layers
+    spec = ModelSpec(vocab_size=vocab, hidden_size=hidden, blocks=(toy_block, attn_block), order=(0, 1),
+                     final_norm=norm, embedding_name="emb", final_norm_name="fn.", head_name="head", max_positions=256)
+    w = _random_tensors(spec, 5)
+    assert "T.mix.scale.weight" in w
+    runner = _runner(spec, torch.float32, w)
+    assert len(runner.cache.state_needs) == 1 and len(runner.cache.groups) == 1
+
+    def plain_forward(toks):
+        wf = {k: v.float() for k, v in w.items()}
+        T = len(toks)
+        h = plain.embedding(torch.tensor(toks), wf["emb"])
+        x = plain.rms_norm(h, wf["T.input_layernorm.weight"], 1e-5)
+        mean = torch.cumsum(x, 0) / torch.arange(1, T + 1)[:, None]
+        h = h + mean * wf["T.mix.scale.weight"]
+        h = h + plain.swiglu(plain.rms_norm(h, wf["T.post_attention_layernorm.weight"], 1e-5), wf, "T.mlp.")
+        sub = _mini_spec(layers=1, hidden=hidden, nq=2, nkv=1, hd=8, inter=40, vocab=vocab)
+        # the attention block on top, through the same plain functions as the other tests
+        m = sub.blocks[0].mixer
+        p = "L0."
+        x = plain.rms_norm(h, wf[p + "input_layernorm.weight"], 1e-5)
+        pos = torch.arange(T)
+        cos, sin = plain.rope_tables(8, 777.0, pos)
+        q = plain.apply_rope(plain.rms_norm(plain.linear(x, wf[p + "self_attn.q_proj.weight"]).view(T, 2, 8), wf[p + "self_attn.q_norm.weight"], 1e-5), cos, sin)
+        k = plain.apply_rope(plain.rms_norm(plain.linear(x, wf[p + "self_attn.k_proj.weight"]).view(T, 1, 8), wf[p + "self_attn.k_norm.weight"], 1e-5), cos, sin)
+        v = plain.linear(x, wf[p + "self_attn.v_proj.weight"]).view(T, 1, 8)
+        h = h + plain.linear(plain.causal_attention(q, k, v, m.softmax_scale).reshape(T, -1), wf[p + "self_attn.o_proj.weight"])
+        h = h + plain.swiglu(plain.rms_norm(h, wf[p + "post_attention_layernorm.weight"], 1e-5), wf, p + "mlp.")
+        return plain.linear(plain.rms_norm(h, wf["fn.weight"], 1e-5), wf["head"])
+
+    rng = random.Random(2)
+    a = [rng.randrange(vocab) for _ in range(19)]
+    b = [rng.randrange(vocab) for _ in range(11)]
+    # two requests interleaved, in portions: each keeps a state of its own
+    got_a, got_b = [], []
+    got_a.append(runner.step([StepEntry("a", a[:5], list(range(5)))]))
+    both = runner.step([StepEntry("b", b[:4], list(range(4))), StepEntry("a", a[5:6], [0])])
+    got_b.append(both[:4]); got_a.append(both[4:])
+    both = runner.step([StepEntry("a", a[6:], list(range(13))), StepEntry("b", b[4:], list(range(7)))])
+    got_a.append(both[:13]); got_b.append(both[13:])
+    assert_close(torch.cat(got_a), plain_forward(a), "float32", "toy request a")
+    assert_close(torch.cat(got_b), plain_forward(b), "float32", "toy request b")
+    runner.end("a")
+    # a new request in a's slot starts from a cleared state
+    again = runner.step([StepEntry("c", a, list(range(len(a))))])
+    assert_close(again, plain_forward(a), "float32", "toy request c in a reused slot")
+    runner.end("b"); runner.end("c")
+    runner.cache.check()
