@@ -1,0 +1,401 @@
+// Paged causal GQA attention on tensor cores for bfloat16, head_dim 32, 64 or 128: prompt portions
+// over a cached prefix and split-KV decode in ONE kernel.
+//
+// A CTA (4 warps) owns 64 query ROWS of one (request, kv head): row r is (token r / group,
+// query head r % group), so the `group` query heads that share a kv head sit next to each other
+// and every K/V tile is fetched once for all of them. A decoded token is simply a request with one
+// query token (group rows). Work items are planned on the host once per step and shared by all
+// layers, as the reference plans its attention tiles (pegainfer-kernels/src/ops/attention.rs:396-477);
+// an item may cover only a slice of the keys (split-KV, the reference's decode path:
+// pegainfer-kernels/csrc/shared/paged_attention.cu:189-263), in which case it writes a normalised
+// partial output and its log-sum-exp to scratch and `attention_merge_kernel` combines the slices.
+//
+// Math: s = (q . k) / sqrt(hd) for keys j <= pos (and j > pos - window), online softmax in float32
+// (exp2 with the scale folded in), o = sum p v (paged_attention.cu:439-567). K/V tiles of 64 keys
+// are gathered page by page with cp.async into swizzled shared memory, double buffered;
+// S = Q K^T and O = P V run as mma.sync m16n8k16 with float32 accumulators.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRows = 64;      // query rows per CTA
+constexpr int kKeys = 64;      // keys per tile
+constexpr int kThreads = 128;
+
+struct AttnParams {
+  const bf16* q; int q_row_stride;
+  bf16* out; int out_row_stride;
+  const bf16* k_cache; const bf16* v_cache; long long page_stride; int page_size;
+  const int* block_table; int bt_stride;
+  const int* cu_seqlens;   // [requests + 1] first row of each request in this step
+  const int* kv_lens;      // [requests] keys visible after this step
+  const int4* items;       // (request, first token of the tile, split, nsplits)
+  int nq, nkv, group;
+  float scale_log2;        // softmax scale * log2(e)
+  int window;              // 0 = none
+  float* part_o; float* part_lse; int max_splits;  // scratch for split items
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Shared-memory tile [kKeys][HD] bf16, 16-byte chunks XOR-swizzled by the row so that the eight
+// rows an ldmatrix reads fall into different banks.
+template <int HD>
+__device__ __forceinline__ int tile_offset(int row, int chunk) {
+  constexpr int kChunks = HD / 8;
+  return row * HD + ((chunk ^ (row & 7)) & (kChunks - 1)) * 8 + ((chunk & ~(kChunks - 1)) * 8);
+}
+
+template <int HD>
+__device__ __forceinline__ void load_tile(bf16* smem, const bf16* cache, const AttnParams& p, const int* bt,
+                                          int kvh, int key0, int key_end) {
+  // 64 rows x (HD/8) chunks; two threads per row, each HD/16 chunks
+  constexpr int kChunks = HD / 8;
+  const int row = threadIdx.x >> 1;
+  const int c0 = (threadIdx.x & 1) * (kChunks / 2);
+  const int key = key0 + row;
+  const bool valid = key < key_end;
+  const bf16* src = cache;
+  if (valid) {
+    const int page = bt[key / p.page_size];
+    src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
+  }
+#pragma unroll
+  for (int c = 0; c < kChunks / 2; ++c) {
+    const int chunk = c0 + c;
+    cp_async16(smem_u32(smem + tile_offset<HD>(row, chunk)), src + chunk * 8, valid);
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads)
+attention_mma_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  // [stage][K | V][kKeys][HD]
+  bf16* const tiles = reinterpret_cast<bf16*>(smem_raw);
+  auto k_tile = [&](int stage) { return tiles + (size_t)stage * 2 * kKeys * HD; };
+  auto v_tile = [&](int stage) { return tiles + (size_t)stage * 2 * kKeys * HD + kKeys * HD; };
+
+  const int4 item = p.items[blockIdx.x];
+  const int req = item.x, tok0 = item.y, split = item.z, nsplits = item.w;
+  const int kvh = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int group = p.group;
+  const int q_start = p.cu_seqlens[req];
+  const int q_len = p.cu_seqlens[req + 1] - q_start;
+  const int kv_len = p.kv_lens[req];
+  const int* bt = p.block_table + (size_t)req * p.bt_stride;
+  const int toks_per_tile = kRows / group;
+  const int tile_toks = min(toks_per_tile, q_len - tok0);
+  const int pos0 = kv_len - q_len + tok0;                 // position of the tile's first token
+  // keys any row of the tile may see
+  int lo = 0;
+  if (p.window > 0) lo = max(0, pos0 - p.window + 1);
+  int hi = pos0 + tile_toks;                              // exclusive: last token's own key included
+  lo &= ~(kKeys - 1);
+  // this item's slice of [lo, hi), in whole tiles
+  const int span_tiles = (hi - lo + kKeys - 1) / kKeys;
+  const int tiles_per_split = (span_tiles + nsplits - 1) / nsplits;
+  const int t_begin = split * tiles_per_split;
+  const int t_end = min(span_tiles, t_begin + tiles_per_split);
+
+  // ---- the two rows this thread owns in its warp's 16-row slab
+  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  int tok[2], head[2], pos[2];
+  bool row_ok[2];
+  {
+    const int rr[2] = {r_lo, r_hi};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int t = rr[i] / group;
+      tok[i] = tok0 + t;
+      head[i] = kvh * group + rr[i] % group;
+      row_ok[i] = t < tile_toks;
+      pos[i] = pos0 + t;
+    }
+  }
+
+  // ---- Q fragments straight from global memory (A operand, row-major)
+  constexpr int kSteps = HD / 16;
+  unsigned qf[kSteps][4];
+  {
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int ks = 0; ks < kSteps; ++ks) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        unsigned a = 0, b = 0;
+        if (row_ok[i]) {
+          const bf16* qp = p.q + (size_t)(q_start + tok[i]) * p.q_row_stride + (size_t)head[i] * HD + ks * 16 + col;
+          a = *reinterpret_cast<const unsigned*>(qp);
+          b = *reinterpret_cast<const unsigned*>(qp + 8);
+        }
+        qf[ks][i] = a;        // rows r_lo (i=0) / r_hi (i=1), cols ks*16 + col
+        qf[ks][i + 2] = b;    // same rows, cols + 8
+      }
+    }
+  }
+
+  constexpr int kOTiles = HD / 8;
+  float o[kOTiles][4];
+#pragma unroll
+  for (int j = 0; j < kOTiles; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // a warp whose 16 rows are all beyond the tile's tokens (decode: group rows of 64) only helps loading
+  const bool warp_active = warp * 16 < tile_toks * group;
+
+  if (t_begin < t_end) {
+    load_tile<HD>(k_tile(0), p.k_cache, p, bt, kvh, lo + t_begin * kKeys, hi);
+    cp_async_commit();
+    load_tile<HD>(v_tile(0), p.v_cache, p, bt, kvh, lo + t_begin * kKeys, hi);
+    cp_async_commit();
+  }
+  for (int t = t_begin; t < t_end; ++t) {
+    const int buf = (t - t_begin) & 1;
+    const int key0 = lo + t * kKeys;
+    const bool more = t + 1 < t_end;
+    if (more) {
+      load_tile<HD>(k_tile(buf ^ 1), p.k_cache, p, bt, kvh, key0 + kKeys, hi);
+      cp_async_commit();
+      load_tile<HD>(v_tile(buf ^ 1), p.v_cache, p, bt, kvh, key0 + kKeys, hi);
+      cp_async_commit();
+      cp_async_wait<3>();   // K of this tile has landed
+    } else {
+      cp_async_wait<1>();
+    }
+    __syncthreads();
+
+    unsigned pf[kKeys / 16][4];
+    if (warp_active) {
+      // ---- S = Q K^T : 16 rows x 64 keys per warp
+      float s[kKeys / 8][4];
+  #pragma unroll
+      for (int j = 0; j < kKeys / 8; ++j)
+  #pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+      {
+        const bf16* ks_ = k_tile(buf);
+        // ldmatrix x4: matrices (keys j*8.., d ks*16..+7), (same keys, d +8), (keys (j+1)*8.., d..), (.., d+8)
+        const int mat = lane >> 3, rin = lane & 7;
+  #pragma unroll
+        for (int ks = 0; ks < kSteps; ++ks) {
+  #pragma unroll
+          for (int j = 0; j < kKeys / 8; j += 2) {
+            const int row = (j + (mat >> 1)) * 8 + rin;
+            const int chunk = ks * 2 + (mat & 1);
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4(b0, b1, b2, b3, smem_u32(ks_ + tile_offset<HD>(row, chunk)));
+            mma_bf16(s[j], qf[ks], b0, b1);
+            mma_bf16(s[j + 1], qf[ks], b2, b3);
+          }
+        }
+      }
+      // ---- mask + online softmax (rows r_lo: s[.][0..1], r_hi: s[.][2..3])
+      float m_new[2] = {m[0], m[1]};
+  #pragma unroll
+      for (int j = 0; j < kKeys / 8; ++j) {
+  #pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+          const bool ok = row_ok[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
+          s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+          m_new[i] = fmaxf(m_new[i], s[j][e]);
+        }
+      }
+      float corr[2];
+  #pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+        corr[i] = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - m_new[i]);
+        l[i] *= corr[i];
+      }
+      const float base[2] = {m_new[0] == -INFINITY ? 0.f : m_new[0], m_new[1] == -INFINITY ? 0.f : m_new[1]};
+  #pragma unroll
+      for (int j = 0; j < kKeys / 8; ++j) {
+        const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
+        const float p2 = exp2f(s[j][2] - base[1]), p3 = exp2f(s[j][3] - base[1]);
+        l[0] += p0 + p1;
+        l[1] += p2 + p3;
+        // accumulator tiles (2i, 2i+1) are the A fragment of key step i
+        pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+  #pragma unroll
+      for (int j = 0; j < kOTiles; ++j) {
+        o[j][0] *= corr[0]; o[j][1] *= corr[0];
+        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      }
+      m[0] = m_new[0];
+      m[1] = m_new[1];
+    }
+
+    if (more) cp_async_wait<2>(); else cp_async_wait<0>();   // V of this tile has landed
+    __syncthreads();
+    // ---- O += P V : k = 64 keys (4 steps), n = HD
+    if (warp_active) {
+      const bf16* vs_ = v_tile(buf);
+      const int mat = lane >> 3, rin = lane & 7;
+#pragma unroll
+      for (int kk = 0; kk < kKeys / 16; ++kk) {
+#pragma unroll
+        for (int j = 0; j < kOTiles; j += 2) {
+          // matrices: (keys kk*16.., d j*8..), (keys +8, d j*8..), (keys kk*16.., d (j+1)*8..), (keys +8, ..)
+          const int row = kk * 16 + (mat & 1) * 8 + rin;
+          const int chunk = j + (mat >> 1);
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs_ + tile_offset<HD>(row, chunk)));
+          mma_bf16(o[j], pf[kk], b0, b1);
+          mma_bf16(o[j + 1], pf[kk], b2, b3);
+        }
+      }
+    }
+    __syncthreads();  // everyone is done with this buffer before the next prefetch overwrites it
+  }
+
+  // ---- epilogue
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  const int col = (lane & 3) * 2;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!row_ok[i]) continue;
+    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+    const size_t grow = (size_t)(q_start + tok[i]);
+    if (nsplits == 1) {
+      bf16* op = p.out + grow * p.out_row_stride + (size_t)head[i] * HD + col;
+#pragma unroll
+      for (int j = 0; j < kOTiles; ++j)
+        *reinterpret_cast<unsigned*>(op + j * 8) = pack_bf16(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+    } else {
+      const size_t slot = (grow * p.nq + head[i]) * p.max_splits + split;
+      float* op = p.part_o + slot * HD + col;
+#pragma unroll
+      for (int j = 0; j < kOTiles; ++j)
+        *reinterpret_cast<float2*>(op + j * 8) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+      if ((lane & 3) == 0) p.part_lse[slot] = l[i] > 0.f ? m[i] + log2f(l[i]) : -INFINITY;  // base-2 log-sum-exp
+    }
+  }
+}
+
+// out[token, head] = sum_s w_s o_s / sum_s w_s with w_s = 2^(lse_s - max lse). One warp per (token, head).
+template <int HD>
+__global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_stride, const float* __restrict__ part_o,
+                                       const float* __restrict__ part_lse, const int* __restrict__ row_splits,
+                                       int nq, int max_splits, int tokens) {
+  const int lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)tokens * nq) return;
+  const int token = (int)(gw / nq), head = (int)(gw % nq);
+  const int ns = row_splits[token];
+  if (ns <= 1) return;  // written directly by the attention kernel
+  const size_t base = ((size_t)token * nq + head) * max_splits;
+  float mx = -INFINITY;
+  for (int s = 0; s < ns; ++s) mx = fmaxf(mx, part_lse[base + s]);
+  constexpr int kPer = HD / 32;
+  float acc[kPer];
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) acc[e] = 0.f;
+  float wsum = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const float lse = part_lse[base + s];
+    const float w = lse == -INFINITY ? 0.f : exp2f(lse - mx);
+    wsum += w;
+    const float* op = part_o + (base + s) * HD + lane * kPer;
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) acc[e] += w * op[e];
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  bf16* dst = out + (size_t)token * out_row_stride + (size_t)head * HD + lane * kPer;
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
+}
+
+template <int HD>
+int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens, int any_split, cudaStream_t s) {
+  constexpr int smem = 4 * kKeys * HD * (int)sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  dim3 grid(num_items, p.nkv);
+  attention_mma_kernel<HD><<<grid, kThreads, smem, s>>>(p);
+  OI_CHECK_LAUNCH();
+  if (any_split) {
+    const long long warps = (long long)tokens * p.nq;
+    attention_merge_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(
+        p.out, p.out_row_stride, p.part_o, p.part_lse, row_splits, p.nq, p.max_splits, tokens);
+    OI_CHECK_LAUNCH();
+  }
+  return OI_OK;
+}
+
+}  // namespace
+
+// items: int32 [num_items, 4] = (request, first token of the tile, split, nsplits), planned by the
+// host. row_splits: int32 [tokens], the number of slices each row's keys were cut into.
+// part_o: float32 [tokens * nq * max_splits * hd], part_lse: float32 [tokens * nq * max_splits]
+// (only touched by rows with more than one slice).
+OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                            const void* v_cache, long long page_stride, int page_size, const int* block_table,
+                            int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                            int num_items, const int* row_splits, int tokens, int any_split, int nq, int nkv,
+                            int hd, float scale, int window, float* part_o, float* part_lse, int max_splits,
+                            void* stream) {
+  OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_mma: head_dim %d not covered (32, 64 or 128)", hd);
+  OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= kRows, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
+  OI_REQUIRE(q_row_stride % 2 == 0 && out_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_mma: misaligned strides");
+  OI_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
+             "attention_mma: misaligned pointers");
+  OI_REQUIRE(!any_split || (part_o && part_lse && row_splits && max_splits > 0), "attention_mma: split items without scratch");
+  if (num_items == 0 || tokens == 0) return OI_OK;
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
+  p.out = (bf16*)out; p.out_row_stride = out_row_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.page_stride = page_stride; p.page_size = page_size;
+  p.block_table = block_table; p.bt_stride = bt_stride;
+  p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.items = (const int4*)items;
+  p.nq = nq; p.nkv = nkv; p.group = nq / nkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
+  p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, s);
+  if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, s);
+  return launch<128>(p, num_items, row_splits, tokens, any_split, s);
+}

@@ -24,7 +24,18 @@ TINY_B = dict(
     num_hidden_layers=3, hidden_size=96, num_attention_heads=6, num_key_value_heads=2, head_dim=32,
     intermediate_size=224, vocab_size=384, rope_theta=1000000.0, rms_norm_eps=1e-5,
     tie_word_embeddings=False, max_position_embeddings=768)
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# Two more whose head sizes the tensor-core attention kernel covers (groups of 4 and 3).
+TINY_C = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=192, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+    intermediate_size=320, vocab_size=500, rope_theta=500000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, max_position_embeddings=1024)
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=160, num_attention_heads=3, num_key_value_heads=1, head_dim=128,
+    intermediate_size=272, vocab_size=300, rope_theta=10000.0, rms_norm_eps=1e-5,
+    tie_word_embeddings=False, max_position_embeddings=1024)
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 # Stated tolerances (never widened to make a cutting pass; every cutting uses the same).
 #  float32: both sides sum in float32 in different orders; logits are O(1).

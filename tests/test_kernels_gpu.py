@@ -308,3 +308,132 @@ def test_sample_matches_plain_distribution(vocab):
             cdf = torch.cumsum(dist, 0)
             lo = float(cdf[tok] - dist[tok])
             assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, f"setting {settings[r]} u={u}: token {tok} covers [{lo}, {float(cdf[tok])}]"
+
+
+# ---------------------------------------------------------------------------
+# the tensor-core attention kernel (bfloat16; prompt tiles and split-KV decode)
+# ---------------------------------------------------------------------------
+class _FakeCache:
+    def __init__(self, page_size):
+        self.page_size = page_size
+
+
+class _FakeCtx:
+    """What the attention dispatcher reads of a StepContext."""
+
+    def __init__(self, q_lens, kv_lens, P):
+        self.q_lens_host, self.kv_lens_host = list(q_lens), list(kv_lens)
+        self.num_tokens = sum(q_lens)
+        cu = [0]
+        for n in q_lens:
+            cu.append(cu[-1] + n)
+        self.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=DEV)
+        self.token_req = torch.tensor([b for b, n in enumerate(q_lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+        self.positions = torch.tensor([kv - n + i for n, kv in zip(q_lens, kv_lens) for i in range(n)], dtype=torch.int32, device=DEV)
+        self.cache = _FakeCache(P)
+        self.scratch = {}
+
+
+class _FakeGroup:
+    def __init__(self, block_table, kv_lens):
+        self.block_table = block_table
+        self.kv_lens = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
+
+
+def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None):
+    from openinfer_b200.kernels import attention as A
+    torch.manual_seed(seed)
+    dtype = torch.bfloat16
+    n_req = len(q_lens)
+    pages_needed = [-(-kv // P) for kv in kv_lens]
+    total_pages = sum(pages_needed) + 5
+    perm = torch.randperm(total_pages).tolist()
+    cache = torch.zeros(total_pages, 2, 2, P, nkv, hd, dtype=dtype)   # two layers per page; layer 1 is used
+    bt = torch.zeros(n_req, max(pages_needed), dtype=torch.int32)
+    ks, vs, at = [], [], 0
+    for b, kv in enumerate(kv_lens):
+        order = perm[at: at + pages_needed[b]]
+        at += pages_needed[b]
+        bt[b, : len(order)] = torch.tensor(order)
+        k, v = torch.randn(kv, nkv, hd).to(dtype), torch.randn(kv, nkv, hd).to(dtype)
+        for j in range(kv):
+            cache[order[j // P], 1, 0, j % P] = k[j]
+            cache[order[j // P], 1, 1, j % P] = v[j]
+        ks.append(k.float())
+        vs.append(v.float())
+    cache = cache.to(DEV)
+    T = sum(q_lens)
+    q = torch.randn(T, nq, hd).to(dtype)
+    wide = torch.zeros(T, (nq + 2 * nkv) * hd, dtype=dtype)
+    wide[:, : nq * hd] = q.view(T, -1)
+    wide = wide.to(DEV)
+    ctx = _FakeCtx(q_lens, kv_lens, P)
+    grp = _FakeGroup(bt.to(DEV), kv_lens)
+    if force_splits:
+        old = A.plan_items
+
+        def forced(ql, kl, group, nkv_, window_, sm):
+            return old(ql, kl, group, nkv_, window_, 10 ** 6 if force_splits == "max" else 1)
+        A.plan_items = forced
+    try:
+        out = torch.full((T, nq * hd), float("nan"), device=DEV, dtype=dtype)
+        ran = A.attention_mma(wide[:, : nq * hd], out, cache[:, 1, 0], cache[:, 1, 1], cache.stride(0), ctx, grp,
+                              nq, nkv, hd, 1.0 / math.sqrt(hd), window)
+    finally:
+        if force_splits:
+            A.plan_items = old
+    assert ran
+    plan = next(iter(ctx.scratch.values()))
+    scale = 1.0 / math.sqrt(hd)
+    row = 0
+    for b, (n, kv) in enumerate(zip(q_lens, kv_lens)):
+        qq = torch.zeros(kv, nq, hd)
+        qq[kv - n:] = q[row: row + n].float()
+        ref = plain.causal_attention(qq, ks[b], vs[b], scale, window)[kv - n:]
+        got = out[row: row + n].float().cpu().view(n, nq, hd)
+        assert torch.isfinite(got).all(), f"request {b}: unwritten or non-finite output"
+        err = (got - ref).abs()
+        assert err.max() < 3e-2, f"request {b} (q {n}, kv {kv}): max err {err.max():.4f} at row {int(err.amax(dim=(1, 2)).argmax())}"
+        row += n
+    return plan
+
+
+@pytest.mark.parametrize("nq,nkv,hd,P,window", [
+    (32, 8, 128, 16, None), (6, 2, 32, 16, None), (8, 2, 64, 8, None), (3, 1, 128, 4, None),
+    (16, 16, 64, 16, None), (5, 1, 32, 1, None), (8, 2, 128, 16, 100), (4, 2, 64, 16, 17), (64, 1, 32, 16, None)])
+def test_attention_mma_mixed_batch(nq, nkv, hd, P, window):
+    """Prompt portions over cached prefixes beside single decoded tokens, in one launch."""
+    q_lens = [9, 1, 70, 1, 33, 2]
+    kv_lens = [70, 131, 70, 1, 300, 65]
+    _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens)
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 128), (6, 2, 32), (8, 1, 64)])
+@pytest.mark.parametrize("window", [None, 200])
+def test_attention_mma_split_kv_decode(nq, nkv, hd, window):
+    """Decode rows whose keys are cut into slices and merged; contexts around tile edges."""
+    kv_lens = [1, 63, 64, 65, 127, 128, 129, 700, 1025]
+    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="max")
+    assert plan.any_split and plan.max_splits > 1
+    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="none")
+    assert not plan.any_split
+
+
+def test_attention_mma_split_prompt_portion():
+    """A short portion over a long prefix is also cut into slices when the grid is small."""
+    plan = _mma_case(8, 2, 64, 16, None, [5, 1], [900, 400], force_splits="max")
+    assert plan.any_split
+
+
+def test_attention_mma_plan():
+    from openinfer_b200.kernels.attention import plan_items
+    items, row_splits, mx = plan_items([40, 1], [100, 513], group=4, nkv=8, window=None, sm_count=148)
+    # 40 tokens at 16 per tile: 3 tiles; + 1 decode tile; 4 * 8 = 32 CTAs < 296 -> slices wanted
+    reqs = sorted(set((int(i[0]), int(i[1])) for i in items))
+    assert reqs == [(0, 0), (0, 16), (0, 32), (1, 0)]
+    assert row_splits.tolist()[40] == 4 and mx == 4      # 513 keys = 9 tiles -> at most 4 slices of >= 2 tiles
+    for r, t0 in reqs:
+        ns = {int(i[3]) for i in items if (int(i[0]), int(i[1])) == (r, t0)}
+        assert len(ns) == 1 and sorted(int(i[2]) for i in items if (int(i[0]), int(i[1])) == (r, t0)) == list(range(ns.pop()))
+    items, row_splits, mx = plan_items([1] * 64, [2048] * 64, group=4, nkv=8, window=None, sm_count=148)
+    assert mx == 1 and len(items) == 64                     # a full grid is not cut

@@ -12,7 +12,7 @@ from helpers import TINY, make_model_folder, random_tokens
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
     out = {}
-    for name, (cfg, seed) in TINY.items():
+    for name, (cfg, seed) in list(TINY.items())[:2]:
         f = make_model_folder(str(tmp_path_factory.mktemp(f"p{name}")), cfg, seed)
         out[name] = plain.read_model_folder(f)
     return out

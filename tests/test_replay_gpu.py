@@ -11,7 +11,7 @@ from helpers import (TINY, assert_close, make_model_folder, random_tokens, repla
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 47, 130, 200, 77, 33], "B": [1, 9, 70, 150, 261, 40]}
+LENGTHS = {"A": [5, 47, 130, 200, 77, 33], "B": [1, 9, 70, 150, 261, 40], "C": [3, 64, 129, 300, 65], "D": [2, 100, 257, 33]}
 
 
 @pytest.fixture(scope="module")
@@ -48,7 +48,7 @@ def _check(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cuttings_match_plain(folders, workloads, name, dtype, mode):
     cfg, reqs, ref = workloads[name]
@@ -64,7 +64,7 @@ def test_cuttings_match_plain(folders, workloads, name, dtype, mode):
         max_tokens = biggest + 128
         steps = trace_mixed(reqs, max_tokens, seed=7)
         assert max(len(s["entries"]) for s in steps) >= 2
-    page = 8 if name == "A" else 16
+    page = {"A": 8, "B": 16, "C": 16, "D": 32}[name]
     runner = _runner(folders[name], dtype, max_tokens, page_size=page)
     got = replay_in_process(runner, steps)
     _check(got, ref, dtype, f"{name}/{dtype}/{mode}")
