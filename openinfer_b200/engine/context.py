@@ -45,3 +45,5 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     scratch: dict = dataclasses.field(default_factory=dict)  # per-step workspace shared by layers
+    # a decode step recorded as a CUDA graph: parts must plan from the batch size alone
+    static_decode: bool = False

@@ -58,6 +58,11 @@ class ModelRunner:
         self._staging: Optional[torch.Tensor] = None
         self._staging_event: Optional[torch.cuda.Event] = None
         self.steps_run = 0
+        self.cuda_graph = False          # record decode-only steps as CUDA graphs and replay them
+        self.max_graph_batch = 256
+        self._graphs: Dict[tuple, tuple] = {}
+        self._graph_pool = None
+        self._graph_safe: Optional[bool] = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -172,9 +177,13 @@ class ModelRunner:
                 cache.close(rid)
             raise
         try:
-            ctx, row_idx = self._build_context(entries, starts)
-            h, pending = self.model.forward(ctx)
-            logits = self.model.logits(h, pending, row_idx) if row_idx is not None else None
+            if (self.graphs_usable() and len(entries) <= self.max_graph_batch
+                    and all(len(e.tokens) == 1 for e in entries)):
+                logits = self._step_decode_graph(entries, starts)
+            else:
+                ctx, row_idx = self._build_context(entries, starts)
+                h, pending = self.model.forward(ctx)
+                logits = self.model.logits(h, pending, row_idx) if row_idx is not None else None
         except Exception:
             for rid in reserved:
                 cache.rollback(rid)
@@ -192,18 +201,9 @@ class ModelRunner:
             self.cache.close(request_id)
 
     # ------------------------------------------------------------------ metadata
-    def _build_context(self, entries: List[StepEntry], starts: List[int]):
-        cache = self.cache
-        P = cache.page_size
-        B = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
-        T = sum(q_lens)
-        kv_lens = [s + n for s, n in zip(starts, q_lens)]
-        G = len(cache.groups)
-        max_pages = max(1, max(-(-kv // P) for kv in kv_lens))
-        want_rows: List[int] = []
-
-        # layout of the packed int32 buffer (every section starts on a 16-byte boundary)
+    @staticmethod
+    def _layout(T: int, B: int, max_pages: int, G: int, n_want: int):
+        """Sections of the packed int32 metadata buffer (each starts on a 16-byte boundary)."""
         sections: Dict[str, int] = {}
         off = 0
         for name, size in (("token_ids", T), ("positions", T), ("token_req", T), ("cu_seqlens", B + 1),
@@ -214,10 +214,18 @@ class ModelRunner:
             for name, size in ((f"slots{g}", T), (f"table{g}", B * max_pages), (f"kv_lens{g}", B)):
                 sections[name] = off
                 off += _align4(size)
-        n_want = sum(len(e.want) for e in entries)
         sections["want"] = off
         off += _align4(max(n_want, 1))
-        host = np.zeros(off, dtype=np.int32)
+        return sections, off
+
+    def _fill(self, host: np.ndarray, sections: Dict[str, int], entries: List[StepEntry], starts: List[int],
+              T: int, B: int, max_pages: int) -> List[int]:
+        """Write one step's metadata into ``host``. ``T`` and ``B`` may exceed the real row and
+        request counts (a padded decode batch): the extra rows belong to no request (token_req -1),
+        store nothing (slot -1) and see one key of page 0. Returns the wanted row numbers."""
+        cache = self.cache
+        P = cache.page_size
+        G = len(cache.groups)
 
         def view(name, size):
             return host[sections[name]: sections[name] + size]
@@ -225,9 +233,14 @@ class ModelRunner:
         tok, pos, req = view("token_ids", T), view("positions", T), view("token_req", T)
         cu = view("cu_seqlens", B + 1)
         slots_host = view("state_slots", B)
+        tok[:] = 0
+        pos[:] = 0
+        req[:] = -1
+        slots_host[:] = 0
+        want_rows: List[int] = []
         row = 0
         for b, e in enumerate(entries):
-            n = q_lens[b]
+            n = len(e.tokens)
             tok[row: row + n] = np.asarray(e.tokens, dtype=np.int32)
             pos[row: row + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
             req[row: row + n] = b
@@ -235,25 +248,30 @@ class ModelRunner:
             slots_host[b] = cache.state_slot(e.request_id)
             want_rows.extend(row + int(w) for w in e.want)
             row += n
-        cu[B] = T
+        for b in range(len(entries), B + 1):   # padding requests bring one row each
+            cu[b] = row + (b - len(entries))
         for g in range(G):
             sl = view(f"slots{g}", T)
             tb = view(f"table{g}", B * max_pages).reshape(B, max_pages)
             kl = view(f"kv_lens{g}", B)
+            sl[:] = -1
+            tb[:] = 0
+            kl[:] = 1
             row = 0
             for b, e in enumerate(entries):
                 table = np.asarray(cache.block_table(e.request_id, g), dtype=np.int32)
-                n = q_lens[b]
+                n = len(e.tokens)
                 p = np.arange(starts[b], starts[b] + n)
                 sl[row: row + n] = table[p // P] * P + (p % P)
                 shown = np.where(table == RELEASED, 0, table)  # never read: behind the window
                 tb[b, : len(shown)] = shown[:max_pages]
-                kl[b] = kv_lens[b]
+                kl[b] = starts[b] + n
                 row += n
-        if n_want:
-            view("want", n_want)[:] = np.asarray(want_rows, dtype=np.int32)
+        return want_rows
 
-        dev = self._stage(host)
+    def _context(self, dev: torch.Tensor, sections: Dict[str, int], T: int, B: int, max_pages: int,
+                 q_lens: List[int], starts: List[int], kv_lens: List[int], slots: List[int]) -> StepContext:
+        cache = self.cache
 
         def dview(name, size):
             return dev[sections[name]: sections[name] + size]
@@ -262,14 +280,115 @@ class ModelRunner:
             GroupStep(slot_mapping=dview(f"slots{g}", T),
                       block_table=dview(f"table{g}", B * max_pages).view(B, max_pages),
                       kv_lens=dview(f"kv_lens{g}", B), window=cache.groups[g].window)
-            for g in range(G)
+            for g in range(len(cache.groups))
         ]
-        ctx = StepContext(
+        return StepContext(
             num_tokens=T, num_requests=B, token_ids=dview("token_ids", T), positions=dview("positions", T),
             token_req=dview("token_req", T), cu_seqlens=dview("cu_seqlens", B + 1),
             state_slots=dview("state_slots", B), groups=groups, cache=cache,
-            q_lens_host=q_lens, starts_host=list(starts), kv_lens_host=kv_lens,
-            state_slots_host=[int(s) for s in slots_host], decode_only=all(n == 1 for n in q_lens),
-            max_q_len=max(q_lens), max_kv_len=max(kv_lens))
-        row_idx = dview("want", n_want) if n_want else None
+            q_lens_host=q_lens, starts_host=list(starts), kv_lens_host=kv_lens, state_slots_host=slots,
+            decode_only=all(n == 1 for n in q_lens), max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+
+    def _build_context(self, entries: List[StepEntry], starts: List[int]):
+        cache = self.cache
+        P = cache.page_size
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        kv_lens = [s + n for s, n in zip(starts, q_lens)]
+        max_pages = max(1, max(-(-kv // P) for kv in kv_lens))
+        n_want = sum(len(e.want) for e in entries)
+        sections, total = self._layout(T, B, max_pages, len(cache.groups), n_want)
+        host = np.zeros(total, dtype=np.int32)
+        want_rows = self._fill(host, sections, entries, starts, T, B, max_pages)
+        if n_want:
+            host[sections["want"]: sections["want"] + n_want] = np.asarray(want_rows, dtype=np.int32)
+        dev = self._stage(host)
+        slots = [cache.state_slot(e.request_id) for e in entries]
+        ctx = self._context(dev, sections, T, B, max_pages, q_lens, starts, kv_lens, slots)
+        row_idx = dev[sections["want"]: sections["want"] + n_want] if n_want else None
         return ctx, row_idx
+
+    # ------------------------------------------------------------------ decode through CUDA graphs
+    def graphs_usable(self) -> bool:
+        """Recorded decode steps are used when asked for and every mixer reads the step's
+        metadata from device tensors only."""
+        if not getattr(self, "cuda_graph", False):
+            return False
+        if getattr(self, "_graph_safe", None) is None:
+            self._graph_safe = all(b.mixer is None or getattr(b.mixer, "graph_safe", False)
+                                   for b in self.model.blocks)
+        return self._graph_safe
+
+    def _decode_graph(self, bucket: int, cap: int):
+        """The recorded decode step for a padded batch of ``bucket`` rows whose block tables
+        hold ``cap`` pages (the reference keeps one graph per batch bucket too,
+        pegainfer-qwen3/src/batch_decode.rs:69-182, pegainfer-core/src/cuda_graph.rs:42-231)."""
+        key = (bucket, cap)
+        entry = self._graphs.get(key)
+        if entry is not None:
+            return entry
+        G = len(self.cache.groups)
+        sections, total = self._layout(bucket, bucket, cap, G, bucket)
+        meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+        host = np.zeros(total, dtype=np.int32)
+        self._fill(host, sections, [], [], bucket, bucket, cap)
+        host[sections["want"]: sections["want"] + bucket] = np.arange(bucket, dtype=np.int32)
+        meta.copy_(torch.from_numpy(host))
+        ctx = self._context(meta, sections, bucket, bucket, cap, [1] * bucket, [0] * bucket, [1] * bucket,
+                            [0] * bucket)
+        ctx.static_decode = True
+        row_idx = meta[sections["want"]: sections["want"] + bucket]
+
+        def run():
+            h, pending = self.model.forward(ctx)
+            return self.model.logits(h, pending, row_idx)
+
+        # warm-up on a side stream (plans and workspaces are made here, outside the recording)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = run()
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        entry = (graph, meta, sections, total, logits, ctx)
+        self._graphs[key] = entry
+        return entry
+
+    def _step_decode_graph(self, entries: List[StepEntry], starts: List[int]) -> Optional[torch.Tensor]:
+        B = len(entries)
+        P = self.cache.page_size
+        bucket = 1
+        while bucket < B:
+            bucket *= 2
+        need_pages = max(-(-(s + 1) // P) for s in starts)
+        cap = 16
+        while cap < need_pages:
+            cap *= 2
+        graph, meta, sections, total, logits, _ = self._decode_graph(bucket, cap)
+        host = np.zeros(total, dtype=np.int32)
+        want_rows = self._fill(host, sections, entries, starts, bucket, bucket, cap)
+        host[sections["want"]: sections["want"] + bucket] = np.arange(bucket, dtype=np.int32)
+        n = host.size
+        if self._staging is None or self._staging.numel() < n:
+            self._staging = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
+            self._staging_event = None
+        if self._staging_event is not None:
+            self._staging_event.synchronize()
+        self._staging[:n].numpy()[:] = host
+        self._staging_last_bytes = n * 4
+        meta.copy_(self._staging[:n], non_blocking=True)
+        self._staging_event = torch.cuda.Event()
+        self._staging_event.record()
+        graph.replay()
+        if not want_rows:
+            return None
+        if want_rows == list(range(len(want_rows))):
+            return logits[: len(want_rows)]
+        return logits[torch.tensor(want_rows, device=self.device)]

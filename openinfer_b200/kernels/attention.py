@@ -101,11 +101,26 @@ def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_
     return np.asarray(items, dtype=np.int32).reshape(-1, 4), row_splits, max_splits
 
 
+def plan_items_static_decode(num_requests: int, nkv: int, sm_count: int):
+    """Items of a decode step whose launch is recorded once and replayed (a CUDA graph): one
+    query token per request, and a number of key slices that depends on the batch size only;
+    the kernel finds each slice's bounds from the request's current length."""
+    ns = 1
+    if num_requests * nkv < 2 * sm_count:
+        ns = min(MAX_SPLITS, -(-2 * sm_count // (num_requests * nkv)))
+    items = np.asarray([(b, 0, s, ns) for b in range(num_requests) for s in range(ns)], dtype=np.int32)
+    return items.reshape(-1, 4), np.full(num_requests, ns, dtype=np.int32), ns
+
+
 def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, device) -> AttentionPlan:
     key = ("attention_mma_plan", id(group_step), group, nkv, window)
     plan = ctx.scratch.get(key)
     if plan is None:
-        items, row_splits, max_splits = plan_items(ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window, _sm_count(device))
+        if getattr(ctx, "static_decode", False):
+            items, row_splits, max_splits = plan_items_static_decode(ctx.num_requests, nkv, _sm_count(device))
+        else:
+            items, row_splits, max_splits = plan_items(ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window,
+                                                       _sm_count(device))
         any_split = max_splits > 1
         packed = np.concatenate([items.reshape(-1), row_splits])
         dev = torch.from_numpy(packed).to(device, non_blocking=True)

@@ -24,6 +24,8 @@ from .spec import AttentionSpec, ParamInfo
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec: AttentionSpec) -> None:
         super().__init__(spec)
         s = spec

@@ -60,6 +60,11 @@ class Norm(Part):
 class Mixer(Part):
     """Mixes information across positions of a request (attention, a recurrence, ...)."""
 
+    # True when ``forward`` reads the step's metadata only through the context's DEVICE
+    # tensors, so that a recorded launch sequence (a CUDA graph) can be replayed for another
+    # step of the same shape. A mixer that reads the host lists must leave this False.
+    graph_safe = False
+
     def kv_need(self) -> Optional[KvNeed]:
         """Paged keys and values this mixer wants, or None."""
         return None

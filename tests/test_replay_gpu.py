@@ -35,10 +35,12 @@ def workloads(folders):
     return out
 
 
-def _runner(folder, dtype, max_tokens, page_size=16):
+def _runner(folder, dtype, max_tokens, page_size=16, cuda_graph=False):
     from openinfer_b200.engine.runner import ModelRunner
-    return ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_size=page_size,
-                                   max_tokens=max_tokens, max_requests=8)
+    r = ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_size=page_size,
+                                max_tokens=max_tokens, max_requests=8)
+    r.cuda_graph = cuda_graph
+    return r
 
 
 def _check(got, ref, dtype, what):
@@ -97,3 +99,20 @@ def test_first_tokens_and_long_decode(folders, workloads):
         steps[-1]["end"] = ["x"]
         got = replay_in_process(runner, steps)
         assert_close(got["x"], ref, dtype, f"token by token {dtype}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
+def test_decode_steps_replayed_as_cuda_graphs(folders, workloads, name, dtype):
+    """Steps that bring one token per request run as recorded CUDA graphs (padded to a batch
+    bucket, key slices fixed by the bucket); the logits must not notice."""
+    cfg, reqs, ref = workloads[name]
+    biggest = max(round64(len(t)) for t in reqs.values())
+    for mode in ("tail", "mixed"):
+        max_tokens = biggest if mode == "tail" else biggest + 192
+        steps = trace_tail(reqs) if mode == "tail" else trace_mixed(reqs, max_tokens, seed=11)
+        runner = _runner(folders[name], dtype, max_tokens, page_size=16, cuda_graph=True)
+        got = replay_in_process(runner, steps)
+        assert runner._graphs, "no step went through a graph"
+        _check(got, ref, dtype, f"graphs {name}/{dtype}/{mode}")
+        runner.cache.check()
