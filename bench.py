@@ -118,6 +118,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points and the prefill")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
+                         "(for `ncu --profile-from-start off`); prints no benchmark line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -193,6 +196,33 @@ def main() -> int:
         for rid in ids:
             runner.end(rid)
         return ms, launches
+
+    if args.profile:
+        if args.profile == "decode":
+            ids = [f"p{i}" for i in range(B)]
+            for rid in ids:
+                fake_context(rid, CONTEXT)
+            out_ids = torch.empty(B, dtype=torch.int32, device=dev)
+            for i in range(W + 1):
+                if i == W:
+                    torch.cuda.synchronize()
+                    torch.cuda.profiler.start()
+                logits = runner.step([StepEntry(rid, [1], [0]) for rid in ids])
+                ops.argmax(out_ids, logits)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        else:
+            toks = [rng.randrange(vocab) for _ in range(PREFILL_TOKENS)]
+            for i in range(W + 1):
+                if i == W:
+                    torch.cuda.synchronize()
+                    torch.cuda.profiler.start()
+                runner.step([StepEntry(f"pf{i}", toks, [PREFILL_TOKENS - 1])])
+                torch.cuda.synchronize()
+                runner.end(f"pf{i}")
+            torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": args.profile, "batch": B, "layers": config.num_hidden_layers}))
+        return 0
 
     sampler = ClockSampler(0)
     sampler.start()

@@ -9,11 +9,19 @@
 """
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
 from typing import Callable, Optional
 
 import torch
 
+from . import lib as _lib
 from . import ops
+
+_lib.declare("oi_gemm_skinny", [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                                c_int, c_int, c_int, c_int, c_int, c_void_p])
+
+SKINNY_MAX_ROWS = 16
+_SM_COUNT = None
 
 # hook for a hand-written bf16 kernel: fn(out, x, w) -> bool (True when it took the shape)
 _bf16_gemm: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tensor], bool]] = None
@@ -22,6 +30,56 @@ _bf16_gemm: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tensor], bool]]
 def set_bf16_gemm(fn: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tensor], bool]]) -> None:
     global _bf16_gemm
     _bf16_gemm = fn
+
+
+def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
+    """How many K slices (CTAs per cluster) the skinny kernel uses, 0 if it does not take the
+    shape: the fewest slices that fill the GPU twice over, each slice's activations within 64 KB
+    of shared memory where possible."""
+    row_tiles = -(-N // 128)
+    valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 32 * (K // c + 64) + 8192 <= 200 * 1024]
+    if not valid:
+        return 0
+    for c in valid:
+        if row_tiles * c >= 2 * sm_count and 32 * (K // c + 64) <= 72 * 1024:
+            return c
+    return valid[-1]
+
+
+def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool) -> bool:
+    """The hand-written weight-streaming kernel, when it takes the shape."""
+    global _SM_COUNT
+    M, N = x.shape[0], w.shape[0]
+    K = w.shape[1]
+    if M > SKINNY_MAX_ROWS or out.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        return False
+    if x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    if _SM_COUNT is None:
+        _SM_COUNT = torch.cuda.get_device_properties(x.device).multi_processor_count
+    c = skinny_cluster_size(N, K, _SM_COUNT)
+    if c == 0:
+        return False
+    L = _lib.load()
+    _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
+                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 1 if silu_mul else 0, c,
+                                torch.cuda.current_stream().cuda_stream), "gemm_skinny")
+    return True
+
+
+def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """(silu(gate) * up) W^T for a fused [M, 2K] gate|up buffer and w [N, K]. For a few rows the
+    activation is formed inside the product kernel; otherwise by its own kernel first."""
+    M, K = gate_up.shape[0], w.shape[1]
+    if gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and _bf16_gemm is None:
+        out = torch.empty((M, w.shape[0]), dtype=gate_up.dtype, device=gate_up.device)
+        if _skinny(out, gate_up, w, True):
+            return out
+    act = torch.empty((M, K), dtype=gate_up.dtype, device=gate_up.device)
+    ops.silu_mul(act, gate_up)
+    return linear(act, w)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
@@ -37,6 +95,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         return out
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if _bf16_gemm is not None and _bf16_gemm(out, x, w):
+            return out
+        if M <= SKINNY_MAX_ROWS and _skinny(out, x, w, False):
             return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

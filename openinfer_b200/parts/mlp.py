@@ -10,8 +10,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import ops
-from ..kernels.linear import linear
+from ..kernels.linear import linear, linear_silu_mul
 from .base import FeedForward
 from .registry import register_feed_forward
 from .spec import GatedMlpSpec, ParamInfo
@@ -43,6 +42,4 @@ class GatedMlp(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         gate_up = linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.silu_mul(act, gate_up)
-        return linear(act, self.w_down)
+        return linear_silu_mul(gate_up, self.w_down)

@@ -437,3 +437,46 @@ def test_attention_mma_plan():
         assert len(ns) == 1 and sorted(int(i[2]) for i in items if (int(i[0]), int(i[1])) == (r, t0)) == list(range(ns.pop()))
     items, row_splits, mx = plan_items([1] * 64, [2048] * 64, group=4, nkv=8, window=None, sm_count=148)
     assert mx == 1 and len(items) == 64                     # a full grid is not cut
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(100, 96), (128, 512), (1000, 1536), (4096 + 48, 4096), (200, 12288)])
+def test_gemm_skinny(M, N, K):
+    """The weight-streaming decode product for every cluster size it may pick, against float64."""
+    from openinfer_b200.kernels import linear as lin
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    from openinfer_b200.kernels import lib as klib
+    L = klib.load()
+    for c in (1, 2, 4, 8):
+        if K % (32 * c):
+            continue
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+            klib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out_dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
+                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, c,
+                                        torch.cuda.current_stream().cuda_stream), "gemm_skinny")
+            tol_ = 2e-2 * ref.abs().max().item() if out_dtype == torch.bfloat16 else 2e-4 * ref.abs().max().item()
+            err = (out.double() - ref).abs().max().item()
+            assert err <= tol_, f"cluster {c} {out_dtype}: max err {err}"
+    # the dispatcher takes it, and a row does not depend on the other rows
+    out = lin.linear(x, w)
+    assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    one = lin.linear(x[M - 1:], w)
+    assert torch.equal(one[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 224), (8, 4096, 12288), (13, 200, 1536)])
+def test_gemm_skinny_with_fused_activation(M, N, K):
+    from openinfer_b200.kernels import linear as lin
+    from openinfer_b200.kernels import ops
+    torch.manual_seed(M + N)
+    gu = torch.randn(M, 2 * K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    act = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    ops.silu_mul(act, gu)
+    ref = act.double() @ w.double().t()
+    out = lin.linear_silu_mul(gu, w)
+    assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
