@@ -311,6 +311,203 @@ attention_mma_kernel(const AttnParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode rows (one query token per request): every WARP owns one slice of a request's keys for
+// one kv head, with a private ring of 16-key K/V tiles in shared memory filled by cp.async. No
+// block-wide barrier: a warp waits only for its own copies, so several tiles per warp are in
+// flight all the time, which is what a bandwidth-bound gather over pages needs. Each warp writes
+// a normalised partial output and its log-sum-exp; attention_merge_kernel combines the slices.
+// ---------------------------------------------------------------------------
+constexpr int kDecWarps = 4;
+constexpr int kDecKeys = 16;     // keys per tile
+constexpr int kDecStages = 3;
+
+template <int HD>
+__device__ __forceinline__ void load_tile16(bf16* smem, const bf16* cache, const AttnParams& p, const int* bt,
+                                            int kvh, int key0, int key_end, int lane) {
+  constexpr int kChunks = HD / 8;               // 16-byte chunks per key row
+  constexpr int kPerLane = kDecKeys * kChunks / 32;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int id = lane + 32 * i;
+    const int row = id / kChunks, chunk = id % kChunks;
+    const int key = key0 + row;
+    const bool valid = key < key_end;
+    const bf16* src = cache;
+    if (valid) {
+      const int page = bt[key / p.page_size];
+      src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD + chunk * 8;
+    }
+    cp_async16(smem_u32(smem + tile_offset<HD>(row, chunk)), src, valid);
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attention_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // [warp][stage][K | V][16][HD]
+  bf16* const ring = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * kDecStages * 2 * kDecKeys * HD;
+  auto k_tile = [&](int stage) { return ring + (size_t)stage * 2 * kDecKeys * HD; };
+  auto v_tile = [&](int stage) { return ring + (size_t)stage * 2 * kDecKeys * HD + kDecKeys * HD; };
+
+  const int4 item = p.items[blockIdx.x];          // (request, -, first slice of this CTA, nsplits)
+  const int req = item.x, split = item.z + warp, nsplits = item.w;
+  const int kvh = blockIdx.y;
+  const int group = p.group;
+  const int row_q = p.cu_seqlens[req];            // the request's single row in this step
+  const int kv_len = p.kv_lens[req];
+  const int* bt = p.block_table + (size_t)req * p.bt_stride;
+  const int pos = kv_len - 1;
+  int lo = 0;
+  if (p.window > 0) lo = max(0, pos - p.window + 1) & ~(kDecKeys - 1);
+  const int span_tiles = (kv_len - lo + kDecKeys - 1) / kDecKeys;
+  const int tiles_per_split = (span_tiles + nsplits - 1) / nsplits;
+  const int t_begin = min(span_tiles, split * tiles_per_split);
+  const int t_end = min(span_tiles, t_begin + tiles_per_split);
+  const bool split_ok = split < nsplits;
+
+  // ---- Q fragments: rows are the `group` query heads of this kv head (rows >= group are zero)
+  constexpr int kSteps = HD / 16;
+  const int r_lo = lane >> 2;                     // rows r_lo and r_lo + 8
+  unsigned qf[kSteps][4];
+  {
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int ks = 0; ks < kSteps; ++ks) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = r_lo + 8 * i;
+        unsigned a = 0, b = 0;
+        if (r < group && split_ok) {
+          const bf16* qp = p.q + (size_t)row_q * p.q_row_stride + (size_t)(kvh * group + r) * HD + ks * 16 + col;
+          a = *reinterpret_cast<const unsigned*>(qp);
+          b = *reinterpret_cast<const unsigned*>(qp + 8);
+        }
+        qf[ks][i] = a;
+        qf[ks][i + 2] = b;
+      }
+    }
+  }
+  constexpr int kOTiles = HD / 8;
+  float o[kOTiles][4];
+#pragma unroll
+  for (int j = 0; j < kOTiles; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  if (split_ok) {
+    // prologue: kDecStages - 1 tiles in flight (a commit per tile, empty when past the end)
+#pragma unroll
+    for (int s = 0; s < kDecStages - 1; ++s) {
+      const int t = t_begin + s;
+      if (t < t_end) {
+        load_tile16<HD>(k_tile(s), p.k_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, lane);
+        load_tile16<HD>(v_tile(s), p.v_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, lane);
+      }
+      cp_async_commit();
+    }
+    for (int t = t_begin; t < t_end; ++t) {
+      const int stage = (t - t_begin) % kDecStages;
+      {   // keep the ring full: the tile kDecStages - 1 ahead goes into the stage freed last iteration
+        const int tn = t + kDecStages - 1;
+        if (tn < t_end) {
+          const int sn = (tn - t_begin) % kDecStages;
+          load_tile16<HD>(k_tile(sn), p.k_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, lane);
+          load_tile16<HD>(v_tile(sn), p.v_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, lane);
+        }
+        cp_async_commit();
+      }
+      cp_async_wait<kDecStages - 1>();   // tile t (this thread's part) has landed ...
+      __syncwarp();                      // ... and so have the other lanes' parts
+      const int key0 = lo + t * kDecKeys;
+
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const bf16* ks_ = k_tile(stage);
+        const int mat = lane >> 3, rin = lane & 7;
+#pragma unroll
+        for (int ks = 0; ks < kSteps; ++ks) {
+          unsigned b0, b1, b2, b3;   // (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+          ldmatrix_x4(b0, b1, b2, b3, smem_u32(ks_ + tile_offset<HD>((mat >> 1) * 8 + rin, ks * 2 + (mat & 1))));
+          mma_bf16(s[0], qf[ks], b0, b1);
+          mma_bf16(s[1], qf[ks], b2, b3);
+        }
+      }
+      float m_new[2] = {m[0], m[1]};
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+          const bool ok = (r_lo + 8 * i) < group && key <= pos && (p.window <= 0 || key > pos - p.window);
+          s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+          m_new[i] = fmaxf(m_new[i], s[j][e]);
+        }
+      }
+      float corr[2], base[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+        corr[i] = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - m_new[i]);
+        l[i] *= corr[i];
+        base[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];
+        m[i] = m_new[i];
+      }
+      unsigned pf[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
+        const float p2 = exp2f(s[j][2] - base[1]), p3 = exp2f(s[j][3] - base[1]);
+        l[0] += p0 + p1;
+        l[1] += p2 + p3;
+        pf[j * 2 + 0] = pack_bf16(p0, p1);
+        pf[j * 2 + 1] = pack_bf16(p2, p3);
+      }
+      {
+        const bf16* vs_ = v_tile(stage);
+        const int mat = lane >> 3, rin = lane & 7;
+#pragma unroll
+        for (int j = 0; j < kOTiles; j += 2) {
+          o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+          o[j + 1][0] *= corr[0]; o[j + 1][1] *= corr[0]; o[j + 1][2] *= corr[1]; o[j + 1][3] *= corr[1];
+          unsigned b0, b1, b2, b3;   // (keys 0-7, d tile j), (keys 8-15, j), (keys 0-7, j+1), (keys 8-15, j+1)
+          ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs_ + tile_offset<HD>((mat & 1) * 8 + rin, j + (mat >> 1))));
+          mma_bf16(o[j], pf, b0, b1);
+          mma_bf16(o[j + 1], pf, b2, b3);
+        }
+      }
+      __syncwarp();   // all lanes are done reading this stage before it is refilled
+    }
+    cp_async_wait<0>();
+  }
+
+  // ---- partial result of this slice
+  if (!split_ok) return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  const int col = (lane & 3) * 2;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r_lo + 8 * i;
+    if (r >= group) continue;
+    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+    const size_t slot = ((size_t)row_q * p.nq + kvh * group + r) * p.max_splits + split;
+    float* op = p.part_o + slot * HD + col;
+#pragma unroll
+    for (int j = 0; j < kOTiles; ++j)
+      *reinterpret_cast<float2*>(op + j * 8) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+    if ((lane & 3) == 0) p.part_lse[slot] = l[i] > 0.f ? m[i] + log2f(l[i]) : -INFINITY;
+  }
+}
+
 // out[token, head] = sum_s w_s o_s / sum_s w_s with w_s = 2^(lse_s - max lse). One warp per (token, head).
 template <int HD>
 __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_stride, const float* __restrict__ part_o,
@@ -364,7 +561,58 @@ int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens
   return OI_OK;
 }
 
+template <int HD>
+int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
+  constexpr int smem = kDecWarps * kDecStages * 2 * kDecKeys * HD * (int)sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  dim3 grid(num_items, p.nkv);
+  attention_decode_kernel<HD><<<grid, kDecWarps * 32, smem, s>>>(p);
+  OI_CHECK_LAUNCH();
+  const long long warps = (long long)tokens * p.nq;
+  attention_merge_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(
+      p.out, p.out_row_stride, p.part_o, p.part_lse, row_splits, p.nq, p.max_splits, tokens);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
 }  // namespace
+
+// Decode rows only (requests that bring one token): items are (request, 0, first slice, nsplits),
+// one CTA per four consecutive slices; every listed request's row is merged from scratch, so
+// row_splits[row] must be nsplits (>= 2) for those rows and <= 1 for all others.
+OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                               const void* v_cache, long long page_stride, int page_size, const int* block_table,
+                               int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                               int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
+                               float scale, int window, float* part_o, float* part_lse, int max_splits,
+                               void* stream) {
+  OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_decode: head_dim %d not covered (32, 64 or 128)", hd);
+  OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16, "attention_decode: group %d/%d not covered (<= 16)", nq, nkv);
+  OI_REQUIRE(q_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_decode: misaligned strides");
+  OI_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
+             "attention_decode: misaligned pointers");
+  OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2, "attention_decode: scratch missing");
+  if (num_items == 0 || tokens == 0) return OI_OK;
+  AttnParams p;
+  p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
+  p.out = (bf16*)out; p.out_row_stride = out_row_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.page_stride = page_stride; p.page_size = page_size;
+  p.block_table = block_table; p.bt_stride = bt_stride;
+  p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens; p.items = (const int4*)items;
+  p.nq = nq; p.nkv = nkv; p.group = nq / nkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
+  p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 32) return launch_decode<32>(p, num_items, row_splits, tokens, s);
+  if (hd == 64) return launch_decode<64>(p, num_items, row_splits, tokens, s);
+  return launch_decode<128>(p, num_items, row_splits, tokens, s);
+}
 
 // items: int32 [num_items, 4] = (request, first token of the tile, split, nsplits), planned by the
 // host. row_splits: int32 [tokens], the number of slices each row's keys were cut into.

@@ -34,7 +34,7 @@ def register_tuned(fn) -> None:
 
 
 # ---------------------------------------------------------------------------
-# tensor-core kernel (bfloat16, head_dim 32 / 64 / 128): host-side planning of work items
+# tensor-core kernels (bfloat16, head_dim 32 / 64 / 128): host-side planning of work items
 # ---------------------------------------------------------------------------
 import dataclasses  # noqa: E402
 from ctypes import c_float, c_int, c_longlong, c_void_p  # noqa: E402
@@ -46,11 +46,18 @@ from . import lib as _lib  # noqa: E402
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 _lib.declare("oi_attention_mma", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I,
                                   _F, _I, _P, _P, _I, _P])
+_lib.declare("oi_attention_decode", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I,
+                                     _F, _I, _P, _P, _I, _P])
 
 ROWS_PER_CTA = 64
 KEYS_PER_TILE = 64
-MAX_SPLITS = 16
-MIN_TILES_PER_SPLIT = 2   # a slice of the keys is at least 128 keys long
+MAX_SPLITS = 16            # slices of a prompt tile's keys
+MIN_TILES_PER_SPLIT = 2    # such a slice is at least 128 keys long
+DECODE_WARPS = 4           # slices of a decode row per CTA (one per warp)
+DECODE_CTAS_PER_SM = 2
+DECODE_MAX_SPLITS = 64
+DECODE_MIN_KEYS_PER_SPLIT = 32
+DECODE_MAX_GROUP = 16
 _SM_COUNT = None
 
 
@@ -63,53 +70,93 @@ def _sm_count(device) -> int:
 
 @dataclasses.dataclass
 class AttentionPlan:
-    items: torch.Tensor          # int32 [n, 4]: request, first token of the tile, split, nsplits
-    row_splits: torch.Tensor     # int32 [tokens]
-    num_items: int
-    any_split: bool
+    tile_items: torch.Tensor      # int32 [n, 4]: request, first token of the tile, slice, slices
+    num_tile_items: int
+    decode_items: torch.Tensor    # int32 [n, 4]: request, 0, first slice of the CTA, slices
+    num_decode_items: int
+    row_splits: torch.Tensor      # int32 [tokens]
+    tile_split: bool              # some prompt tile was cut into slices (merged after the tile kernel)
     max_splits: int
     part_o: Optional[torch.Tensor]
     part_lse: Optional[torch.Tensor]
 
 
-def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_count: int):
-    """Work items of one step: for every request its query tiles (64 rows = 64 // group tokens
-    times `group` heads); when the grid would leave SMs idle (decode at small batch), a tile's
-    keys are cut into slices. Returns (items [n, 4], row_splits [tokens], max_splits)."""
+def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int]) -> int:
+    """Slices per decode row: as many as fill the GPU once (two CTAs of four slices per SM), a
+    multiple of four, each at least 32 keys long when the lengths are known."""
+    pairs = max(1, num_rows * nkv)
+    ns = DECODE_WARPS * max(1, (DECODE_CTAS_PER_SM * sm_count) // pairs)
+    ns = min(ns, DECODE_MAX_SPLITS)
+    if max_kv_len is not None:
+        ns = min(ns, max(DECODE_WARPS, (max_kv_len // DECODE_MIN_KEYS_PER_SPLIT) // DECODE_WARPS * DECODE_WARPS))
+    return ns
+
+
+def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_count: int,
+               decode_kernel: bool = True):
+    """Work items of one step.
+
+    Requests that bring one token go to the decode kernel (when the group fits its 16 rows):
+    each row's keys are cut into ``decode_splits`` slices, four per CTA. The others are cut
+    into query tiles (64 rows = 64 // group tokens times `group` heads) for the tile kernel;
+    when that grid would leave SMs idle and there are no decode rows, a tile's keys are cut
+    into slices too. Returns (tile_items [n, 4], decode_items [n, 4], row_splits [tokens],
+    max_splits, tile_split)."""
     tpt = ROWS_PER_CTA // group
+    starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int64)
+    row_splits = np.ones(int(starts[-1]), dtype=np.int32)
+    use_decode = decode_kernel and group <= DECODE_MAX_GROUP
+    decode_reqs = [b for b, n in enumerate(q_lens) if n == 1] if use_decode else []
+    decode_set = set(decode_reqs)
     tiles = []
     for b, (n, kv) in enumerate(zip(q_lens, kv_lens)):
+        if b in decode_set:
+            continue
         for t0 in range(0, n, tpt):
             toks = min(tpt, n - t0)
             pos0 = kv - n + t0
             lo = (max(0, pos0 - window + 1) if window else 0) & ~(KEYS_PER_TILE - 1)
             span_tiles = -(-(pos0 + toks - lo) // KEYS_PER_TILE)
             tiles.append((b, t0, toks, span_tiles))
-    want = 1
-    if len(tiles) * nkv < 2 * sm_count:
-        want = min(MAX_SPLITS, -(-2 * sm_count // (len(tiles) * nkv)))
-    items = []
-    row_splits = np.ones(sum(q_lens), dtype=np.int32)
-    starts = np.concatenate([[0], np.cumsum(q_lens)])
     max_splits = 1
+    decode_items = []
+    if decode_reqs:
+        ns = decode_splits(len(decode_reqs), nkv, sm_count, max(kv_lens[b] for b in decode_reqs))
+        max_splits = ns
+        for b in decode_reqs:
+            row_splits[starts[b]] = ns
+            decode_items.extend((b, 0, s0, ns) for s0 in range(0, ns, DECODE_WARPS))
+    want = 1
+    if tiles and not decode_reqs and len(tiles) * nkv < 2 * sm_count:
+        want = min(MAX_SPLITS, -(-2 * sm_count // (len(tiles) * nkv)))
+    tile_items = []
+    tile_split = False
     for b, t0, toks, span_tiles in tiles:
         ns = max(1, min(want, span_tiles // MIN_TILES_PER_SPLIT))
-        max_splits = max(max_splits, ns)
-        row_splits[starts[b] + t0: starts[b] + t0 + toks] = ns
-        for s in range(ns):
-            items.append((b, t0, s, ns))
-    return np.asarray(items, dtype=np.int32).reshape(-1, 4), row_splits, max_splits
+        if ns > 1:
+            tile_split = True
+            max_splits = max(max_splits, ns)
+            row_splits[starts[b] + t0: starts[b] + t0 + toks] = ns
+        tile_items.extend((b, t0, s, ns) for s in range(ns))
+    return (np.asarray(tile_items, dtype=np.int32).reshape(-1, 4), np.asarray(decode_items, dtype=np.int32).reshape(-1, 4),
+            row_splits, max_splits, tile_split)
 
 
-def plan_items_static_decode(num_requests: int, nkv: int, sm_count: int):
+def plan_items_static_decode(num_requests: int, group: int, nkv: int, sm_count: int):
     """Items of a decode step whose launch is recorded once and replayed (a CUDA graph): one
     query token per request, and a number of key slices that depends on the batch size only;
-    the kernel finds each slice's bounds from the request's current length."""
+    the kernels find each slice's bounds from the request's current length."""
+    empty = np.zeros((0, 4), dtype=np.int32)
+    if group <= DECODE_MAX_GROUP:
+        ns = decode_splits(num_requests, nkv, sm_count, None)
+        items = np.asarray([(b, 0, s0, ns) for b in range(num_requests) for s0 in range(0, ns, DECODE_WARPS)],
+                           dtype=np.int32).reshape(-1, 4)
+        return empty, items, np.full(num_requests, ns, dtype=np.int32), ns, False
     ns = 1
     if num_requests * nkv < 2 * sm_count:
         ns = min(MAX_SPLITS, -(-2 * sm_count // (num_requests * nkv)))
-    items = np.asarray([(b, 0, s, ns) for b in range(num_requests) for s in range(ns)], dtype=np.int32)
-    return items.reshape(-1, 4), np.full(num_requests, ns, dtype=np.int32), ns
+    items = np.asarray([(b, 0, s, ns) for b in range(num_requests) for s in range(ns)], dtype=np.int32).reshape(-1, 4)
+    return items, empty, np.full(num_requests, ns, dtype=np.int32), ns, ns > 1
 
 
 def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, device) -> AttentionPlan:
@@ -117,40 +164,51 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
     plan = ctx.scratch.get(key)
     if plan is None:
         if getattr(ctx, "static_decode", False):
-            items, row_splits, max_splits = plan_items_static_decode(ctx.num_requests, nkv, _sm_count(device))
+            t_items, d_items, row_splits, max_splits, tile_split = plan_items_static_decode(
+                ctx.num_requests, group, nkv, _sm_count(device))
         else:
-            items, row_splits, max_splits = plan_items(ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window,
-                                                       _sm_count(device))
-        any_split = max_splits > 1
-        packed = np.concatenate([items.reshape(-1), row_splits])
+            t_items, d_items, row_splits, max_splits, tile_split = plan_items(
+                ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window, _sm_count(device))
+        packed = np.concatenate([t_items.reshape(-1), d_items.reshape(-1), row_splits])
         dev = torch.from_numpy(packed).to(device, non_blocking=True)
-        n = items.shape[0]
+        nt, nd = t_items.shape[0], d_items.shape[0]
         part_o = part_lse = None
-        if any_split:
+        if max_splits > 1:
             part_o = torch.empty(ctx.num_tokens * nq * max_splits * hd, dtype=torch.float32, device=device)
             part_lse = torch.empty(ctx.num_tokens * nq * max_splits, dtype=torch.float32, device=device)
-        plan = AttentionPlan(dev[: n * 4].view(n, 4), dev[n * 4:], n, any_split, max_splits, part_o, part_lse)
+        plan = AttentionPlan(dev[: nt * 4].view(nt, 4), nt, dev[nt * 4: (nt + nd) * 4].view(nd, 4), nd,
+                             dev[(nt + nd) * 4:], tile_split, max_splits, part_o, part_lse)
         ctx.scratch[key] = plan
     return plan
 
 
 def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window) -> bool:
-    """The tensor-core kernel, when it covers the shape: bfloat16, head_dim 32, 64 or 128."""
+    """The tensor-core kernels, when they cover the shape: bfloat16, head_dim 32, 64 or 128."""
     if q.dtype != torch.bfloat16 or hd not in (32, 64, 128) or nq // nkv > ROWS_PER_CTA:
         return False
     if q.stride(0) % 2 or page_stride % 8:
         return False
-    plan = getattr(ctx, "attention_plan_override", None) or _plan_for(
-        ctx, group_step, nq // nkv, nq, nkv, hd, window, q.device)
+    plan = _plan_for(ctx, group_step, nq // nkv, nq, nkv, hd, window, q.device)
     L = _lib.load()
-    _lib.check(L.oi_attention_mma(
-        q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-        int(page_stride), ctx.cache.page_size, group_step.block_table.data_ptr(), group_step.block_table.stride(0),
-        ctx.cu_seqlens.data_ptr(), group_step.kv_lens.data_ptr(), plan.items.data_ptr(), plan.num_items,
-        plan.row_splits.data_ptr(), out.shape[0], 1 if plan.any_split else 0, nq, nkv, hd, float(scale),
-        int(window) if window else 0, 0 if plan.part_o is None else plan.part_o.data_ptr(),
-        0 if plan.part_lse is None else plan.part_lse.data_ptr(), plan.max_splits,
-        torch.cuda.current_stream().cuda_stream), "attention_mma")
+    stream = torch.cuda.current_stream().cuda_stream
+    bt = group_step.block_table
+    po = 0 if plan.part_o is None else plan.part_o.data_ptr()
+    pl = 0 if plan.part_lse is None else plan.part_lse.data_ptr()
+    win = int(window) if window else 0
+    if plan.num_tile_items:
+        _lib.check(L.oi_attention_mma(
+            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
+            group_step.kv_lens.data_ptr(), plan.tile_items.data_ptr(), plan.num_tile_items,
+            plan.row_splits.data_ptr(), out.shape[0], 1 if plan.tile_split else 0, nq, nkv, hd, float(scale), win,
+            po, pl, plan.max_splits, stream), "attention_mma")
+    if plan.num_decode_items:
+        _lib.check(L.oi_attention_decode(
+            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
+            group_step.kv_lens.data_ptr(), plan.decode_items.data_ptr(), plan.num_decode_items,
+            plan.row_splits.data_ptr(), out.shape[0], nq, nkv, hd, float(scale), win, po, pl, plan.max_splits,
+            stream), "attention_decode")
     return True
 
 

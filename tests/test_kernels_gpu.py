@@ -372,7 +372,11 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
     if force_splits:
         old = A.plan_items
 
-        def forced(ql, kl, group, nkv_, window_, sm):
+        def forced(ql, kl, group, nkv_, window_, sm, decode_kernel=True):
+            if force_splits == "tiles":     # decode rows through the tile kernel, cut into slices
+                return old(ql, kl, group, nkv_, window_, 10 ** 6, decode_kernel=False)
+            if force_splits == "tiles_whole":
+                return old(ql, kl, group, nkv_, window_, 1, decode_kernel=False)
             return old(ql, kl, group, nkv_, window_, 10 ** 6 if force_splits == "max" else 1)
         A.plan_items = forced
     try:
@@ -414,29 +418,35 @@ def test_attention_mma_split_kv_decode(nq, nkv, hd, window):
     """Decode rows whose keys are cut into slices and merged; contexts around tile edges."""
     kv_lens = [1, 63, 64, 65, 127, 128, 129, 700, 1025]
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="max")
-    assert plan.any_split and plan.max_splits > 1
+    assert plan.num_decode_items and plan.max_splits >= 8 and not plan.num_tile_items    # the decode kernel, many slices
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="none")
-    assert not plan.any_split
+    assert plan.num_decode_items and plan.max_splits == 4                                # the decode kernel, four slices
+    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="tiles")
+    assert plan.tile_split and not plan.num_decode_items                                 # the tile kernel, sliced
+    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="tiles_whole")
+    assert not plan.tile_split and plan.max_splits == 1
 
 
 def test_attention_mma_split_prompt_portion():
     """A short portion over a long prefix is also cut into slices when the grid is small."""
+    plan = _mma_case(8, 2, 64, 16, None, [5, 3], [900, 400], force_splits="max")
+    assert plan.tile_split
+    # beside decode rows the tiles stay whole (one merge pass, after the decode kernel)
     plan = _mma_case(8, 2, 64, 16, None, [5, 1], [900, 400], force_splits="max")
-    assert plan.any_split
+    assert not plan.tile_split and plan.num_decode_items
 
 
 def test_attention_mma_plan():
     from openinfer_b200.kernels.attention import plan_items
-    items, row_splits, mx = plan_items([40, 1], [100, 513], group=4, nkv=8, window=None, sm_count=148)
-    # 40 tokens at 16 per tile: 3 tiles; + 1 decode tile; 4 * 8 = 32 CTAs < 296 -> slices wanted
-    reqs = sorted(set((int(i[0]), int(i[1])) for i in items))
-    assert reqs == [(0, 0), (0, 16), (0, 32), (1, 0)]
-    assert row_splits.tolist()[40] == 4 and mx == 4      # 513 keys = 9 tiles -> at most 4 slices of >= 2 tiles
-    for r, t0 in reqs:
-        ns = {int(i[3]) for i in items if (int(i[0]), int(i[1])) == (r, t0)}
-        assert len(ns) == 1 and sorted(int(i[2]) for i in items if (int(i[0]), int(i[1])) == (r, t0)) == list(range(ns.pop()))
-    items, row_splits, mx = plan_items([1] * 64, [2048] * 64, group=4, nkv=8, window=None, sm_count=148)
-    assert mx == 1 and len(items) == 64                     # a full grid is not cut
+    tiles, dec, row_splits, mx, tile_split = plan_items([40, 1], [100, 513], group=4, nkv=8, window=None, sm_count=148)
+    # 40 tokens at 16 per tile: 3 whole tiles; the decode row: 513 keys -> 16 slices of >= 32 keys, 4 per CTA
+    assert sorted((int(i[0]), int(i[1]), int(i[3])) for i in tiles) == [(0, 0, 1), (0, 16, 1), (0, 32, 1)]
+    assert not tile_split and mx == 16 and row_splits.tolist() == [1] * 40 + [16]
+    assert [(int(i[0]), int(i[2]), int(i[3])) for i in dec] == [(1, 0, 16), (1, 4, 16), (1, 8, 16), (1, 12, 16)]
+    tiles, dec, row_splits, mx, _ = plan_items([1] * 64, [2048] * 64, group=4, nkv=8, window=None, sm_count=148)
+    assert mx == 4 and len(dec) == 64 and len(tiles) == 0   # a full grid: one CTA of four slices per row
+    tiles, dec, row_splits, mx, tile_split = plan_items([5], [900], group=4, nkv=2, window=None, sm_count=148)
+    assert tile_split and mx == 7 and len(tiles) == 7       # 15 key tiles -> slices of >= 2 tiles
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
@@ -451,7 +461,7 @@ def test_gemm_skinny(M, N, K):
     from openinfer_b200.kernels import lib as klib
     L = klib.load()
     for c in (1, 2, 4, 8):
-        if K % (32 * c):
+        if K % (32 * c) or 32 * (K // c + 64) + 8192 > 200 * 1024:   # the slice must fit in shared memory
             continue
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
