@@ -3,10 +3,13 @@ layers that share a geometry, and slots for per-request state of fixed size.
 
 A *group* is the set of layers (more exactly: of calls in the model's run order)
 whose mixers asked for the same (kv heads, head size, window). Each group has a
-pool of pages of its own; one page holds ``page_size`` positions of every layer of
-the group, K and V: ``[pages, layers_in_group, 2, page_size, kv_heads, head_dim]``
-(the reference's single group uses the same page-first layout,
-pegainfer-kv-cache/src/layout.rs:5-33). A request holds, per group, a block table:
+pool of pages of its own; a page id names ``page_size`` positions of every layer of
+the group, K and V. The device tensor is laid out layer first,
+``[layers_in_group, 2, pages, page_size, kv_heads, head_dim]``: what one layer's
+attention reads in a step then lies in two dense regions (its K pages and its V pages)
+instead of being strewn over the whole pool at a stride of one page of all layers, as in
+the reference's page-first buffer (pegainfer-kv-cache/src/layout.rs:5-33), which keeps
+the address translation and the DRAM rows of a layer's pass local. A request holds, per group, a block table:
 page ids in position order. Pages go back to the pool when the request ends, or,
 in a group with a window, as soon as every position of the page is further back
 than the window of any query still to come.
@@ -131,7 +134,7 @@ class CacheManager:
 
             for g in self.groups:
                 g.tensor = torch.zeros(
-                    (num_pages, g.layers, 2, self.page_size, g.need.num_kv_heads, g.need.head_dim),
+                    (g.layers, 2, num_pages, self.page_size, g.need.num_kv_heads, g.need.head_dim),
                     dtype=dtype, device=device)
             for need in self.state_needs:
                 sdtype = dtype if need.dtype == "model" else torch.float32
@@ -147,7 +150,7 @@ class CacheManager:
         t = self.groups[handle.group].tensor
         if t is None:
             raise RuntimeError("the cache has no device memory (allocate(device=...) first)")
-        return t[:, handle.layer, 0], t[:, handle.layer, 1], t.stride(0)
+        return t[handle.layer, 0], t[handle.layer, 1], t.stride(2)
 
     def state_tensor(self, state_id: int):
         return self.state_tensors[state_id]
