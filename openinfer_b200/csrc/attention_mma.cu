@@ -322,23 +322,60 @@ constexpr int kDecWarps = 4;
 constexpr int kDecKeys = 16;     // keys per tile
 constexpr int kDecStages = 3;
 
+// Per-lane constants of the 16-key tile copy: which (row, chunk) pairs a lane moves, where they go
+// in the swizzled tile and where they come from relative to the tile's first key.
+template <int HD>
+struct TileLane {
+  static constexpr int kChunks = HD / 8;                 // 16-byte chunks per key row
+  static constexpr int kPerLane = kDecKeys * kChunks / 32;
+  int smem_off[kPerLane];    // element offset inside the tile
+  int glob_off[kPerLane];    // element offset from the first key's row of this kv head
+  int row[kPerLane];
+  __device__ __forceinline__ void init(int lane, int nkv) {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int id = lane + 32 * i;
+      row[i] = id / kChunks;
+      const int chunk = id % kChunks;
+      smem_off[i] = tile_offset<HD>(row[i], chunk);
+      glob_off[i] = row[i] * nkv * HD + chunk * 8;
+    }
+  }
+};
+
+// Copy keys [key0, key0 + 16) of one kv head into a tile; rows at or beyond key_end are zero-filled.
+// `aligned`: the page size is a multiple of 16, so the tile lies in one page (one table lookup).
 template <int HD>
 __device__ __forceinline__ void load_tile16(bf16* smem, const bf16* cache, const AttnParams& p, const int* bt,
-                                            int kvh, int key0, int key_end, int lane) {
-  constexpr int kChunks = HD / 8;               // 16-byte chunks per key row
-  constexpr int kPerLane = kDecKeys * kChunks / 32;
+                                            int kvh, int key0, int key_end, const TileLane<HD>& tl, bool aligned) {
+  constexpr int kPerLane = TileLane<HD>::kPerLane;
+  const unsigned sbase = smem_u32(smem);
+  if (aligned) {
+    const int page = bt[key0 / p.page_size];
+    const bf16* base = cache + (size_t)page * p.page_stride + (size_t)(key0 % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
+    if (key0 + kDecKeys <= key_end) {
 #pragma unroll
-  for (int i = 0; i < kPerLane; ++i) {
-    const int id = lane + 32 * i;
-    const int row = id / kChunks, chunk = id % kChunks;
-    const int key = key0 + row;
-    const bool valid = key < key_end;
-    const bf16* src = cache;
-    if (valid) {
-      const int page = bt[key / p.page_size];
-      src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD + chunk * 8;
+      for (int i = 0; i < kPerLane; ++i) cp_async16(sbase + tl.smem_off[i] * 2, base + tl.glob_off[i], true);
+    } else {
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) {
+        const bool valid = key0 + tl.row[i] < key_end;
+        cp_async16(sbase + tl.smem_off[i] * 2, valid ? base + tl.glob_off[i] : cache, valid);
+      }
     }
-    cp_async16(smem_u32(smem + tile_offset<HD>(row, chunk)), src, valid);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int key = key0 + tl.row[i];
+      const bool valid = key < key_end;
+      const bf16* src = cache;
+      if (valid) {
+        const int page = bt[key / p.page_size];
+        src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD +
+              (tl.glob_off[i] - tl.row[i] * p.nkv * HD);
+      }
+      cp_async16(sbase + tl.smem_off[i] * 2, src, valid);
+    }
   }
 }
 
@@ -367,6 +404,15 @@ attention_decode_kernel(const AttnParams p) {
   const int t_begin = min(span_tiles, split * tiles_per_split);
   const int t_end = min(span_tiles, t_begin + tiles_per_split);
   const bool split_ok = split < nsplits;
+  const bool aligned = (p.page_size % kDecKeys) == 0;
+  TileLane<HD> tl;
+  tl.init(lane, p.nkv);
+  // ldmatrix addresses: lane -> (matrix, row in matrix); element offset = row * HD + ((chunk ^ (row & 7)) & mask) * 8
+  const int lm_mat = lane >> 3, lm_rin = lane & 7;
+  const int k_row = (lm_mat >> 1) * 8 + lm_rin;             // K: matrices 0,1 keys 0-7; 2,3 keys 8-15
+  const int k_row_off = k_row * HD, k_swz = (lm_mat & 1) ^ (k_row & 7);   // chunk = 2 ks + (mat & 1)
+  const int v_row = (lm_mat & 1) * 8 + lm_rin;              // V: matrices 0,2 keys 0-7; 1,3 keys 8-15
+  const int v_row_off = v_row * HD, v_swz = (lm_mat >> 1) ^ (v_row & 7);  // chunk = j + (mat >> 1)
 
   // ---- Q fragments: rows are the `group` query heads of this kv head (rows >= group are zero)
   constexpr int kSteps = HD / 16;
@@ -404,8 +450,8 @@ attention_decode_kernel(const AttnParams p) {
     for (int s = 0; s < kDecStages - 1; ++s) {
       const int t = t_begin + s;
       if (t < t_end) {
-        load_tile16<HD>(k_tile(s), p.k_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, lane);
-        load_tile16<HD>(v_tile(s), p.v_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, lane);
+        load_tile16<HD>(k_tile(s), p.k_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, tl, aligned);
+        load_tile16<HD>(v_tile(s), p.v_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, tl, aligned);
       }
       cp_async_commit();
     }
@@ -415,8 +461,8 @@ attention_decode_kernel(const AttnParams p) {
         const int tn = t + kDecStages - 1;
         if (tn < t_end) {
           const int sn = (tn - t_begin) % kDecStages;
-          load_tile16<HD>(k_tile(sn), p.k_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, lane);
-          load_tile16<HD>(v_tile(sn), p.v_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, lane);
+          load_tile16<HD>(k_tile(sn), p.k_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, tl, aligned);
+          load_tile16<HD>(v_tile(sn), p.v_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, tl, aligned);
         }
         cp_async_commit();
       }
@@ -426,26 +472,40 @@ attention_decode_kernel(const AttnParams p) {
 
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       {
-        const bf16* ks_ = k_tile(stage);
-        const int mat = lane >> 3, rin = lane & 7;
+        const unsigned kbase = smem_u32(k_tile(stage));
 #pragma unroll
         for (int ks = 0; ks < kSteps; ++ks) {
           unsigned b0, b1, b2, b3;   // (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
-          ldmatrix_x4(b0, b1, b2, b3, smem_u32(ks_ + tile_offset<HD>((mat >> 1) * 8 + rin, ks * 2 + (mat & 1))));
+          // the chunk index only enters through an XOR with the (fixed) row: one XOR per step
+          ldmatrix_x4(b0, b1, b2, b3, kbase + (k_row_off + ((((ks * 2) ^ k_swz) & (HD / 8 - 1)) * 8)) * 2);
           mma_bf16(s[0], qf[ks], b0, b1);
           mma_bf16(s[1], qf[ks], b2, b3);
         }
       }
       float m_new[2] = {m[0], m[1]};
+      // a tile whose every key every row sees needs no mask (rows beyond the group hold zeros
+      // and are never stored)
+      const bool full = key0 + kDecKeys <= kv_len && (p.window <= 0 || key0 > pos - p.window);
+      if (full) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 2; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1;
-          const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-          const bool ok = (r_lo + 8 * i) < group && key <= pos && (p.window <= 0 || key > pos - p.window);
-          s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
-          m_new[i] = fmaxf(m_new[i], s[j][e]);
+          for (int e = 0; e < 4; ++e) {
+            s[j][e] *= p.scale_log2;
+            m_new[e >> 1] = fmaxf(m_new[e >> 1], s[j][e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = e >> 1;
+            const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+            const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
+            s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+            m_new[i] = fmaxf(m_new[i], s[j][e]);
+          }
         }
       }
       float corr[2], base[2];
@@ -469,14 +529,18 @@ attention_decode_kernel(const AttnParams p) {
         pf[j * 2 + 1] = pack_bf16(p2, p3);
       }
       {
-        const bf16* vs_ = v_tile(stage);
-        const int mat = lane >> 3, rin = lane & 7;
+        const unsigned vbase = smem_u32(v_tile(stage));
+        // the running maximum rarely moves once a slice is under way: skip the rescaling then
+        if (!__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f)) {
+#pragma unroll
+          for (int j = 0; j < kOTiles; ++j) {
+            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+          }
+        }
 #pragma unroll
         for (int j = 0; j < kOTiles; j += 2) {
-          o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
-          o[j + 1][0] *= corr[0]; o[j + 1][1] *= corr[0]; o[j + 1][2] *= corr[1]; o[j + 1][3] *= corr[1];
           unsigned b0, b1, b2, b3;   // (keys 0-7, d tile j), (keys 8-15, j), (keys 0-7, j+1), (keys 8-15, j+1)
-          ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs_ + tile_offset<HD>((mat & 1) * 8 + rin, j + (mat >> 1))));
+          ldmatrix_x4_trans(b0, b1, b2, b3, vbase + (v_row_off + (((j ^ v_swz) & (HD / 8 - 1)) * 8)) * 2);
           mma_bf16(o[j], pf, b0, b1);
           mma_bf16(o[j + 1], pf, b2, b3);
         }

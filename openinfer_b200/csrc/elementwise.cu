@@ -98,6 +98,93 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* 
   }
 }
 
+// bfloat16 rows whose length is a multiple of 8 and a bfloat16 weight: every thread moves whole
+// 16-byte vectors, all loads (row, residual, weight) are issued before anything waits on them.
+template <int VPT>
+__global__ void rmsnorm_bf16_vec_kernel(bf16* __restrict__ out, bf16* __restrict__ x, const bf16* __restrict__ delta,
+                                        const bf16* __restrict__ w, const int* __restrict__ row_idx, int hidden,
+                                        float eps, float w_offset) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
+  const int nvec = hidden / 8;
+  uint4* xr = reinterpret_cast<uint4*>(x + src * hidden);
+  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + src * hidden) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 xv[VPT], dv[VPT], wv[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      xv[k] = xr[v];
+      if (dr) dv[k] = dr[v];
+      wv[k] = wr[v];
+    }
+  }
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv[k]);
+      const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = __bfloat1622float2(x2[e]);
+        if (dr) {
+          const float2 d = __bfloat1622float2(d2[e]);
+          const __nv_bfloat162 rounded = __floats2bfloat162_rn(f.x + d.x, f.y + d.y);
+          reinterpret_cast<__nv_bfloat162*>(&xv[k])[e] = rounded;
+          f = __bfloat1622float2(rounded);
+        }
+        vals[k][2 * e] = f.x;
+        vals[k][2 * e + 1] = f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+      if (dr && !row_idx) xr[v] = xv[k];   // the residual sum is stored (gathered rows may repeat: not stored)
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  uint4* orow = reinterpret_cast<uint4*>(out + (size_t)r * hidden);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) {
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[k]);
+      uint4 ov;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 wf = __bfloat1622float2(w2[e]);
+        o2[e] = __floats2bfloat162_rn(vals[k][2 * e] * inv * (w_offset + wf.x), vals[k][2 * e + 1] * inv * (w_offset + wf.y));
+      }
+      orow[v] = ov;
+    }
+  }
+}
+
+static int launch_rmsnorm_bf16_vec(void* out, void* x, const void* delta, const void* w, const int* row_idx, int rows,
+                                   int hidden, float eps, float w_offset, cudaStream_t s) {
+  const int nvec = hidden / 8;
+  int threads = ((nvec + 31) / 32) * 32;
+  int vpt = 1;
+  while (threads > 1024) {
+    vpt *= 2;
+    threads = (((nvec + vpt - 1) / vpt + 31) / 32) * 32;
+  }
+#define OI_NORM_VEC(V)                                                                                       \
+  rmsnorm_bf16_vec_kernel<V><<<rows, threads, 0, s>>>((bf16*)out, (bf16*)x, (const bf16*)delta, (const bf16*)w, \
+                                                      row_idx, hidden, eps, w_offset)
+  if (vpt == 1) OI_NORM_VEC(1);
+  else if (vpt == 2) OI_NORM_VEC(2);
+  else OI_NORM_VEC(4);
+#undef OI_NORM_VEC
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
 template <typename T>
 static int launch_rmsnorm(void* out, void* x, const void* delta, const void* w, int w_dtype,
                           const int* row_idx, int rows, int hidden, float eps, float w_offset,
@@ -123,7 +210,13 @@ OI_API int oi_rmsnorm(void* out, void* x, const void* delta, int dtype, const vo
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == OI_F32) return launch_rmsnorm<float>(out, x, delta, w, w_dtype, row_idx, rows, hidden, eps, w_offset, s);
-  if (dtype == OI_BF16) return launch_rmsnorm<bf16>(out, x, delta, w, w_dtype, row_idx, rows, hidden, eps, w_offset, s);
+  if (dtype == OI_BF16) {
+    const bool aligned = ((uintptr_t)out % 16 == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                         (!delta || (uintptr_t)delta % 16 == 0);
+    if (w_dtype == OI_BF16 && hidden % 8 == 0 && hidden <= 32768 && aligned)
+      return launch_rmsnorm_bf16_vec(out, x, delta, w, row_idx, rows, hidden, eps, w_offset, s);
+    return launch_rmsnorm<bf16>(out, x, delta, w, w_dtype, row_idx, rows, hidden, eps, w_offset, s);
+  }
   OI_REQUIRE(false, "rmsnorm: unknown dtype code %d", dtype);
 }
 

@@ -56,6 +56,50 @@ __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ l
   }
 }
 
+// Two-stage argmax for a few rows of a large vocabulary: many blocks per row, then one block per row.
+constexpr int kArgmaxChunk = 4096;
+
+__global__ void argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi, const float* __restrict__ logits,
+                                      int vocab, long long row_stride, int nchunks) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int r = blockIdx.y, chunk = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const int lo = chunk * kArgmaxChunk, hi = min(vocab, lo + kArgmaxChunk);
+  ArgPair best{-INFINITY, 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = row[i];
+    if (v == v) best = better(best, ArgPair{v, i});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ArgPair b{sv[0], si[0]};
+    for (int wdx = 1; wdx < (int)(blockDim.x >> 5); ++wdx) b = better(b, ArgPair{sv[wdx], si[wdx]});
+    pv[(size_t)r * nchunks + chunk] = b.v;
+    pi[(size_t)r * nchunks + chunk] = b.i;
+  }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const int* __restrict__ pi,
+                                    int nchunks) {
+  const int r = blockIdx.x;
+  ArgPair best{-INFINITY, 0x7fffffff};
+  for (int c = threadIdx.x; c < nchunks; c += 32) best = better(best, ArgPair{pv[(size_t)r * nchunks + c], pi[(size_t)r * nchunks + c]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
 // count and mass of { p >= thr } over one row (p >= 0, compared as bit patterns)
 __device__ __forceinline__ void count_mass(const float* __restrict__ p, int vocab, unsigned thr_bits,
                                            unsigned floor_bits, float* red, int& count, float& mass) {
@@ -173,10 +217,24 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
 
 }  // namespace
 
-OI_API int oi_argmax(int* out, const float* logits, int rows, int vocab, long long row_stride, void* stream) {
+// Number of float/int pairs of scratch per row that oi_argmax wants for this vocabulary.
+OI_API int oi_argmax_chunks(int vocab) { return (vocab + kArgmaxChunk - 1) / kArgmaxChunk; }
+
+// partial_vals / partial_idx: scratch of rows * oi_argmax_chunks(vocab) entries each; may be null,
+// then one block scans each row.
+OI_API int oi_argmax(int* out, const float* logits, int rows, int vocab, long long row_stride, float* partial_vals,
+                     int* partial_idx, void* stream) {
   OI_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
   if (rows == 0) return OI_OK;
-  argmax_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, vocab, row_stride);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nchunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
+  if (partial_vals && partial_idx && nchunks >= 4 && rows * nchunks <= 65535 * 16) {
+    argmax_partial_kernel<<<dim3(nchunks, rows), 256, 0, s>>>(partial_vals, partial_idx, logits, vocab, row_stride, nchunks);
+    OI_CHECK_LAUNCH();
+    argmax_final_kernel<<<rows, 32, 0, s>>>(out, partial_vals, partial_idx, nchunks);
+  } else {
+    argmax_kernel<<<rows, 1024, 0, s>>>(out, logits, vocab, row_stride);
+  }
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

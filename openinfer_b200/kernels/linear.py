@@ -21,6 +21,10 @@ _lib.declare("oi_gemm_skinny", [c_void_p, c_int, c_longlong, c_void_p, c_longlon
                                 c_int, c_int, c_int, c_int, c_int, c_void_p])
 
 SKINNY_MAX_ROWS = 16
+# Measured on B200 (cold weights, M = 8, K = 4096): the skinny kernel beats the library where a
+# product is short enough for fixed costs to matter (N 4096..6144: 12-15 us vs 14-16 us) and loses on
+# long ones (N 24576: 43 vs 38 us; N 151936: 221 vs 208 us), so those stay with the library.
+SKINNY_MAX_WEIGHT_ROWS = 8192
 _SM_COUNT = None
 
 # hook for a hand-written bf16 kernel: fn(out, x, w) -> bool (True when it took the shape)
@@ -51,7 +55,7 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool)
     global _SM_COUNT
     M, N = x.shape[0], w.shape[0]
     K = w.shape[1]
-    if M > SKINNY_MAX_ROWS or out.dtype not in (torch.bfloat16, torch.float32):
+    if M > SKINNY_MAX_ROWS or N > SKINNY_MAX_WEIGHT_ROWS or out.dtype not in (torch.bfloat16, torch.float32):
         return False
     if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
         return False

@@ -192,7 +192,13 @@ def argmax(out: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.numel() != rows:
         raise KernelError("argmax: logits must be float32 rows")
     L = _lib.load()
-    _lib.check(L.oi_argmax(out.data_ptr(), logits.data_ptr(), rows, vocab, logits.stride(0), _stream()), "argmax")
+    nchunks = -(-vocab // 4096)
+    pv = pi = None
+    if nchunks >= 4:  # a large vocabulary: many blocks per row, partial results in scratch
+        pv = torch.empty(rows * nchunks, dtype=torch.float32, device=logits.device)
+        pi = torch.empty(rows * nchunks, dtype=torch.int32, device=logits.device)
+    _lib.check(L.oi_argmax(out.data_ptr(), logits.data_ptr(), rows, vocab, logits.stride(0), _ptr(pv), _ptr(pi),
+                           _stream()), "argmax")
     return out
 
 
