@@ -577,6 +577,8 @@ template <int HD>
 __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_stride, const float* __restrict__ part_o,
                                        const float* __restrict__ part_lse, const int* __restrict__ row_splits,
                                        int nq, int max_splits, int tokens) {
+  // a programmatically launched product after this kernel may start streaming its weights now
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gw >= (long long)tokens * nq) return;

@@ -105,6 +105,9 @@ __global__ void rmsnorm_bf16_vec_kernel(bf16* __restrict__ out, bf16* __restrict
                                         const bf16* __restrict__ w, const int* __restrict__ row_idx, int hidden,
                                         float eps, float w_offset) {
   __shared__ float red[32];
+  // let a dependent launch (the product that follows, if it was launched programmatically) start
+  // streaming its weights now; it still waits for this grid to finish before it reads `out`
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int r = blockIdx.x;
   const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
   const int nvec = hidden / 8;

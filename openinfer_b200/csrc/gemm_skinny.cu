@@ -2,13 +2,17 @@
 // bfloat16 operands, float32 accumulation. The step is bound by streaming W from HBM once, so the
 // kernel is built around memory parallelism, not tensor throughput:
 //
-//  * a CTA (8 warps) owns 128 rows of W and one slice of K; the CTAs of a thread-block CLUSTER own
+//  * a CTA (4 warps) owns 64 rows of W and one slice of K; the CTAs of a thread-block CLUSTER own
 //    the slices of the same rows and add their partial sums through distributed shared memory in
 //    rank order (deterministic, no atomics, no scratch in global memory);
-//  * each warp streams its 16 rows with 16-byte loads, 8 loads per lane in flight, and feeds
-//    mma.sync m16n8k16 with W as the A operand and the activations (staged once per CTA in shared
-//    memory) as B. The k index inside a 32-wide block is permuted identically for both operands
-//    (a dot product does not care), so a lane's 16 contiguous bytes ARE its fragment registers;
+//  * each warp streams its 16 rows through a private ring in shared memory filled by 16-byte
+//    cp.async copies, five stages (10 KB) in flight per warp and no barrier (a lane reads back what
+//    it copied itself), and feeds mma.sync m16n8k16 with W as the A operand and the activations
+//    (staged once per CTA in shared memory) as B. The k index inside a 32-wide block is permuted
+//    identically for both operands (a dot product does not care), so a lane's 16 contiguous
+//    bytes ARE its fragment registers;
+//  * the ring is primed before the kernel waits for its predecessor on the stream (programmatic
+//    dependent launch), so weights stream in under the tail of the kernel that produces x;
 //  * optionally the activation is formed while it is staged: x = silu(g) * u from a fused
 //    [M, 2K] gate|up buffer, rounded to bfloat16 exactly as the stand-alone kernel does, which
 //    removes a kernel and a round trip through memory from the feed-forward.
@@ -24,14 +28,18 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kRowsPerCta = 128;
-constexpr int kWarps = 8;
+constexpr int kWarps = 4;
+constexpr int kRowsPerCta = kWarps * 16;
+constexpr int kU = 2;          // 32-wide k blocks per ring stage
+constexpr int kStages = 6;     // ring depth per warp: five stages (10 KB) in flight per warp
+
 // Token rows in shared memory are padded so that the row stride is 4 (mod 8) 16-byte chunks: the
 // eight lanes that a 128-bit shared load serves at once (two tokens x four chunks) then hit
 // eight different bank groups.
 __host__ __device__ constexpr int row_stride_elems(int k_slice) {
   return k_slice + (((k_slice / 8) % 8 == 0) ? 32 : 64);
 }
+__host__ __device__ constexpr size_t ring_bytes() { return (size_t)kWarps * kStages * kU * 2 * 32 * 16; }
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -39,32 +47,63 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-__device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;  // src-size 0: zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ uint4 lds128(unsigned addr) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
 
 __device__ __forceinline__ float silu(float g) { return g / (1.f + expf(-g)); }
 
 // NT: token tiles of 8 (M <= 8 * NT). kCluster: CTAs along K add up through distributed shared memory.
+// kPdl: launched with programmatic stream serialization: the weight ring is primed BEFORE waiting
+// for the kernel that produces x, so the first 40 KB of W per CTA stream in under its tail.
 template <int NT, typename TOut, bool kSiluMul, bool kCluster>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict__ x, long long ldx,
-                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice) {
+                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int pdl) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int stride = row_stride_elems(k_slice);                 // elements per token row
-  bf16* x_s = reinterpret_cast<bf16*>(smem_raw);                // [8 * NT][stride]
-  float* part = reinterpret_cast<float*>(smem_raw + (size_t)8 * NT * stride * sizeof(bf16));  // [8 * NT][128]
+  unsigned char* ring_raw = smem_raw;                           // [warp][stage][u][row a | row b][lane] 16 B
+  bf16* x_s = reinterpret_cast<bf16*>(smem_raw + ring_bytes()); // [8 * NT][stride]
+  float* part = reinterpret_cast<float*>(smem_raw + ring_bytes() + (size_t)8 * NT * stride * sizeof(bf16));  // [8 * NT][64]
 
   const int rank = blockIdx.x;                                  // slice of K == rank in the cluster
   const int k0 = rank * k_slice;
   const int n0 = blockIdx.y * kRowsPerCta;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  // ---- stage the activation slice (rows >= M are zero)
+  // ---- the weight stream: lane (g, c) owns 8 consecutive k of rows g and g + 8 in every 32-wide block
+  const int g = lane >> 2, c = lane & 3;
+  const int row_a = min(n0 + warp * 16 + g, N - 1), row_b = min(n0 + warp * 16 + g + 8, N - 1);
+  const bf16* pa = W + (size_t)row_a * ldw + k0 + c * 8;
+  const bf16* pb = W + (size_t)row_b * ldw + k0 + c * 8;
+  const unsigned my_ring = (unsigned)__cvta_generic_to_shared(ring_raw) + (unsigned)(warp * kStages * kU * 2 * 32 + lane) * 16u;
+  const int nkb = k_slice / 32;
+  const int n_it = (nkb + kU - 1) / kU;
+  auto issue = [&](int it) {   // stage `it` of the stream into its ring slot (zero fill past the end)
+    const unsigned dst = my_ring + (unsigned)((it % kStages) * kU * 2 * 32) * 16u;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int kb = it * kU + u;
+      const bool valid = it < n_it && kb < nkb;
+      cp_async16(dst + (unsigned)(u * 2 * 32) * 16u, valid ? pa + kb * 32 : W, valid);
+      cp_async16(dst + (unsigned)((u * 2 + 1) * 32) * 16u, valid ? pb + kb * 32 : W, valid);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) issue(s);
+
+  // ---- stage the activation slice (rows >= M are zero); x is the previous kernel's output
+  if (pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
   {
     const int vec_per_row = k_slice / 8;
     for (int i = tid; i < 8 * NT * vec_per_row; i += kWarps * 32) {
@@ -79,8 +118,8 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
           __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&val);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-            o2[e] = __floats2bfloat162_rn(silu(g.x) * u.x, silu(g.y) * u.y);
+            const float2 gg = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+            o2[e] = __floats2bfloat162_rn(silu(gg.x) * u.x, silu(gg.y) * u.y);
           }
         } else {
           val = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k0 + v * 8);
@@ -91,47 +130,32 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
   }
   __syncthreads();
 
-  // ---- stream W: lane (g, c) owns 8 consecutive k of rows g and g + 8 in every 32-wide block
-  const int g = lane >> 2, c = lane & 3;
-  const int row_a = min(n0 + warp * 16 + g, N - 1), row_b = min(n0 + warp * 16 + g + 8, N - 1);
-  const bf16* pa = W + (size_t)row_a * ldw + k0 + c * 8;
-  const bf16* pb = W + (size_t)row_b * ldw + k0 + c * 8;
-  const bf16* xs = x_s + (size_t)g * stride + c * 8;
+  const unsigned xs = (unsigned)__cvta_generic_to_shared(x_s) + (unsigned)(g * stride + c * 8) * 2u;
   float acc[NT][4];
 #pragma unroll
   for (int t = 0; t < NT; ++t)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
-  const int nkb = k_slice / 32;
-  constexpr int U = 8;
-  int kb = 0;
-  for (; kb + U <= nkb; kb += U) {
-    uint4 wa[U], wb[U];
+  for (int it = 0; it < n_it; ++it) {
+    issue(it + kStages - 1);            // refills the slot consumed in the previous iteration
+    cp_async_wait<kStages - 1>();       // stage `it` (this lane's own copies) has landed
+    const unsigned src = my_ring + (unsigned)((it % kStages) * kU * 2 * 32) * 16u;
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      wa[u] = ldg_stream(pa + (kb + u) * 32);
-      wb[u] = ldg_stream(pb + (kb + u) * 32);
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < kU; ++u) {
+      const uint4 wa = lds128(src + (unsigned)(u * 2 * 32) * 16u);
+      const uint4 wb = lds128(src + (unsigned)((u * 2 + 1) * 32) * 16u);
+      const int kb = it * kU + u;
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)t * 8 * stride + (kb + u) * 32);
-        mma_bf16(acc[t], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xv.x, xv.y);
-        mma_bf16(acc[t], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xv.z, xv.w);
+        const uint4 xv = lds128(xs + (unsigned)(t * 8 * stride + kb * 32) * 2u);
+        mma_bf16(acc[t], wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
+        mma_bf16(acc[t], wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
       }
     }
   }
-  for (; kb < nkb; ++kb) {
-    const uint4 wa = ldg_stream(pa + kb * 32), wb = ldg_stream(pb + kb * 32);
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)t * 8 * stride + kb * 32);
-      mma_bf16(acc[t], wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
-      mma_bf16(acc[t], wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
-    }
-  }
+  cp_async_wait<0>();
+  if (pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
   // ---- partial sums of this K slice: part[token][row in tile]
 #pragma unroll
@@ -148,7 +172,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
     cg::cluster_group cluster = cg::this_cluster();
     const int csize = (int)cluster.num_blocks();
     cluster.sync();
-    // rank r adds up rows [r * 128 / csize, (r + 1) * 128 / csize) over all slices, in rank order
+    // rank r adds up rows [r * 64 / csize, (r + 1) * 64 / csize) over all slices, in rank order
     const int rows_mine = kRowsPerCta / csize;
     const int row_lo = rank * rows_mine;
     for (int i = tid; i < M * rows_mine; i += kWarps * 32) {
@@ -172,11 +196,15 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
   }
 }
 
+size_t smem_bytes(int NT, int k_slice) {
+  return ring_bytes() + (size_t)8 * NT * row_stride_elems(k_slice) * sizeof(bf16) + (size_t)8 * NT * kRowsPerCta * sizeof(float);
+}
+
 template <int NT, typename TOut, bool kSiluMul>
 int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N,
-           int K, int csize, cudaStream_t s) {
+           int K, int csize, int pdl, cudaStream_t s) {
   const int k_slice = K / csize;
-  const size_t smem = (size_t)8 * NT * row_stride_elems(k_slice) * sizeof(bf16) + (size_t)8 * NT * kRowsPerCta * sizeof(float);
+  const size_t smem = smem_bytes(NT, k_slice);
   static size_t configured[2] = {0, 0};   // largest dynamic shared memory set so far, per kernel variant
   const int row_tiles = (N + kRowsPerCta - 1) / kRowsPerCta;
   cudaLaunchConfig_t cfg = {};
@@ -184,29 +212,36 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
   cfg.blockDim = dim3(kWarps * 32, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
   if (csize > 1) {
     auto kernel = gemm_skinny_kernel<NT, TOut, kSiluMul, true>;
     if (smem > configured[1]) {
       OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured[1] = smem;
     }
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = csize;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = csize;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice));
+    cfg.numAttrs = na;
+    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl));
   } else {
     auto kernel = gemm_skinny_kernel<NT, TOut, kSiluMul, false>;
     if (smem > configured[0]) {
       OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured[0] = smem;
     }
-    cfg.attrs = nullptr;
-    cfg.numAttrs = 0;
-    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice));
+    cfg.attrs = na ? attr : nullptr;
+    cfg.numAttrs = na;
+    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl));
   }
   return OI_OK;
 }
@@ -215,8 +250,10 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
 
 // silu_mul != 0: x is a fused [M, 2K] gate|up buffer and the activation silu(gate) * up is formed
 // on the fly. cluster_size in {1, 2, 4, 8}: the number of K slices (CTAs per cluster).
+// pdl != 0: launch with programmatic stream serialization (the weight stream starts while the
+// kernel before this one on the stream is still finishing; x is only read after it has finished).
 OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
-                          long long ldw, int M, int N, int K, int silu_mul, int cluster_size, void* stream) {
+                          long long ldw, int M, int N, int K, int silu_mul, int cluster_size, int pdl, void* stream) {
   OI_REQUIRE(M >= 1 && M <= 16, "gemm_skinny: M=%d outside 1..16", M);
   OI_REQUIRE(N >= 1 && K >= 32, "gemm_skinny: bad sizes N=%d K=%d", N, K);
   OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
@@ -225,10 +262,10 @@ OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x
   OI_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0,
              "gemm_skinny: operands must be 16-byte aligned with row strides that are multiples of 8");
   const int NT = M <= 8 ? 1 : 2;
-  const size_t smem = (size_t)8 * NT * row_stride_elems(K / cluster_size) * sizeof(bf16) + (size_t)8 * NT * kRowsPerCta * sizeof(float);
+  const size_t smem = smem_bytes(NT, K / cluster_size);
   OI_REQUIRE(smem <= 200 * 1024, "gemm_skinny: K slice %d needs %zu bytes of shared memory", K / cluster_size, smem);
   cudaStream_t s = (cudaStream_t)stream;
-#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s)
+#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, pdl, s)
   if (out_dtype == OI_BF16) {
     if (NT == 1) { if (silu_mul) OI_SKINNY(1, bf16, true); else OI_SKINNY(1, bf16, false); }
     else         { if (silu_mul) OI_SKINNY(2, bf16, true); else OI_SKINNY(2, bf16, false); }

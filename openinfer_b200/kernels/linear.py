@@ -18,7 +18,10 @@ from . import lib as _lib
 from . import ops
 
 _lib.declare("oi_gemm_skinny", [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
-                                c_int, c_int, c_int, c_int, c_int, c_void_p])
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+
+# programmatic dependent launch of the decode products (see gemm_skinny.cu)
+USE_PDL = True
 
 SKINNY_MAX_ROWS = 16
 # Measured on B200 (cold weights, M = 8, K = 4096): the skinny kernel beats the library where a
@@ -40,12 +43,12 @@ def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
     """How many K slices (CTAs per cluster) the skinny kernel uses, 0 if it does not take the
     shape: the fewest slices that fill the GPU twice over, each slice's activations within 64 KB
     of shared memory where possible."""
-    row_tiles = -(-N // 128)
-    valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 32 * (K // c + 64) + 8192 <= 200 * 1024]
+    row_tiles = -(-N // 64)
+    valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 24576 + 32 * (K // c + 64) + 4096 <= 200 * 1024]
     if not valid:
         return 0
     for c in valid:
-        if row_tiles * c >= 2 * sm_count and 32 * (K // c + 64) <= 72 * 1024:
+        if row_tiles * c >= 3 * sm_count and 32 * (K // c + 64) <= 40 * 1024:
             return c
     return valid[-1]
 
@@ -69,7 +72,7 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool)
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 1 if silu_mul else 0, c,
-                                torch.cuda.current_stream().cuda_stream), "gemm_skinny")
+                                1 if USE_PDL else 0, torch.cuda.current_stream().cuda_stream), "gemm_skinny")
     return True
 
 

@@ -461,12 +461,12 @@ def test_gemm_skinny(M, N, K):
     from openinfer_b200.kernels import lib as klib
     L = klib.load()
     for c in (1, 2, 4, 8):
-        if K % (32 * c) or 32 * (K // c + 64) + 8192 > 200 * 1024:   # the slice must fit in shared memory
+        if K % (32 * c) or 24576 + 32 * (K // c + 64) + 4096 > 200 * 1024:   # the slice must fit in shared memory
             continue
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
             klib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out_dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, c,
+                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, c, c % 4 == 0,
                                         torch.cuda.current_stream().cuda_stream), "gemm_skinny")
             tol_ = 2e-2 * ref.abs().max().item() if out_dtype == torch.bfloat16 else 2e-4 * ref.abs().max().item()
             err = (out.double() - ref).abs().max().item()
