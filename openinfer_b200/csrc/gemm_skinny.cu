@@ -146,6 +146,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
       const uint4 wa = lds128(src + (unsigned)(u * 2 * 32) * 16u);
       const uint4 wb = lds128(src + (unsigned)((u * 2 + 1) * 32) * 16u);
       const int kb = it * kU + u;
+      if (kb >= nkb) break;   // the zero-filled tail of the last stage: nothing to add (and x_s ends here)
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         const uint4 xv = lds128(xs + (unsigned)(t * 8 * stride + kb * 32) * 2u);

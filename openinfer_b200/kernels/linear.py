@@ -21,13 +21,19 @@ _lib.declare("oi_gemm_skinny", [c_void_p, c_int, c_longlong, c_void_p, c_longlon
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
 
 # programmatic dependent launch of the decode products (see gemm_skinny.cu)
-USE_PDL = True
+import os as _os  # noqa: E402
+USE_PDL = _os.environ.get('OI_PDL', '1') == '1'
+_FORCE_C = int(_os.environ.get('OI_SKINNY_C', '0'))
 
 SKINNY_MAX_ROWS = 16
 # Measured on B200 (cold weights, M = 8, K = 4096): the skinny kernel beats the library where a
 # product is short enough for fixed costs to matter (N 4096..6144: 12-15 us vs 14-16 us) and loses on
 # long ones (N 24576: 43 vs 38 us; N 151936: 221 vs 208 us), so those stay with the library.
 SKINNY_MAX_WEIGHT_ROWS = 8192
+# Forming silu(gate) * up while the product kernel stages its activations repeats the exponentials
+# once per 64-row tile of the weight (64 times at N = 4096): measured 44.7 us for the fused down
+# projection against 25 + 3.2 us for the two kernels. The fused path stays available and tested.
+FUSE_SILU_MUL = False
 _SM_COUNT = None
 
 # hook for a hand-written bf16 kernel: fn(out, x, w) -> bool (True when it took the shape)
@@ -47,8 +53,9 @@ def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
     valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 24576 + 32 * (K // c + 64) + 4096 <= 200 * 1024]
     if not valid:
         return 0
-    for c in valid:
-        if row_tiles * c >= 3 * sm_count and 32 * (K // c + 64) <= 40 * 1024:
+    # measured on B200 at M = 8: four slices are best for the short products (N 4096..6144)
+    for c in (4, 2, 8, 1):
+        if c in valid:
             return c
     return valid[-1]
 
@@ -69,6 +76,8 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool)
     c = skinny_cluster_size(N, K, _SM_COUNT)
     if c == 0:
         return False
+    if _FORCE_C and K % (32 * _FORCE_C) == 0 and 24576 + 32 * (K // _FORCE_C + 64) + 4096 <= 200 * 1024:
+        c = _FORCE_C
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 1 if silu_mul else 0, c,
@@ -80,7 +89,7 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """(silu(gate) * up) W^T for a fused [M, 2K] gate|up buffer and w [N, K]. For a few rows the
     activation is formed inside the product kernel; otherwise by its own kernel first."""
     M, K = gate_up.shape[0], w.shape[1]
-    if gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS and _bf16_gemm is None:
+    if FUSE_SILU_MUL and gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS:
         out = torch.empty((M, w.shape[0]), dtype=gate_up.dtype, device=gate_up.device)
         if _skinny(out, gate_up, w, True):
             return out
