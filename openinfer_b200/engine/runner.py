@@ -353,11 +353,13 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        before = kernel_lib.launches
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = run()
+        recorded = kernel_lib.launches - before   # entry-point calls one replay stands for
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        entry = (graph, meta, sections, total, logits, ctx)
+        entry = (graph, meta, sections, total, logits, (ctx, recorded))
         self._graphs[key] = entry
         return entry
 
@@ -371,7 +373,7 @@ class ModelRunner:
         cap = 16
         while cap < need_pages:
             cap *= 2
-        graph, meta, sections, total, logits, _ = self._decode_graph(bucket, cap)
+        graph, meta, sections, total, logits, (_, recorded) = self._decode_graph(bucket, cap)
         host = np.zeros(total, dtype=np.int32)
         want_rows = self._fill(host, sections, entries, starts, bucket, bucket, cap)
         host[sections["want"]: sections["want"] + bucket] = np.arange(bucket, dtype=np.int32)
@@ -387,6 +389,7 @@ class ModelRunner:
         self._staging_event = torch.cuda.Event()
         self._staging_event.record()
         graph.replay()
+        kernel_lib.launches += recorded
         if not want_rows:
             return None
         if want_rows == list(range(len(want_rows))):
