@@ -1,0 +1,347 @@
+// C[M, N] = A[M, K] * W[N, K]^T for bfloat16 operands on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands staged in shared memory by TMA.
+//
+// One CTA computes one 128 x BN tile of C (BN = 256 or 128). Warp roles:
+//   warp 0     one elected thread issues the TMA loads of the A tile [128 x 64] and the W tile
+//              [BN x 64] of every k block into a ring of stages (128-byte swizzle, the layout the
+//              tensor core reads directly), signalling an mbarrier per stage with the byte count;
+//   warp 1     allocates tensor memory; one elected thread issues four tcgen05.mma (K = 16 each)
+//              per stage and commits them to the stage's "empty" barrier, and after the last k
+//              block to the "accumulator ready" barrier;
+//   warps 2-5  wait for the accumulator, read it back with tcgen05.ld (each warp its quarter of the
+//              128 lanes, 32 columns at a time), round once and store rows of C.
+// Every wait on an mbarrier is bounded: a wait that runs out sets an error word in global memory
+// and a flag in shared memory that ends all roles; the CTA then lets its copies land (bounded),
+// frees its tensor memory and returns. No load uses cluster multicast: every CTA fetches its own
+// tiles (W tiles are shared between neighbouring CTAs through L2).
+//
+// This is the hand-written counterpart of the library call the reference makes for every projection
+// (pegainfer-kernels/csrc/shared/linear.cu:312-362: bf16 in, float32 accumulate, row-major weight).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a wait gives up after two seconds
+
+__device__ int g_gemm_error = 0;       // set to a non-zero code when a bounded wait ran out
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises the abort flag) when it ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
+  unsigned long long t0 = 0;
+  for (unsigned i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((i & 255u) == 255u) {          // look at the clock now and then
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_gemm_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long desc_a, unsigned long long desc_b,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The barrier gets one arrival when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what TMA writes): start address, stride between 8-row groups = 1024 bytes, version 1,
+// layout type 2 (128-byte swizzle). The leading-dimension offset is not used by this layout.
+__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);        // bits [0, 14)
+  d |= (unsigned long long)1 << 16;                              // leading byte offset (ignored), bits [16, 30)
+  d |= (unsigned long long)(1024 >> 4) << 32;                    // stride byte offset, bits [32, 46)
+  d |= (unsigned long long)1 << 46;                              // descriptor version, bits [46, 48)
+  d |= (unsigned long long)2 << 61;                              // layout type: SWIZZLE_128B
+  return d;
+}
+
+template <int BN, int kStages>
+struct Smem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;       // full[kStages], empty[kStages], acc, then tmem slot, abort
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 1) * 8 + 16 + 1024;   // + slack to align the base to 1024
+};
+
+template <int BN, int kStages, typename TOut>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+  using L = Smem<BN, kStages>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const unsigned smem_base = smem_u32(smem);
+  const unsigned bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  const unsigned acc_bar = bar_base + 8u * (2 * kStages);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L::kBarOffset + (2 * kStages + 1) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), BN);     // BN float32 columns x 128 lanes
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        if (kb >= kStages && !mbar_wait(empty_bar(s), ((kb / kStages) - 1) & 1, abort_flag, 1)) break;
+        mbar_expect_tx(full_bar(s), L::kStageBytes);
+        const unsigned a_dst = smem_base + s * L::kStageBytes;
+        tma_load_2d(a_dst, &map_a, kb * BK, m0, full_bar(s));
+        tma_load_2d(a_dst + L::kABytes, &map_b, kb * BK, n0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = float32, A = B = bfloat16, both K-major, N = BN, M = 128
+      constexpr unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kStages;
+        ok = mbar_wait(full_bar(s), (kb / kStages) & 1, abort_flag, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned a_addr = smem_base + s * L::kStageBytes;
+        const unsigned long long da = make_desc(a_addr), db = make_desc(a_addr + L::kABytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          // 16 elements = 32 bytes further along K inside the swizzle row: +2 in the address field
+          umma_bf16(tmem_acc, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));           // the stage may be refilled once these MMAs have read it
+      }
+      if (ok) umma_commit(acc_bar);          // the accumulator is complete
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;            // a warp may only touch lanes [32 * (warp % 4), +32)
+    if (mbar_wait(acc_bar, 0, abort_flag, 3)) {
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        unsigned v[32];
+        tmem_ld32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)c, v);
+        tmem_ld_wait();
+        if (row < M) {
+          TOut* dst = C + (size_t)row * ldc + n0 + c;
+          if (n0 + c + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+            if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  o2[e] = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2 * e]), __uint_as_float(v[q * 8 + 2 * e + 1]));
+                reinterpret_cast<uint4*>(dst)[q] = o;
+              }
+            } else {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                reinterpret_cast<uint4*>(dst)[q] = make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            }
+          } else {
+            for (int e = 0; e < 32; ++e)
+              if (n0 + c + e < N) dst[e] = from_f32<TOut>(__uint_as_float(v[e]));
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // copies that were issued may still be landing in this CTA's shared memory: give them time
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_acc, BN);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// rows x K bfloat16 matrix with row stride ld (elements); tiles of box_rows x 64, 128-byte swizzle,
+// zeros outside the matrix
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  OI_REQUIRE(fn != nullptr, "gemm_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  OI_REQUIRE(r == CUDA_SUCCESS, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return OI_OK;
+}
+
+template <int BN, int kStages, typename TOut>
+int launch(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
+           cudaStream_t s) {
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, W, N, K, ldw, BN);
+  if (rc) return rc;
+  auto kernel = gemm_tcgen05_kernel<BN, kStages, TOut>;
+  constexpr int smem = Smem<BN, kStages>::kTotal;
+  static bool configured = false;
+  if (!configured) {
+    OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
+  kernel<<<grid, kThreads, smem, s>>>(ma, mb, (TOut*)C, ldc, M, N, K);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+}  // namespace
+
+// A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw; C: [M, N] bfloat16 or
+// float32, row stride ldc. K and the row strides must be multiples of 8 elements and the bases
+// 16-byte aligned (TMA). tile_n: 256 or 128.
+OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W,
+                           long long ldw, int M, int N, int K, int tile_n, void* stream) {
+  OI_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+  OI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and row strides must be multiples of 8");
+  OI_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+  OI_REQUIRE(tile_n == 256 || tile_n == 128, "gemm_tcgen05: tile_n %d", tile_n);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (c_dtype == OI_BF16) {
+    if (tile_n == 256) return launch<256, 4, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    return launch<128, 6, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
+  }
+  if (c_dtype == OI_F32) {
+    if (tile_n == 256) return launch<256, 4, float>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    return launch<128, 6, float>(C, ldc, A, lda, W, ldw, M, N, K, s);
+  }
+  OI_REQUIRE(false, "gemm_tcgen05: unknown output dtype code %d", c_dtype);
+}
+
+// 0 when no bounded wait has run out since the last call; otherwise which role gave up
+// (1 producer, 2 MMA issuer, 3 epilogue). Synchronises the device; clears the word.
+OI_API int oi_gemm_tcgen05_status(int* status) {
+  int v = 0;
+  OI_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    OI_CHECK_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  }
+  *status = v;
+  return OI_OK;
+}

@@ -1,0 +1,46 @@
+"""Wrapper of the hand-written tcgen05 / TMEM / TMA product for bfloat16 operands."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p
+
+import torch
+
+from . import lib as _lib
+from .lib import KernelError
+
+_lib.declare("oi_gemm_tcgen05", [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                                 c_int, c_int, c_int, c_int, c_void_p])
+_lib.declare("oi_gemm_tcgen05_status", [ctypes.POINTER(c_int)])
+
+
+def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the kernel accepts these operands (bfloat16 in, bfloat16 or float32 out, TMA alignment)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    K = x.shape[1]
+    return (K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (float32 accumulation in TMEM)."""
+    if not (x.is_cuda and w.is_cuda and out.is_cuda):
+        raise KernelError("gemm_tcgen05: operands must be on a CUDA device; this package has no CPU path")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or not takes(out, x, w):
+        raise KernelError(f"gemm_tcgen05: operands not accepted: x={tuple(x.shape)} w={tuple(w.shape)} out={tuple(out.shape)}")
+    L = _lib.load()
+    _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
+                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, tile_n,
+                                 torch.cuda.current_stream().cuda_stream), "gemm_tcgen05")
+    return out
+
+
+def status() -> int:
+    """0, or the role whose bounded wait ran out since the last call (synchronises the device)."""
+    L = _lib.load()
+    v = c_int(0)
+    _lib.check(L.oi_gemm_tcgen05_status(ctypes.byref(v)), "gemm_tcgen05_status")
+    return v.value

@@ -490,3 +490,28 @@ def test_gemm_skinny_with_fused_activation(M, N, K):
     ref = act.double() @ w.double().t()
     out = lin.linear_silu_mul(gu, w)
     assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("tile_n", [256, 128])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 4096), (300, 520, 1000), (2048, 1024, 512),
+                                   (17, 100, 72), (129, 257, 8)])
+def test_gemm_tcgen05(M, N, K, tile_n):
+    """The tcgen05 / TMEM / TMA product against float64: whole tiles, ragged edges in M, N and K."""
+    from openinfer_b200.kernels import gemm_tcgen05 as g
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    scale = ref.abs().max().item()
+    for out_dtype, tol_ in ((torch.bfloat16, 1e-2), (torch.float32, 1e-4)):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+        g.gemm(out, x, w, tile_n)
+        assert g.status() == 0, "a bounded wait ran out"
+        err = (out.double() - ref).abs().max().item()
+        assert err <= tol_ * scale, f"{out_dtype}: max err {err} (scale {scale})"
+    # operand rows with a stride wider than K (a view into a larger buffer)
+    big = torch.randn(M, K + 16, device=DEV).to(torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    g.gemm(out, big[:, :K], w, tile_n)
+    assert g.status() == 0
+    assert (out.double() - big[:, :K].double() @ w.double().t()).abs().max().item() <= 1e-4 * scale
