@@ -245,25 +245,30 @@ OI_API int oi_add_inplace(void* x, const void* delta, int dtype, long long n, vo
 }
 
 // ---------------------------------------------------------------------------
-// SiLU * mul on a fused [rows, 2*inter] gate|up buffer: out[r, i] = silu(g) * u
+// SiLU * mul on a fused [rows, 2*inter] gate|up buffer: out[r, i] = silu(g_i) * u_i.
+// Layout of a row: blocks of `block` gate values followed by the `block` up values of the same
+// indices; block == inter is the plain [all gates | all ups] layout. (A product kernel whose tile
+// holds a gate block and its up block side by side can form the activation in its epilogue.)
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, size_t n) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int block, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i - r * inter;
-    const float g = to_f32(gate_up[r * 2 * inter + c]);
-    const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
+    const size_t gi = r * 2 * inter + (c / block) * 2 * block + (c % block);
+    const float g = to_f32(gate_up[gi]);
+    const float u = to_f32(gate_up[gi + block]);
     out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
   }
 }
 
-// 8 bf16 per thread when inter is a multiple of 8
+// 8 bf16 per thread when inter and block are multiples of 8
 __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up,
-                                       int inter8, size_t n8) {
+                                       int inter8, int block8, size_t n8) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter8, c = i - r * inter8;
-    uint4 gv = gate_up[r * 2 * inter8 + c];
-    uint4 uv = gate_up[r * 2 * inter8 + inter8 + c];
+    const size_t gi = r * 2 * inter8 + (c / block8) * 2 * block8 + (c % block8);
+    uint4 gv = gate_up[gi];
+    uint4 uv = gate_up[gi + block8];
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
     uint4 ov;
@@ -278,19 +283,20 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __r
   }
 }
 
-OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, void* stream) {
+OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, int block, void* stream) {
   OI_REQUIRE(rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
+  OI_REQUIRE(block > 0 && inter % block == 0, "silu_mul: block %d does not divide inter %d", block, inter);
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const size_t n = (size_t)rows * inter;
-  if (dtype == OI_BF16 && inter % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
+  if (dtype == OI_BF16 && inter % 8 == 0 && block % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
     const size_t n8 = n / 8;
     const int blocks = (int)((n8 + 255) / 256 > 148 * 16 ? 148 * 16 : (n8 + 255) / 256);
-    silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((uint4*)out, (const uint4*)gate_up, inter / 8, n8);
+    silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8);
   } else {
     const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-    if (dtype == OI_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gate_up, inter, n);
-    else if (dtype == OI_BF16) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, n);
+    if (dtype == OI_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gate_up, inter, block, n);
+    else if (dtype == OI_BF16) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, block, n);
     else OI_REQUIRE(false, "silu_mul: unknown dtype code %d", dtype);
   }
   OI_CHECK_LAUNCH();

@@ -68,7 +68,7 @@ __device__ __forceinline__ float silu(float g) { return g / (1.f + expf(-g)); }
 template <int NT, typename TOut, bool kSiluMul, bool kCluster>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict__ x, long long ldx,
-                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int pdl) {
+                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int pdl, int act_block) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int stride = row_stride_elems(k_slice);                 // elements per token row
   unsigned char* ring_raw = smem_raw;                           // [warp][stage][u][row a | row b][lane] 16 B
@@ -111,8 +111,10 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
       uint4 val = make_uint4(0, 0, 0, 0);
       if (m < M) {
         if (kSiluMul) {
-          const uint4 gv = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k0 + v * 8);
-          const uint4 uv = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + K + k0 + v * 8);
+          const int k = k0 + v * 8;   // gate block b, then up block b: see oi_silu_mul
+          const size_t gi = (size_t)m * ldx + (size_t)(k / act_block) * 2 * act_block + (k % act_block);
+          const uint4 gv = *reinterpret_cast<const uint4*>(x + gi);
+          const uint4 uv = *reinterpret_cast<const uint4*>(x + gi + act_block);
           const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
           const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
           __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&val);
@@ -203,7 +205,7 @@ size_t smem_bytes(int NT, int k_slice) {
 
 template <int NT, typename TOut, bool kSiluMul>
 int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N,
-           int K, int csize, int pdl, cudaStream_t s) {
+           int K, int csize, int pdl, int act_block, cudaStream_t s) {
   const int k_slice = K / csize;
   const size_t smem = smem_bytes(NT, k_slice);
   static size_t configured[2] = {0, 0};   // largest dynamic shared memory set so far, per kernel variant
@@ -233,7 +235,7 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
     ++na;
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl));
+    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl, act_block));
   } else {
     auto kernel = gemm_skinny_kernel<NT, TOut, kSiluMul, false>;
     if (smem > configured[0]) {
@@ -242,15 +244,16 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
     }
     cfg.attrs = na ? attr : nullptr;
     cfg.numAttrs = na;
-    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl));
+    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl, act_block));
   }
   return OI_OK;
 }
 
 }  // namespace
 
-// silu_mul != 0: x is a fused [M, 2K] gate|up buffer and the activation silu(gate) * up is formed
-// on the fly. cluster_size in {1, 2, 4, 8}: the number of K slices (CTAs per cluster).
+// silu_mul != 0: x is a fused [M, 2K] gate|up buffer laid out in blocks of `silu_mul` gate values
+// followed by their up values (silu_mul == K: all gates, then all ups) and the activation
+// silu(gate) * up is formed on the fly. cluster_size in {1, 2, 4, 8}: the number of K slices (CTAs per cluster).
 // pdl != 0: launch with programmatic stream serialization (the weight stream starts while the
 // kernel before this one on the stream is still finishing; x is only read after it has finished).
 OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
@@ -260,13 +263,14 @@ OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x
   OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
              "gemm_skinny: cluster size %d", cluster_size);
   OI_REQUIRE(K % (32 * cluster_size) == 0, "gemm_skinny: K=%d is not a multiple of 32 * %d", K, cluster_size);
+  OI_REQUIRE(silu_mul == 0 || (silu_mul % 8 == 0 && K % silu_mul == 0), "gemm_skinny: activation block %d does not fit K=%d", silu_mul, K);
   OI_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0,
              "gemm_skinny: operands must be 16-byte aligned with row strides that are multiples of 8");
   const int NT = M <= 8 ? 1 : 2;
   const size_t smem = smem_bytes(NT, K / cluster_size);
   OI_REQUIRE(smem <= 200 * 1024, "gemm_skinny: K slice %d needs %zu bytes of shared memory", K / cluster_size, smem);
   cudaStream_t s = (cudaStream_t)stream;
-#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, pdl, s)
+#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, pdl, silu_mul, s)
   if (out_dtype == OI_BF16) {
     if (NT == 1) { if (silu_mul) OI_SKINNY(1, bf16, true); else OI_SKINNY(1, bf16, false); }
     else         { if (silu_mul) OI_SKINNY(2, bf16, true); else OI_SKINNY(2, bf16, false); }

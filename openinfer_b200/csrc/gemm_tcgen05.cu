@@ -1,7 +1,9 @@
 // C[M, N] = A[M, K] * W[N, K]^T for bfloat16 operands on the 5th-generation tensor cores:
 // tcgen05.mma with the accumulator in tensor memory, operands staged in shared memory by TMA.
 //
-// One CTA computes one 128 x BN tile of C (BN = 256 or 128). Warp roles:
+// A persistent CTA per SM computes 128 x BN tiles of C (BN = 256 or 128) one after the other, the
+// accumulator double buffered in tensor memory so that a tile's epilogue overlaps the next tile's
+// products. Warp roles:
 //   warp 0     one elected thread issues the TMA loads of the A tile [128 x 64] and the W tile
 //              [BN x 64] of every k block into a ring of stages (128-byte swizzle, the layout the
 //              tensor core reads directly), signalling an mbarrier per stage with the byte count;
@@ -127,11 +129,17 @@ struct Smem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;       // full[kStages], empty[kStages], acc, then tmem slot, abort
-  static constexpr int kTotal = kBarOffset + (2 * kStages + 1) * 8 + 16 + 1024;   // + slack to align the base to 1024
+  static constexpr int kBarOffset = kStages * kStageBytes;   // full[kStages], empty[kStages], acc_full[2], acc_empty[2], tmem slot, abort
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16 + 1024;   // + slack to align the base to 1024
 };
 
-template <int BN, int kStages, typename TOut>
+// Persistent: CTA b works on tiles b, b + gridDim.x, ... (row tiles fastest, so CTAs that run at the
+// same time share W tiles through L2). The accumulator is double buffered in tensor memory
+// (2 x BN columns): while the epilogue warps drain tile i, the MMA warp already fills tile i + 1.
+// kSiluMul: W holds, per tile of BN rows, BN/2 gate rows followed by the BN/2 up rows of the same
+// indices; the epilogue writes silu(gate) * up, [M, N/2] with row stride ldc, instead of the product.
+template <int BN, int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TOut* __restrict__ C, long long ldc, int M, int N, int K) {
@@ -142,12 +150,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const unsigned bar_base = smem_base + L::kBarOffset;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  const unsigned acc_bar = bar_base + 8u * (2 * kStages);
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L::kBarOffset + (2 * kStages + 1) * 8);
+  auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -155,29 +165,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);      // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), BN);     // BN float32 columns x 128 lanes
+    tmem_alloc(smem_u32(tmem_slot), 2 * BN);   // two accumulators of BN float32 columns x 128 lanes
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const unsigned tmem_acc = *tmem_slot;
+  const unsigned tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % kStages;
-        if (kb >= kStages && !mbar_wait(empty_bar(s), ((kb / kStages) - 1) & 1, abort_flag, 1)) break;
-        mbar_expect_tx(full_bar(s), L::kStageBytes);
-        const unsigned a_dst = smem_base + s * L::kStageBytes;
-        tma_load_2d(a_dst, &map_a, kb * BK, m0, full_bar(s));
-        tma_load_2d(a_dst + L::kABytes, &map_b, kb * BK, n0, full_bar(s));
+      long long it = 0;   // k blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = (int)(it % kStages);
+          if (it >= kStages && !mbar_wait(empty_bar(s), (unsigned)((it / kStages) - 1) & 1, abort_flag, 1)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), L::kStageBytes);
+          const unsigned a_dst = smem_base + s * L::kStageBytes;
+          tma_load_2d(a_dst, &map_a, kb * BK, m0, full_bar(s));
+          tma_load_2d(a_dst + L::kABytes, &map_b, kb * BK, n0, full_bar(s));
+        }
       }
     }
   } else if (warp == 1) {
@@ -185,33 +203,81 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       // instruction descriptor: D = float32, A = B = bfloat16, both K-major, N = BN, M = 128
       constexpr unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+      long long it = 0;
+      int local = 0;      // tiles done by this CTA
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % kStages;
-        ok = mbar_wait(full_bar(s), (kb / kStages) & 1, abort_flag, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const unsigned a_addr = smem_base + s * L::kStageBytes;
-        const unsigned long long da = make_desc(a_addr), db = make_desc(a_addr + L::kABytes);
-#pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          // 16 elements = 32 bytes further along K inside the swizzle row: +2 in the address field
-          umma_bf16(tmem_acc, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int a = local & 1;
+        if (local >= 2) {   // the epilogue must have drained this accumulator (tile local - 2)
+          ok = mbar_wait(acc_empty_bar(a), (unsigned)((local >> 1) - 1) & 1, abort_flag, 4);
+          if (!ok) break;
+          tc_fence_after();
         }
-        umma_commit(empty_bar(s));           // the stage may be refilled once these MMAs have read it
+        const unsigned tmem_acc = tmem_base + (unsigned)(a * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = (int)(it % kStages);
+          ok = mbar_wait(full_bar(s), (unsigned)(it / kStages) & 1, abort_flag, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const unsigned a_addr = smem_base + s * L::kStageBytes;
+          const unsigned long long da = make_desc(a_addr), db = make_desc(a_addr + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 elements = 32 bytes further along K inside the swizzle row: +2 in the address field
+            umma_bf16(tmem_acc, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));         // the stage may be refilled once these MMAs have read it
+        }
+        if (ok) umma_commit(acc_full_bar(a));   // this tile's accumulator is complete
       }
-      if (ok) umma_commit(acc_bar);          // the accumulator is complete
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;            // a warp may only touch lanes [32 * (warp % 4), +32)
-    if (mbar_wait(acc_bar, 0, abort_flag, 3)) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int a = local & 1;
+      if (!mbar_wait(acc_full_bar(a), (unsigned)(local >> 1) & 1, abort_flag, 3)) break;
       tc_fence_after();
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
+      const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
+      if constexpr (kSiluMul) {
+        const int n_out = N / 2, o0 = n0 / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          unsigned g[32], u[32];
+          tmem_ld32(tmem_acc + (unsigned)c, g);
+          tmem_ld32(tmem_acc + (unsigned)(BN / 2 + c), u);
+          tmem_ld_wait();
+          if (row < M) {
+            TOut* dst = C + (size_t)row * ldc + o0 + c;
+            float a[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float gg = __uint_as_float(g[e]);
+              a[e] = gg / (1.f + __expf(-gg)) * __uint_as_float(u[e]);
+            }
+            if (o0 + c + 32 <= n_out && (((uintptr_t)dst) & 15) == 0 && sizeof(TOut) == 2) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(a[q * 8 + 2 * e], a[q * 8 + 2 * e + 1]);
+                reinterpret_cast<uint4*>(dst)[q] = o;
+              }
+            } else {
+              for (int e = 0; e < 32; ++e)
+                if (o0 + c + e < n_out) dst[e] = from_f32<TOut>(a[e]);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         unsigned v[32];
-        tmem_ld32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)c, v);
+        tmem_ld32(tmem_acc + (unsigned)c, v);
         tmem_ld_wait();
         if (row < M) {
           TOut* dst = C + (size_t)row * ldc + n0 + c;
@@ -237,6 +303,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      }
+      // this warp has read its part of the accumulator: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(acc_empty_bar(a)) : "memory");
     }
   }
 
@@ -250,7 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_acc, BN);
+    tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -289,7 +360,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
   return OI_OK;
 }
 
-template <int BN, int kStages, typename TOut>
+template <int BN, int kStages, typename TOut, bool kSiluMul = false>
 int launch(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
            cudaStream_t s) {
   CUtensorMap ma, mb;
@@ -297,15 +368,21 @@ int launch(void* C, long long ldc, const void* A, long long lda, const void* W, 
   if (rc) return rc;
   rc = make_map(&mb, W, N, K, ldw, BN);
   if (rc) return rc;
-  auto kernel = gemm_tcgen05_kernel<BN, kStages, TOut>;
+  auto kernel = gemm_tcgen05_kernel<BN, kStages, TOut, kSiluMul>;
   constexpr int smem = Smem<BN, kStages>::kTotal;
   static bool configured = false;
   if (!configured) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-  kernel<<<grid, kThreads, smem, s>>>(ma, mb, (TOut*)C, ldc, M, N, K);
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    OI_CHECK_CUDA(cudaGetDevice(&dev));
+    OI_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, smem, s>>>(ma, mb, (TOut*)C, ldc, M, N, K);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -315,13 +392,20 @@ int launch(void* C, long long ldc, const void* A, long long lda, const void* W, 
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw; C: [M, N] bfloat16 or
 // float32, row stride ldc. K and the row strides must be multiples of 8 elements and the bases
 // 16-byte aligned (TMA). tile_n: 256 or 128.
+// silu_mul != 0 (tile_n 256, bfloat16 out, N a multiple of 256): W's rows come in blocks of 128 gate
+// rows followed by their 128 up rows, and C is [M, N / 2] = silu(gate) * up.
 OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W,
-                           long long ldw, int M, int N, int K, int tile_n, void* stream) {
+                           long long ldw, int M, int N, int K, int tile_n, int silu_mul, void* stream) {
   OI_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   OI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and row strides must be multiples of 8");
   OI_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tcgen05: operands must be 16-byte aligned");
   OI_REQUIRE(tile_n == 256 || tile_n == 128, "gemm_tcgen05: tile_n %d", tile_n);
   cudaStream_t s = (cudaStream_t)stream;
+  if (silu_mul) {
+    OI_REQUIRE(tile_n == 256 && c_dtype == OI_BF16 && N % 256 == 0,
+               "gemm_tcgen05: the fused activation needs tile_n 256, bfloat16 output and N %% 256 == 0 (N=%d)", N);
+    return launch<256, 4, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s);
+  }
   if (c_dtype == OI_BF16) {
     if (tile_n == 256) return launch<256, 4, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
     return launch<128, 6, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
@@ -334,7 +418,8 @@ OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, l
 }
 
 // 0 when no bounded wait has run out since the last call; otherwise which role gave up
-// (1 producer, 2 MMA issuer, 3 epilogue). Synchronises the device; clears the word.
+// (1 producer, 2 MMA issuer waiting for operands, 3 epilogue, 4 MMA issuer waiting for a drained
+// accumulator). Synchronises the device; clears the word.
 OI_API int oi_gemm_tcgen05_status(int* status) {
   int v = 0;
   OI_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)));

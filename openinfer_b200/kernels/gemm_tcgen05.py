@@ -10,7 +10,9 @@ from . import lib as _lib
 from .lib import KernelError
 
 _lib.declare("oi_gemm_tcgen05", [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
-                                 c_int, c_int, c_int, c_int, c_void_p])
+                                 c_int, c_int, c_int, c_int, c_int, c_void_p])
+
+ACT_BLOCK = 128   # gate rows per tile half of the fused gate/up product
 _lib.declare("oi_gemm_tcgen05_status", [ctypes.POINTER(c_int)])
 
 
@@ -33,8 +35,22 @@ def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256)
         raise KernelError(f"gemm_tcgen05: operands not accepted: x={tuple(x.shape)} w={tuple(w.shape)} out={tuple(out.shape)}")
     L = _lib.load()
     _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, tile_n,
+                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, tile_n, 0,
                                  torch.cuda.current_stream().cuda_stream), "gemm_tcgen05")
+    return out
+
+
+def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """out[M, I] = silu(x Wg^T) * (x Wu^T) in one kernel. ``w_gate_up`` is [2 I, K] with rows in blocks
+    of 128 gate rows followed by the 128 up rows of the same indices (I a multiple of 128)."""
+    M, K = x.shape
+    N = w_gate_up.shape[0]
+    if N % (2 * ACT_BLOCK) or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or not takes(out, x, w_gate_up):
+        raise KernelError(f"gemm_silu_mul: operands not accepted: x={tuple(x.shape)} w={tuple(w_gate_up.shape)} out={tuple(out.shape)}")
+    L = _lib.load()
+    _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w_gate_up.data_ptr(),
+                                 w_gate_up.stride(0), M, N, K, 256, 1, torch.cuda.current_stream().cuda_stream),
+               "gemm_tcgen05 (fused activation)")
     return out
 
 

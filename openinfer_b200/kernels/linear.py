@@ -60,7 +60,7 @@ def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
     return valid[-1]
 
 
-def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool) -> bool:
+def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) -> bool:
     """The hand-written weight-streaming kernel, when it takes the shape."""
     global _SM_COUNT
     M, N = x.shape[0], w.shape[0]
@@ -80,21 +80,22 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool)
         c = _FORCE_C
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 1 if silu_mul else 0, c,
+                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, int(silu_mul), c,
                                 1 if USE_PDL else 0, torch.cuda.current_stream().cuda_stream), "gemm_skinny")
     return True
 
 
-def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """(silu(gate) * up) W^T for a fused [M, 2K] gate|up buffer and w [N, K]. For a few rows the
-    activation is formed inside the product kernel; otherwise by its own kernel first."""
+def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
+    """(silu(gate) * up) W^T for a fused [M, 2K] gate|up buffer (blocks of ``block`` gates then
+    their ups; default all gates, then all ups) and w [N, K]."""
     M, K = gate_up.shape[0], w.shape[1]
+    block = K if block is None else block
     if FUSE_SILU_MUL and gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS:
         out = torch.empty((M, w.shape[0]), dtype=gate_up.dtype, device=gate_up.device)
-        if _skinny(out, gate_up, w, True):
+        if _skinny(out, gate_up, w, block):
             return out
     act = torch.empty((M, K), dtype=gate_up.dtype, device=gate_up.device)
-    ops.silu_mul(act, gate_up)
+    ops.silu_mul(act, gate_up, block)
     return linear(act, w)
 
 
@@ -112,7 +113,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if _bf16_gemm is not None and _bf16_gemm(out, x, w):
             return out
-        if M <= SKINNY_MAX_ROWS and _skinny(out, x, w, False):
+        if M <= SKINNY_MAX_ROWS and _skinny(out, x, w, 0):
             return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)

@@ -93,14 +93,16 @@ def add_inplace(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
-    """out[r, i] = silu(gate_up[r, i]) * gate_up[r, inter + i]"""
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
+    """out[r, i] = silu(gate_i) * up_i for a fused gate|up buffer [rows, 2 * inter] laid out in
+    blocks of ``block`` gate values followed by their up values (default: all gates, then all ups)."""
     _cuda(out, gate_up)
     rows, inter = out.shape
+    block = inter if block is None else int(block)
     if gate_up.shape != (rows, 2 * inter) or out.dtype != gate_up.dtype or not (out.is_contiguous() and gate_up.is_contiguous()):
         raise KernelError(f"silu_mul: shapes out={tuple(out.shape)} gate_up={tuple(gate_up.shape)}")
     L = _lib.load()
-    _lib.check(L.oi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _code(out, "silu_mul"), rows, inter, _stream()), "silu_mul")
+    _lib.check(L.oi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _code(out, "silu_mul"), rows, inter, block, _stream()), "silu_mul")
     return out
 
 

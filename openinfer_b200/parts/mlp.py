@@ -10,7 +10,11 @@ from typing import Dict, Optional
 
 import torch
 
+from ..kernels import gemm_tcgen05
 from ..kernels.linear import linear, linear_silu_mul
+
+# rows from which the gate/up product with the activation in its epilogue is used (prompt portions)
+FUSED_MIN_ROWS = 128
 from .base import FeedForward
 from .registry import register_feed_forward
 from .spec import GatedMlpSpec, ParamInfo
@@ -37,9 +41,21 @@ class GatedMlp(FeedForward):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if g.dtype != u.dtype:
             raise ValueError("gate_proj and up_proj must be stored in one dtype to be fused")
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        inter = self.spec.intermediate_size
+        # Rows of the fused matrix: blocks of `block` gate rows followed by the up rows of the same
+        # indices. With block = 128 a 256-row tile of the tensor-core product holds a gate block and
+        # its up block side by side, and the activation is formed in that kernel's epilogue.
+        self.block = gemm_tcgen05.ACT_BLOCK if (g.dtype == torch.bfloat16 and inter % gemm_tcgen05.ACT_BLOCK == 0) else inter
+        nb = inter // self.block
+        self.w_gate_up = torch.stack([g.view(nb, self.block, -1), u.view(nb, self.block, -1)], dim=1).reshape(2 * inter, -1).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        inter = self.spec.intermediate_size
+        if (self.block == gemm_tcgen05.ACT_BLOCK and x.shape[0] >= FUSED_MIN_ROWS and x.dtype == torch.bfloat16):
+            act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
+            if gemm_tcgen05.takes(act, x, self.w_gate_up):
+                gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up)
+                return linear(act, self.w_down)
         gate_up = linear(x, self.w_gate_up)
-        return linear_silu_mul(gate_up, self.w_down)
+        return linear_silu_mul(gate_up, self.w_down, self.block)

@@ -515,3 +515,34 @@ def test_gemm_tcgen05(M, N, K, tile_n):
     g.gemm(out, big[:, :K], w, tile_n)
     assert g.status() == 0
     assert (out.double() - big[:, :K].double() @ w.double().t()).abs().max().item() <= 1e-4 * scale
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 384, 200), (2048, 1024, 512)])
+def test_gemm_tcgen05_with_activation_in_the_epilogue(M, I, K):
+    """silu(x Wg^T) * (x Wu^T) from one kernel, gate and up rows interleaved in blocks of 128."""
+    from openinfer_b200.kernels import gemm_tcgen05 as g
+    torch.manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    wg = (torch.randn(I, K, device=DEV) * 0.1).to(torch.bfloat16)
+    wu = (torch.randn(I, K, device=DEV) * 0.1).to(torch.bfloat16)
+    nb = I // 128
+    w = torch.stack([wg.view(nb, 128, K), wu.view(nb, 128, K)], dim=1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    g.gemm_silu_mul(out, x, w)
+    assert g.status() == 0
+    gg, uu = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    assert (out.double() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul_block_layout(dtype):
+    from openinfer_b200.kernels import ops
+    rows, inter, block = 5, 384, 128
+    g = (torch.randn(rows, inter, device=DEV) * 2).to(dtype)
+    u = torch.randn(rows, inter, device=DEV).to(dtype)
+    gu = torch.stack([g.view(rows, -1, block), u.view(rows, -1, block)], dim=2).reshape(rows, 2 * inter).contiguous()
+    out = torch.empty(rows, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(out, gu, block)
+    ref = g.float() / (1 + torch.exp(-g.float())) * u.float()
+    assert torch.allclose(out.float(), ref, **tol(dtype))
