@@ -18,7 +18,6 @@
 
 namespace {
 
-constexpr int kRows = 64;      // query rows per CTA
 constexpr int kKeys = 64;      // keys per tile
 constexpr int kThreads = 128;
 
@@ -94,12 +93,17 @@ __device__ __forceinline__ void load_tile(bf16* smem, const bf16* cache, const A
   }
 }
 
-template <int HD>
+// MT: 16-row slabs per warp. MT = 2 (128 rows per CTA) lets every K/V fragment read from shared
+// memory feed two MMAs, which halves the shared-memory traffic per flop: the version for prompt
+// portions. MT = 1 (64 rows per CTA) wastes less on short portions.
+template <int HD, int MT>
 __global__ void __launch_bounds__(kThreads)
 attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  // [stage][K | V][kKeys][HD]
-  bf16* const tiles = reinterpret_cast<bf16*>(smem_raw);
+  constexpr int kTileRows = 64 * MT;
+  // [Q: kTileRows x HD][stage][K | V][kKeys][HD]
+  bf16* const q_sm = reinterpret_cast<bf16*>(smem_raw);
+  bf16* const tiles = q_sm + kTileRows * HD;
   auto k_tile = [&](int stage) { return tiles + (size_t)stage * 2 * kKeys * HD; };
   auto v_tile = [&](int stage) { return tiles + (size_t)stage * 2 * kKeys * HD + kKeys * HD; };
 
@@ -112,13 +116,13 @@ attention_mma_kernel(const AttnParams p) {
   const int q_len = p.cu_seqlens[req + 1] - q_start;
   const int kv_len = p.kv_lens[req];
   const int* bt = p.block_table + (size_t)req * p.bt_stride;
-  const int toks_per_tile = kRows / group;
+  const int toks_per_tile = kTileRows / group;
   const int tile_toks = min(toks_per_tile, q_len - tok0);
   const int pos0 = kv_len - q_len + tok0;                 // position of the tile's first token
   // keys any row of the tile may see
   int lo = 0;
   if (p.window > 0) lo = max(0, pos0 - p.window + 1);
-  int hi = pos0 + tile_toks;                              // exclusive: last token's own key included
+  const int hi = pos0 + tile_toks;                        // exclusive: last token's own key included
   lo &= ~(kKeys - 1);
   // this item's slice of [lo, hi), in whole tiles
   const int span_tiles = (hi - lo + kKeys - 1) / kKeys;
@@ -126,52 +130,60 @@ attention_mma_kernel(const AttnParams p) {
   const int t_begin = split * tiles_per_split;
   const int t_end = min(span_tiles, t_begin + tiles_per_split);
 
-  // ---- the two rows this thread owns in its warp's 16-row slab
-  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
-  int tok[2], head[2], pos[2];
-  bool row_ok[2];
+  // ---- Q tile into shared memory (rows = (token, head) pairs; rows past the tile are zero)
   {
-    const int rr[2] = {r_lo, r_hi};
+    constexpr int kChunks = HD / 8;
+    for (int i = threadIdx.x; i < kTileRows * kChunks; i += kThreads) {
+      const int r = i / kChunks, chunk = i % kChunks;
+      const int t = r / group;
+      const bool valid = t < tile_toks;
+      const bf16* src = p.q;
+      if (valid) src = p.q + (size_t)(q_start + tok0 + t) * p.q_row_stride + (size_t)(kvh * group + r % group) * HD + chunk * 8;
+      cp_async16(smem_u32(q_sm + tile_offset<HD>(r, chunk)), src, valid);
+    }
+    cp_async_commit();
+  }
+
+  // ---- the rows this thread owns: slab mt, halves i: row = warp*16*MT + mt*16 + lane/4 + 8*i
+  const int warp_row0 = warp * 16 * MT;
+  int pos[MT][2];
+  bool row_ok[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const int t = rr[i] / group;
-      tok[i] = tok0 + t;
-      head[i] = kvh * group + rr[i] % group;
-      row_ok[i] = t < tile_toks;
-      pos[i] = pos0 + t;
+      const int r = warp_row0 + mt * 16 + (lane >> 2) + 8 * i;
+      const int t = r / group;
+      row_ok[mt][i] = t < tile_toks;
+      pos[mt][i] = pos0 + t;
     }
-  }
+  // the last position any row of this warp holds: tiles beyond it are skipped by this warp
+  const int warp_last_pos = pos0 + min(tile_toks - 1, (warp_row0 + 16 * MT - 1) / group);
+  const int warp_first_pos = pos0 + warp_row0 / group;
+  const bool warp_active = warp_row0 < tile_toks * group;
 
-  // ---- Q fragments straight from global memory (A operand, row-major)
   constexpr int kSteps = HD / 16;
-  unsigned qf[kSteps][4];
-  {
-    const int col = (lane & 3) * 2;
-#pragma unroll
-    for (int ks = 0; ks < kSteps; ++ks) {
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        unsigned a = 0, b = 0;
-        if (row_ok[i]) {
-          const bf16* qp = p.q + (size_t)(q_start + tok[i]) * p.q_row_stride + (size_t)head[i] * HD + ks * 16 + col;
-          a = *reinterpret_cast<const unsigned*>(qp);
-          b = *reinterpret_cast<const unsigned*>(qp + 8);
-        }
-        qf[ks][i] = a;        // rows r_lo (i=0) / r_hi (i=1), cols ks*16 + col
-        qf[ks][i + 2] = b;    // same rows, cols + 8
-      }
-    }
-  }
-
   constexpr int kOTiles = HD / 8;
-  float o[kOTiles][4];
+  float o[MT][kOTiles][4];
 #pragma unroll
-  for (int j = 0; j < kOTiles; ++j)
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  // a warp whose 16 rows are all beyond the tile's tokens (decode: group rows of 64) only helps loading
-  const bool warp_active = warp * 16 < tile_toks * group;
+    for (int j = 0; j < kOTiles; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[mt][j][e] = 0.f;
+  float m[MT][2], l[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) { m[mt][0] = m[mt][1] = -INFINITY; l[mt][0] = l[mt][1] = 0.f; }
+
+  // ldmatrix lane constants (element offsets; chunk indices enter through one XOR)
+  const int lm_mat = lane >> 3, lm_rin = lane & 7;
+  const int q_row = (lm_mat & 1) * 8 + lm_rin;              // A operand: matrices 0,2 rows 0-7; 1,3 rows 8-15
+  const int q_swz_hi = lm_mat >> 1;                         // chunk = 2 ks + (mat >> 1)
+  const int k_row = (lm_mat >> 1) * 8 + lm_rin;             // K: matrices 0,1 keys 0-7; 2,3 keys 8-15
+  const int k_swz = (lm_mat & 1) ^ (k_row & 7);             // chunk = 2 ks + (mat & 1)
+  const int v_row = (lm_mat & 1) * 8 + lm_rin;              // V: matrices 0,2 keys 0-7; 1,3 keys 8-15
+  const int v_swz = (lm_mat >> 1) ^ (v_row & 7);            // chunk = j + (mat >> 1)
+  constexpr int kMask = HD / 8 - 1;
 
   if (t_begin < t_end) {
     load_tile<HD>(k_tile(0), p.k_cache, p, bt, kvh, lo + t_begin * kKeys, hi);
@@ -188,125 +200,154 @@ attention_mma_kernel(const AttnParams p) {
       cp_async_commit();
       load_tile<HD>(v_tile(buf ^ 1), p.v_cache, p, bt, kvh, key0 + kKeys, hi);
       cp_async_commit();
-      cp_async_wait<3>();   // K of this tile has landed
+      cp_async_wait<3>();   // Q and K of this tile have landed
     } else {
       cp_async_wait<1>();
     }
     __syncthreads();
 
-    unsigned pf[kKeys / 16][4];
-    if (warp_active) {
-      // ---- S = Q K^T : 16 rows x 64 keys per warp
-      float s[kKeys / 8][4];
-  #pragma unroll
-      for (int j = 0; j < kKeys / 8; ++j)
-  #pragma unroll
-        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+    // a warp all of whose rows lie before this tile's first key has nothing to do here
+    const bool compute = warp_active && key0 <= warp_last_pos;
+    unsigned pf[MT][kKeys / 16][4];
+    if (compute) {
+      // ---- S = Q K^T : 16*MT rows x 64 keys per warp
+      float s[MT][kKeys / 8][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < kKeys / 8; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[mt][j][e] = 0.f;
       {
-        const bf16* ks_ = k_tile(buf);
-        // ldmatrix x4: matrices (keys j*8.., d ks*16..+7), (same keys, d +8), (keys (j+1)*8.., d..), (.., d+8)
-        const int mat = lane >> 3, rin = lane & 7;
-  #pragma unroll
+        const unsigned kbase = smem_u32(k_tile(buf));
+        const unsigned qbase = smem_u32(q_sm);
+#pragma unroll
         for (int ks = 0; ks < kSteps; ++ks) {
-  #pragma unroll
+          unsigned qf[MT][4];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const int r = warp_row0 + mt * 16 + q_row;
+            ldmatrix_x4(qf[mt][0], qf[mt][1], qf[mt][2], qf[mt][3],
+                        qbase + (r * HD + ((((ks * 2) ^ q_swz_hi ^ (r & 7)) & kMask) * 8)) * 2);
+          }
+#pragma unroll
           for (int j = 0; j < kKeys / 8; j += 2) {
-            const int row = (j + (mat >> 1)) * 8 + rin;
-            const int chunk = ks * 2 + (mat & 1);
-            unsigned b0, b1, b2, b3;
-            ldmatrix_x4(b0, b1, b2, b3, smem_u32(ks_ + tile_offset<HD>(row, chunk)));
-            mma_bf16(s[j], qf[ks], b0, b1);
-            mma_bf16(s[j + 1], qf[ks], b2, b3);
+            unsigned b0, b1, b2, b3;   // (keys j*8.., d lo), (same keys, d hi), (keys (j+1)*8.., d lo), (.., d hi)
+            ldmatrix_x4(b0, b1, b2, b3, kbase + ((j * 8 + k_row) * HD + ((((ks * 2) ^ k_swz) & kMask) * 8)) * 2);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              mma_bf16(s[mt][j], qf[mt], b0, b1);
+              mma_bf16(s[mt][j + 1], qf[mt], b2, b3);
+            }
           }
         }
       }
-      // ---- mask + online softmax (rows r_lo: s[.][0..1], r_hi: s[.][2..3])
-      float m_new[2] = {m[0], m[1]};
-  #pragma unroll
-      for (int j = 0; j < kKeys / 8; ++j) {
-  #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = e >> 1;
-          const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-          const bool ok = row_ok[i] && key <= pos[i] && (p.window <= 0 || key > pos[i] - p.window);
-          s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
-          m_new[i] = fmaxf(m_new[i], s[j][e]);
+      // ---- mask (only where a row may not see the whole tile) + online softmax
+      const bool full = key0 + kKeys - 1 <= warp_first_pos && (p.window <= 0 || key0 > warp_last_pos - p.window) &&
+                        warp_row0 + 16 * MT <= tile_toks * group;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        float m_new[2] = {m[mt][0], m[mt][1]};
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < kKeys / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              s[mt][j][e] *= p.scale_log2;
+              m_new[e >> 1] = fmaxf(m_new[e >> 1], s[mt][j][e]);
+            }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kKeys / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = e >> 1;
+              const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+              const bool ok = row_ok[mt][i] && key <= pos[mt][i] && (p.window <= 0 || key > pos[mt][i] - p.window);
+              s[mt][j][e] = ok ? s[mt][j][e] * p.scale_log2 : -INFINITY;
+              m_new[i] = fmaxf(m_new[i], s[mt][j][e]);
+            }
+        }
+        float corr[2], base[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
+          m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
+          corr[i] = (m[mt][i] == -INFINITY) ? 0.f : exp2f(m[mt][i] - m_new[i]);
+          l[mt][i] *= corr[i];
+          base[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];
+          m[mt][i] = m_new[i];
+        }
+#pragma unroll
+        for (int j = 0; j < kKeys / 8; ++j) {
+          const float p0 = exp2f(s[mt][j][0] - base[0]), p1 = exp2f(s[mt][j][1] - base[0]);
+          const float p2 = exp2f(s[mt][j][2] - base[1]), p3 = exp2f(s[mt][j][3] - base[1]);
+          l[mt][0] += p0 + p1;
+          l[mt][1] += p2 + p3;
+          // accumulator tiles (2i, 2i+1) are the A fragment of key step i
+          pf[mt][j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+          pf[mt][j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        if (!__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f)) {
+#pragma unroll
+          for (int j = 0; j < kOTiles; ++j) {
+            o[mt][j][0] *= corr[0]; o[mt][j][1] *= corr[0];
+            o[mt][j][2] *= corr[1]; o[mt][j][3] *= corr[1];
+          }
         }
       }
-      float corr[2];
-  #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
-        m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-        corr[i] = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - m_new[i]);
-        l[i] *= corr[i];
-      }
-      const float base[2] = {m_new[0] == -INFINITY ? 0.f : m_new[0], m_new[1] == -INFINITY ? 0.f : m_new[1]};
-  #pragma unroll
-      for (int j = 0; j < kKeys / 8; ++j) {
-        const float p0 = exp2f(s[j][0] - base[0]), p1 = exp2f(s[j][1] - base[0]);
-        const float p2 = exp2f(s[j][2] - base[1]), p3 = exp2f(s[j][3] - base[1]);
-        l[0] += p0 + p1;
-        l[1] += p2 + p3;
-        // accumulator tiles (2i, 2i+1) are the A fragment of key step i
-        pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
-        pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
-      }
-  #pragma unroll
-      for (int j = 0; j < kOTiles; ++j) {
-        o[j][0] *= corr[0]; o[j][1] *= corr[0];
-        o[j][2] *= corr[1]; o[j][3] *= corr[1];
-      }
-      m[0] = m_new[0];
-      m[1] = m_new[1];
     }
 
     if (more) cp_async_wait<2>(); else cp_async_wait<0>();   // V of this tile has landed
     __syncthreads();
     // ---- O += P V : k = 64 keys (4 steps), n = HD
-    if (warp_active) {
-      const bf16* vs_ = v_tile(buf);
-      const int mat = lane >> 3, rin = lane & 7;
+    if (compute) {
+      const unsigned vbase = smem_u32(v_tile(buf));
 #pragma unroll
       for (int kk = 0; kk < kKeys / 16; ++kk) {
 #pragma unroll
         for (int j = 0; j < kOTiles; j += 2) {
-          // matrices: (keys kk*16.., d j*8..), (keys +8, d j*8..), (keys kk*16.., d (j+1)*8..), (keys +8, ..)
-          const int row = kk * 16 + (mat & 1) * 8 + rin;
-          const int chunk = j + (mat >> 1);
-          unsigned b0, b1, b2, b3;
-          ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(vs_ + tile_offset<HD>(row, chunk)));
-          mma_bf16(o[j], pf[kk], b0, b1);
-          mma_bf16(o[j + 1], pf[kk], b2, b3);
+          unsigned b0, b1, b2, b3;   // (keys kk*16.., d j*8..), (keys +8, same d), (keys kk*16.., d (j+1)*8..), (keys +8, ..)
+          ldmatrix_x4_trans(b0, b1, b2, b3, vbase + ((kk * 16 + v_row) * HD + (((j ^ v_swz) & kMask) * 8)) * 2);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_bf16(o[mt][j], pf[mt][kk], b0, b1);
+            mma_bf16(o[mt][j + 1], pf[mt][kk], b2, b3);
+          }
         }
       }
     }
     __syncthreads();  // everyone is done with this buffer before the next prefetch overwrites it
   }
+  cp_async_wait<0>();
 
   // ---- epilogue
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
-    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
-  }
   const int col = (lane & 3) * 2;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    if (!row_ok[i]) continue;
-    const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
-    const size_t grow = (size_t)(q_start + tok[i]);
-    if (nsplits == 1) {
-      bf16* op = p.out + grow * p.out_row_stride + (size_t)head[i] * HD + col;
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-      for (int j = 0; j < kOTiles; ++j)
-        *reinterpret_cast<unsigned*>(op + j * 8) = pack_bf16(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
-    } else {
-      const size_t slot = (grow * p.nq + head[i]) * p.max_splits + split;
-      float* op = p.part_o + slot * HD + col;
+    for (int i = 0; i < 2; ++i) {
+      float li = l[mt][i];
+      li += __shfl_xor_sync(0xffffffffu, li, 1);
+      li += __shfl_xor_sync(0xffffffffu, li, 2);
+      if (!row_ok[mt][i]) continue;
+      const int r = warp_row0 + mt * 16 + (lane >> 2) + 8 * i;
+      const int head = kvh * group + r % group;
+      const size_t grow = (size_t)(q_start + tok0 + r / group);
+      const float inv = li > 0.f ? 1.f / li : 0.f;
+      if (nsplits == 1) {
+        bf16* op = p.out + grow * p.out_row_stride + (size_t)head * HD + col;
 #pragma unroll
-      for (int j = 0; j < kOTiles; ++j)
-        *reinterpret_cast<float2*>(op + j * 8) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
-      if ((lane & 3) == 0) p.part_lse[slot] = l[i] > 0.f ? m[i] + log2f(l[i]) : -INFINITY;  // base-2 log-sum-exp
+        for (int j = 0; j < kOTiles; ++j)
+          *reinterpret_cast<unsigned*>(op + j * 8) = pack_bf16(o[mt][j][2 * i] * inv, o[mt][j][2 * i + 1] * inv);
+      } else {
+        const size_t slot = (grow * p.nq + head) * p.max_splits + split;
+        float* op = p.part_o + slot * HD + col;
+#pragma unroll
+        for (int j = 0; j < kOTiles; ++j)
+          *reinterpret_cast<float2*>(op + j * 8) = make_float2(o[mt][j][2 * i] * inv, o[mt][j][2 * i + 1] * inv);
+        if ((lane & 3) == 0) p.part_lse[slot] = li > 0.f ? m[mt][i] + log2f(li) : -INFINITY;  // base-2 log-sum-exp
+      }
     }
   }
 }
@@ -607,17 +648,25 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_strid
   for (int e = 0; e < kPer; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
 }
 
-template <int HD>
-int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens, int any_split, cudaStream_t s) {
-  constexpr int smem = 4 * kKeys * HD * (int)sizeof(bf16);
+template <int HD, int MT>
+int launch_tiles(const AttnParams& p, int num_items, cudaStream_t s) {
+  constexpr int smem = (64 * MT + 4 * kKeys) * HD * (int)sizeof(bf16);
   static bool configured = false;
   if (!configured) {
-    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
   dim3 grid(num_items, p.nkv);
-  attention_mma_kernel<HD><<<grid, kThreads, smem, s>>>(p);
+  attention_mma_kernel<HD, MT><<<grid, kThreads, smem, s>>>(p);
   OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+template <int HD>
+int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens, int any_split, int rows_per_cta,
+           cudaStream_t s) {
+  const int rc = rows_per_cta == 128 ? launch_tiles<HD, 2>(p, num_items, s) : launch_tiles<HD, 1>(p, num_items, s);
+  if (rc) return rc;
   if (any_split) {
     const long long warps = (long long)tokens * p.nq;
     attention_merge_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(
@@ -681,7 +730,7 @@ OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int o
 }
 
 // items: int32 [num_items, 4] = (request, first token of the tile, split, nsplits), planned by the
-// host. row_splits: int32 [tokens], the number of slices each row's keys were cut into.
+// host for tiles of rows_per_cta (64 or 128) query rows = rows_per_cta / group tokens. row_splits: int32 [tokens], the number of slices each row's keys were cut into.
 // part_o: float32 [tokens * nq * max_splits * hd], part_lse: float32 [tokens * nq * max_splits]
 // (only touched by rows with more than one slice).
 OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
@@ -689,9 +738,10 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
                             int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
                             int num_items, const int* row_splits, int tokens, int any_split, int nq, int nkv,
                             int hd, float scale, int window, float* part_o, float* part_lse, int max_splits,
-                            void* stream) {
+                            int rows_per_cta, void* stream) {
+  OI_REQUIRE(rows_per_cta == 64 || rows_per_cta == 128, "attention_mma: rows_per_cta %d (64 or 128)", rows_per_cta);
   OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_mma: head_dim %d not covered (32, 64 or 128)", hd);
-  OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= kRows, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
+  OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= rows_per_cta, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
   OI_REQUIRE(q_row_stride % 2 == 0 && out_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_mma: misaligned strides");
   OI_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
              "attention_mma: misaligned pointers");
@@ -709,7 +759,7 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
   p.window = window;
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
   cudaStream_t s = (cudaStream_t)stream;
-  if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, s);
-  if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, s);
-  return launch<128>(p, num_items, row_splits, tokens, any_split, s);
+  if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
+  if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
+  return launch<128>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
 }

@@ -45,11 +45,12 @@ from . import lib as _lib  # noqa: E402
 
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 _lib.declare("oi_attention_mma", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I,
-                                  _F, _I, _P, _P, _I, _P])
+                                  _F, _I, _P, _P, _I, _I, _P])
 _lib.declare("oi_attention_decode", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I,
                                      _F, _I, _P, _P, _I, _P])
 
-ROWS_PER_CTA = 64
+ROWS_PER_CTA = 64          # query rows (tokens x group) of a small tile
+ROWS_PER_CTA_LARGE = 128   # of a large tile, used when some portion fills one
 KEYS_PER_TILE = 64
 MAX_SPLITS = 16            # slices of a prompt tile's keys
 MIN_TILES_PER_SPLIT = 2    # such a slice is at least 128 keys long
@@ -75,6 +76,7 @@ class AttentionPlan:
     decode_items: torch.Tensor    # int32 [n, 4]: request, 0, first slice of the CTA, slices
     num_decode_items: int
     row_splits: torch.Tensor      # int32 [tokens]
+    rows_per_cta: int             # 64 or 128 query rows per tile
     tile_split: bool              # some prompt tile was cut into slices (merged after the tile kernel)
     max_splits: int
     part_o: Optional[torch.Tensor]
@@ -92,17 +94,26 @@ def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[i
     return ns
 
 
+def tile_rows(q_lens, group: int, decode_kernel: bool = True) -> int:
+    """Query rows per tile: 128 when some prompt portion fills such a tile, else 64."""
+    big = [n for n in q_lens if not (decode_kernel and n == 1 and group <= DECODE_MAX_GROUP)]
+    if group <= ROWS_PER_CTA and any(n * group >= ROWS_PER_CTA_LARGE for n in big):
+        return ROWS_PER_CTA_LARGE
+    return ROWS_PER_CTA if group <= ROWS_PER_CTA else ROWS_PER_CTA_LARGE
+
+
 def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_count: int,
-               decode_kernel: bool = True):
+               decode_kernel: bool = True, rows_per_cta: Optional[int] = None):
     """Work items of one step.
 
     Requests that bring one token go to the decode kernel (when the group fits its 16 rows):
     each row's keys are cut into ``decode_splits`` slices, four per CTA. The others are cut
-    into query tiles (64 rows = 64 // group tokens times `group` heads) for the tile kernel;
+    into query tiles (``rows_per_cta`` rows = rows // group tokens times `group` heads) for the tile kernel;
     when that grid would leave SMs idle and there are no decode rows, a tile's keys are cut
     into slices too. Returns (tile_items [n, 4], decode_items [n, 4], row_splits [tokens],
     max_splits, tile_split)."""
-    tpt = ROWS_PER_CTA // group
+    rows_per_cta = rows_per_cta or tile_rows(q_lens, group, decode_kernel)
+    tpt = rows_per_cta // group
     starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int64)
     row_splits = np.ones(int(starts[-1]), dtype=np.int32)
     use_decode = decode_kernel and group <= DECODE_MAX_GROUP
@@ -164,11 +175,13 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
     plan = ctx.scratch.get(key)
     if plan is None:
         if getattr(ctx, "static_decode", False):
+            rows = ROWS_PER_CTA if group <= ROWS_PER_CTA else ROWS_PER_CTA_LARGE
             t_items, d_items, row_splits, max_splits, tile_split = plan_items_static_decode(
                 ctx.num_requests, group, nkv, _sm_count(device))
         else:
+            rows = tile_rows(ctx.q_lens_host, group)
             t_items, d_items, row_splits, max_splits, tile_split = plan_items(
-                ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window, _sm_count(device))
+                ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window, _sm_count(device), rows_per_cta=rows)
         packed = np.concatenate([t_items.reshape(-1), d_items.reshape(-1), row_splits])
         dev = torch.from_numpy(packed).to(device, non_blocking=True)
         nt, nd = t_items.shape[0], d_items.shape[0]
@@ -177,14 +190,14 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
             part_o = torch.empty(ctx.num_tokens * nq * max_splits * hd, dtype=torch.float32, device=device)
             part_lse = torch.empty(ctx.num_tokens * nq * max_splits, dtype=torch.float32, device=device)
         plan = AttentionPlan(dev[: nt * 4].view(nt, 4), nt, dev[nt * 4: (nt + nd) * 4].view(nd, 4), nd,
-                             dev[(nt + nd) * 4:], tile_split, max_splits, part_o, part_lse)
+                             dev[(nt + nd) * 4:], rows, tile_split, max_splits, part_o, part_lse)
         ctx.scratch[key] = plan
     return plan
 
 
 def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window) -> bool:
     """The tensor-core kernels, when they cover the shape: bfloat16, head_dim 32, 64 or 128."""
-    if q.dtype != torch.bfloat16 or hd not in (32, 64, 128) or nq // nkv > ROWS_PER_CTA:
+    if q.dtype != torch.bfloat16 or hd not in (32, 64, 128) or nq // nkv > ROWS_PER_CTA_LARGE:
         return False
     if q.stride(0) % 2 or page_stride % 8:
         return False
@@ -201,7 +214,7 @@ def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nk
             int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
             group_step.kv_lens.data_ptr(), plan.tile_items.data_ptr(), plan.num_tile_items,
             plan.row_splits.data_ptr(), out.shape[0], 1 if plan.tile_split else 0, nq, nkv, hd, float(scale), win,
-            po, pl, plan.max_splits, stream), "attention_mma")
+            po, pl, plan.max_splits, plan.rows_per_cta, stream), "attention_mma")
     if plan.num_decode_items:
         _lib.check(L.oi_attention_decode(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),

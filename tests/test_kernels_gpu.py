@@ -372,12 +372,12 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
     if force_splits:
         old = A.plan_items
 
-        def forced(ql, kl, group, nkv_, window_, sm, decode_kernel=True):
+        def forced(ql, kl, group, nkv_, window_, sm, decode_kernel=True, rows_per_cta=None):
             if force_splits == "tiles":     # decode rows through the tile kernel, cut into slices
-                return old(ql, kl, group, nkv_, window_, 10 ** 6, decode_kernel=False)
+                return old(ql, kl, group, nkv_, window_, 10 ** 6, decode_kernel=False, rows_per_cta=rows_per_cta)
             if force_splits == "tiles_whole":
-                return old(ql, kl, group, nkv_, window_, 1, decode_kernel=False)
-            return old(ql, kl, group, nkv_, window_, 10 ** 6 if force_splits == "max" else 1)
+                return old(ql, kl, group, nkv_, window_, 1, decode_kernel=False, rows_per_cta=rows_per_cta)
+            return old(ql, kl, group, nkv_, window_, 10 ** 6 if force_splits == "max" else 1, rows_per_cta=rows_per_cta)
         A.plan_items = forced
     try:
         out = torch.full((T, nq * hd), float("nan"), device=DEV, dtype=dtype)
@@ -409,7 +409,11 @@ def test_attention_mma_mixed_batch(nq, nkv, hd, P, window):
     """Prompt portions over cached prefixes beside single decoded tokens, in one launch."""
     q_lens = [9, 1, 70, 1, 33, 2]
     kv_lens = [70, 131, 70, 1, 300, 65]
-    _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens)
+    plan = _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens)
+    assert plan.rows_per_cta == (128 if 70 * (nq // nkv) >= 128 else 64)
+    # short portions only: the small tile
+    plan = _mma_case(nq, nkv, hd, P, window, [3, 1, 2], [70, 131, 300])
+    assert plan.rows_per_cta == (64 if 3 * (nq // nkv) < 128 else 128)
 
 
 @pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 128), (6, 2, 32), (8, 1, 64)])
