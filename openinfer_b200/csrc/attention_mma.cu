@@ -59,6 +59,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (x <= 0 here; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -72,20 +78,24 @@ __device__ __forceinline__ int tile_offset(int row, int chunk) {
   return row * HD + ((chunk ^ (row & 7)) & (kChunks - 1)) * 8 + ((chunk & ~(kChunks - 1)) * 8);
 }
 
+// The page that holds this thread's key row of the tile starting at key0 (-1 beyond key_end).
+// Looked up one tile ahead of its use, so that the copies are not held up by the table read.
+__device__ __forceinline__ int tile_page(const AttnParams& p, const int* bt, int key0, int key_end) {
+  const int key = key0 + (threadIdx.x >> 1);
+  return key < key_end ? bt[key / p.page_size] : -1;
+}
+
 template <int HD>
-__device__ __forceinline__ void load_tile(bf16* smem, const bf16* cache, const AttnParams& p, const int* bt,
-                                          int kvh, int key0, int key_end) {
+__device__ __forceinline__ void load_tile(bf16* smem, const bf16* cache, const AttnParams& p, int page,
+                                          int kvh, int key0) {
   // 64 rows x (HD/8) chunks; two threads per row, each HD/16 chunks
   constexpr int kChunks = HD / 8;
   const int row = threadIdx.x >> 1;
   const int c0 = (threadIdx.x & 1) * (kChunks / 2);
   const int key = key0 + row;
-  const bool valid = key < key_end;
+  const bool valid = page >= 0;
   const bf16* src = cache;
-  if (valid) {
-    const int page = bt[key / p.page_size];
-    src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
-  }
+  if (valid) src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
 #pragma unroll
   for (int c = 0; c < kChunks / 2; ++c) {
     const int chunk = c0 + c;
@@ -185,10 +195,13 @@ attention_mma_kernel(const AttnParams p) {
   const int v_swz = (lm_mat >> 1) ^ (v_row & 7);            // chunk = j + (mat >> 1)
   constexpr int kMask = HD / 8 - 1;
 
+  int page_next = -1;      // page of this thread's row in the tile after the one being loaded
   if (t_begin < t_end) {
-    load_tile<HD>(k_tile(0), p.k_cache, p, bt, kvh, lo + t_begin * kKeys, hi);
+    const int page0 = tile_page(p, bt, lo + t_begin * kKeys, hi);
+    page_next = t_begin + 1 < t_end ? tile_page(p, bt, lo + (t_begin + 1) * kKeys, hi) : -1;
+    load_tile<HD>(k_tile(0), p.k_cache, p, page0, kvh, lo + t_begin * kKeys);
     cp_async_commit();
-    load_tile<HD>(v_tile(0), p.v_cache, p, bt, kvh, lo + t_begin * kKeys, hi);
+    load_tile<HD>(v_tile(0), p.v_cache, p, page0, kvh, lo + t_begin * kKeys);
     cp_async_commit();
   }
   for (int t = t_begin; t < t_end; ++t) {
@@ -196,9 +209,11 @@ attention_mma_kernel(const AttnParams p) {
     const int key0 = lo + t * kKeys;
     const bool more = t + 1 < t_end;
     if (more) {
-      load_tile<HD>(k_tile(buf ^ 1), p.k_cache, p, bt, kvh, key0 + kKeys, hi);
+      const int page = page_next;
+      page_next = t + 2 < t_end ? tile_page(p, bt, key0 + 2 * kKeys, hi) : -1;   // used next iteration
+      load_tile<HD>(k_tile(buf ^ 1), p.k_cache, p, page, kvh, key0 + kKeys);
       cp_async_commit();
-      load_tile<HD>(v_tile(buf ^ 1), p.v_cache, p, bt, kvh, key0 + kKeys, hi);
+      load_tile<HD>(v_tile(buf ^ 1), p.v_cache, p, page, kvh, key0 + kKeys);
       cp_async_commit();
       cp_async_wait<3>();   // Q and K of this tile have landed
     } else {
@@ -247,15 +262,14 @@ attention_mma_kernel(const AttnParams p) {
                         warp_row0 + 16 * MT <= tile_toks * group;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
+        // the running maximum m is kept of the RAW scores; the scale enters in one fused
+        // multiply-add per element: p = 2^(s * scale - m * scale)
         float m_new[2] = {m[mt][0], m[mt][1]};
         if (full) {
 #pragma unroll
           for (int j = 0; j < kKeys / 8; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              s[mt][j][e] *= p.scale_log2;
-              m_new[e >> 1] = fmaxf(m_new[e >> 1], s[mt][j][e]);
-            }
+            for (int e = 0; e < 4; ++e) m_new[e >> 1] = fmaxf(m_new[e >> 1], s[mt][j][e]);
         } else {
 #pragma unroll
           for (int j = 0; j < kKeys / 8; ++j)
@@ -264,7 +278,7 @@ attention_mma_kernel(const AttnParams p) {
               const int i = e >> 1;
               const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
               const bool ok = row_ok[mt][i] && key <= pos[mt][i] && (p.window <= 0 || key > pos[mt][i] - p.window);
-              s[mt][j][e] = ok ? s[mt][j][e] * p.scale_log2 : -INFINITY;
+              s[mt][j][e] = ok ? s[mt][j][e] : -INFINITY;
               m_new[i] = fmaxf(m_new[i], s[mt][j][e]);
             }
         }
@@ -273,15 +287,15 @@ attention_mma_kernel(const AttnParams p) {
         for (int i = 0; i < 2; ++i) {
           m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
           m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-          corr[i] = (m[mt][i] == -INFINITY) ? 0.f : exp2f(m[mt][i] - m_new[i]);
+          corr[i] = (m[mt][i] == -INFINITY) ? 0.f : fast_exp2((m[mt][i] - m_new[i]) * p.scale_log2);
           l[mt][i] *= corr[i];
-          base[i] = m_new[i] == -INFINITY ? 0.f : m_new[i];
+          base[i] = m_new[i] == -INFINITY ? 0.f : m_new[i] * p.scale_log2;
           m[mt][i] = m_new[i];
         }
 #pragma unroll
         for (int j = 0; j < kKeys / 8; ++j) {
-          const float p0 = exp2f(s[mt][j][0] - base[0]), p1 = exp2f(s[mt][j][1] - base[0]);
-          const float p2 = exp2f(s[mt][j][2] - base[1]), p3 = exp2f(s[mt][j][3] - base[1]);
+          const float p0 = fast_exp2(fmaf(s[mt][j][0], p.scale_log2, -base[0])), p1 = fast_exp2(fmaf(s[mt][j][1], p.scale_log2, -base[0]));
+          const float p2 = fast_exp2(fmaf(s[mt][j][2], p.scale_log2, -base[1])), p3 = fast_exp2(fmaf(s[mt][j][3], p.scale_log2, -base[1]));
           l[mt][0] += p0 + p1;
           l[mt][1] += p2 + p3;
           // accumulator tiles (2i, 2i+1) are the A fragment of key step i
@@ -346,7 +360,7 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
         for (int j = 0; j < kOTiles; ++j)
           *reinterpret_cast<float2*>(op + j * 8) = make_float2(o[mt][j][2 * i] * inv, o[mt][j][2 * i + 1] * inv);
-        if ((lane & 3) == 0) p.part_lse[slot] = li > 0.f ? m[mt][i] + log2f(li) : -INFINITY;  // base-2 log-sum-exp
+        if ((lane & 3) == 0) p.part_lse[slot] = li > 0.f ? m[mt][i] * p.scale_log2 + log2f(li) : -INFINITY;  // base-2 log-sum-exp
       }
     }
   }

@@ -142,6 +142,8 @@ def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_
         want = min(MAX_SPLITS, -(-2 * sm_count // (len(tiles) * nkv)))
     tile_items = []
     tile_split = False
+    # tiles with the most keys first: the long ones must not be the last to start
+    tiles.sort(key=lambda t: -t[3])
     for b, t0, toks, span_tiles in tiles:
         ns = max(1, min(want, span_tiles // MIN_TILES_PER_SPLIT))
         if ns > 1:

@@ -443,8 +443,9 @@ def test_attention_mma_split_prompt_portion():
 def test_attention_mma_plan():
     from openinfer_b200.kernels.attention import plan_items
     tiles, dec, row_splits, mx, tile_split = plan_items([40, 1], [100, 513], group=4, nkv=8, window=None, sm_count=148)
-    # 40 tokens at 16 per tile: 3 whole tiles; the decode row: 513 keys -> 16 slices of >= 32 keys, 4 per CTA
-    assert sorted((int(i[0]), int(i[1]), int(i[3])) for i in tiles) == [(0, 0, 1), (0, 16, 1), (0, 32, 1)]
+    # 40 tokens x group 4 fill a 128-row tile: 32 tokens per tile, 2 whole tiles;
+    # the decode row: 513 keys -> 16 slices of >= 32 keys, 4 per CTA
+    assert sorted((int(i[0]), int(i[1]), int(i[3])) for i in tiles) == [(0, 0, 1), (0, 32, 1)]
     assert not tile_split and mx == 16 and row_splits.tolist() == [1] * 40 + [16]
     assert [(int(i[0]), int(i[2]), int(i[3])) for i in dec] == [(1, 0, 16), (1, 4, 16), (1, 8, 16), (1, 12, 16)]
     tiles, dec, row_splits, mx, _ = plan_items([1] * 64, [2048] * 64, group=4, nkv=8, window=None, sm_count=148)
