@@ -398,24 +398,30 @@ struct TileLane {
   }
 };
 
-// Copy keys [key0, key0 + 16) of one kv head into a tile; rows at or beyond key_end are zero-filled.
-// `aligned`: the page size is a multiple of 16, so the tile lies in one page (one table lookup).
+// Copy keys [key0, key0 + 16) of one kv head into a K tile and a V tile; rows at or beyond key_end
+// are zero-filled. V lies at a fixed distance from K in the cache (`v_delta` elements).
+// `aligned`: the page size is a multiple of 16, so the tile lies in one page: one table lookup, and
+// (page index, offset in page) are advanced by the caller without a division.
 template <int HD>
-__device__ __forceinline__ void load_tile16(bf16* smem, const bf16* cache, const AttnParams& p, const int* bt,
-                                            int kvh, int key0, int key_end, const TileLane<HD>& tl, bool aligned) {
+__device__ __forceinline__ void load_kv_tile16(bf16* k_smem, bf16* v_smem, const AttnParams& p, const int* bt,
+                                               long long v_delta, int kvh, int key0, int key_end,
+                                               const TileLane<HD>& tl, bool aligned, int pg, int off) {
   constexpr int kPerLane = TileLane<HD>::kPerLane;
-  const unsigned sbase = smem_u32(smem);
+  const unsigned kb = smem_u32(k_smem), vb = smem_u32(v_smem);
   if (aligned) {
-    const int page = bt[key0 / p.page_size];
-    const bf16* base = cache + (size_t)page * p.page_stride + (size_t)(key0 % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
+    const int page = bt[pg];
+    const bf16* base = p.k_cache + (size_t)page * p.page_stride + (size_t)off * p.nkv * HD + (size_t)kvh * HD;
     if (key0 + kDecKeys <= key_end) {
 #pragma unroll
-      for (int i = 0; i < kPerLane; ++i) cp_async16(sbase + tl.smem_off[i] * 2, base + tl.glob_off[i], true);
+      for (int i = 0; i < kPerLane; ++i) cp_async16(kb + tl.smem_off[i] * 2, base + tl.glob_off[i], true);
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i) cp_async16(vb + tl.smem_off[i] * 2, base + v_delta + tl.glob_off[i], true);
     } else {
 #pragma unroll
       for (int i = 0; i < kPerLane; ++i) {
         const bool valid = key0 + tl.row[i] < key_end;
-        cp_async16(sbase + tl.smem_off[i] * 2, valid ? base + tl.glob_off[i] : cache, valid);
+        cp_async16(kb + tl.smem_off[i] * 2, valid ? base + tl.glob_off[i] : p.k_cache, valid);
+        cp_async16(vb + tl.smem_off[i] * 2, valid ? base + v_delta + tl.glob_off[i] : p.k_cache, valid);
       }
     }
   } else {
@@ -423,13 +429,14 @@ __device__ __forceinline__ void load_tile16(bf16* smem, const bf16* cache, const
     for (int i = 0; i < kPerLane; ++i) {
       const int key = key0 + tl.row[i];
       const bool valid = key < key_end;
-      const bf16* src = cache;
+      const bf16* src = p.k_cache;
       if (valid) {
         const int page = bt[key / p.page_size];
-        src = cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD +
+        src = p.k_cache + (size_t)page * p.page_stride + (size_t)(key % p.page_size) * p.nkv * HD + (size_t)kvh * HD +
               (tl.glob_off[i] - tl.row[i] * p.nkv * HD);
       }
-      cp_async16(sbase + tl.smem_off[i] * 2, src, valid);
+      cp_async16(kb + tl.smem_off[i] * 2, src, valid);
+      cp_async16(vb + tl.smem_off[i] * 2, valid ? src + v_delta : src, valid);
     }
   }
 }
@@ -500,27 +507,28 @@ attention_decode_kernel(const AttnParams p) {
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   if (split_ok) {
-    // prologue: kDecStages - 1 tiles in flight (a commit per tile, empty when past the end)
-#pragma unroll
-    for (int s = 0; s < kDecStages - 1; ++s) {
-      const int t = t_begin + s;
-      if (t < t_end) {
-        load_tile16<HD>(k_tile(s), p.k_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, tl, aligned);
-        load_tile16<HD>(v_tile(s), p.v_cache, p, bt, kvh, lo + t * kDecKeys, kv_len, tl, aligned);
+    // the next tile to copy: its first key, its page (index into the block table) and offset there
+    const long long v_delta = p.v_cache - p.k_cache;
+    int ld_t = t_begin, ld_stage = 0;
+    int ld_key = lo + t_begin * kDecKeys;
+    int ld_pg = ld_key / p.page_size, ld_off = ld_key % p.page_size;
+    auto issue_next = [&]() {   // one commit per call, empty when past the end
+      if (ld_t < t_end) {
+        load_kv_tile16<HD>(k_tile(ld_stage), v_tile(ld_stage), p, bt, v_delta, kvh, ld_key, kv_len, tl, aligned, ld_pg, ld_off);
+        ++ld_t;
+        ld_key += kDecKeys;
+        ld_off += kDecKeys;
+        if (ld_off >= p.page_size) { ld_off -= p.page_size; ++ld_pg; }   // aligned case: exact
+        ld_stage = ld_stage + 1 == kDecStages ? 0 : ld_stage + 1;
       }
       cp_async_commit();
-    }
+    };
+    // prologue: kDecStages - 1 tiles in flight
+#pragma unroll
+    for (int s = 0; s < kDecStages - 1; ++s) issue_next();
+    int stage = 0;
     for (int t = t_begin; t < t_end; ++t) {
-      const int stage = (t - t_begin) % kDecStages;
-      {   // keep the ring full: the tile kDecStages - 1 ahead goes into the stage freed last iteration
-        const int tn = t + kDecStages - 1;
-        if (tn < t_end) {
-          const int sn = (tn - t_begin) % kDecStages;
-          load_tile16<HD>(k_tile(sn), p.k_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, tl, aligned);
-          load_tile16<HD>(v_tile(sn), p.v_cache, p, bt, kvh, lo + tn * kDecKeys, kv_len, tl, aligned);
-        }
-        cp_async_commit();
-      }
+      issue_next();   // keeps the ring full: goes into the stage freed last iteration
       cp_async_wait<kDecStages - 1>();   // tile t (this thread's part) has landed ...
       __syncwarp();                      // ... and so have the other lanes' parts
       const int key0 = lo + t * kDecKeys;
@@ -601,6 +609,7 @@ attention_decode_kernel(const AttnParams p) {
         }
       }
       __syncwarp();   // all lanes are done reading this stage before it is refilled
+      stage = stage + 1 == kDecStages ? 0 : stage + 1;
     }
     cp_async_wait<0>();
   }
@@ -627,7 +636,9 @@ attention_decode_kernel(const AttnParams p) {
   }
 }
 
-// out[token, head] = sum_s w_s o_s / sum_s w_s with w_s = 2^(lse_s - max lse). One warp per (token, head).
+// out[token, head] = sum_s w_s o_s / sum_s w_s with w_s = 2^(lse_s - max lse). One warp per
+// (token, head): the lanes fetch the slices' log-sum-exps side by side (up to 64 slices), and the
+// partial outputs are read eight slices at a time so that the loads overlap.
 template <int HD>
 __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_stride, const float* __restrict__ part_o,
                                        const float* __restrict__ part_lse, const int* __restrict__ row_splits,
@@ -641,20 +652,35 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_strid
   const int ns = row_splits[token];
   if (ns <= 1) return;  // written directly by the attention kernel
   const size_t base = ((size_t)token * nq + head) * max_splits;
-  float mx = -INFINITY;
-  for (int s = 0; s < ns; ++s) mx = fmaxf(mx, part_lse[base + s]);
   constexpr int kPer = HD / 32;
   float acc[kPer];
 #pragma unroll
   for (int e = 0; e < kPer; ++e) acc[e] = 0.f;
-  float wsum = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float lse = part_lse[base + s];
-    const float w = lse == -INFINITY ? 0.f : exp2f(lse - mx);
-    wsum += w;
-    const float* op = part_o + (base + s) * HD + lane * kPer;
+  // ns <= 64 (checked by the entry points): lane i holds slices i and i + 32
+  const float l0 = lane < ns ? part_lse[base + lane] : -INFINITY;
+  const float l1 = 32 + lane < ns ? part_lse[base + 32 + lane] : -INFINITY;
+  const float mx = warp_max(fmaxf(l0, l1));
+  const float w0 = l0 == -INFINITY ? 0.f : exp2f(l0 - mx), w1 = l1 == -INFINITY ? 0.f : exp2f(l1 - mx);
+  const float wsum = warp_sum(w0 + w1);
+  for (int s = 0; s < ns; s += 8) {
+    float v[8][kPer];
 #pragma unroll
-    for (int e = 0; e < kPer; ++e) acc[e] += w * op[e];
+    for (int u = 0; u < 8; ++u) {
+      if (s + u < ns) {
+        const float* op = part_o + (base + s + u) * HD + lane * kPer;
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) v[u][e] = op[e];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int idx = s + u;
+      const float w = __shfl_sync(0xffffffffu, idx < 32 ? w0 : w1, idx & 31);
+      if (idx < ns) {
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) acc[e] += w * v[u][e];
+      }
+    }
   }
   const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
   bf16* dst = out + (size_t)token * out_row_stride + (size_t)head * HD + lane * kPer;
@@ -724,7 +750,8 @@ OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int o
   OI_REQUIRE(q_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_decode: misaligned strides");
   OI_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
              "attention_decode: misaligned pointers");
-  OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2, "attention_decode: scratch missing");
+  OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2 && max_splits <= 64,
+             "attention_decode: scratch missing, or slices outside 2..64");
   if (num_items == 0 || tokens == 0) return OI_OK;
   AttnParams p;
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
@@ -759,7 +786,8 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
   OI_REQUIRE(q_row_stride % 2 == 0 && out_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_mma: misaligned strides");
   OI_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
              "attention_mma: misaligned pointers");
-  OI_REQUIRE(!any_split || (part_o && part_lse && row_splits && max_splits > 0), "attention_mma: split items without scratch");
+  OI_REQUIRE(!any_split || (part_o && part_lse && row_splits && max_splits > 0 && max_splits <= 64),
+             "attention_mma: split items without scratch, or more than 64 slices");
   if (num_items == 0 || tokens == 0) return OI_OK;
   AttnParams p;
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;

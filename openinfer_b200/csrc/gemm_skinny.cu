@@ -88,19 +88,29 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
   const unsigned my_ring = (unsigned)__cvta_generic_to_shared(ring_raw) + (unsigned)(warp * kStages * kU * 2 * 32 + lane) * 16u;
   const int nkb = k_slice / 32;
   const int n_it = (nkb + kU - 1) / kU;
-  auto issue = [&](int it) {   // stage `it` of the stream into its ring slot (zero fill past the end)
-    const unsigned dst = my_ring + (unsigned)((it % kStages) * kU * 2 * 32) * 16u;
+  // the stream is issued through running pointers: no multiplication or division per stage
+  int ld_it = 0, ld_slot = 0;
+  const bf16* ld_a = pa;
+  const bf16* ld_b = pb;
+  const bool even = (nkb % kU) == 0;   // every stage holds kU whole blocks
+  auto issue = [&]() {   // the next stage of the stream into its ring slot; one commit per call
+    if (ld_it < n_it) {
+      const unsigned dst = my_ring + (unsigned)(ld_slot * kU * 2 * 32) * 16u;
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int kb = it * kU + u;
-      const bool valid = it < n_it && kb < nkb;
-      cp_async16(dst + (unsigned)(u * 2 * 32) * 16u, valid ? pa + kb * 32 : W, valid);
-      cp_async16(dst + (unsigned)((u * 2 + 1) * 32) * 16u, valid ? pb + kb * 32 : W, valid);
+      for (int u = 0; u < kU; ++u) {
+        const bool valid = even || ld_it * kU + u < nkb;   // past the end: zero fill
+        cp_async16(dst + (unsigned)(u * 2 * 32) * 16u, valid ? ld_a + u * 32 : W, valid);
+        cp_async16(dst + (unsigned)((u * 2 + 1) * 32) * 16u, valid ? ld_b + u * 32 : W, valid);
+      }
+      ld_a += kU * 32;
+      ld_b += kU * 32;
+      ++ld_it;
+      ld_slot = ld_slot + 1 == kStages ? 0 : ld_slot + 1;
     }
     cp_async_commit();
   };
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) issue(s);
+  for (int s = 0; s < kStages - 1; ++s) issue();
 
   // ---- stage the activation slice (rows >= M are zero); x is the previous kernel's output
   if (pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
@@ -139,10 +149,13 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
+  int slot = 0;
+  unsigned xk = xs;                     // this lane's activation chunk of the current k block
   for (int it = 0; it < n_it; ++it) {
-    issue(it + kStages - 1);            // refills the slot consumed in the previous iteration
+    issue();                            // refills the slot consumed in the previous iteration
     cp_async_wait<kStages - 1>();       // stage `it` (this lane's own copies) has landed
-    const unsigned src = my_ring + (unsigned)((it % kStages) * kU * 2 * 32) * 16u;
+    const unsigned src = my_ring + (unsigned)(slot * kU * 2 * 32) * 16u;
+    slot = slot + 1 == kStages ? 0 : slot + 1;
 #pragma unroll
     for (int u = 0; u < kU; ++u) {
       const uint4 wa = lds128(src + (unsigned)(u * 2 * 32) * 16u);
@@ -151,10 +164,11 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
       if (kb >= nkb) break;   // the zero-filled tail of the last stage: nothing to add (and x_s ends here)
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        const uint4 xv = lds128(xs + (unsigned)(t * 8 * stride + kb * 32) * 2u);
+        const uint4 xv = lds128(xk + (unsigned)(t * 8 * stride) * 2u);
         mma_bf16(acc[t], wa.x, wb.x, wa.y, wb.y, xv.x, xv.y);
         mma_bf16(acc[t], wa.z, wb.z, wa.w, wb.w, xv.z, xv.w);
       }
+      xk += 64u;                        // 32 elements further along k
     }
   }
   cp_async_wait<0>();

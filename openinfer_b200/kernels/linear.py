@@ -50,7 +50,7 @@ def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
     shape: the fewest slices that fill the GPU twice over, each slice's activations within 64 KB
     of shared memory where possible."""
     row_tiles = -(-N // 64)
-    valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 24576 + 32 * (K // c + 64) + 4096 <= 200 * 1024]
+    valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 49152 + 32 * (K // c + 64) + 4096 <= 200 * 1024]
     if not valid:
         return 0
     # measured on B200 at M = 8: four slices are best for the short products (N 4096..6144)
@@ -76,7 +76,7 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) 
     c = skinny_cluster_size(N, K, _SM_COUNT)
     if c == 0:
         return False
-    if _FORCE_C and K % (32 * _FORCE_C) == 0 and 24576 + 32 * (K // _FORCE_C + 64) + 4096 <= 200 * 1024:
+    if _FORCE_C and K % (32 * _FORCE_C) == 0 and 49152 + 32 * (K // _FORCE_C + 64) + 4096 <= 200 * 1024:
         c = _FORCE_C
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),

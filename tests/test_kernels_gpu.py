@@ -466,7 +466,7 @@ def test_gemm_skinny(M, N, K):
     from openinfer_b200.kernels import lib as klib
     L = klib.load()
     for c in (1, 2, 4, 8):
-        if K % (32 * c) or 24576 + 32 * (K // c + 64) + 4096 > 200 * 1024:   # the slice must fit in shared memory
+        if K % (32 * c) or 49152 + 32 * (K // c + 64) + 4096 > 200 * 1024:   # the slice must fit in shared memory
             continue
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
