@@ -117,9 +117,11 @@ attention_mma_kernel(const AttnParams p) {
   auto k_tile = [&](int stage) { return tiles + (size_t)stage * 2 * kKeys * HD; };
   auto v_tile = [&](int stage) { return tiles + (size_t)stage * 2 * kKeys * HD + kKeys * HD; };
 
-  const int4 item = p.items[blockIdx.x];
+  // items come longest first; the kv heads of an item are neighbours in the grid, so the launch
+  // order is longest first over the whole grid
+  const int4 item = p.items[blockIdx.x / p.nkv];
   const int req = item.x, tok0 = item.y, split = item.z, nsplits = item.w;
-  const int kvh = blockIdx.y;
+  const int kvh = blockIdx.x % p.nkv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int group = p.group;
   const int q_start = p.cu_seqlens[req];
@@ -696,8 +698,7 @@ int launch_tiles(const AttnParams& p, int num_items, cudaStream_t s) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  dim3 grid(num_items, p.nkv);
-  attention_mma_kernel<HD, MT><<<grid, kThreads, smem, s>>>(p);
+  attention_mma_kernel<HD, MT><<<(unsigned)((long long)num_items * p.nkv), kThreads, smem, s>>>(p);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

@@ -75,20 +75,21 @@ __global__ void qk_norm_rope_kv_kernel(
 
 // bfloat16 fast path: a lane handles PAIRS of neighbouring elements with 4-byte accesses (the
 // element (2p, 2p+1) of the first rotary half together with its partner pair in the second half),
-// so a head of 128 is two loads, two table reads and two stores per lane.
+// so a head of 128 is two loads, two table reads and two stores per lane. The grid is
+// (tokens, heads / 4): no division to find a warp's token and head.
+template <typename TW>   // storage type of the norm weights
 __global__ void qk_norm_rope_kv_bf16x2_kernel(
     bf16* __restrict__ qkv, int row_stride, int nq, int nkv, int hd,
-    const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_dtype, float eps,
+    const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
     float w_offset, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
     int rot_half, int max_pos, const int* __restrict__ positions, const int* __restrict__ slots,
     bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, long long page_stride, int page_size,
-    int heads_total, int tokens) {
+    int heads_total) {
   const int lane = threadIdx.x & 31;
-  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (gw >= (long long)tokens * heads_total) return;
-  const int token = (int)(gw / heads_total);
-  const int head = (int)(gw - (long long)token * heads_total);
-  bf16* src = qkv + (size_t)token * row_stride + (size_t)head * hd;
+  const int token = blockIdx.x;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (head >= heads_total) return;
+  bf16* src = qkv + (size_t)token * row_stride + head * hd;
   const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
   bf16* dst = src;
   if (kind != 0) {
@@ -96,7 +97,7 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
     if (slot < 0) return;
     const int kvh = kind == 1 ? head - nq : head - nq - nkv;
     bf16* base = kind == 1 ? k_cache : v_cache;
-    dst = base + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * nkv * hd + (size_t)kvh * hd;
+    dst = base + (size_t)(slot / page_size) * page_stride + (size_t)((slot % page_size) * nkv + kvh) * hd;
   }
   const int npairs = hd / 2;
   const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
@@ -105,11 +106,15 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
     for (int p = lane; p < npairs; p += 32) dst2[p] = src2[p];
     return;
   }
-  const void* w = kind == 0 ? q_norm_w : k_norm_w;
+  const TW* w = kind == 0 ? q_norm_w : k_norm_w;
   const int rot_pairs = rot_half / 2;          // pairs in one rotary half
-  // all loads first
-  constexpr int kMax = 4;                      // hd <= 256: at most 4 (pair, partner pair) sets per lane... 2 per 128
-  float2 a[kMax], b[kMax];
+  int pos = positions[token];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const float2* cos2 = reinterpret_cast<const float2*>(cos_tab + (size_t)pos * rot_half);
+  const float2* sin2 = reinterpret_cast<const float2*>(sin_tab + (size_t)pos * rot_half);
+  // all loads first: a lane holds at most 2 (pair, partner pair) sets (hd <= 256)
+  constexpr int kMax = 2;
+  float2 a[kMax], b[kMax], c[kMax], sn[kMax], wa[kMax], wb[kMax];
   float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < kMax; ++k) {
@@ -117,6 +122,12 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
     if (p < rot_pairs) {
       a[k] = __bfloat1622float2(src2[p]);
       b[k] = __bfloat1622float2(src2[p + rot_pairs]);
+      c[k] = cos2[p];
+      sn[k] = sin2[p];
+      if (w) {
+        wa[k] = make_float2(w_offset + to_f32(w[2 * p]), w_offset + to_f32(w[2 * p + 1]));
+        wb[k] = make_float2(w_offset + to_f32(w[2 * p + rot_half]), w_offset + to_f32(w[2 * p + rot_half + 1]));
+      }
       ss += a[k].x * a[k].x + a[k].y * a[k].y + b[k].x * b[k].x + b[k].y * b[k].y;
     }
   }
@@ -129,32 +140,24 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
     ss = warp_sum(ss);
     inv = rsqrtf(ss / (float)hd + eps);
   }
-  int pos = positions[token];
-  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-  const float2* cos2 = reinterpret_cast<const float2*>(cos_tab + (size_t)pos * rot_half);
-  const float2* sin2 = reinterpret_cast<const float2*>(sin_tab + (size_t)pos * rot_half);
 #pragma unroll
   for (int k = 0; k < kMax; ++k) {
     const int p = lane + 32 * k;
     if (p < rot_pairs) {
       float2 x = a[k], y = b[k];
       if (w) {
-        const int i = 2 * p;
-        x.x *= inv * (w_offset + load_as_f32(w, norm_dtype, i));
-        x.y *= inv * (w_offset + load_as_f32(w, norm_dtype, i + 1));
-        y.x *= inv * (w_offset + load_as_f32(w, norm_dtype, i + rot_half));
-        y.y *= inv * (w_offset + load_as_f32(w, norm_dtype, i + rot_half + 1));
+        x.x *= inv * wa[k].x; x.y *= inv * wa[k].y;
+        y.x *= inv * wb[k].x; y.y *= inv * wb[k].y;
       }
-      const float2 c = cos2[p], sn = sin2[p];
-      dst2[p] = __floats2bfloat162_rn(x.x * c.x - y.x * sn.x, x.y * c.y - y.y * sn.y);
-      dst2[p + rot_pairs] = __floats2bfloat162_rn(x.x * sn.x + y.x * c.x, x.y * sn.y + y.y * c.y);
+      dst2[p] = __floats2bfloat162_rn(x.x * c[k].x - y.x * sn[k].x, x.y * c[k].y - y.y * sn[k].y);
+      dst2[p + rot_pairs] = __floats2bfloat162_rn(x.x * sn[k].x + y.x * c[k].x, x.y * sn[k].y + y.y * c[k].y);
     }
   }
   for (int p = 2 * rot_pairs + lane; p < npairs; p += 32) {
     float2 t = __bfloat1622float2(src2[p]);
     if (w) {
-      t.x *= inv * (w_offset + load_as_f32(w, norm_dtype, 2 * p));
-      t.y *= inv * (w_offset + load_as_f32(w, norm_dtype, 2 * p + 1));
+      t.x *= inv * (w_offset + to_f32(w[2 * p]));
+      t.y *= inv * (w_offset + to_f32(w[2 * p + 1]));
     }
     dst2[p] = __floats2bfloat162_rn(t.x, t.y);
   }
@@ -182,13 +185,20 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
         (float*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
         sin_tab, rot_half, max_pos, positions, slots, (float*)k_cache, (float*)v_cache, page_stride,
         page_size, heads_total, tokens);
-  } else if (dtype == OI_BF16 && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 &&
+  } else if (dtype == OI_BF16 && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 && tokens <= 2147483647 &&
              (uintptr_t)qkv % 4 == 0 && page_stride % 2 == 0 && (!write_kv || ((uintptr_t)k_cache % 4 == 0 && (uintptr_t)v_cache % 4 == 0)) &&
              (uintptr_t)cos_tab % 8 == 0 && (uintptr_t)sin_tab % 8 == 0) {
-    qk_norm_rope_kv_bf16x2_kernel<<<blocks, 128, 0, s>>>(
-        (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
-        sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride,
-        page_size, heads_total, tokens);
+    const dim3 grid(tokens, (heads_total + 3) / 4);
+    if (norm_dtype == OI_BF16)
+      qk_norm_rope_kv_bf16x2_kernel<bf16><<<grid, 128, 0, s>>>(
+          (bf16*)qkv, row_stride, nq, nkv, hd, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, w_offset, cos_tab,
+          sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
+          heads_total);
+    else
+      qk_norm_rope_kv_bf16x2_kernel<float><<<grid, 128, 0, s>>>(
+          (bf16*)qkv, row_stride, nq, nkv, hd, (const float*)q_norm_w, (const float*)k_norm_w, eps, w_offset, cos_tab,
+          sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
+          heads_total);
   } else if (dtype == OI_BF16) {
     qk_norm_rope_kv_kernel<bf16><<<blocks, 128, 0, s>>>(
         (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
