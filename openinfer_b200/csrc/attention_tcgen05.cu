@@ -1,0 +1,528 @@
+// Causal paged GQA attention for prompt portions on the 5th-generation tensor cores (bfloat16,
+// head_dim 128): S = Q K^T and O_tile = P V run as tcgen05.mma with their results in tensor memory;
+// Q, K and V tiles are fetched by TMA, K and V straight out of the cache pages.
+//
+// A CTA owns 128 query rows of one (request, kv head): row r is (token r / group, head r % group),
+// as in the mma.sync kernels. Roles:
+//   warp 0      producer: one thread issues the TMA loads: the Q tile once (two 128 x 64 boxes out of
+//               the projection buffer, rows ordered token-major by a 3-D box), then per 64-key tile the
+//               K and V boxes of the pages the block table names (4-D maps over the layer's cache);
+//   warp 1      MMA issuer: per tile S = Q K^T (M 128, N 64, K 128: 8 instructions, both operands
+//               K-major in shared memory), and, once the softmax warps have put P into shared memory,
+//               O += P V (M 128, N 128, K 64: 4 instructions, V read MN-major as it lies in its page),
+//               accumulated in tensor memory over all tiles;
+//   warps 2-5   one thread per query row: reads its row of S from tensor memory, masks, keeps the
+//               running maximum and sum in float32 (no shuffles: the row is the thread's own) and writes
+//               P as bfloat16 into the swizzled shared tile. P is taken relative to a REFERENCE maximum
+//               that is only moved when the true maximum has outgrown it by a factor 2^8; only then is
+//               the accumulator in tensor memory rescaled (load, multiply, store). At the end the
+//               thread reads its output row, divides by the sum and stores it.
+// S is double buffered so that the next tile's S is computed while this tile's softmax runs; two
+// CTAs fit on an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
+// other's gaps. Every mbarrier wait is bounded (two seconds): a wait that runs out sets an error word
+// and a flag that ends all roles, after which the CTA frees its tensor memory and returns.
+// No load uses cluster multicast.
+//
+// Math as the other attention kernels: s = (q . k) / sqrt(hd) for keys j <= pos (and j > pos - window),
+// softmax in float32 with exp2 and the scale folded in, o = sum p v
+// (pegainfer-kernels/csrc/shared/paged_attention.cu:439-567).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int HD = 128;
+constexpr int kRows = 128;          // query rows per CTA
+constexpr int kKeys = 64;           // keys per tile
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ int g_attn_error = 0;
+
+struct Params {
+  const int4* items;        // (request, first token of the tile, -, -)
+  const int* cu_seqlens;
+  const int* kv_lens;
+  const int* block_table;
+  int bt_stride;
+  int page_size, box_keys;  // keys per TMA box = min(page_size, 64)
+  int num_pages;
+  int nq, nkv, group;
+  float scale_log2;
+  int window;
+  bf16* out;
+  int out_row_stride;
+};
+
+// ---- PTX wrappers (see gemm_tcgen05.cu for the same set) ---------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
+  unsigned long long t0 = 0;
+  for (unsigned i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((i & 255u) == 255u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_attn_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long desc_a, unsigned long long desc_b,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// K-major operand, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart (Q, K, P tiles).
+__device__ __forceinline__ unsigned long long desc_k_major(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+// MN-major operand (V as it lies in its page: a row = one key, 64 head dims = 128 bytes): 8 keys form a
+// 1024-byte group (stride byte offset), the second 64 head dims start `lbo_bytes` further on
+// (leading byte offset).
+__device__ __forceinline__ unsigned long long desc_mn_major(unsigned smem_addr, unsigned lbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
+  d |= (unsigned long long)(lbo_bytes >> 4) << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+
+// shared memory map (bytes from a 1024-aligned base)
+constexpr int kQBytes = kRows * HD * 2;            // 32 KB: two halves [128 rows][64 dims]
+constexpr int kKBytes = kKeys * HD * 2;            // 16 KB: two halves [64 keys][64 dims]
+constexpr int kVBytes = kKeys * HD * 2;            // 16 KB
+constexpr int kPBytes = kRows * kKeys * 2;         // 16 KB: [128 rows][64 keys]
+constexpr int kOffK = kQBytes;
+constexpr int kOffV = kOffK + kStages * kKBytes;
+constexpr int kOffP = kOffV + kStages * kVBytes;
+constexpr int kOffBar = kOffP + kPBytes;
+// barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_full
+constexpr int kNumBars = 1 + 2 * kStages + 2 + 2;
+constexpr float kRescaleThreshold = 8.f;           // in log2 units: P stays below 2^8
+constexpr int kSmemTotal = kOffBar + kNumBars * 8 + 16 + 1024;
+constexpr unsigned kTmemCols = 256;                // S0 [0,64) S1 [64,128) O_tile [128,256)
+
+__global__ void __launch_bounds__(kThreads)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const unsigned sbase = smem_u32(smem);
+  const unsigned bar0 = sbase + kOffBar;
+  const unsigned q_full = bar0;
+  auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kStages + s); };
+  auto s_full = [&](int b) { return bar0 + 8u * (1 + 2 * kStages + b); };
+  const unsigned p_full = bar0 + 8u * (3 + 2 * kStages);
+  const unsigned o_full = bar0 + 8u * (4 + 2 * kStages);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + kOffBar + kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int4 item = p.items[blockIdx.x / p.nkv];
+  const int req = item.x, tok0 = item.y;
+  const int kvh = blockIdx.x % p.nkv;
+  const int group = p.group;
+  const int q_start = p.cu_seqlens[req];
+  const int q_len = p.cu_seqlens[req + 1] - q_start;
+  const int kv_len = p.kv_lens[req];
+  const int toks_per_tile = kRows / group;
+  const int tile_toks = min(toks_per_tile, q_len - tok0);
+  const int pos0 = kv_len - q_len + tok0;
+  int lo = 0;
+  if (p.window > 0) lo = max(0, pos0 - p.window + 1);
+  lo &= ~(kKeys - 1);
+  const int hi = pos0 + tile_toks;
+  const int num_tiles = (hi - lo + kKeys - 1) / kKeys;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+    mbar_init(s_full(0), 1);
+    mbar_init(s_full(1), 1);
+    mbar_init(p_full, 4);      // one arrival per softmax warp
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      // Q: rows (token, head) of this kv head's group; box (64 dims, group heads, 128 / group tokens)
+      mbar_expect_tx(q_full, kQBytes);
+      tma_load_3d(sbase, &map_q, 0, kvh * group, q_start + tok0, q_full);
+      tma_load_3d(sbase + kQBytes / 2, &map_q, 64, kvh * group, q_start + tok0, q_full);
+      const int* bt = p.block_table + (size_t)req * p.bt_stride;
+      const int boxes = kKeys / p.box_keys;
+      for (int t = 0; t < num_tiles; ++t) {
+        const int s = t % kStages;
+        if (t >= kStages && !mbar_wait(kv_empty(s), (unsigned)((t / kStages) - 1) & 1, abort_flag, 1)) break;
+        mbar_expect_tx(kv_full(s), kKBytes + kVBytes);
+        const int key0 = lo + t * kKeys;
+        const unsigned k_dst = sbase + kOffK + s * kKBytes, v_dst = sbase + kOffV + s * kVBytes;
+        for (int b = 0; b < boxes; ++b) {
+          const int key = key0 + b * p.box_keys;
+          int col = key / p.page_size;
+          col = col < p.bt_stride ? col : p.bt_stride - 1;       // keys past the request are masked anyway
+          int page = bt[col];
+          page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
+          const int in_page = key % p.page_size;
+          const unsigned off = (unsigned)(b * p.box_keys) * 128u;   // rows of 128 bytes
+          tma_load_4d(k_dst + off, &map_k, 0, kvh, in_page, page, kv_full(s));
+          tma_load_4d(k_dst + kKBytes / 2 + off, &map_k, 64, kvh, in_page, page, kv_full(s));
+          tma_load_4d(v_dst + off, &map_v, 0, kvh, in_page, page, kv_full(s));
+          tma_load_4d(v_dst + kVBytes / 2 + off, &map_v, 64, kvh, in_page, page, kv_full(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // S: D f32, A = Q (bf16, K-major), B = K (bf16, K-major), M 128, N 64
+      constexpr unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(kKeys >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
+      // O_tile: A = P (K-major), B = V (MN-major: bit 16), M 128, N 128
+      constexpr unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(kRows >> 4) << 24);
+      bool ok = mbar_wait(q_full, 0, abort_flag, 2);
+      auto issue_s = [&](int t) {   // S(t) = Q K(t)^T into S buffer t & 1
+        const int s = t % kStages;
+        if (!mbar_wait(kv_full(s), (unsigned)(t / kStages) & 1, abort_flag, 3)) return false;
+        tc_fence_after();
+        const unsigned k_addr = sbase + kOffK + s * kKBytes;
+        const unsigned tmem_s = tmem + (unsigned)((t & 1) * kKeys);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          // 16 dims = 32 bytes along the swizzle row; dims 64.. are in the second half tile
+          const unsigned a = sbase + (k >= 4 ? kQBytes / 2 : 0) + (k & 3) * 32;
+          const unsigned b = k_addr + (k >= 4 ? kKBytes / 2 : 0) + (k & 3) * 32;
+          umma_bf16(tmem_s, desc_k_major(a), desc_k_major(b), idesc_s, k != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full(t & 1));
+        return true;
+      };
+      if (ok && num_tiles > 0) ok = issue_s(0);
+      for (int t = 0; t < num_tiles && ok; ++t) {
+        if (t + 1 < num_tiles) {        // the next S is computed while this tile's softmax runs
+          ok = issue_s(t + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(p_full, (unsigned)t & 1, abort_flag, 4);   // P(t) is in shared memory, O is rescaled
+        if (!ok) break;
+        tc_fence_after();
+        const int s = t % kStages;
+        const unsigned v_addr = sbase + kOffV + s * kVBytes;
+        const unsigned p_addr = sbase + kOffP;
+#pragma unroll
+        for (int k = 0; k < kKeys / 16; ++k) {
+          // A: P rows of 128 bytes (64 keys), 16 keys = 32 bytes along the row
+          // B: V, 16 keys = two 8-key groups = 2048 bytes further; the second 64 dims kVBytes / 2 away
+          umma_bf16(tmem + 128u, desc_k_major(p_addr + k * 32), desc_mn_major(v_addr + k * 2048, kVBytes / 2), idesc_o,
+                    (t | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(o_full);
+        umma_commit(kv_empty(s));       // K(t) and V(t) have been read: the stage may be refilled
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one row per thread
+    const int quarter = warp & 3;                       // TMEM lanes [32 * quarter, +32)
+    const int r = quarter * 32 + lane;                  // query row of this thread
+    const int t_row = r / group;
+    const bool row_ok = t_row < tile_toks;
+    const int pos = pos0 + t_row;
+    const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
+    float m_ref = -INFINITY;                            // the maximum P is taken relative to (raw score units)
+    float l = 0.f;
+    unsigned char* p_row = smem + kOffP + r * 128;      // this row of the P tile (128 bytes, swizzled chunks)
+    bool ok = true;
+    for (int t = 0; t < num_tiles && ok; ++t) {
+      const int key0 = lo + t * kKeys;
+      ok = mbar_wait(s_full(t & 1), (unsigned)(t >> 1) & 1, abort_flag, 6);
+      if (!ok) break;
+      tc_fence_after();
+      float sv[kKeys];
+      {
+        unsigned v0[32], v1[32];
+        tmem_ld32(lane_base + (unsigned)((t & 1) * kKeys), v0);
+        tmem_ld32(lane_base + (unsigned)((t & 1) * kKeys + 32), v1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) { sv[e] = __uint_as_float(v0[e]); sv[32 + e] = __uint_as_float(v1[e]); }
+      }
+      const bool full = row_ok && key0 + kKeys - 1 <= pos && (p.window <= 0 || key0 > pos - p.window);
+      if (!full) {
+#pragma unroll
+        for (int e = 0; e < kKeys; ++e) {
+          const int key = key0 + e;
+          const bool vis = row_ok && key <= pos && (p.window <= 0 || key > pos - p.window);
+          sv[e] = vis ? sv[e] : -INFINITY;
+        }
+      }
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < kKeys; ++e) m_tile = fmaxf(m_tile, sv[e]);
+      // move the reference only when the maximum has outgrown it by 2^8 (or there is none yet)
+      const bool move = m_tile > m_ref && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > kRescaleThreshold);
+      // the second product of the previous tile reads the P tile and updates O until o_full(t - 1)
+      if (t > 0) {
+        ok = mbar_wait(o_full, (unsigned)(t - 1) & 1, abort_flag, 7);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, move && t > 0 && m_ref != -INFINITY)) {
+        // rescale this warp's rows of the accumulator in tensor memory (factor 1 for rows that stay)
+        const float f = (move && m_ref != -INFINITY) ? fast_exp2((m_ref - m_tile) * p.scale_log2) : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          unsigned v[32];
+          tmem_ld32(lane_base + 128u + (unsigned)c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
+          asm volatile(
+              "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+              "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+              "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+              ::"r"(lane_base + 128u + (unsigned)c), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+                "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
+                "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+        l *= f;
+      }
+      if (move) m_ref = m_tile;
+      const float base = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
+      // P(t) = 2^(s * scale - m_ref * scale), rounded to bfloat16, into the swizzled row
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 chunk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&chunk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], p.scale_log2, -base));
+          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], p.scale_log2, -base));
+          l += p0 + p1;
+          h[e] = __floats2bfloat162_rn(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = chunk;
+      }
+      // make the generic-proxy writes of P visible to the tensor core (async proxy), then hand over
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && num_tiles > 0) {
+      ok = mbar_wait(o_full, (unsigned)(num_tiles - 1) & 1, abort_flag, 8);
+      if (ok) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* dst = p.out + (size_t)(q_start + tok0 + t_row) * p.out_row_stride + (size_t)(kvh * group + r % group) * HD;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          unsigned v[32];
+          tmem_ld32(lane_base + 128u + (unsigned)c, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 o;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                h[e] = __floats2bfloat162_rn(__uint_as_float(v[q4 * 8 + 2 * e]) * inv, __uint_as_float(v[q4 * 8 + 2 * e + 1]) * inv);
+              reinterpret_cast<uint4*>(dst + c)[q4] = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);   // let copies in flight land
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+}  // namespace
+
+// Prompt tiles of 128 query rows; items as for oi_attention_mma with rows_per_cta 128 and no key
+// slices. Requirements (else the caller uses the mma.sync kernel): head_dim 128, 128 % group == 0,
+// page_size a power of two >= 16 (64 % page_size == 0 or page_size % 64 == 0), 16-byte aligned
+// buffers with row strides that are multiples of 8 elements. q: [tokens, q_row_stride] (heads of
+// 128 from column 0); cache: [num_pages, page_size, nkv, 128] with page_stride elements per page.
+OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int tokens, void* out, int out_row_stride,
+                                const void* k_cache, const void* v_cache, long long page_stride, int page_size,
+                                int num_pages, const int* block_table, int bt_stride, const int* cu_seqlens,
+                                const int* kv_lens, const int* items, int num_items, int nq, int nkv, int hd,
+                                float scale, int window, void* stream) {
+  OI_REQUIRE(hd == HD, "attention_tcgen05: head_dim %d not covered (128)", hd);
+  OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && kRows % (nq / nkv) == 0, "attention_tcgen05: group %d/%d not covered", nq, nkv);
+  OI_REQUIRE(page_size >= 16 && (page_size & (page_size - 1)) == 0, "attention_tcgen05: page size %d not covered", page_size);
+  OI_REQUIRE(q_row_stride % 8 == 0 && page_stride % 8 == 0 && out_row_stride % 8 == 0 && (uintptr_t)q % 16 == 0 &&
+                 (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0 && (uintptr_t)out % 16 == 0,
+             "attention_tcgen05: misaligned operands");
+  if (num_items == 0 || tokens == 0) return OI_OK;
+  EncodeTiledFn enc = encode_fn();
+  OI_REQUIRE(enc != nullptr, "attention_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
+  const int group = nq / nkv;
+  const int box_keys = page_size < kKeys ? page_size : kKeys;
+  CUtensorMap mq, mk, mv;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nq, (cuuint64_t)tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_row_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)(kRows / group)};
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    OI_REQUIRE(r == CUDA_SUCCESS, "attention_tcgen05: tensor map for q failed (%d)", (int)r);
+  }
+  for (int which = 0; which < 2; ++which) {
+    cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)nkv, (cuuint64_t)page_size, (cuuint64_t)num_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)nkv * HD * 2, (cuuint64_t)page_stride * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_keys, 1};
+    cuuint32_t es[4] = {1, 1, 1, 1};
+    CUresult r = enc(which ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_cache : k_cache),
+                     dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    OI_REQUIRE(r == CUDA_SUCCESS, "attention_tcgen05: tensor map for the cache failed (%d)", (int)r);
+  }
+  Params p;
+  p.items = (const int4*)items; p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens;
+  p.block_table = block_table; p.bt_stride = bt_stride;
+  p.page_size = page_size; p.box_keys = box_keys; p.num_pages = num_pages;
+  p.nq = nq; p.nkv = nkv; p.group = group;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window;
+  p.out = (bf16*)out; p.out_row_stride = out_row_stride;
+  static bool configured = false;
+  if (!configured) {
+    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+    configured = true;
+  }
+  attention_tcgen05_kernel<<<(unsigned)((long long)num_items * nkv), kThreads, kSmemTotal, (cudaStream_t)stream>>>(mq, mk, mv, p);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+OI_API int oi_attention_tcgen05_status(int* status) {
+  int v = 0;
+  OI_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    OI_CHECK_CUDA(cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int)));
+  }
+  *status = v;
+  return OI_OK;
+}

@@ -37,6 +37,7 @@ def register_tuned(fn) -> None:
 # tensor-core kernels (bfloat16, head_dim 32 / 64 / 128): host-side planning of work items
 # ---------------------------------------------------------------------------
 import dataclasses  # noqa: E402
+import ctypes  # noqa: E402
 from ctypes import c_float, c_int, c_longlong, c_void_p  # noqa: E402
 
 import numpy as np  # noqa: E402
@@ -48,6 +49,14 @@ _lib.declare("oi_attention_mma", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P
                                   _F, _I, _P, _P, _I, _I, _P])
 _lib.declare("oi_attention_decode", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I,
                                      _F, _I, _P, _P, _I, _P])
+
+_lib.declare("oi_attention_tcgen05", [_P, _L, _I, _P, _I, _P, _P, _L, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I,
+                                      _F, _I, _P])
+_lib.declare("oi_attention_tcgen05_status", [ctypes.POINTER(c_int)])
+
+# prompt tiles through the tcgen05 / TMEM / TMA kernel where it covers the shape (head_dim 128, a group
+# that divides 128, pages of 16/32/64/... keys); the mma.sync kernel otherwise
+USE_TCGEN05 = True
 
 ROWS_PER_CTA = 64          # query rows (tokens x group) of a small tile
 ROWS_PER_CTA_LARGE = 128   # of a large tile, used when some portion fills one
@@ -197,6 +206,22 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
     return plan
 
 
+def _tcgen05_takes(plan, q, out, k_cache, page_size, nq, nkv, hd, page_stride) -> bool:
+    group = nq // nkv
+    return (USE_TCGEN05 and hd == 128 and plan.rows_per_cta == ROWS_PER_CTA_LARGE and not plan.tile_split
+            and ROWS_PER_CTA_LARGE % group == 0 and page_size >= 16 and page_size & (page_size - 1) == 0
+            and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and page_stride % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and k_cache.data_ptr() % 16 == 0)
+
+
+def tcgen05_status() -> int:
+    """0, or the code of the bounded wait that ran out in the tcgen05 attention kernel since the
+    last call (synchronises the device)."""
+    v = c_int(0)
+    _lib.check(_lib.load().oi_attention_tcgen05_status(ctypes.byref(v)), "attention_tcgen05_status")
+    return v.value
+
+
 def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window) -> bool:
     """The tensor-core kernels, when they cover the shape: bfloat16, head_dim 32, 64 or 128."""
     if q.dtype != torch.bfloat16 or hd not in (32, 64, 128) or nq // nkv > ROWS_PER_CTA_LARGE:
@@ -210,7 +235,13 @@ def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nk
     po = 0 if plan.part_o is None else plan.part_o.data_ptr()
     pl = 0 if plan.part_lse is None else plan.part_lse.data_ptr()
     win = int(window) if window else 0
-    if plan.num_tile_items:
+    if plan.num_tile_items and _tcgen05_takes(plan, q, out, k_cache, ctx.cache.page_size, nq, nkv, hd, page_stride):
+        _lib.check(L.oi_attention_tcgen05(
+            q.data_ptr(), q.stride(0), q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            int(page_stride), ctx.cache.page_size, k_cache.shape[0], bt.data_ptr(), bt.stride(0),
+            ctx.cu_seqlens.data_ptr(), group_step.kv_lens.data_ptr(), plan.tile_items.data_ptr(), plan.num_tile_items,
+            nq, nkv, hd, float(scale), win, stream), "attention_tcgen05")
+    elif plan.num_tile_items:
         _lib.check(L.oi_attention_mma(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
             int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),

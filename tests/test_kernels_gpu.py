@@ -387,6 +387,7 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
         if force_splits:
             A.plan_items = old
     assert ran
+    assert A.tcgen05_status() == 0, "a bounded wait ran out in the tcgen05 attention kernel"
     plan = next(iter(ctx.scratch.values()))
     scale = 1.0 / math.sqrt(hd)
     row = 0
@@ -402,11 +403,16 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
     return plan
 
 
+@pytest.mark.parametrize("tcgen05", [True, False])
 @pytest.mark.parametrize("nq,nkv,hd,P,window", [
     (32, 8, 128, 16, None), (6, 2, 32, 16, None), (8, 2, 64, 8, None), (3, 1, 128, 4, None),
-    (16, 16, 64, 16, None), (5, 1, 32, 1, None), (8, 2, 128, 16, 100), (4, 2, 64, 16, 17), (64, 1, 32, 16, None)])
-def test_attention_mma_mixed_batch(nq, nkv, hd, P, window):
-    """Prompt portions over cached prefixes beside single decoded tokens, in one launch."""
+    (16, 16, 64, 16, None), (5, 1, 32, 1, None), (8, 2, 128, 16, 100), (4, 2, 64, 16, 17), (64, 1, 32, 16, None),
+    (2, 2, 128, 32, None), (16, 2, 128, 64, 70), (4, 1, 128, 128, None)])
+def test_attention_mma_mixed_batch(nq, nkv, hd, P, window, tcgen05, monkeypatch):
+    """Prompt portions over cached prefixes beside single decoded tokens, in one launch; the tiles
+    through the tcgen05 kernel where it covers the shape, and through the mma.sync kernel."""
+    from openinfer_b200.kernels import attention as A
+    monkeypatch.setattr(A, "USE_TCGEN05", tcgen05)
     q_lens = [9, 1, 70, 1, 33, 2]
     kv_lens = [70, 131, 70, 1, 300, 65]
     plan = _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens)
