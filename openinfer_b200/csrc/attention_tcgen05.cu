@@ -177,15 +177,19 @@ constexpr int kOffBar = kOffP + kPBytes;
 // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_full
 constexpr int kNumBars = 1 + 2 * kStages + 2 + 2;
 constexpr float kRescaleThreshold = 8.f;           // in log2 units: P stays below 2^8
-constexpr int kSmemTotal = kOffBar + kNumBars * 8 + 16 + 1024;
+constexpr int kSmemTotal = kOffBar + kNumBars * 8 + 16;   // 112 KB + barriers: two CTAs per SM
 constexpr unsigned kTmemCols = 256;                // S0 [0,64) S1 [64,128) O_tile [128,256)
 
 __global__ void __launch_bounds__(kThreads)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // the swizzled tiles need a 1024-byte aligned base; no slack is added for it (two CTAs must fit on an SM)
+  extern __shared__ __align__(1024) unsigned char smem[];
   const unsigned sbase = smem_u32(smem);
+  if (sbase & 1023u) {                 // never seen; refuse rather than compute garbage
+    if (threadIdx.x == 0) atomicCAS(&g_attn_error, 0, 9);
+    return;
+  }
   const unsigned bar0 = sbase + kOffBar;
   const unsigned q_full = bar0;
   auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
