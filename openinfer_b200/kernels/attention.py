@@ -45,14 +45,7 @@ import numpy as np  # noqa: E402
 from . import lib as _lib  # noqa: E402
 
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
-_lib.declare("oi_attention_mma", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I,
-                                  _F, _I, _P, _P, _I, _I, _P])
-_lib.declare("oi_attention_decode", [_P, _I, _P, _I, _P, _P, _L, _I, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I,
-                                     _F, _I, _P, _P, _I, _P])
 
-_lib.declare("oi_attention_tcgen05", [_P, _L, _I, _P, _I, _P, _P, _L, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I,
-                                      _F, _I, _P])
-_lib.declare("oi_attention_tcgen05_status", [ctypes.POINTER(c_int)])
 
 # prompt tiles through the tcgen05 / TMEM / TMA kernel where it covers the shape (head_dim 128, a group
 # that divides 128, pages of 16/32/64/... keys); the mma.sync kernel otherwise

@@ -9,11 +9,8 @@ import torch
 from . import lib as _lib
 from .lib import KernelError
 
-_lib.declare("oi_gemm_tcgen05", [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
-                                 c_int, c_int, c_int, c_int, c_int, c_void_p])
 
 ACT_BLOCK = 128   # gate rows per tile half of the fused gate/up product
-_lib.declare("oi_gemm_tcgen05_status", [ctypes.POINTER(c_int)])
 
 
 def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -31,6 +31,14 @@ _SIGNATURES = {
     "oi_gemm_generic": [P, I, P, I, P, I, I, I, I, L, L, L, P],
     "oi_argmax": [P, P, I, I, L, P, P, P],
     "oi_sample": [P, P, L, P, I, I, P, P, P, P, P, P],
+    "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, I, P],
+    "oi_gemm_tcgen05": [P, I, L, P, L, P, L, I, I, I, I, I, P],
+    "oi_gemm_tcgen05_status": [ctypes.POINTER(c_int)],
+    "oi_attention_mma": [P, I, P, I, P, P, L, I, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P, P, I, I, P],
+    "oi_attention_decode": [P, I, P, I, P, P, L, I, P, I, P, P, P, I, P, I, I, I, I, F, I, P, P, I, P],
+    "oi_attention_tcgen05": [P, L, I, P, I, P, P, L, I, I, P, I, P, P, P, I, I, I, I, F, I, P],
+    "oi_attention_tcgen05_status": [ctypes.POINTER(c_int)],
+    "oi_argmax_noalloc": [P, P, I, I, L, P],
 }
 
 
@@ -66,13 +74,13 @@ def load(verbose: bool = True) -> ctypes.CDLL:
         return lib
 
 
-# entry points added by later source files; declared when present
+# entry points of code outside this package (an extension's own kernels linked into the library)
 _OPTIONAL = {}
 
 
 def declare(name: str, argtypes) -> None:
-    """Register the signature of a further entry point (used by the wrappers of
-    kernels that live in their own source files)."""
+    """Register the signature of a further entry point. Every entry point of this package is listed
+    in ``_SIGNATURES`` above, so that none can be called with undeclared (32-bit) arguments."""
     _OPTIONAL[name] = argtypes
     if _lib is not None:
         _declare_optional(_lib)

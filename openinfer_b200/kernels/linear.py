@@ -17,8 +17,6 @@ import torch
 from . import lib as _lib
 from . import ops
 
-_lib.declare("oi_gemm_skinny", [c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
 
 # programmatic dependent launch of the decode products (see gemm_skinny.cu)
 import os as _os  # noqa: E402
