@@ -35,7 +35,15 @@ TINY_D = dict(
     num_hidden_layers=2, hidden_size=160, num_attention_heads=3, num_key_value_heads=1, head_dim=128,
     intermediate_size=272, vocab_size=300, rope_theta=10000.0, rms_norm_eps=1e-5,
     tie_word_embeddings=False, max_position_embeddings=1024)
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+# Real head geometry at reduced depth and vocabulary: head 128 with a group of 2, an intermediate size
+# that is a multiple of 128: the shapes the tcgen05 kernels (products, fused gate/up, prompt attention),
+# the skinny decode products and the split decode attention take in the engine.
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=512, num_attention_heads=8, num_key_value_heads=4, head_dim=128,
+    intermediate_size=1536, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, max_position_embeddings=2048)
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 # Stated tolerances (never widened to make a cutting pass; every cutting uses the same).
 #  float32: both sides sum in float32 in different orders; logits are O(1).

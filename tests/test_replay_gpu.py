@@ -11,7 +11,8 @@ from helpers import (TINY, assert_close, make_model_folder, random_tokens, repla
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 47, 130, 200, 77, 33], "B": [1, 9, 70, 150, 261, 40], "C": [3, 64, 129, 300, 65], "D": [2, 100, 257, 33]}
+LENGTHS = {"A": [5, 47, 130, 200, 77, 33], "B": [1, 9, 70, 150, 261, 40], "C": [3, 64, 129, 300, 65], "D": [2, 100, 257, 33],
+           "E": [400, 130, 1, 260, 17]}
 
 
 @pytest.fixture(scope="module")
@@ -50,7 +51,7 @@ def _check(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 def test_cuttings_match_plain(folders, workloads, name, dtype, mode):
     cfg, reqs, ref = workloads[name]
@@ -66,12 +67,14 @@ def test_cuttings_match_plain(folders, workloads, name, dtype, mode):
         max_tokens = biggest + 128
         steps = trace_mixed(reqs, max_tokens, seed=7)
         assert max(len(s["entries"]) for s in steps) >= 2
-    page = {"A": 8, "B": 16, "C": 16, "D": 32}[name]
+    page = {"A": 8, "B": 16, "C": 16, "D": 32, "E": 16}[name]
     runner = _runner(folders[name], dtype, max_tokens, page_size=page)
     got = replay_in_process(runner, steps)
     _check(got, ref, dtype, f"{name}/{dtype}/{mode}")
     runner.cache.check()
     assert runner.cache.min_free_pages() == runner.cache.num_pages, "pages were not all given back"
+    from openinfer_b200.kernels import attention as A, gemm_tcgen05 as G
+    assert A.tcgen05_status() == 0 and G.status() == 0, "a bounded wait ran out in a tcgen05 kernel"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -102,7 +105,7 @@ def test_first_tokens_and_long_decode(folders, workloads):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["B", "C", "D"])
+@pytest.mark.parametrize("name", ["B", "C", "D", "E"])
 def test_decode_steps_replayed_as_cuda_graphs(folders, workloads, name, dtype):
     """Steps that bring one token per request run as recorded CUDA graphs (padded to a batch
     bucket, key slices fixed by the bucket); the logits must not notice."""
