@@ -33,6 +33,12 @@ QWEN3_8B = dict(
     num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
     vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
     max_position_embeddings=4096)
+# BASELINE configs[3] and [4]: the other two Qwen3 sizes (selected with --model)
+QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600)
+MODELS = {"8b": ("Qwen3-8B sizes", QWEN3_8B), "0.6b": ("Qwen3-0.6B sizes", QWEN3_06B), "32b": ("Qwen3-32B sizes", QWEN3_32B)}
 CONTEXT = 2048
 PAGE = 16
 PREFILL_TOKENS = 2048
@@ -117,6 +123,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--model", default="8b", choices=sorted(MODELS), help="layer sizes (default: the headline 8B)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points and the prefill")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
@@ -144,7 +151,8 @@ def main() -> int:
     from openinfer_b200.sampling.params import SamplingParams
 
     peaks, peaks_src = read_peaks()
-    cfg_dict = dict(QWEN3_8B)
+    model_name, model_cfg = MODELS[args.model]
+    cfg_dict = dict(model_cfg)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
@@ -260,13 +268,13 @@ def main() -> int:
     e2e["h2d_bytes_per_step"] = int(runner._staging_last_bytes) if hasattr(runner, "_staging_last_bytes") else None
 
     out = {
-        "metric": "decode tokens/s (Qwen3-8B sizes, random weights, batch 8, context 2048)",
+        "metric": f"decode tokens/s ({model_name}, random weights, batch {B}, context 2048)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (random weights, uniform random token ids)",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-8B sizes", "layers": config.num_hidden_layers, "layers_full": full_layers,
+            "model": model_name, "layers": config.num_hidden_layers, "layers_full": full_layers,
             "hidden": config.hidden_size, "q_heads": config.num_attention_heads,
             "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
             "intermediate": config.intermediate_size, "vocab": config.vocab_size,
