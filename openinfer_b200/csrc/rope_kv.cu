@@ -75,8 +75,9 @@ __global__ void qk_norm_rope_kv_kernel(
 
 // bfloat16 fast path: a lane handles PAIRS of neighbouring elements with 4-byte accesses (the
 // element (2p, 2p+1) of the first rotary half together with its partner pair in the second half),
-// so a head of 128 is two loads, two table reads and two stores per lane. The grid is
-// (tokens, heads / 4): no division to find a warp's token and head.
+// so a head of 128 is two loads and two stores per lane. A warp walks over `heads_per_warp` heads of
+// ONE token: the position, the cache slot, the cos/sin values and the norm weights of its lanes are
+// fetched once and reused for every head.
 template <typename TW>   // storage type of the norm weights
 __global__ void qk_norm_rope_kv_bf16x2_kernel(
     bf16* __restrict__ qkv, int row_stride, int nq, int nkv, int hd,
@@ -84,82 +85,96 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
     float w_offset, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
     int rot_half, int max_pos, const int* __restrict__ positions, const int* __restrict__ slots,
     bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, long long page_stride, int page_size,
-    int heads_total) {
+    int heads_total, int heads_per_warp) {
   const int lane = threadIdx.x & 31;
   const int token = blockIdx.x;
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (head >= heads_total) return;
-  bf16* src = qkv + (size_t)token * row_stride + head * hd;
-  const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
-  bf16* dst = src;
-  if (kind != 0) {
-    const int slot = slots[token];
-    if (slot < 0) return;
-    const int kvh = kind == 1 ? head - nq : head - nq - nkv;
-    bf16* base = kind == 1 ? k_cache : v_cache;
-    dst = base + (size_t)(slot / page_size) * page_stride + (size_t)((slot % page_size) * nkv + kvh) * hd;
-  }
+  const int head0 = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * heads_per_warp;
+  if (head0 >= heads_total) return;
+  const int head1 = min(heads_total, head0 + heads_per_warp);
   const int npairs = hd / 2;
-  const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
-  __nv_bfloat162* dst2 = reinterpret_cast<__nv_bfloat162*>(dst);
-  if (kind == 2) {
-    for (int p = lane; p < npairs; p += 32) dst2[p] = src2[p];
-    return;
-  }
-  const TW* w = kind == 0 ? q_norm_w : k_norm_w;
   const int rot_pairs = rot_half / 2;          // pairs in one rotary half
   int pos = positions[token];
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const int slot = slots ? slots[token] : -1;
+  const size_t cache_off = slot >= 0 ? (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * nkv * hd : 0;
   const float2* cos2 = reinterpret_cast<const float2*>(cos_tab + (size_t)pos * rot_half);
   const float2* sin2 = reinterpret_cast<const float2*>(sin_tab + (size_t)pos * rot_half);
-  // all loads first: a lane holds at most 2 (pair, partner pair) sets (hd <= 256)
+  // per-lane constants: a lane holds at most 2 (pair, partner pair) sets (hd <= 256)
   constexpr int kMax = 2;
-  float2 a[kMax], b[kMax], c[kMax], sn[kMax], wa[kMax], wb[kMax];
-  float ss = 0.f;
+  float2 c[kMax], sn[kMax], wqa[kMax], wqb[kMax], wka[kMax], wkb[kMax];
 #pragma unroll
   for (int k = 0; k < kMax; ++k) {
     const int p = lane + 32 * k;
     if (p < rot_pairs) {
-      a[k] = __bfloat1622float2(src2[p]);
-      b[k] = __bfloat1622float2(src2[p + rot_pairs]);
       c[k] = cos2[p];
       sn[k] = sin2[p];
-      if (w) {
-        wa[k] = make_float2(w_offset + to_f32(w[2 * p]), w_offset + to_f32(w[2 * p + 1]));
-        wb[k] = make_float2(w_offset + to_f32(w[2 * p + rot_half]), w_offset + to_f32(w[2 * p + rot_half + 1]));
+      if (q_norm_w) {
+        wqa[k] = make_float2(w_offset + to_f32(q_norm_w[2 * p]), w_offset + to_f32(q_norm_w[2 * p + 1]));
+        wqb[k] = make_float2(w_offset + to_f32(q_norm_w[2 * p + rot_half]), w_offset + to_f32(q_norm_w[2 * p + rot_half + 1]));
       }
-      ss += a[k].x * a[k].x + a[k].y * a[k].y + b[k].x * b[k].x + b[k].y * b[k].y;
+      if (k_norm_w) {
+        wka[k] = make_float2(w_offset + to_f32(k_norm_w[2 * p]), w_offset + to_f32(k_norm_w[2 * p + 1]));
+        wkb[k] = make_float2(w_offset + to_f32(k_norm_w[2 * p + rot_half]), w_offset + to_f32(k_norm_w[2 * p + rot_half + 1]));
+      }
     }
   }
-  for (int p = 2 * rot_pairs + lane; p < npairs; p += 32) {   // dims beyond the rotary part
-    const float2 t = __bfloat1622float2(src2[p]);
-    ss += t.x * t.x + t.y * t.y;
-  }
-  float inv = 1.f;
-  if (w) {
-    ss = warp_sum(ss);
-    inv = rsqrtf(ss / (float)hd + eps);
-  }
+  bf16* row = qkv + (size_t)token * row_stride;
+  for (int head = head0; head < head1; ++head) {
+    const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
+    const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(row + head * hd);
+    __nv_bfloat162* dst2 = const_cast<__nv_bfloat162*>(src2);   // q: in place
+    if (kind != 0) {
+      if (slot < 0) continue;    // a padding row: nothing to store
+      const int kvh = kind == 1 ? head - nq : head - nq - nkv;
+      dst2 = reinterpret_cast<__nv_bfloat162*>((kind == 1 ? k_cache : v_cache) + cache_off + (size_t)kvh * hd);
+    }
+    if (kind == 2) {
+      for (int p = lane; p < npairs; p += 32) dst2[p] = src2[p];
+      continue;
+    }
+    const TW* w = kind == 0 ? q_norm_w : k_norm_w;
+    float2 a[kMax], b[kMax];
+    float ss = 0.f;
 #pragma unroll
-  for (int k = 0; k < kMax; ++k) {
-    const int p = lane + 32 * k;
-    if (p < rot_pairs) {
-      float2 x = a[k], y = b[k];
-      if (w) {
-        x.x *= inv * wa[k].x; x.y *= inv * wa[k].y;
-        y.x *= inv * wb[k].x; y.y *= inv * wb[k].y;
+    for (int k = 0; k < kMax; ++k) {
+      const int p = lane + 32 * k;
+      if (p < rot_pairs) {
+        a[k] = __bfloat1622float2(src2[p]);
+        b[k] = __bfloat1622float2(src2[p + rot_pairs]);
+        ss += a[k].x * a[k].x + a[k].y * a[k].y + b[k].x * b[k].x + b[k].y * b[k].y;
       }
-      dst2[p] = __floats2bfloat162_rn(x.x * c[k].x - y.x * sn[k].x, x.y * c[k].y - y.y * sn[k].y);
-      dst2[p + rot_pairs] = __floats2bfloat162_rn(x.x * sn[k].x + y.x * c[k].x, x.y * sn[k].y + y.y * c[k].y);
     }
-  }
-  for (int p = 2 * rot_pairs + lane; p < npairs; p += 32) {
-    float2 t = __bfloat1622float2(src2[p]);
+    for (int p = 2 * rot_pairs + lane; p < npairs; p += 32) {   // dims beyond the rotary part
+      const float2 t = __bfloat1622float2(src2[p]);
+      ss += t.x * t.x + t.y * t.y;
+    }
+    float inv = 1.f;
     if (w) {
-      t.x *= inv * (w_offset + to_f32(w[2 * p]));
-      t.y *= inv * (w_offset + to_f32(w[2 * p + 1]));
+      ss = warp_sum(ss);
+      inv = rsqrtf(ss / (float)hd + eps);
     }
-    dst2[p] = __floats2bfloat162_rn(t.x, t.y);
+#pragma unroll
+    for (int k = 0; k < kMax; ++k) {
+      const int p = lane + 32 * k;
+      if (p < rot_pairs) {
+        float2 x = a[k], y = b[k];
+        if (w) {
+          const float2 wa = kind == 0 ? wqa[k] : wka[k], wb = kind == 0 ? wqb[k] : wkb[k];
+          x.x *= inv * wa.x; x.y *= inv * wa.y;
+          y.x *= inv * wb.x; y.y *= inv * wb.y;
+        }
+        dst2[p] = __floats2bfloat162_rn(x.x * c[k].x - y.x * sn[k].x, x.y * c[k].y - y.y * sn[k].y);
+        dst2[p + rot_pairs] = __floats2bfloat162_rn(x.x * sn[k].x + y.x * c[k].x, x.y * sn[k].y + y.y * c[k].y);
+      }
+    }
+    for (int p = 2 * rot_pairs + lane; p < npairs; p += 32) {
+      float2 t = __bfloat1622float2(src2[p]);
+      if (w) {
+        t.x *= inv * (w_offset + to_f32(w[2 * p]));
+        t.y *= inv * (w_offset + to_f32(w[2 * p + 1]));
+      }
+      dst2[p] = __floats2bfloat162_rn(t.x, t.y);
+    }
   }
 }
 
@@ -188,17 +203,19 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
   } else if (dtype == OI_BF16 && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 && tokens <= 2147483647 &&
              (uintptr_t)qkv % 4 == 0 && page_stride % 2 == 0 && (!write_kv || ((uintptr_t)k_cache % 4 == 0 && (uintptr_t)v_cache % 4 == 0)) &&
              (uintptr_t)cos_tab % 8 == 0 && (uintptr_t)sin_tab % 8 == 0) {
-    const dim3 grid(tokens, (heads_total + 3) / 4);
+    // few tokens (decode): one head per warp for parallelism; many tokens: a warp walks over 8 heads
+    const int heads_per_warp = tokens >= 256 ? 8 : 1;
+    const dim3 grid(tokens, (heads_total + 4 * heads_per_warp - 1) / (4 * heads_per_warp));
     if (norm_dtype == OI_BF16)
       qk_norm_rope_kv_bf16x2_kernel<bf16><<<grid, 128, 0, s>>>(
           (bf16*)qkv, row_stride, nq, nkv, hd, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, w_offset, cos_tab,
           sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
-          heads_total);
+          heads_total, heads_per_warp);
     else
       qk_norm_rope_kv_bf16x2_kernel<float><<<grid, 128, 0, s>>>(
           (bf16*)qkv, row_stride, nq, nkv, hd, (const float*)q_norm_w, (const float*)k_norm_w, eps, w_offset, cos_tab,
           sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
-          heads_total);
+          heads_total, heads_per_warp);
   } else if (dtype == OI_BF16) {
     qk_norm_rope_kv_kernel<bf16><<<blocks, 128, 0, s>>>(
         (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,

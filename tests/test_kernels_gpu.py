@@ -557,3 +557,38 @@ def test_silu_mul_block_layout(dtype):
     ops.silu_mul(out, gu, block)
     ref = g.float() / (1 + torch.exp(-g.float())) * u.float()
     assert torch.allclose(out.float(), ref, **tol(dtype))
+
+
+@pytest.mark.parametrize("nq,nkv,hd,rot", [(8, 2, 128, 128), (5, 1, 64, 32), (3, 3, 32, 32)])
+def test_qk_norm_rope_kv_write_many_tokens(nq, nkv, hd, rot):
+    """Prompt-sized launches take the path in which a warp walks over several heads of a token."""
+    from openinfer_b200.kernels import ops
+    from openinfer_b200.parts.position import RotaryEncoding
+    from openinfer_b200.parts.spec import PositionSpec
+    torch.manual_seed(hd)
+    dtype = torch.bfloat16
+    T, P, theta, eps, max_pos = 300, 16, 1e6, 1e-6, 512
+    pages = 24
+    width = (nq + 2 * nkv) * hd
+    qkv = torch.randn(T, width, device=DEV).to(dtype)
+    src = qkv.clone().float().cpu()
+    positions = torch.randint(0, max_pos, (T,), dtype=torch.int32)
+    slots = torch.randperm(pages * P)[:T].to(torch.int32)
+    slots[7] = -1
+    qw, kw = (1 + 0.1 * torch.randn(hd)).to(dtype), (1 + 0.1 * torch.randn(hd)).to(dtype)
+    cos, sin = RotaryEncoding(PositionSpec("rope", rot, theta, max_pos)).rotation_tables(torch.device(DEV))
+    cache = torch.zeros(2, pages, P, nkv, hd, device=DEV, dtype=dtype)   # [k/v, pages, P, nkv, hd]
+    ops.qk_norm_rope_kv(qkv, nq, nkv, hd, q_norm_w=qw.to(DEV), k_norm_w=kw.to(DEV), eps=eps, weight_offset=0.0,
+                        cos=cos, sin=sin, positions=positions.to(DEV), slots=slots.to(DEV), k_cache=cache[0],
+                        v_cache=cache[1], page_stride=cache.stride(1), page_size=P)
+    q_ref = _rope_ref(src[:, : nq * hd].view(T, nq, hd), positions, rot, theta, qw.float(), eps, 0.0)
+    k_ref = _rope_ref(src[:, nq * hd: (nq + nkv) * hd].view(T, nkv, hd), positions, rot, theta, kw.float(), eps, 0.0)
+    v_ref = src[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    assert torch.allclose(qkv[:, : nq * hd].float().cpu().view(T, nq, hd), q_ref, atol=2e-2, rtol=2e-2)
+    flat = cache.float().cpu().view(2, pages * P, nkv, hd)
+    ok = slots >= 0
+    assert torch.allclose(flat[0][slots[ok].long()], k_ref[ok], atol=2e-2, rtol=2e-2)
+    assert torch.equal(flat[1][slots[ok].long()], v_ref[ok])
+    untouched = torch.ones(pages * P, dtype=torch.bool)
+    untouched[slots[ok].long()] = False
+    assert flat[:, untouched].abs().sum() == 0
