@@ -78,7 +78,7 @@ __global__ void qk_norm_rope_kv_kernel(
 // so a head of 128 is two loads and two stores per lane. A warp walks over `heads_per_warp` heads of
 // ONE token: the position, the cache slot, the cos/sin values and the norm weights of its lanes are
 // fetched once and reused for every head.
-template <typename TW>   // storage type of the norm weights
+template <typename TW, int kMax>   // TW: storage type of the norm weights; kMax: pair sets per lane (1: rotary_dim <= 128)
 __global__ void qk_norm_rope_kv_bf16x2_kernel(
     bf16* __restrict__ qkv, int row_stride, int nq, int nkv, int hd,
     const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
@@ -99,8 +99,7 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
   const size_t cache_off = slot >= 0 ? (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * nkv * hd : 0;
   const float2* cos2 = reinterpret_cast<const float2*>(cos_tab + (size_t)pos * rot_half);
   const float2* sin2 = reinterpret_cast<const float2*>(sin_tab + (size_t)pos * rot_half);
-  // per-lane constants: a lane holds at most 2 (pair, partner pair) sets (hd <= 256)
-  constexpr int kMax = 2;
+  // per-lane constants: a lane holds kMax (pair, partner pair) sets
   float2 c[kMax], sn[kMax], wqa[kMax], wqb[kMax], wka[kMax], wkb[kMax];
 #pragma unroll
   for (int k = 0; k < kMax; ++k) {
@@ -203,19 +202,21 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
   } else if (dtype == OI_BF16 && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 && tokens <= 2147483647 &&
              (uintptr_t)qkv % 4 == 0 && page_stride % 2 == 0 && (!write_kv || ((uintptr_t)k_cache % 4 == 0 && (uintptr_t)v_cache % 4 == 0)) &&
              (uintptr_t)cos_tab % 8 == 0 && (uintptr_t)sin_tab % 8 == 0) {
-    // few tokens (decode): one head per warp for parallelism; many tokens: a warp walks over 8 heads
-    const int heads_per_warp = tokens >= 256 ? 8 : 1;
+    // few tokens (decode): one head per warp for parallelism; many tokens: a warp walks over 2 heads
+    const int heads_per_warp = tokens >= 256 ? 2 : 1;
     const dim3 grid(tokens, (heads_total + 4 * heads_per_warp - 1) / (4 * heads_per_warp));
-    if (norm_dtype == OI_BF16)
-      qk_norm_rope_kv_bf16x2_kernel<bf16><<<grid, 128, 0, s>>>(
-          (bf16*)qkv, row_stride, nq, nkv, hd, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, w_offset, cos_tab,
-          sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
-          heads_total, heads_per_warp);
-    else
-      qk_norm_rope_kv_bf16x2_kernel<float><<<grid, 128, 0, s>>>(
-          (bf16*)qkv, row_stride, nq, nkv, hd, (const float*)q_norm_w, (const float*)k_norm_w, eps, w_offset, cos_tab,
-          sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size,
-          heads_total, heads_per_warp);
+#define OI_ROPE_ARGS(TW_)                                                                                          \
+  (bf16*)qkv, row_stride, nq, nkv, hd, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps, w_offset, cos_tab, sin_tab, \
+      rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size, heads_total,     \
+      heads_per_warp
+    if (rot_half <= 64) {
+      if (norm_dtype == OI_BF16) qk_norm_rope_kv_bf16x2_kernel<bf16, 1><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(bf16));
+      else qk_norm_rope_kv_bf16x2_kernel<float, 1><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(float));
+    } else {
+      if (norm_dtype == OI_BF16) qk_norm_rope_kv_bf16x2_kernel<bf16, 2><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(bf16));
+      else qk_norm_rope_kv_bf16x2_kernel<float, 2><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(float));
+    }
+#undef OI_ROPE_ARGS
   } else if (dtype == OI_BF16) {
     qk_norm_rope_kv_kernel<bf16><<<blocks, 128, 0, s>>>(
         (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
