@@ -8,17 +8,17 @@
 //               the projection buffer, rows ordered token-major by a 3-D box), then per 64-key tile the
 //               K and V boxes of the pages the block table names (4-D maps over the layer's cache);
 //   warp 1      MMA issuer: per tile S = Q K^T (M 128, N 64, K 128: 8 instructions, both operands
-//               K-major in shared memory), and, once the softmax warps have put P into tensor memory,
-//               O += P V (M 128, N 128, K 64: 4 instructions, P read from tensor memory, V read
-//               MN-major as it lies in its page), accumulated in tensor memory over all tiles;
+//               K-major in shared memory), and, once the softmax warps have put P into shared memory,
+//               O += P V (M 128, N 128, K 64: 4 instructions, V read MN-major as it lies in its page),
+//               accumulated in tensor memory over all tiles;
 //   warps 2-5   one thread per query row: reads its row of S from tensor memory, masks, keeps the
 //               running maximum and sum in float32 (no shuffles: the row is the thread's own) and writes
-//               P as packed bfloat16 pairs over its row of S in tensor memory. P is taken relative to a REFERENCE maximum
+//               P as bfloat16 into the swizzled shared tile. P is taken relative to a REFERENCE maximum
 //               that is only moved when the true maximum has outgrown it by a factor 2^8; only then is
 //               the accumulator in tensor memory rescaled (load, multiply, store). At the end the
 //               thread reads its output row, divides by the sum and stores it.
 // S is double buffered so that the next tile's S is computed while this tile's softmax runs; two
-// CTAs fit on an SM (96 KB of shared memory, 256 columns of tensor memory each) and fill each
+// CTAs fit on an SM (112 KB of shared memory, 256 columns of tensor memory each) and fill each
 // other's gaps. Every mbarrier wait is bounded (two seconds): a wait that runs out sets an error word
 // and a flag that ends all roles, after which the CTA frees its tensor memory and returns.
 // No load uses cluster multicast.
@@ -119,15 +119,6 @@ __device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long de
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
       ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
-// A operand from tensor memory (row i of A in lane i, two consecutive k per 32-bit column)
-__device__ __forceinline__ void umma_bf16_ts(unsigned tmem_c, unsigned tmem_a, unsigned long long desc_b,
-                                             unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
-      ::"r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void umma_commit(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -178,13 +169,15 @@ __device__ __forceinline__ unsigned long long desc_mn_major(unsigned smem_addr, 
 constexpr int kQBytes = kRows * HD * 2;            // 32 KB: two halves [128 rows][64 dims]
 constexpr int kKBytes = kKeys * HD * 2;            // 16 KB: two halves [64 keys][64 dims]
 constexpr int kVBytes = kKeys * HD * 2;            // 16 KB
+constexpr int kPBytes = kRows * kKeys * 2;         // 16 KB: [128 rows][64 keys]
 constexpr int kOffK = kQBytes;
 constexpr int kOffV = kOffK + kStages * kKBytes;
-constexpr int kOffBar = kOffV + kStages * kVBytes;
+constexpr int kOffP = kOffV + kStages * kVBytes;
+constexpr int kOffBar = kOffP + kPBytes;
 // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_full
 constexpr int kNumBars = 1 + 2 * kStages + 2 + 2;
 constexpr float kRescaleThreshold = 8.f;           // in log2 units: P stays below 2^8
-constexpr int kSmemTotal = kOffBar + kNumBars * 8 + 16;   // 96 KB + barriers: two CTAs per SM
+constexpr int kSmemTotal = kOffBar + kNumBars * 8 + 16;   // 112 KB + barriers: two CTAs per SM
 constexpr unsigned kTmemCols = 256;                // S0 [0,64) S1 [64,128) O_tile [128,256)
 
 __global__ void __launch_bounds__(kThreads)
@@ -303,18 +296,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           ok = issue_s(t + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(p_full, (unsigned)t & 1, abort_flag, 4);   // P(t) is in tensor memory, O is rescaled
+        ok = mbar_wait(p_full, (unsigned)t & 1, abort_flag, 4);   // P(t) is in shared memory, O is rescaled
         if (!ok) break;
         tc_fence_after();
         const int s = t % kStages;
         const unsigned v_addr = sbase + kOffV + s * kVBytes;
-        const unsigned p_tmem = tmem + (unsigned)((t & 1) * kKeys);   // P(t) lies over S(t): 32 columns of bf16 pairs
+        const unsigned p_addr = sbase + kOffP;
 #pragma unroll
         for (int k = 0; k < kKeys / 16; ++k) {
-          // A: P, 16 keys = 8 columns of packed pairs
+          // A: P rows of 128 bytes (64 keys), 16 keys = 32 bytes along the row
           // B: V, 16 keys = two 8-key groups = 2048 bytes further; the second 64 dims kVBytes / 2 away
-          umma_bf16_ts(tmem + 128u, p_tmem + (unsigned)(k * 8), desc_mn_major(v_addr + k * 2048, kVBytes / 2), idesc_o,
-                       (t | k) != 0 ? 1u : 0u);
+          umma_bf16(tmem + 128u, desc_k_major(p_addr + k * 32), desc_mn_major(v_addr + k * 2048, kVBytes / 2), idesc_o,
+                    (t | k) != 0 ? 1u : 0u);
         }
         umma_commit(o_full);
         umma_commit(kv_empty(s));       // K(t) and V(t) have been read: the stage may be refilled
@@ -330,6 +323,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const unsigned lane_base = tmem + ((unsigned)(quarter * 32) << 16);
     float m_ref = -INFINITY;                            // the maximum P is taken relative to (raw score units)
     float l = 0.f;
+    unsigned char* p_row = smem + kOffP + r * 128;      // this row of the P tile (128 bytes, swizzled chunks)
     bool ok = true;
     for (int t = 0; t < num_tiles && ok; ++t) {
       const int key0 = lo + t * kKeys;
@@ -363,12 +357,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       // move the reference only when the maximum has outgrown it by 2^8 (or there is none yet)
       const bool move = m_tile > m_ref && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > kRescaleThreshold);
-      if (__any_sync(0xffffffffu, move && t > 0 && m_ref != -INFINITY)) {
-        // rescale this warp's rows of the accumulator in tensor memory (factor 1 for rows that stay);
-        // the previous tile's second product must have finished updating it
+      // the second product of the previous tile reads the P tile and updates O until o_full(t - 1)
+      if (t > 0) {
         ok = mbar_wait(o_full, (unsigned)(t - 1) & 1, abort_flag, 7);
         if (!ok) break;
         tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, move && t > 0 && m_ref != -INFINITY)) {
+        // rescale this warp's rows of the accumulator in tensor memory (factor 1 for rows that stay)
         const float f = (move && m_ref != -INFINITY) ? fast_exp2((m_ref - m_tile) * p.scale_log2) : 1.f;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
@@ -391,28 +387,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       if (move) m_ref = m_tile;
       const float base = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-      // P(t) = 2^(s * scale - m_ref * scale), rounded to bfloat16, two keys per 32-bit column, written
-      // over this row of S(t) in tensor memory (every thread has read its own row before)
+      // P(t) = 2^(s * scale - m_ref * scale), rounded to bfloat16, into the swizzled row
       float lsum[4] = {0.f, 0.f, 0.f, 0.f};
-      unsigned pk[kKeys / 2];
 #pragma unroll
-      for (int e = 0; e < kKeys / 2; ++e) {
-        const float p0 = fast_exp2(fmaf(sv[2 * e], p.scale_log2, -base));
-        const float p1 = fast_exp2(fmaf(sv[2 * e + 1], p.scale_log2, -base));
-        lsum[e & 3] += p0 + p1;
-        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);   // .x (low half) = the even key
-        pk[e] = *reinterpret_cast<const unsigned*>(&h);
+      for (int c = 0; c < 8; ++c) {
+        uint4 chunk;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&chunk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], p.scale_log2, -base));
+          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], p.scale_log2, -base));
+          lsum[e] += p0 + p1;
+          h[e] = __floats2bfloat162_rn(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = chunk;
       }
       l += (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
-      asm volatile(
-          "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-          "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-          "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
-          ::"r"(lane_base + (unsigned)((t & 1) * kKeys)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
-            "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]),
-            "r"(pk[15]), "r"(pk[16]), "r"(pk[17]), "r"(pk[18]), "r"(pk[19]), "r"(pk[20]), "r"(pk[21]), "r"(pk[22]), "r"(pk[23]),
-            "r"(pk[24]), "r"(pk[25]), "r"(pk[26]), "r"(pk[27]), "r"(pk[28]), "r"(pk[29]), "r"(pk[30]), "r"(pk[31]) : "memory");
-      asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+      // make the generic-proxy writes of P visible to the tensor core (async proxy), then hand over
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
