@@ -4,16 +4,22 @@
 //
 // A CTA owns 128 query rows of one (request, kv head): row r is (token r / group, head r % group),
 // as in the mma.sync kernels. Roles:
-//   warp 0      producer: one thread issues the TMA loads: the Q tile once (two 128 x 64 boxes out of
-//               the projection buffer, rows ordered token-major by a 3-D box), then per 64-key tile the
-//               K and V boxes of the pages the block table names (4-D maps over the layer's cache);
+//   warp 0      producer: the Q tile once (two 128 x 64 boxes out of the projection buffer, rows
+//               ordered token-major by a 3-D box), then per 64-key tile the K and V boxes of the pages
+//               the block table names (4-D maps over the layer's cache). Each box is issued by a lane
+//               of its own (a box of one 16-key page costs about 90 cycles of issue, one after the
+//               other from a single thread), page ids are read 32 at a time one round ahead, and K
+//               and V have barriers of their own: a K stage is free as soon as S has been computed
+//               from it, so the next K tiles never wait for a P V product;
 //   warp 1      MMA issuer: per tile S = Q K^T (M 128, N 64, K 128: 8 instructions, both operands
 //               K-major in shared memory), and, once the softmax warps have put P into shared memory,
 //               O += P V (M 128, N 128, K 64: 4 instructions, V read MN-major as it lies in its page),
 //               accumulated in tensor memory over all tiles;
 //   warps 2-5   one thread per query row: reads its row of S from tensor memory, masks, keeps the
 //               running maximum and sum in float32 (no shuffles: the row is the thread's own) and writes
-//               P as bfloat16 into the swizzled shared tile. P is taken relative to a REFERENCE maximum
+//               P as bfloat16 into the swizzled shared tile (the exponentials are computed into
+//               registers first, beside the previous tile's P V product, and stored once that product
+//               has released the tile). P is taken relative to a REFERENCE maximum
 //               that is only moved when the true maximum has outgrown it by a factor 2^8; only then is
 //               the accumulator in tensor memory rescaled (load, multiply, store). At the end the
 //               thread reads its output row, divides by the sum and stores it.
@@ -174,8 +180,8 @@ constexpr int kOffK = kQBytes;
 constexpr int kOffV = kOffK + kStages * kKBytes;
 constexpr int kOffP = kOffV + kStages * kVBytes;
 constexpr int kOffBar = kOffP + kPBytes;
-// barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_full
-constexpr int kNumBars = 1 + 2 * kStages + 2 + 2;
+// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_full
+constexpr int kNumBars = 1 + 4 * kStages + 2 + 2;
 constexpr float kRescaleThreshold = 8.f;           // in log2 units: P stays below 2^8
 constexpr int kSmemTotal = kOffBar + kNumBars * 8 + 16;   // 112 KB + barriers: two CTAs per SM
 constexpr unsigned kTmemCols = 256;                // S0 [0,64) S1 [64,128) O_tile [128,256)
@@ -192,11 +198,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   }
   const unsigned bar0 = sbase + kOffBar;
   const unsigned q_full = bar0;
-  auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bar0 + 8u * (1 + kStages + s); };
-  auto s_full = [&](int b) { return bar0 + 8u * (1 + 2 * kStages + b); };
-  const unsigned p_full = bar0 + 8u * (3 + 2 * kStages);
-  const unsigned o_full = bar0 + 8u * (4 + 2 * kStages);
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (1 + kStages + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (1 + 2 * kStages + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (1 + 3 * kStages + s); };
+  auto s_full = [&](int b) { return bar0 + 8u * (1 + 4 * kStages + b); };
+  const unsigned p_full = bar0 + 8u * (3 + 4 * kStages);
+  const unsigned o_full = bar0 + 8u * (4 + 4 * kStages);
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + kOffBar + kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -219,7 +227,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
+    }
     mbar_init(s_full(0), 1);
     mbar_init(s_full(1), 1);
     mbar_init(p_full, 4);      // one arrival per softmax warp
@@ -237,34 +248,56 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const unsigned tmem = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ producer
+    // ------------------------------------------------------------------ producer (the whole warp runs the loop)
     if (lane == 0) {
       // Q: rows (token, head) of this kv head's group; box (64 dims, group heads, 128 / group tokens)
       mbar_expect_tx(q_full, kQBytes);
       tma_load_3d(sbase, &map_q, 0, kvh * group, q_start + tok0, q_full);
       tma_load_3d(sbase + kQBytes / 2, &map_q, 64, kvh * group, q_start + tok0, q_full);
-      const int* bt = p.block_table + (size_t)req * p.bt_stride;
-      const int boxes = kKeys / p.box_keys;
-      for (int t = 0; t < num_tiles; ++t) {
-        const int s = t % kStages;
-        if (t >= kStages && !mbar_wait(kv_empty(s), (unsigned)((t / kStages) - 1) & 1, abort_flag, 1)) break;
-        mbar_expect_tx(kv_full(s), kKBytes + kVBytes);
-        const int key0 = lo + t * kKeys;
-        const unsigned k_dst = sbase + kOffK + s * kKBytes, v_dst = sbase + kOffV + s * kVBytes;
-        for (int b = 0; b < boxes; ++b) {
-          const int key = key0 + b * p.box_keys;
-          int col = key / p.page_size;
-          col = col < p.bt_stride ? col : p.bt_stride - 1;       // keys past the request are masked anyway
-          int page = bt[col];
-          page = page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
-          const int in_page = key % p.page_size;
-          const unsigned off = (unsigned)(b * p.box_keys) * 128u;   // rows of 128 bytes
-          tma_load_4d(k_dst + off, &map_k, 0, kvh, in_page, page, kv_full(s));
-          tma_load_4d(k_dst + kKBytes / 2 + off, &map_k, 64, kvh, in_page, page, kv_full(s));
-          tma_load_4d(v_dst + off, &map_v, 0, kvh, in_page, page, kv_full(s));
-          tma_load_4d(v_dst + kVBytes / 2 + off, &map_v, 64, kvh, in_page, page, kv_full(s));
+    }
+    const int* bt = p.block_table + (size_t)req * p.bt_stride;
+    const int boxes = kKeys / p.box_keys;
+    // Page ids come 32 boxes at a time, one per lane and one round ahead of their use, so that no copy
+    // waits for a read of the block table.
+    auto pages_of_round = [&](int round) {
+      const int key = lo + (round * 32 + lane) * p.box_keys;
+      int col = key / p.page_size;
+      col = col < p.bt_stride ? col : p.bt_stride - 1;           // keys past the request are masked anyway
+      const int page = bt[col];
+      return page < 0 ? 0 : (page >= p.num_pages ? p.num_pages - 1 : page);
+    };
+    int pages_now = pages_of_round(0), pages_next = pages_of_round(1);
+    bool ok = true;
+    for (int t = 0; t < num_tiles; ++t) {
+      const int s = t % kStages;
+      const int key0 = lo + t * kKeys;
+      int my_page[4];                                           // boxes <= 4 (pages of 16 keys and more)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int g = t * boxes + b;
+        if (b < boxes) {
+          if ((g & 31) == 0 && g > 0) { pages_now = pages_next; pages_next = pages_of_round((g >> 5) + 1); }
+          my_page[b] = __shfl_sync(0xffffffffu, pages_now, g & 31);
         }
       }
+      // every lane below 2 * boxes issues one copy of K and one of V: (box, half of the head dims)
+      const int my_box = lane >> 1, my_half = lane & 1;
+      int page = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) page = my_box == b ? my_page[b] : page;
+      const int in_page = (key0 + my_box * p.box_keys) & (p.page_size - 1);
+      const unsigned off = (unsigned)(my_box * p.box_keys) * 128u + (unsigned)my_half * (kKBytes / 2);   // rows of 128 bytes
+      const unsigned k_dst = sbase + kOffK + s * kKBytes + off, v_dst = sbase + kOffV + s * kVBytes + off;
+      if (t >= kStages) ok = mbar_wait(k_empty(s), (unsigned)((t / kStages) - 1) & 1, abort_flag, 1);
+      if (!ok) break;
+      if (lane == 0) mbar_expect_tx(k_full(s), kKBytes);
+      __syncwarp();
+      if (lane < 2 * boxes) tma_load_4d(k_dst, &map_k, my_half * 64, kvh, in_page, page, k_full(s));
+      if (t >= kStages) ok = mbar_wait(v_empty(s), (unsigned)((t / kStages) - 1) & 1, abort_flag, 5);
+      if (!ok) break;
+      if (lane == 0) mbar_expect_tx(v_full(s), kVBytes);
+      __syncwarp();
+      if (lane < 2 * boxes) tma_load_4d(v_dst, &map_v, my_half * 64, kvh, in_page, page, v_full(s));
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -276,7 +309,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       bool ok = mbar_wait(q_full, 0, abort_flag, 2);
       auto issue_s = [&](int t) {   // S(t) = Q K(t)^T into S buffer t & 1
         const int s = t % kStages;
-        if (!mbar_wait(kv_full(s), (unsigned)(t / kStages) & 1, abort_flag, 3)) return false;
+        if (!mbar_wait(k_full(s), (unsigned)(t / kStages) & 1, abort_flag, 3)) return false;
         tc_fence_after();
         const unsigned k_addr = sbase + kOffK + s * kKBytes;
         const unsigned tmem_s = tmem + (unsigned)((t & 1) * kKeys);
@@ -288,6 +321,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           umma_bf16(tmem_s, desc_k_major(a), desc_k_major(b), idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(s_full(t & 1));
+        umma_commit(k_empty(s));        // K(t) has been read: its stage may be refilled
         return true;
       };
       if (ok && num_tiles > 0) ok = issue_s(0);
@@ -296,10 +330,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           ok = issue_s(t + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(p_full, (unsigned)t & 1, abort_flag, 4);   // P(t) is in shared memory, O is rescaled
+        const int s = t % kStages;
+        ok = mbar_wait(v_full(s), (unsigned)(t / kStages) & 1, abort_flag, 10) &&
+             mbar_wait(p_full, (unsigned)t & 1, abort_flag, 4);   // P(t) is in shared memory, O is rescaled
         if (!ok) break;
         tc_fence_after();
-        const int s = t % kStages;
         const unsigned v_addr = sbase + kOffV + s * kVBytes;
         const unsigned p_addr = sbase + kOffP;
 #pragma unroll
@@ -310,7 +345,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     (t | k) != 0 ? 1u : 0u);
         }
         umma_commit(o_full);
-        umma_commit(kv_empty(s));       // K(t) and V(t) have been read: the stage may be refilled
+        umma_commit(v_empty(s));        // V(t) has been read
       }
     }
   } else {
@@ -357,15 +392,34 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       // move the reference only when the maximum has outgrown it by 2^8 (or there is none yet)
       const bool move = m_tile > m_ref && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > kRescaleThreshold);
+      // P(t) = 2^(s * scale - m_ref * scale), rounded to bfloat16, kept in registers: the second product
+      // of the previous tile still reads the P tile, and this arithmetic runs beside it
+      const bool rescale = move && t > 0 && m_ref != -INFINITY;
+      const float f = rescale ? fast_exp2((m_ref - m_tile) * p.scale_log2) : 1.f;
+      if (move) m_ref = m_tile;
+      const float base = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
+      float lsum[4] = {0.f, 0.f, 0.f, 0.f};
+      uint4 chunks[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&chunks[c]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], p.scale_log2, -base));
+          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], p.scale_log2, -base));
+          lsum[e] += p0 + p1;
+          h[e] = __floats2bfloat162_rn(p0, p1);
+        }
+      }
+      l = l * f + ((lsum[0] + lsum[1]) + (lsum[2] + lsum[3]));
       // the second product of the previous tile reads the P tile and updates O until o_full(t - 1)
       if (t > 0) {
         ok = mbar_wait(o_full, (unsigned)(t - 1) & 1, abort_flag, 7);
         if (!ok) break;
         tc_fence_after();
       }
-      if (__any_sync(0xffffffffu, move && t > 0 && m_ref != -INFINITY)) {
+      if (__any_sync(0xffffffffu, rescale)) {
         // rescale this warp's rows of the accumulator in tensor memory (factor 1 for rows that stay)
-        const float f = (move && m_ref != -INFINITY) ? fast_exp2((m_ref - m_tile) * p.scale_log2) : 1.f;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           unsigned v[32];
@@ -383,26 +437,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
         }
         asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-        l *= f;
       }
-      if (move) m_ref = m_tile;
-      const float base = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-      // P(t) = 2^(s * scale - m_ref * scale), rounded to bfloat16, into the swizzled row
-      float lsum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint4 chunk;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&chunk);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], p.scale_log2, -base));
-          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], p.scale_log2, -base));
-          lsum[e] += p0 + p1;
-          h[e] = __floats2bfloat162_rn(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = chunk;
-      }
-      l += (lsum[0] + lsum[1]) + (lsum[2] + lsum[3]);
+      for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = chunks[c];
       // make the generic-proxy writes of P visible to the tensor core (async proxy), then hand over
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       tc_fence_before();
