@@ -37,6 +37,7 @@ __device__ __forceinline__ Partial warp_best(Partial p) {
 // `scratch` is the address the host looked up; it equals g_argmax_scratch on this device.
 __global__ void argmax_noalloc_partial_kernel(Partial* __restrict__ scratch, const float* __restrict__ logits,
                                               int vocab, long long row_stride, int nchunks) {
+  pdl_start();
   __shared__ Partial sh[8];
   const int r = blockIdx.y, chunk = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
@@ -57,6 +58,7 @@ __global__ void argmax_noalloc_partial_kernel(Partial* __restrict__ scratch, con
 }
 
 __global__ void argmax_noalloc_final_kernel(int* __restrict__ out, const Partial* __restrict__ scratch, int nchunks) {
+  pdl_start();
   const int r = blockIdx.x;
   Partial best{-INFINITY, 0x7fffffff};
   for (int c = threadIdx.x; c < nchunks; c += 32) best = better(best, scratch[(size_t)r * nchunks + c]);
@@ -92,9 +94,9 @@ OI_API int oi_argmax_noalloc(int* out, const float* logits, int rows, int vocab,
   }
   Partial* scratch = g_scratch_addr[device];
   cudaStream_t s = (cudaStream_t)stream;
-  argmax_noalloc_partial_kernel<<<dim3((unsigned)nchunks, rows), 256, 0, s>>>(scratch, logits, vocab, row_stride, (int)nchunks);
+  oi_launch(argmax_noalloc_partial_kernel, dim3((unsigned)nchunks, rows), 256, 0, s, scratch, logits, vocab, row_stride, (int)nchunks);
   OI_CHECK_LAUNCH();
-  argmax_noalloc_final_kernel<<<rows, 32, 0, s>>>(out, scratch, (int)nchunks);
+  oi_launch(argmax_noalloc_final_kernel, rows, 32, 0, s, out, scratch, (int)nchunks);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

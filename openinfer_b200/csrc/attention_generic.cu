@@ -43,6 +43,7 @@ __global__ void attention_generic_kernel(
     const T* __restrict__ k_cache, const T* __restrict__ v_cache, long long page_stride, int page_size,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
     const int* __restrict__ positions, int nq, int nkv, int hd, float scale, int window, int tokens) {
+  pdl_start();
   __shared__ float q_sh[kWarps][ATTN_MAX_HD];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int token = blockIdx.x;
@@ -126,12 +127,12 @@ OI_API int oi_attention_generic(const void* q, int q_row_stride, void* out, int 
   dim3 grid(tokens, (nq + kWarps - 1) / kWarps);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == OI_F32) {
-    attention_generic_kernel<float, kWarps><<<grid, kWarps * 32, 0, s>>>(
+    oi_launch(attention_generic_kernel<float, kWarps>, grid, kWarps * 32, 0, s, 
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache,
         (const float*)v_cache, page_stride, page_size, block_table, bt_stride, token_req, positions, nq,
         nkv, hd, scale, window, tokens);
   } else if (dtype == OI_BF16) {
-    attention_generic_kernel<bf16, kWarps><<<grid, kWarps * 32, 0, s>>>(
+    oi_launch(attention_generic_kernel<bf16, kWarps>, grid, kWarps * 32, 0, s, 
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache,
         (const bf16*)v_cache, page_stride, page_size, block_table, bt_stride, token_req, positions, nq,
         nkv, hd, scale, window, tokens);

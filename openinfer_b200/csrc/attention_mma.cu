@@ -109,6 +109,7 @@ __device__ __forceinline__ void load_tile(bf16* smem, const bf16* cache, const A
 template <int HD, int MT>
 __global__ void __launch_bounds__(kThreads)
 attention_mma_kernel(const AttnParams p) {
+  pdl_start();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int kTileRows = 64 * MT;
   // [Q: kTileRows x HD][stage][K | V][kKeys][HD]
@@ -446,6 +447,7 @@ __device__ __forceinline__ void load_kv_tile16(bf16* k_smem, bf16* v_smem, const
 template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attention_decode_kernel(const AttnParams p) {
+  pdl_start();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // [warp][stage][K | V][16][HD]
@@ -645,8 +647,7 @@ template <int HD>
 __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_stride, const float* __restrict__ part_o,
                                        const float* __restrict__ part_lse, const int* __restrict__ row_splits,
                                        int nq, int max_splits, int tokens) {
-  // a programmatically launched product after this kernel may start streaming its weights now
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  pdl_start();
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gw >= (long long)tokens * nq) return;
@@ -698,7 +699,7 @@ int launch_tiles(const AttnParams& p, int num_items, cudaStream_t s) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  attention_mma_kernel<HD, MT><<<(unsigned)((long long)num_items * p.nkv), kThreads, smem, s>>>(p);
+  oi_launch(attention_mma_kernel<HD, MT>, (unsigned)((long long)num_items * p.nkv), kThreads, smem, s, p);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -710,7 +711,7 @@ int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens
   if (rc) return rc;
   if (any_split) {
     const long long warps = (long long)tokens * p.nq;
-    attention_merge_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(
+    oi_launch(attention_merge_kernel<HD>, (unsigned)((warps + 3) / 4), 128, 0, s, 
         p.out, p.out_row_stride, p.part_o, p.part_lse, row_splits, p.nq, p.max_splits, tokens);
     OI_CHECK_LAUNCH();
   }
@@ -726,10 +727,10 @@ int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int
     configured = true;
   }
   dim3 grid(num_items, p.nkv);
-  attention_decode_kernel<HD><<<grid, kDecWarps * 32, smem, s>>>(p);
+  oi_launch(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, p);
   OI_CHECK_LAUNCH();
   const long long warps = (long long)tokens * p.nq;
-  attention_merge_kernel<HD><<<(unsigned)((warps + 3) / 4), 128, 0, s>>>(
+  oi_launch(attention_merge_kernel<HD>, (unsigned)((warps + 3) / 4), 128, 0, s, 
       p.out, p.out_row_stride, p.part_o, p.part_lse, row_splits, p.nq, p.max_splits, tokens);
   OI_CHECK_LAUNCH();
   return OI_OK;

@@ -189,6 +189,7 @@ constexpr unsigned kTmemCols = 256;                // S0 [0,64) S1 [64,128) O_ti
 __global__ void __launch_bounds__(kThreads)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Params p) {
+  pdl_start();
   // the swizzled tiles need a 1024-byte aligned base; no slack is added for it (two CTAs must fit on an SM)
   extern __shared__ __align__(1024) unsigned char smem[];
   const unsigned sbase = smem_u32(smem);
@@ -558,7 +559,7 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     configured = true;
   }
-  attention_tcgen05_kernel<<<(unsigned)((long long)num_items * nkv), kThreads, kSmemTotal, (cudaStream_t)stream>>>(mq, mk, mv, p);
+  oi_launch(attention_tcgen05_kernel, (unsigned)((long long)num_items * nkv), kThreads, kSmemTotal, (cudaStream_t)stream, mq, mk, mv, p);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

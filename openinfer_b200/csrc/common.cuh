@@ -56,6 +56,57 @@ void oi_set_error(const char* fmt, ...);
 
 typedef __nv_bfloat16 bf16;
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch. Every kernel of the library is launched through oi_launch and
+// opens with pdl_start(): it lets the NEXT kernel on the stream be scheduled at once and then
+// waits until the kernel BEFORE it has finished and its writes are visible. Nothing that another
+// kernel writes or reads-then-overwrites is touched before that wait, so the memory effects stay
+// in stream order; what overlaps is the launch latency, the prologues, and in the weight-streaming
+// products the first loads of the (never written) weights, which they request before waiting.
+// A kernel launched without the attribute (oi_set_pdl(0), or after a library kernel) sees both
+// instructions as no-ops.
+// ---------------------------------------------------------------------------------------------
+int oi_pdl_enabled();
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_start() {
+  pdl_trigger();
+  pdl_wait();
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-serialization attribute when
+// enabled, and optionally a cluster of `cluster_x` CTAs along x. Check with OI_CHECK_LAUNCH().
+template <typename... Params, typename... Args>
+inline void oi_launch_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (oi_pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (cluster_x > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)cluster_x;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = na ? attr : nullptr;
+  cfg.numAttrs = (unsigned)na;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);   // the error stays for cudaGetLastError
+}
+template <typename... Params, typename... Args>
+inline void oi_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  oi_launch_cluster(kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 

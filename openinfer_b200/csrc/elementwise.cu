@@ -12,6 +12,7 @@
 template <typename TO, typename TW>
 __global__ void embedding_kernel(TO* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab) {
+  pdl_start();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host validates ids; never read outside
@@ -23,6 +24,7 @@ __global__ void embedding_kernel(TO* __restrict__ out, const TW* __restrict__ ta
 // same element type on both sides and rows that are whole 16-byte vectors: a plain copy
 __global__ void embedding_vec_kernel(uint4* __restrict__ out, const uint4* __restrict__ table,
                                      const int* __restrict__ ids, int vecs_per_row, int vocab) {
+  pdl_start();
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -41,16 +43,16 @@ OI_API int oi_embedding(void* out, int out_dtype, const void* table, int table_d
   if (out_dtype == table_dtype && (hidden * esize) % 16 == 0 &&
       ((uintptr_t)out % 16 == 0) && ((uintptr_t)table % 16 == 0)) {
     const int vecs = (int)(hidden * esize / 16);
-    embedding_vec_kernel<<<tokens, vecs < 256 ? ((vecs + 31) / 32) * 32 : 256, 0, s>>>(
+    oi_launch(embedding_vec_kernel, tokens, vecs < 256 ? ((vecs + 31) / 32) * 32 : 256, 0, s, 
         (uint4*)out, (const uint4*)table, ids, vecs, vocab);
   } else if (out_dtype == OI_F32 && table_dtype == OI_F32) {
-    embedding_kernel<float, float><<<tokens, 256, 0, s>>>((float*)out, (const float*)table, ids, hidden, vocab);
+    oi_launch(embedding_kernel<float, float>, tokens, 256, 0, s, (float*)out, (const float*)table, ids, hidden, vocab);
   } else if (out_dtype == OI_BF16 && table_dtype == OI_BF16) {
-    embedding_kernel<bf16, bf16><<<tokens, 256, 0, s>>>((bf16*)out, (const bf16*)table, ids, hidden, vocab);
+    oi_launch(embedding_kernel<bf16, bf16>, tokens, 256, 0, s, (bf16*)out, (const bf16*)table, ids, hidden, vocab);
   } else if (out_dtype == OI_F32 && table_dtype == OI_BF16) {
-    embedding_kernel<float, bf16><<<tokens, 256, 0, s>>>((float*)out, (const bf16*)table, ids, hidden, vocab);
+    oi_launch(embedding_kernel<float, bf16>, tokens, 256, 0, s, (float*)out, (const bf16*)table, ids, hidden, vocab);
   } else if (out_dtype == OI_BF16 && table_dtype == OI_F32) {
-    embedding_kernel<bf16, float><<<tokens, 256, 0, s>>>((bf16*)out, (const float*)table, ids, hidden, vocab);
+    oi_launch(embedding_kernel<bf16, float>, tokens, 256, 0, s, (bf16*)out, (const float*)table, ids, hidden, vocab);
   } else {
     OI_REQUIRE(false, "embedding: unknown dtype codes %d/%d", out_dtype, table_dtype);
   }
@@ -70,6 +72,7 @@ template <typename T, bool kCache>
 __global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* __restrict__ delta,
                                const void* __restrict__ w, int w_dtype, const int* __restrict__ row_idx,
                                int hidden, float eps, float w_offset) {
+  pdl_start();
   extern __shared__ float row_cache[];
   __shared__ float red[32];
   const int r = blockIdx.x;
@@ -104,10 +107,8 @@ template <int VPT>
 __global__ void rmsnorm_bf16_vec_kernel(bf16* __restrict__ out, bf16* __restrict__ x, const bf16* __restrict__ delta,
                                         const bf16* __restrict__ w, const int* __restrict__ row_idx, int hidden,
                                         float eps, float w_offset) {
+  pdl_start();
   __shared__ float red[32];
-  // let a dependent launch (the product that follows, if it was launched programmatically) start
-  // streaming its weights now; it still waits for this grid to finish before it reads `out`
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int r = blockIdx.x;
   const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
   const int nvec = hidden / 8;
@@ -178,7 +179,7 @@ static int launch_rmsnorm_bf16_vec(void* out, void* x, const void* delta, const 
     threads = (((nvec + vpt - 1) / vpt + 31) / 32) * 32;
   }
 #define OI_NORM_VEC(V)                                                                                       \
-  rmsnorm_bf16_vec_kernel<V><<<rows, threads, 0, s>>>((bf16*)out, (bf16*)x, (const bf16*)delta, (const bf16*)w, \
+  oi_launch(rmsnorm_bf16_vec_kernel<V>, rows, threads, 0, s, (bf16*)out, (bf16*)x, (const bf16*)delta, (const bf16*)w, \
                                                       row_idx, hidden, eps, w_offset)
   if (vpt == 1) OI_NORM_VEC(1);
   else if (vpt == 2) OI_NORM_VEC(2);
@@ -195,10 +196,10 @@ static int launch_rmsnorm(void* out, void* x, const void* delta, const void* w, 
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem <= 48 * 1024) {
-    rmsnorm_kernel<T, true><<<rows, threads, smem, s>>>((T*)out, (T*)x, (const T*)delta, w, w_dtype,
+    oi_launch(rmsnorm_kernel<T, true>, rows, threads, smem, s, (T*)out, (T*)x, (const T*)delta, w, w_dtype,
                                                         row_idx, hidden, eps, w_offset);
   } else {
-    rmsnorm_kernel<T, false><<<rows, threads, 0, s>>>((T*)out, (T*)x, (const T*)delta, w, w_dtype,
+    oi_launch(rmsnorm_kernel<T, false>, rows, threads, 0, s, (T*)out, (T*)x, (const T*)delta, w, w_dtype,
                                                       row_idx, hidden, eps, w_offset);
   }
   OI_CHECK_LAUNCH();
@@ -228,6 +229,7 @@ OI_API int oi_rmsnorm(void* out, void* x, const void* delta, int dtype, const vo
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void add_inplace_kernel(T* __restrict__ x, const T* __restrict__ delta, size_t n) {
+  pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     x[i] = from_f32<T>(to_f32(x[i]) + to_f32(delta[i]));
 }
@@ -237,8 +239,8 @@ OI_API int oi_add_inplace(void* x, const void* delta, int dtype, long long n, vo
   if (n == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-  if (dtype == OI_F32) add_inplace_kernel<float><<<blocks, 256, 0, s>>>((float*)x, (const float*)delta, (size_t)n);
-  else if (dtype == OI_BF16) add_inplace_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)x, (const bf16*)delta, (size_t)n);
+  if (dtype == OI_F32) oi_launch(add_inplace_kernel<float>, blocks, 256, 0, s, (float*)x, (const float*)delta, (size_t)n);
+  else if (dtype == OI_BF16) oi_launch(add_inplace_kernel<bf16>, blocks, 256, 0, s, (bf16*)x, (const bf16*)delta, (size_t)n);
   else OI_REQUIRE(false, "add: unknown dtype code %d", dtype);
   OI_CHECK_LAUNCH();
   return OI_OK;
@@ -252,6 +254,7 @@ OI_API int oi_add_inplace(void* x, const void* delta, int dtype, long long n, vo
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int block, size_t n) {
+  pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i - r * inter;
     const size_t gi = r * 2 * inter + (c / block) * 2 * block + (c % block);
@@ -264,6 +267,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
 // 8 bf16 per thread when inter and block are multiples of 8
 __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up,
                                        int inter8, int block8, size_t n8) {
+  pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter8, c = i - r * inter8;
     const size_t gi = r * 2 * inter8 + (c / block8) * 2 * block8 + (c % block8);
@@ -292,11 +296,11 @@ OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int 
   if (dtype == OI_BF16 && inter % 8 == 0 && block % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
     const size_t n8 = n / 8;
     const int blocks = (int)((n8 + 255) / 256 > 148 * 16 ? 148 * 16 : (n8 + 255) / 256);
-    silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8);
+    oi_launch(silu_mul_bf16x8_kernel, blocks, 256, 0, s, (uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8);
   } else {
     const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-    if (dtype == OI_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gate_up, inter, block, n);
-    else if (dtype == OI_BF16) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)gate_up, inter, block, n);
+    if (dtype == OI_F32) oi_launch(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, inter, block, n);
+    else if (dtype == OI_BF16) oi_launch(silu_mul_kernel<bf16>, blocks, 256, 0, s, (bf16*)out, (const bf16*)gate_up, inter, block, n);
     else OI_REQUIRE(false, "silu_mul: unknown dtype code %d", dtype);
   }
   OI_CHECK_LAUNCH();

@@ -14,6 +14,7 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_generic_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __restrict__ W, int M, int N,
                     int K, long long lda, long long ldw, long long ldc) {
+  pdl_start();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -66,7 +67,7 @@ template <typename TA, typename TW, typename TC>
 int launch(void* C, const void* A, const void* W, int M, int N, int K, long long lda, long long ldw,
            long long ldc, cudaStream_t s) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_generic_kernel<TA, TW, TC><<<grid, 256, 0, s>>>((TC*)C, (const TA*)A, (const TW*)W, M, N, K, lda, ldw, ldc);
+  oi_launch(gemm_generic_kernel<TA, TW, TC>, grid, 256, 0, s, (TC*)C, (const TA*)A, (const TW*)W, M, N, K, lda, ldw, ldc);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

@@ -63,12 +63,13 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
 __device__ __forceinline__ float silu(float g) { return g / (1.f + expf(-g)); }
 
 // NT: token tiles of 8 (M <= 8 * NT). kCluster: CTAs along K add up through distributed shared memory.
-// kPdl: launched with programmatic stream serialization: the weight ring is primed BEFORE waiting
-// for the kernel that produces x, so the first 40 KB of W per CTA stream in under its tail.
+// The weight ring is primed BEFORE waiting for the kernel that produces x (programmatic dependent
+// launch), so the first 40 KB of W per CTA stream in under its tail.
 template <int NT, typename TOut, bool kSiluMul, bool kCluster>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict__ x, long long ldx,
-                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int pdl, int act_block) {
+                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int act_block) {
+  pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int stride = row_stride_elems(k_slice);                 // elements per token row
   unsigned char* ring_raw = smem_raw;                           // [warp][stage][u][row a | row b][lane] 16 B
@@ -113,7 +114,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
   for (int s = 0; s < kStages - 1; ++s) issue();
 
   // ---- stage the activation slice (rows >= M are zero); x is the previous kernel's output
-  if (pdl) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  pdl_wait();
   {
     const int vec_per_row = k_slice / 8;
     for (int i = tid; i < 8 * NT * vec_per_row; i += kWarps * 32) {
@@ -172,7 +173,6 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
     }
   }
   cp_async_wait<0>();
-  if (pdl) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
   // ---- partial sums of this K slice: part[token][row in tile]
 #pragma unroll
@@ -219,47 +219,29 @@ size_t smem_bytes(int NT, int k_slice) {
 
 template <int NT, typename TOut, bool kSiluMul>
 int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N,
-           int K, int csize, int pdl, int act_block, cudaStream_t s) {
+           int K, int csize, int act_block, cudaStream_t s) {
   const int k_slice = K / csize;
   const size_t smem = smem_bytes(NT, k_slice);
   static size_t configured[2] = {0, 0};   // largest dynamic shared memory set so far, per kernel variant
   const int row_tiles = (N + kRowsPerCta - 1) / kRowsPerCta;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(csize, row_tiles, 1);
-  cfg.blockDim = dim3(kWarps * 32, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[2];
-  int na = 0;
-  if (pdl) {
-    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
+  const dim3 grid(csize, row_tiles, 1);
   if (csize > 1) {
     auto kernel = gemm_skinny_kernel<NT, TOut, kSiluMul, true>;
     if (smem > configured[1]) {
       OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured[1] = smem;
     }
-    attr[na].id = cudaLaunchAttributeClusterDimension;
-    attr[na].val.clusterDim.x = csize;
-    attr[na].val.clusterDim.y = 1;
-    attr[na].val.clusterDim.z = 1;
-    ++na;
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl, act_block));
+    oi_launch_cluster(kernel, grid, kWarps * 32, smem, s, csize, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K,
+                      k_slice, act_block);
   } else {
     auto kernel = gemm_skinny_kernel<NT, TOut, kSiluMul, false>;
     if (smem > configured[0]) {
       OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured[0] = smem;
     }
-    cfg.attrs = na ? attr : nullptr;
-    cfg.numAttrs = na;
-    OI_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, pdl, act_block));
+    oi_launch(kernel, grid, kWarps * 32, smem, s, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, act_block);
   }
+  OI_CHECK_LAUNCH();
   return OI_OK;
 }
 
@@ -268,10 +250,8 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
 // silu_mul != 0: x is a fused [M, 2K] gate|up buffer laid out in blocks of `silu_mul` gate values
 // followed by their up values (silu_mul == K: all gates, then all ups) and the activation
 // silu(gate) * up is formed on the fly. cluster_size in {1, 2, 4, 8}: the number of K slices (CTAs per cluster).
-// pdl != 0: launch with programmatic stream serialization (the weight stream starts while the
-// kernel before this one on the stream is still finishing; x is only read after it has finished).
 OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
-                          long long ldw, int M, int N, int K, int silu_mul, int cluster_size, int pdl, void* stream) {
+                          long long ldw, int M, int N, int K, int silu_mul, int cluster_size, void* stream) {
   OI_REQUIRE(M >= 1 && M <= 16, "gemm_skinny: M=%d outside 1..16", M);
   OI_REQUIRE(N >= 1 && K >= 32, "gemm_skinny: bad sizes N=%d K=%d", N, K);
   OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
@@ -284,7 +264,7 @@ OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x
   const size_t smem = smem_bytes(NT, K / cluster_size);
   OI_REQUIRE(smem <= 200 * 1024, "gemm_skinny: K slice %d needs %zu bytes of shared memory", K / cluster_size, smem);
   cudaStream_t s = (cudaStream_t)stream;
-#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, pdl, silu_mul, s)
+#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, silu_mul, s)
   if (out_dtype == OI_BF16) {
     if (NT == 1) { if (silu_mul) OI_SKINNY(1, bf16, true); else OI_SKINNY(1, bf16, false); }
     else         { if (silu_mul) OI_SKINNY(2, bf16, true); else OI_SKINNY(2, bf16, false); }

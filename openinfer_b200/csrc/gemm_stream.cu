@@ -1,0 +1,274 @@
+// out[M, N] = x[M, K] * W[N, K]^T for few rows of x (decode: M <= 128) as a weight STREAM through the
+// 5th-generation tensor cores. The product is formed transposed: 128 weight rows are the M side of
+// tcgen05.mma (operand A), the tokens its N side (operand B, padded to 16 / 32 / 64 / 128 by TMA's
+// zero fill), so a weight byte goes HBM -> TMA -> shared memory -> tensor core without passing
+// through a register, and the accumulator [128 weight rows x tokens] lies in tensor memory.
+//
+// Grid (c, ceil(N / 128)): a cluster of c CTAs along x shares one tile of 128 weight rows, CTA r of
+// the cluster streaming k blocks [r * kb_per_rank, ...) of it. Roles in a CTA:
+//   warp 0     one thread issues the TMA loads into a ring of stages (a [128 x 64] box of W with an
+//              evict-first L2 policy, a [tokens x 64] box of x); the first ring-full of WEIGHT boxes
+//              is requested before waiting for the kernel that produces x (programmatic dependent
+//              launch), so the stream starts under the predecessor's tail;
+//   warp 1     one thread issues four tcgen05.mma (K = 16 each) per stage, commits the stage back to
+//              the producer, and commits the accumulator once at the end;
+//   warps 2-5  read the accumulator (tcgen05.ld, one weight row per thread) and either store it
+//              (c = 1) or leave it as a float32 partial in shared memory.
+// With c > 1 the partials are added up through distributed shared memory in rank order (CTA r adds
+// rows [r * 128 / c, ...) of the tile over all ranks), so the result does not depend on timing.
+// Two CTAs fit on an SM (<= 112 KB of stages each). Every mbarrier wait is bounded (two seconds): a
+// wait that runs out sets an error word and a flag that ends all roles of the CTA, which still
+// joins its cluster's barriers, frees its tensor memory and returns. No load uses cluster multicast.
+//
+// The reference calls a library product for every projection, also in decode
+// (pegainfer-kernels/csrc/shared/linear.cu:312-362: bf16 in, float32 accumulate, row-major weight).
+#include <cooperative_groups.h>
+
+#include "tcgen05.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int BM = 128;                // weight rows per tile
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kThreads = 192;
+
+__device__ int g_stream_error = 0;     // set to a non-zero code when a bounded wait ran out
+
+template <int BN>
+struct Layout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (112 * 1024) / kStageBytes;            // 6, 5, 4, 3 for BN 16, 32, 64, 128
+  static constexpr int kBarOffset = kStages * kStageBytes;              // full[kStages], empty[kStages], acc_full
+  static constexpr int kNumBars = 2 * kStages + 1;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static_assert(BN * BM * 4 <= kBarOffset, "the partial sums reuse the stages");
+};
+
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(kThreads)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   TOut* __restrict__ out, long long ldc, int M, int N, int num_kb, int kb_per_rank) {
+  pdl_trigger();   // the next kernel may be scheduled now: it reads nothing of ours before we are done
+  using L = Layout<BN>;
+  constexpr int kStages = L::kStages;
+  // the swizzled tiles need a 1024-byte aligned base; no slack is added for it (two CTAs must fit on an SM)
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const unsigned smem_base = tc::smem_u32(smem);
+  const bool misaligned = (smem_base & 1023u) != 0;   // never seen; refuse rather than compute garbage
+  const unsigned bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  const unsigned acc_full = bar_base + 8u * (2 * kStages);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L::kBarOffset + L::kNumBars * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* part = reinterpret_cast<float*>(smem);        // [token][128 rows], written when the stages are drained
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = blockIdx.x, csize = gridDim.x;
+  const int n0 = blockIdx.y * BM;
+  const int kb0 = rank * kb_per_rank;
+  int nkb = num_kb - kb0;
+  nkb = nkb < kb_per_rank ? nkb : kb_per_rank;
+  nkb = nkb > 0 ? nkb : 0;
+  if (misaligned) {
+    nkb = 0;
+    if (threadIdx.x == 0) atomicCAS(&g_stream_error, 0, 9);
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(full_bar(s), 1);
+      tc::mbar_init(empty_bar(s), 1);
+    }
+    tc::mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tc::smem_u32(tmem_slot), L::kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before();
+  __syncthreads();
+  tc::fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const unsigned long long once = tc::policy_evict_first();
+      const int pre = nkb < kStages ? nkb : kStages;
+      for (int s = 0; s < pre; ++s) {
+        tc::mbar_expect_tx(full_bar(s), L::kStageBytes);
+        tc::tma_load_2d_hint(smem_base + s * L::kStageBytes, &map_w, (kb0 + s) * BK, n0, full_bar(s), once);
+      }
+      // x is written by the kernel before this one: nothing of it is read before that kernel is done
+      pdl_wait();
+      for (int s = 0; s < pre; ++s)
+        tc::tma_load_2d(smem_base + s * L::kStageBytes + L::kABytes, &map_x, (kb0 + s) * BK, 0, full_bar(s));
+      for (int kb = pre; kb < nkb; ++kb) {
+        const int s = kb % kStages;
+        if (!tc::mbar_wait(empty_bar(s), (unsigned)((kb / kStages) - 1) & 1, abort_flag, &g_stream_error, 1)) break;
+        tc::mbar_expect_tx(full_bar(s), L::kStageBytes);
+        const unsigned dst = smem_base + s * L::kStageBytes;
+        tc::tma_load_2d_hint(dst, &map_w, (kb0 + kb) * BK, n0, full_bar(s), once);
+        tc::tma_load_2d(dst + L::kABytes, &map_x, (kb0 + kb) * BK, 0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr unsigned idesc = tc::idesc_bf16_f32(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % kStages;
+        ok = tc::mbar_wait(full_bar(s), (unsigned)(kb / kStages) & 1, abort_flag, &g_stream_error, 2);
+        if (!ok) break;
+        tc::fence_after();
+        const unsigned a_addr = smem_base + s * L::kStageBytes;
+        const unsigned long long da = tc::desc_k_major_sw128(a_addr), db = tc::desc_k_major_sw128(a_addr + L::kABytes);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          // 16 elements = 32 bytes further along K inside the swizzle row: +2 in the address field
+          tc::umma_bf16(tmem_base, da + 2ull * k, db + 2ull * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        }
+        tc::umma_commit(empty_bar(s));       // the stage may be refilled once these MMAs have read it
+      }
+      if (ok && nkb > 0) tc::umma_commit(acc_full);
+    }
+  } else {
+    // ------------------------------------------------------------------ accumulator read-out (warps 2..5)
+    const int quarter = warp & 3;            // a warp may only touch lanes [32 * (warp % 4), +32)
+    const int row = quarter * 32 + lane;     // weight row of this thread within the tile
+    const int n = n0 + row;
+    bool ok = true;
+    if (nkb > 0) {
+      ok = tc::mbar_wait(acc_full, 0, abort_flag, &g_stream_error, 3);
+      tc::fence_after();
+    }
+    const unsigned tmem_row = tmem_base + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN && c0 < M; c0 += 16) {
+      unsigned v[16];
+      if (nkb > 0 && ok) {
+        tc::tmem_ld16(tmem_row + (unsigned)c0, v);
+        tc::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = 0u;
+      }
+      if (csize == 1) {
+        if (n < N) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            if (c0 + e < M) out[(size_t)(c0 + e) * ldc + n] = from_f32<TOut>(__uint_as_float(v[e]));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) part[(c0 + e) * BM + row] = __uint_as_float(v[e]);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ sum over the K slices, teardown
+  tc::fence_before();
+  if (csize > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int rows_mine = BM / csize;
+    const int row_lo = rank * rows_mine;
+    for (int i = threadIdx.x; i < M * rows_mine; i += kThreads) {
+      const int m = i / rows_mine, row = row_lo + (i - m * rows_mine);
+      float sum = 0.f;
+      for (int q = 0; q < csize; ++q) {
+        const float* remote = cluster.map_shared_rank(part, q);
+        sum += remote[m * BM + row];
+      }
+      if (n0 + row < N) out[(size_t)m * ldc + n0 + row] = from_f32<TOut>(sum);
+    }
+    cluster.sync();   // nobody leaves while its shared memory may still be read
+  } else {
+    __syncthreads();
+  }
+  if (*abort_flag && threadIdx.x == 0) {
+    // copies that were issued may still be landing in this CTA's shared memory: give them time
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after();
+    tc::tmem_dealloc(tmem_base, L::kTmemCols);
+  }
+}
+
+template <int BN, typename TOut>
+int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N, int K,
+           int csize, cudaStream_t s) {
+  using L = Layout<BN>;
+  CUtensorMap mw, mx;
+  int rc = tc::make_map_2d_bf16(&mw, W, N, K, ldw, BM);
+  OI_REQUIRE(rc == 0, "gemm_stream: tensor map for the weight failed (%d)", rc);
+  rc = tc::make_map_2d_bf16(&mx, x, M, K, ldx, BN);
+  OI_REQUIRE(rc == 0, "gemm_stream: tensor map for x failed (%d)", rc);
+  auto kernel = gemm_stream_kernel<BN, TOut>;
+  static bool configured = false;
+  if (!configured) {
+    OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  const int num_kb = (K + BK - 1) / BK;
+  const int kb_per_rank = (num_kb + csize - 1) / csize;
+  oi_launch_cluster(kernel, dim3(csize, (N + BM - 1) / BM, 1), kThreads, L::kTotal, s, csize, mw, mx, (TOut*)out, ldc, M, N,
+                    num_kb, kb_per_rank);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+}  // namespace
+
+// x: [M, K] bfloat16 (row stride ldx), W: [N, K] bfloat16 (row stride ldw), out: [M, N] bfloat16 or
+// float32 (row stride ldc), 1 <= M <= 128. K and the row strides of x and W must be multiples of 8
+// elements and their bases 16-byte aligned (TMA). cluster_size in {1, 2, 4, 8}: the number of K
+// slices; it must not exceed the number of 64-wide k blocks.
+OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
+                          long long ldw, int M, int N, int K, int cluster_size, void* stream) {
+  OI_REQUIRE(M >= 1 && M <= 128, "gemm_stream: M=%d outside 1..128", M);
+  OI_REQUIRE(N >= 1 && K >= 8, "gemm_stream: bad sizes N=%d K=%d", N, K);
+  OI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_stream: K and row strides must be multiples of 8");
+  OI_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_stream: operands must be 16-byte aligned");
+  OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
+             "gemm_stream: cluster size %d", cluster_size);
+  const int num_kb = (K + BK - 1) / BK;
+  OI_REQUIRE((cluster_size - 1) * ((num_kb + cluster_size - 1) / cluster_size) < num_kb,
+             "gemm_stream: %d slices leave one without a k block (K=%d)", cluster_size, K);
+  cudaStream_t s = (cudaStream_t)stream;
+#define OI_STREAM(BN_)                                                                                     \
+  do {                                                                                                     \
+    if (out_dtype == OI_BF16) return launch<BN_, bf16>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
+    if (out_dtype == OI_F32) return launch<BN_, float>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
+  } while (0)
+  if (M <= 16) OI_STREAM(16);
+  else if (M <= 32) OI_STREAM(32);
+  else if (M <= 64) OI_STREAM(64);
+  else OI_STREAM(128);
+#undef OI_STREAM
+  OI_REQUIRE(false, "gemm_stream: unknown output dtype code %d", out_dtype);
+}
+
+// 0 when no bounded wait has run out since the last call; otherwise which role gave up (1 producer,
+// 2 MMA issuer, 3 read-out, 9 misaligned shared memory). Synchronises the device; clears the word.
+OI_API int oi_gemm_stream_status(int* status) {
+  int v = 0;
+  OI_CHECK_CUDA(cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)));
+  if (v != 0) {
+    int zero = 0;
+    OI_CHECK_CUDA(cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int)));
+  }
+  *status = v;
+  return OI_OK;
+}

@@ -143,6 +143,7 @@ template <int BN, int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+  pdl_start();
   using L = Smem<BN, kStages>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -382,7 +383,7 @@ int launch(void* C, long long ldc, const void* A, long long lda, const void* W, 
     OI_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  kernel<<<tiles < sm_count ? tiles : sm_count, kThreads, smem, s>>>(ma, mb, (TOut*)C, ldc, M, N, K);
+  oi_launch(kernel, tiles < sm_count ? tiles : sm_count, kThreads, smem, s, ma, mb, (TOut*)C, ldc, M, N, K);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

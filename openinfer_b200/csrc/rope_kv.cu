@@ -21,6 +21,7 @@ __global__ void qk_norm_rope_kv_kernel(
     int rot_half, int max_pos, const int* __restrict__ positions, const int* __restrict__ slots,
     T* __restrict__ k_cache, T* __restrict__ v_cache, long long page_stride, int page_size,
     int heads_total, int tokens) {
+  pdl_start();
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gw >= (long long)tokens * heads_total) return;
@@ -86,6 +87,7 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
     int rot_half, int max_pos, const int* __restrict__ positions, const int* __restrict__ slots,
     bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, long long page_stride, int page_size,
     int heads_total, int heads_per_warp) {
+  pdl_start();
   const int lane = threadIdx.x & 31;
   const int token = blockIdx.x;
   const int head0 = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * heads_per_warp;
@@ -195,7 +197,7 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
   const int blocks = (int)((warps + 3) / 4);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == OI_F32) {
-    qk_norm_rope_kv_kernel<float><<<blocks, 128, 0, s>>>(
+    oi_launch(qk_norm_rope_kv_kernel<float>, blocks, 128, 0, s, 
         (float*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
         sin_tab, rot_half, max_pos, positions, slots, (float*)k_cache, (float*)v_cache, page_stride,
         page_size, heads_total, tokens);
@@ -210,15 +212,15 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
       rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride, page_size, heads_total,     \
       heads_per_warp
     if (rot_half <= 64) {
-      if (norm_dtype == OI_BF16) qk_norm_rope_kv_bf16x2_kernel<bf16, 1><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(bf16));
-      else qk_norm_rope_kv_bf16x2_kernel<float, 1><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(float));
+      if (norm_dtype == OI_BF16) oi_launch(qk_norm_rope_kv_bf16x2_kernel<bf16, 1>, grid, 128, 0, s, OI_ROPE_ARGS(bf16));
+      else oi_launch(qk_norm_rope_kv_bf16x2_kernel<float, 1>, grid, 128, 0, s, OI_ROPE_ARGS(float));
     } else {
-      if (norm_dtype == OI_BF16) qk_norm_rope_kv_bf16x2_kernel<bf16, 2><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(bf16));
-      else qk_norm_rope_kv_bf16x2_kernel<float, 2><<<grid, 128, 0, s>>>(OI_ROPE_ARGS(float));
+      if (norm_dtype == OI_BF16) oi_launch(qk_norm_rope_kv_bf16x2_kernel<bf16, 2>, grid, 128, 0, s, OI_ROPE_ARGS(bf16));
+      else oi_launch(qk_norm_rope_kv_bf16x2_kernel<float, 2>, grid, 128, 0, s, OI_ROPE_ARGS(float));
     }
 #undef OI_ROPE_ARGS
   } else if (dtype == OI_BF16) {
-    qk_norm_rope_kv_kernel<bf16><<<blocks, 128, 0, s>>>(
+    oi_launch(qk_norm_rope_kv_kernel<bf16>, blocks, 128, 0, s, 
         (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
         sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride,
         page_size, heads_total, tokens);

@@ -18,6 +18,14 @@ OI_API const char* oi_last_error() { return g_error; }
 // ABI version: bumped when an entry point's signature changes.
 OI_API int oi_abi_version() { return 1; }
 
+// Programmatic dependent launch of the library's kernels (see common.cuh): on unless switched off.
+static int g_pdl = 1;
+int oi_pdl_enabled() { return g_pdl; }
+OI_API int oi_set_pdl(int enabled) {
+  g_pdl = enabled ? 1 : 0;
+  return OI_OK;
+}
+
 OI_API int oi_device_info(int device, int* sm_major, int* sm_minor, int* sm_count, long long* l2_bytes) {
   cudaDeviceProp prop;
   OI_CHECK_CUDA(cudaGetDeviceProperties(&prop, device));

@@ -26,6 +26,7 @@ __device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
 
 __global__ void argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int vocab,
                               long long row_stride) {
+  pdl_start();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + (size_t)blockIdx.x * row_stride;
@@ -61,6 +62,7 @@ constexpr int kArgmaxChunk = 4096;
 
 __global__ void argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi, const float* __restrict__ logits,
                                       int vocab, long long row_stride, int nchunks) {
+  pdl_start();
   __shared__ float sv[8];
   __shared__ int si[8];
   const int r = blockIdx.y, chunk = blockIdx.x;
@@ -89,6 +91,7 @@ __global__ void argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ 
 
 __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const int* __restrict__ pi,
                                     int nchunks) {
+  pdl_start();
   const int r = blockIdx.x;
   ArgPair best{-INFINITY, 0x7fffffff};
   for (int c = threadIdx.x; c < nchunks; c += 32) best = better(best, ArgPair{pv[(size_t)r * nchunks + c], pi[(size_t)r * nchunks + c]});
@@ -120,6 +123,7 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
                               float* __restrict__ probs, int vocab, const float* __restrict__ temperature,
                               const int* __restrict__ top_k, const float* __restrict__ top_p,
                               const float* __restrict__ min_p, const float* __restrict__ uniform) {
+  pdl_start();
   __shared__ float red[32];
   __shared__ float chunk_sum[1024];
   __shared__ int picked;
@@ -229,11 +233,11 @@ OI_API int oi_argmax(int* out, const float* logits, int rows, int vocab, long lo
   cudaStream_t s = (cudaStream_t)stream;
   const int nchunks = (vocab + kArgmaxChunk - 1) / kArgmaxChunk;
   if (partial_vals && partial_idx && nchunks >= 4 && rows * nchunks <= 65535 * 16) {
-    argmax_partial_kernel<<<dim3(nchunks, rows), 256, 0, s>>>(partial_vals, partial_idx, logits, vocab, row_stride, nchunks);
+    oi_launch(argmax_partial_kernel, dim3(nchunks, rows), 256, 0, s, partial_vals, partial_idx, logits, vocab, row_stride, nchunks);
     OI_CHECK_LAUNCH();
-    argmax_final_kernel<<<rows, 32, 0, s>>>(out, partial_vals, partial_idx, nchunks);
+    oi_launch(argmax_final_kernel, rows, 32, 0, s, out, partial_vals, partial_idx, nchunks);
   } else {
-    argmax_kernel<<<rows, 1024, 0, s>>>(out, logits, vocab, row_stride);
+    oi_launch(argmax_kernel, rows, 1024, 0, s, out, logits, vocab, row_stride);
   }
   OI_CHECK_LAUNCH();
   return OI_OK;
@@ -247,7 +251,7 @@ OI_API int oi_sample(int* out, const float* logits, long long row_stride, float*
   OI_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   OI_REQUIRE(probs != nullptr, "sample: scratch missing");
   if (rows == 0) return OI_OK;
-  sample_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>(out, logits, row_stride, probs, vocab, temperature,
+  oi_launch(sample_kernel, rows, 1024, 0, (cudaStream_t)stream, out, logits, row_stride, probs, vocab, temperature,
                                                          top_k, top_p, min_p, uniform);
   OI_CHECK_LAUNCH();
   return OI_OK;

@@ -1,15 +1,19 @@
-"""y = x W^T for the projections: picks the product kernel by operand types.
+"""y = x W^T for the projections: picks the product kernel by operand types and shape.
 
-* bfloat16 x bfloat16: the tensor-core path. The reference's engine calls the vendor
-  library for every projection (pegainfer-kernels/csrc/shared/linear.cu:312-362,
-  ``cublasGemmEx`` with float32 accumulation); the same library call stands here until
-  a hand-written tcgen05 kernel takes the shape (see ``set_bf16_gemm``).
+* bfloat16 x bfloat16, up to 16 rows (decode): the hand-written weight-streaming kernel on the
+  5th-generation tensor cores (``gemm_stream.cu``: TMA -> shared memory -> tcgen05.mma with the
+  weight rows on the M side), which reads nothing but weights before the kernel ahead of it on
+  the stream has finished and therefore starts its stream under that kernel's tail.
+* bfloat16 x bfloat16 otherwise: a registered hand-written kernel (``set_bf16_gemm``) if it takes
+  the shape, else the vendor library. The reference's engine calls the vendor library for every
+  projection (pegainfer-kernels/csrc/shared/linear.cu:312-362, ``cublasGemmEx`` with float32
+  accumulation).
 * anything with a float32 operand: the hand-written float32-accumulate kernel on the
   ordinary pipes (no reduced-precision matrix mode), summed in ascending k.
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_longlong, c_void_p
+import os as _os
 from typing import Callable, Optional
 
 import torch
@@ -17,18 +21,12 @@ import torch
 from . import lib as _lib
 from . import ops
 
+# which hand-written kernel takes the decode products: "stream" (tcgen05), "skinny" (mma.sync), "library"
+DECODE_GEMM = _os.environ.get("OI_DECODE_GEMM", "stream")
+_FORCE_C = int(_os.environ.get("OI_GEMM_C", "0"))
 
-# programmatic dependent launch of the decode products (see gemm_skinny.cu)
-import os as _os  # noqa: E402
-USE_PDL = _os.environ.get('OI_PDL', '1') == '1'
-_FORCE_C = int(_os.environ.get('OI_SKINNY_C', '0'))
-
-SKINNY_MAX_ROWS = 16
-# Measured on B200 (cold weights, M = 8, K = 4096): the skinny kernel beats the library where a
-# product is short enough for fixed costs to matter (N 4096..6144: 12-15 us vs 14-16 us) and loses on
-# long ones (N 24576: 43 vs 38 us; N 151936: 221 vs 208 us), so those stay with the library.
-SKINNY_MAX_WEIGHT_ROWS = 8192
-# Forming silu(gate) * up while the product kernel stages its activations repeats the exponentials
+DECODE_MAX_ROWS = 16
+# Forming silu(gate) * up while the skinny kernel stages its activations repeats the exponentials
 # once per 64-row tile of the weight (64 times at N = 4096): measured 44.7 us for the fused down
 # projection against 25 + 3.2 us for the two kernels. The fused path stays available and tested.
 FUSE_SILU_MUL = False
@@ -43,11 +41,64 @@ def set_bf16_gemm(fn: Optional[Callable[[torch.Tensor, torch.Tensor, torch.Tenso
     _bf16_gemm = fn
 
 
+def _sm_count(device) -> int:
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT
+
+
+def stream_cluster_size(N: int, K: int, sm_count: int) -> int:
+    """How many K slices (CTAs per cluster) the streaming kernel uses: one when the tiles of 128
+    weight rows alone fill the GPU, else the fewest slices that give every SM a CTA, each slice at
+    least two k blocks long. Measured on B200 at M = 8 (us, inside a CUDA graph): N 6144 K 4096:
+    14.2 with 4 slices (16.1 with 2, 17.0 with 8); N 4096 K 4096: 11.1 with 8 (11.8 with 4);
+    N 4096 K 12288: 20.9 with 8 (22.1 with 4); N 24576 and N 151936: one slice (34.4 and 188)."""
+    tiles = -(-N // 128)
+    num_kb = -(-K // 64)
+    c = 1
+    while c < 8 and tiles * c < sm_count and num_kb // (2 * c) >= 2:
+        c *= 2
+    return c
+
+
+def _operands_ok(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        return False
+    return not (x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16)
+
+
+def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The tcgen05 weight-streaming kernel, when it takes the shape."""
+    M, N, K = x.shape[0], w.shape[0], w.shape[1]
+    if K % 8 or not _operands_ok(out, x, w):
+        return False
+    c = stream_cluster_size(N, K, _sm_count(x.device))
+    if _FORCE_C:
+        c = _FORCE_C
+    num_kb = -(-K // 64)
+    while c > 1 and (c - 1) * (-(-num_kb // c)) >= num_kb:
+        c //= 2
+    L = _lib.load()
+    _lib.check(L.oi_gemm_stream(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
+                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c,
+                                torch.cuda.current_stream().cuda_stream), "gemm_stream")
+    return True
+
+
+def stream_status() -> int:
+    """0, or which bounded wait of the streaming kernel ran out since the last call (synchronises)."""
+    from ctypes import byref, c_int
+    v = c_int(0)
+    _lib.check(_lib.load().oi_gemm_stream_status(byref(v)), "gemm_stream_status")
+    return v.value
+
+
 def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
     """How many K slices (CTAs per cluster) the skinny kernel uses, 0 if it does not take the
-    shape: the fewest slices that fill the GPU twice over, each slice's activations within 64 KB
-    of shared memory where possible."""
-    row_tiles = -(-N // 64)
+    shape (each slice's activations must fit in shared memory beside the 48 KB of weight rings)."""
     valid = [c for c in (1, 2, 4, 8) if K % (32 * c) == 0 and 49152 + 32 * (K // c + 64) + 4096 <= 200 * 1024]
     if not valid:
         return 0
@@ -59,19 +110,11 @@ def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
 
 
 def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) -> bool:
-    """The hand-written weight-streaming kernel, when it takes the shape."""
-    global _SM_COUNT
-    M, N = x.shape[0], w.shape[0]
-    K = w.shape[1]
-    if M > SKINNY_MAX_ROWS or N > SKINNY_MAX_WEIGHT_ROWS or out.dtype not in (torch.bfloat16, torch.float32):
+    """The mma.sync weight-streaming kernel, when it takes the shape."""
+    M, N, K = x.shape[0], w.shape[0], w.shape[1]
+    if M > DECODE_MAX_ROWS or not _operands_ok(out, x, w):
         return False
-    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
-        return False
-    if x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16:
-        return False
-    if _SM_COUNT is None:
-        _SM_COUNT = torch.cuda.get_device_properties(x.device).multi_processor_count
-    c = skinny_cluster_size(N, K, _SM_COUNT)
+    c = skinny_cluster_size(N, K, _sm_count(x.device))
     if c == 0:
         return False
     if _FORCE_C and K % (32 * _FORCE_C) == 0 and 49152 + 32 * (K // _FORCE_C + 64) + 4096 <= 200 * 1024:
@@ -79,7 +122,7 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) 
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, int(silu_mul), c,
-                                1 if USE_PDL else 0, torch.cuda.current_stream().cuda_stream), "gemm_skinny")
+                                torch.cuda.current_stream().cuda_stream), "gemm_skinny")
     return True
 
 
@@ -88,7 +131,7 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, block: Optional[int]
     their ups; default all gates, then all ups) and w [N, K]."""
     M, K = gate_up.shape[0], w.shape[1]
     block = K if block is None else block
-    if FUSE_SILU_MUL and gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS:
+    if FUSE_SILU_MUL and gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= DECODE_MAX_ROWS:
         out = torch.empty((M, w.shape[0]), dtype=gate_up.dtype, device=gate_up.device)
         if _skinny(out, gate_up, w, block):
             return out
@@ -111,8 +154,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if _bf16_gemm is not None and _bf16_gemm(out, x, w):
             return out
-        if M <= SKINNY_MAX_ROWS and _skinny(out, x, w, 0):
-            return out
+        if M <= DECODE_MAX_ROWS:
+            if DECODE_GEMM == "stream" and _stream(out, x, w):
+                return out
+            if DECODE_GEMM in ("stream", "skinny") and _skinny(out, x, w, 0):
+                return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:

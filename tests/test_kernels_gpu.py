@@ -477,16 +477,59 @@ def test_gemm_skinny(M, N, K):
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
             klib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out_dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, c, c % 4 == 0,
+                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, c,
                                         torch.cuda.current_stream().cuda_stream), "gemm_skinny")
             tol_ = 2e-2 * ref.abs().max().item() if out_dtype == torch.bfloat16 else 2e-4 * ref.abs().max().item()
             err = (out.double() - ref).abs().max().item()
             assert err <= tol_, f"cluster {c} {out_dtype}: max err {err}"
-    # the dispatcher takes it, and a row does not depend on the other rows
-    out = lin.linear(x, w)
-    assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
-    one = lin.linear(x[M - 1:], w)
-    assert torch.equal(one[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 512), (3, 100, 72), (16, 4096 + 48, 4096), (17, 300, 1000),
+                                   (40, 520, 4096), (100, 384, 2048), (128, 1000, 8192), (8, 200, 12288)])
+def test_gemm_stream(M, N, K):
+    """The tcgen05 weight-streaming product (weight rows on the M side of the MMA, tokens padded to
+    16 / 32 / 64 / 128 by the copy's zero fill) for every number of K slices, against float64."""
+    from openinfer_b200.kernels import linear as lin
+    from openinfer_b200.kernels import lib as klib
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    L = klib.load()
+    num_kb = -(-K // 64)
+    for c in (1, 2, 4, 8):
+        if (c - 1) * (-(-num_kb // c)) >= num_kb:     # a slice without a k block: refused by the entry point
+            continue
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+            klib.check(L.oi_gemm_stream(out.data_ptr(), 1 if out_dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
+                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c,
+                                        torch.cuda.current_stream().cuda_stream), "gemm_stream")
+            tol_ = 2e-2 * ref.abs().max().item() if out_dtype == torch.bfloat16 else 2e-4 * ref.abs().max().item()
+            err = (out.double() - ref).abs().max().item()
+            assert err <= tol_, f"{c} slices {out_dtype}: max err {err}"
+    assert lin.stream_status() == 0, "a bounded wait ran out in the streaming product"
+    if M <= lin.DECODE_MAX_ROWS:
+        # the dispatcher takes it, and a row does not depend on the other rows
+        out = lin.linear(x, w)
+        assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+        one = lin.linear(x[M - 1:], w)
+        assert torch.equal(one[0], out[M - 1])
+
+
+def test_gemm_stream_refuses_bad_operands():
+    from openinfer_b200.kernels import lib as klib
+    L = klib.load()
+    x = torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros(4, 128, device=DEV, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    # two slices of a single k block, 129 rows of x, a misaligned weight
+    for args in [(4, 128, 64, 2), (129, 128, 64, 1)]:
+        rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), *args, stream)
+        assert rc != 0 and b"gemm_stream" in L.oi_last_error()
+    rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr() + 2, w.stride(0), 4, 127, 64, 1, stream)
+    assert rc != 0 and b"aligned" in L.oi_last_error()
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 96, 224), (8, 4096, 12288), (13, 200, 1536)])
