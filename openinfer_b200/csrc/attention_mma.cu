@@ -14,7 +14,11 @@
 // (exp2 with the scale folded in), o = sum p v (paged_attention.cu:439-567). K/V tiles of 64 keys
 // are gathered page by page with cp.async into swizzled shared memory, double buffered;
 // S = Q K^T and O = P V run as mma.sync m16n8k16 with float32 accumulators.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -33,6 +37,7 @@ struct AttnParams {
   float scale_log2;        // softmax scale * log2(e)
   int window;              // 0 = none
   float* part_o; float* part_lse; int max_splits;  // scratch for split items
+  int merge_in_kernel;     // decode kernel: the CTAs of a row form a cluster and merge their slices themselves
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
@@ -619,13 +624,56 @@ attention_decode_kernel(const AttnParams p) {
   }
 
   // ---- partial result of this slice
-  if (!split_ok) return;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
   }
   const int col = (lane & 3) * 2;
+  if (p.merge_in_kernel) {
+    // The CTAs of this (request, kv head) are one cluster. Every warp leaves its normalised partial
+    // [group][HD] and log-sum-exps [group] in its own drained ring; then CTA r of the cluster merges
+    // the outputs r * 128 + t, ... over all slices in slice order, reading the other CTAs' shared
+    // memory directly (the formula of attention_merge_kernel, without the trip through global memory).
+    float* my_o = reinterpret_cast<float*>(ring);
+    float* my_lse = my_o + 16 * HD;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = r_lo + 8 * i;
+      if (r >= group) continue;
+      const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+#pragma unroll
+      for (int j = 0; j < kOTiles; ++j)
+        *reinterpret_cast<float2*>(my_o + r * HD + j * 8 + col) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+      if ((lane & 3) == 0) my_lse[r] = (split_ok && l[i] > 0.f) ? m[i] + log2f(l[i]) : -INFINITY;
+    }
+    cg::cluster_group cluster = cg::this_cluster();
+    const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    if (csize > 1) cluster.sync(); else __syncthreads();
+    constexpr size_t kRingFloats = (size_t)kDecStages * 2 * kDecKeys * HD / 2;   // one warp's ring, in floats
+    float* const cta_base = reinterpret_cast<float*>(smem_raw);
+    for (int idx = rank * (kDecWarps * 32) + threadIdx.x; idx < group * HD; idx += csize * kDecWarps * 32) {
+      const int r = idx / HD, d = idx - r * HD;
+      float mx = -INFINITY;
+      for (int sl = 0; sl < nsplits; ++sl) {
+        const float* base = csize > 1 ? cluster.map_shared_rank(cta_base, sl / kDecWarps) : cta_base;
+        mx = fmaxf(mx, base[(sl % kDecWarps) * kRingFloats + 16 * HD + r]);
+      }
+      float acc = 0.f, wsum = 0.f;
+      for (int sl = 0; sl < nsplits; ++sl) {
+        const float* base = (csize > 1 ? cluster.map_shared_rank(cta_base, sl / kDecWarps) : cta_base) + (sl % kDecWarps) * kRingFloats;
+        const float lse = base[16 * HD + r];
+        const float w = lse == -INFINITY ? 0.f : exp2f(lse - mx);
+        wsum += w;
+        acc += w * base[r * HD + d];
+      }
+      p.out[(size_t)row_q * p.out_row_stride + (size_t)(kvh * group + r) * HD + d] =
+          __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+    }
+    if (csize > 1) cluster.sync();   // nobody leaves while its shared memory may still be read
+    return;
+  }
+  if (!split_ok) return;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = r_lo + 8 * i;
@@ -727,10 +775,15 @@ int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int
     configured = true;
   }
   dim3 grid(num_items, p.nkv);
+  if (p.merge_in_kernel) {
+    oi_launch_cluster(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, p.max_splits / kDecWarps, p);
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
   oi_launch(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, p);
   OI_CHECK_LAUNCH();
   const long long warps = (long long)tokens * p.nq;
-  oi_launch(attention_merge_kernel<HD>, (unsigned)((warps + 3) / 4), 128, 0, s, 
+  oi_launch(attention_merge_kernel<HD>, (unsigned)((warps + 3) / 4), 128, 0, s,
       p.out, p.out_row_stride, p.part_o, p.part_lse, row_splits, p.nq, p.max_splits, tokens);
   OI_CHECK_LAUNCH();
   return OI_OK;
@@ -739,21 +792,31 @@ int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int
 }  // namespace
 
 // Decode rows only (requests that bring one token): items are (request, 0, first slice, nsplits),
-// one CTA per four consecutive slices; every listed request's row is merged from scratch, so
+// one CTA per four consecutive slices, every item with nsplits == max_splits. With
+// merge_in_kernel != 0 (max_splits a multiple of 4, at most 32; the items of a request adjacent
+// and in slice order) the max_splits / 4 CTAs of a row run as a thread-block cluster and merge their
+// slices through distributed shared memory; part_o, part_lse and row_splits are not used. Otherwise
+// every listed request's row is merged by a second kernel from scratch in global memory, so
 // row_splits[row] must be nsplits (>= 2) for those rows and <= 1 for all others.
 OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
                                const void* v_cache, long long page_stride, int page_size, const int* block_table,
                                int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
                                int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
                                float scale, int window, float* part_o, float* part_lse, int max_splits,
-                               void* stream) {
+                               int merge_in_kernel, void* stream) {
   OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_decode: head_dim %d not covered (32, 64 or 128)", hd);
   OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16, "attention_decode: group %d/%d not covered (<= 16)", nq, nkv);
   OI_REQUIRE(q_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_decode: misaligned strides");
   OI_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0),
              "attention_decode: misaligned pointers");
-  OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2 && max_splits <= 64,
-             "attention_decode: scratch missing, or slices outside 2..64");
+  if (merge_in_kernel) {
+    OI_REQUIRE(max_splits >= 4 && max_splits <= 32 && max_splits % 4 == 0 && num_items % (max_splits / 4) == 0,
+               "attention_decode: %d slices cannot be merged in the kernel (a multiple of 4 up to 32)", max_splits);
+    OI_REQUIRE((uintptr_t)out % 2 == 0, "attention_decode: misaligned output");
+  } else {
+    OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2 && max_splits <= 64,
+               "attention_decode: scratch missing, or slices outside 2..64");
+  }
   if (num_items == 0 || tokens == 0) return OI_OK;
   AttnParams p;
   p.q = (const bf16*)q; p.q_row_stride = q_row_stride;
@@ -766,6 +829,7 @@ OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int o
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
+  p.merge_in_kernel = merge_in_kernel ? 1 : 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 32) return launch_decode<32>(p, num_items, row_splits, tokens, s);
   if (hd == 64) return launch_decode<64>(p, num_items, row_splits, tokens, s);
@@ -802,6 +866,7 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
+  p.merge_in_kernel = 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
   if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);

@@ -59,6 +59,7 @@ MIN_TILES_PER_SPLIT = 2    # such a slice is at least 128 keys long
 DECODE_WARPS = 4           # slices of a decode row per CTA (one per warp)
 DECODE_CTAS_PER_SM = 2
 DECODE_MAX_SPLITS = 64
+DECODE_MERGE_IN_KERNEL_MAX_SPLITS = 32   # up to 8 CTAs of a row form a cluster and merge their slices themselves
 DECODE_MIN_KEYS_PER_SPLIT = 32
 DECODE_MAX_GROUP = 16
 _SM_COUNT = None
@@ -83,6 +84,7 @@ class AttentionPlan:
     max_splits: int
     part_o: Optional[torch.Tensor]
     part_lse: Optional[torch.Tensor]
+    decode_merge_in_kernel: bool = False
 
 
 def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int]) -> int:
@@ -190,11 +192,14 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
         dev = torch.from_numpy(packed).to(device, non_blocking=True)
         nt, nd = t_items.shape[0], d_items.shape[0]
         part_o = part_lse = None
-        if max_splits > 1:
+        # decode rows merge their slices inside the kernel when their CTAs fit a cluster; prompt tiles
+        # are only ever cut when there are no decode rows
+        in_kernel = nd > 0 and max_splits <= DECODE_MERGE_IN_KERNEL_MAX_SPLITS
+        if max_splits > 1 and not in_kernel:
             part_o = torch.empty(ctx.num_tokens * nq * max_splits * hd, dtype=torch.float32, device=device)
             part_lse = torch.empty(ctx.num_tokens * nq * max_splits, dtype=torch.float32, device=device)
         plan = AttentionPlan(dev[: nt * 4].view(nt, 4), nt, dev[nt * 4: (nt + nd) * 4].view(nd, 4), nd,
-                             dev[(nt + nd) * 4:], rows, tile_split, max_splits, part_o, part_lse)
+                             dev[(nt + nd) * 4:], rows, tile_split, max_splits, part_o, part_lse, in_kernel)
         ctx.scratch[key] = plan
     return plan
 
@@ -247,7 +252,7 @@ def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nk
             int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
             group_step.kv_lens.data_ptr(), plan.decode_items.data_ptr(), plan.num_decode_items,
             plan.row_splits.data_ptr(), out.shape[0], nq, nkv, hd, float(scale), win, po, pl, plan.max_splits,
-            stream), "attention_decode")
+            1 if plan.decode_merge_in_kernel else 0, stream), "attention_decode")
     return True
 
 

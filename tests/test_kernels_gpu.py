@@ -427,10 +427,15 @@ def test_attention_mma_mixed_batch(nq, nkv, hd, P, window, tcgen05, monkeypatch)
 def test_attention_mma_split_kv_decode(nq, nkv, hd, window):
     """Decode rows whose keys are cut into slices and merged; contexts around tile edges."""
     kv_lens = [1, 63, 64, 65, 127, 128, 129, 700, 1025]
-    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="max")
-    assert plan.num_decode_items and plan.max_splits >= 8 and not plan.num_tile_items    # the decode kernel, many slices
+    long = kv_lens + [2100]
+    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(long), long, force_splits="max")
+    # the decode kernel, 64 slices: too many CTAs per row for a cluster, merged by the second kernel
+    assert plan.num_decode_items and plan.max_splits == 64 and not plan.num_tile_items and not plan.decode_merge_in_kernel
+    plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens)
+    # as planned for this GPU: 16 or 32 slices, the 4 or 8 CTAs of a row merge through distributed shared memory
+    assert plan.num_decode_items and plan.max_splits in (16, 32) and plan.decode_merge_in_kernel
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="none")
-    assert plan.num_decode_items and plan.max_splits == 4                                # the decode kernel, four slices
+    assert plan.num_decode_items and plan.max_splits == 4 and plan.decode_merge_in_kernel   # four slices: one CTA per row
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="tiles")
     assert plan.tile_split and not plan.num_decode_items                                 # the tile kernel, sliced
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens, force_splits="tiles_whole")
