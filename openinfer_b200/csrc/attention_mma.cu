@@ -452,7 +452,7 @@ __device__ __forceinline__ void load_kv_tile16(bf16* k_smem, bf16* v_smem, const
 template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attention_decode_kernel(const AttnParams p) {
-  pdl_start();
+  pdl_trigger();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // [warp][stage][K | V][16][HD]
@@ -485,6 +485,39 @@ attention_decode_kernel(const AttnParams p) {
   const int v_row = (lm_mat & 1) * 8 + lm_rin;              // V: matrices 0,2 keys 0-7; 1,3 keys 8-15
   const int v_row_off = v_row * HD, v_swz = (lm_mat >> 1) ^ (v_row & 7);  // chunk = j + (mat >> 1)
 
+  constexpr int kOTiles = HD / 8;
+  float o[kOTiles][4];
+#pragma unroll
+  for (int j = 0; j < kOTiles; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  // the next tile to copy: its first key, its page (index into the block table) and offset there
+  const long long v_delta = p.v_cache - p.k_cache;
+  int ld_t = t_begin, ld_stage = 0;
+  int ld_key = lo + t_begin * kDecKeys;
+  int ld_pg = ld_key / p.page_size, ld_off = ld_key % p.page_size;
+  auto issue_next = [&]() {   // one commit per call, empty when past the end
+    if (ld_t < t_end) {
+      load_kv_tile16<HD>(k_tile(ld_stage), v_tile(ld_stage), p, bt, v_delta, kvh, ld_key, kv_len, tl, aligned, ld_pg, ld_off);
+      ++ld_t;
+      ld_key += kDecKeys;
+      ld_off += kDecKeys;
+      if (ld_off >= p.page_size) { ld_off -= p.page_size; ++ld_pg; }   // aligned case: exact
+      ld_stage = ld_stage + 1 == kDecStages ? 0 : ld_stage + 1;
+    }
+    cp_async_commit();
+  };
+  // Prologue: kDecStages - 1 tiles in flight. Keys of earlier steps do not change any more, so their
+  // tiles are requested BEFORE waiting for the kernels ahead on the stream; the row's last tile holds
+  // the key this step has just written and is requested, like q, only after the wait. (The lengths,
+  // the block table and the items were copied to the device before the step's first kernel.)
+  int primed = 0;
+  if (split_ok) {
+    for (; primed < kDecStages - 1 && ld_t != span_tiles - 1; ++primed) issue_next();
+  }
+  pdl_wait();
   // ---- Q fragments: rows are the `group` query heads of this kv head (rows >= group are zero)
   constexpr int kSteps = HD / 16;
   const int r_lo = lane >> 2;                     // rows r_lo and r_lo + 8
@@ -507,34 +540,8 @@ attention_decode_kernel(const AttnParams p) {
       }
     }
   }
-  constexpr int kOTiles = HD / 8;
-  float o[kOTiles][4];
-#pragma unroll
-  for (int j = 0; j < kOTiles; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-
   if (split_ok) {
-    // the next tile to copy: its first key, its page (index into the block table) and offset there
-    const long long v_delta = p.v_cache - p.k_cache;
-    int ld_t = t_begin, ld_stage = 0;
-    int ld_key = lo + t_begin * kDecKeys;
-    int ld_pg = ld_key / p.page_size, ld_off = ld_key % p.page_size;
-    auto issue_next = [&]() {   // one commit per call, empty when past the end
-      if (ld_t < t_end) {
-        load_kv_tile16<HD>(k_tile(ld_stage), v_tile(ld_stage), p, bt, v_delta, kvh, ld_key, kv_len, tl, aligned, ld_pg, ld_off);
-        ++ld_t;
-        ld_key += kDecKeys;
-        ld_off += kDecKeys;
-        if (ld_off >= p.page_size) { ld_off -= p.page_size; ++ld_pg; }   // aligned case: exact
-        ld_stage = ld_stage + 1 == kDecStages ? 0 : ld_stage + 1;
-      }
-      cp_async_commit();
-    };
-    // prologue: kDecStages - 1 tiles in flight
-#pragma unroll
-    for (int s = 0; s < kDecStages - 1; ++s) issue_next();
+    for (; primed < kDecStages - 1; ++primed) issue_next();
     int stage = 0;
     for (int t = t_begin; t < t_end; ++t) {
       issue_next();   // keeps the ring full: goes into the stage freed last iteration
