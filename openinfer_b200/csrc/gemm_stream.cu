@@ -49,7 +49,10 @@ struct Layout {
   static_assert(BN * BM * 4 <= kBarOffset, "the partial sums reuse the stages");
 };
 
-template <int BN, typename TOut>
+// kSiluMul: W's rows come in blocks of 64 gate rows followed by the 64 up rows of the same indices, so a
+// tile holds gate rows in lanes 0-63 of the accumulator and their up rows in lanes 64-127; the result
+// is out[M, N / 2] = silu(gate) * up, formed where the K slices are added up.
+template <int BN, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    TOut* __restrict__ out, long long ldc, int M, int N, int num_kb, int kb_per_rank) {
@@ -162,7 +165,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int e = 0; e < 16; ++e) v[e] = 0u;
       }
-      if (csize == 1) {
+      if (csize == 1 && !kSiluMul) {
         if (n < N) {
 #pragma unroll
           for (int e = 0; e < 16; ++e)
@@ -177,21 +180,25 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   // ------------------------------------------------------------------ sum over the K slices, teardown
   tc::fence_before();
-  if (csize > 1) {
+  if (csize > 1 || kSiluMul) {
     cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    const int rows_mine = BM / csize;
+    if (csize > 1) cluster.sync(); else __syncthreads();
+    constexpr int kOutRows = kSiluMul ? BM / 2 : BM;   // output columns per tile
+    const int rows_mine = kOutRows / csize;
     const int row_lo = rank * rows_mine;
+    const int n_out = kSiluMul ? N / 2 : N, o0 = kSiluMul ? n0 / 2 : n0;
     for (int i = threadIdx.x; i < M * rows_mine; i += kThreads) {
       const int m = i / rows_mine, row = row_lo + (i - m * rows_mine);
-      float sum = 0.f;
+      float sum = 0.f, up = 0.f;
       for (int q = 0; q < csize; ++q) {
-        const float* remote = cluster.map_shared_rank(part, q);
+        const float* remote = csize > 1 ? cluster.map_shared_rank(part, q) : part;
         sum += remote[m * BM + row];
+        if (kSiluMul) up += remote[m * BM + BM / 2 + row];
       }
-      if (n0 + row < N) out[(size_t)m * ldc + n0 + row] = from_f32<TOut>(sum);
+      if (kSiluMul) sum = sum / (1.f + __expf(-sum)) * up;
+      if (o0 + row < n_out) out[(size_t)m * ldc + o0 + row] = from_f32<TOut>(sum);
     }
-    cluster.sync();   // nobody leaves while its shared memory may still be read
+    if (csize > 1) cluster.sync();   // nobody leaves while its shared memory may still be read
   } else {
     __syncthreads();
   }
@@ -206,7 +213,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
-template <int BN, typename TOut>
+template <int BN, typename TOut, bool kSiluMul>
 int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N, int K,
            int csize, cudaStream_t s) {
   using L = Layout<BN>;
@@ -215,7 +222,7 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
   OI_REQUIRE(rc == 0, "gemm_stream: tensor map for the weight failed (%d)", rc);
   rc = tc::make_map_2d_bf16(&mx, x, M, K, ldx, BN);
   OI_REQUIRE(rc == 0, "gemm_stream: tensor map for x failed (%d)", rc);
-  auto kernel = gemm_stream_kernel<BN, TOut>;
+  auto kernel = gemm_stream_kernel<BN, TOut, kSiluMul>;
   static bool configured = false;
   if (!configured) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -234,23 +241,27 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
 // x: [M, K] bfloat16 (row stride ldx), W: [N, K] bfloat16 (row stride ldw), out: [M, N] bfloat16 or
 // float32 (row stride ldc), 1 <= M <= 128. K and the row strides of x and W must be multiples of 8
 // elements and their bases 16-byte aligned (TMA). cluster_size in {1, 2, 4, 8}: the number of K
-// slices; it must not exceed the number of 64-wide k blocks.
+// slices; it must not exceed the number of 64-wide k blocks. silu_mul != 0 (N a multiple of 128): W's rows
+// come in blocks of 64 gate rows followed by their 64 up rows and out is [M, N / 2] = silu(gate) * up.
 OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
-                          long long ldw, int M, int N, int K, int cluster_size, void* stream) {
+                          long long ldw, int M, int N, int K, int cluster_size, int silu_mul, void* stream) {
   OI_REQUIRE(M >= 1 && M <= 128, "gemm_stream: M=%d outside 1..128", M);
   OI_REQUIRE(N >= 1 && K >= 8, "gemm_stream: bad sizes N=%d K=%d", N, K);
   OI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_stream: K and row strides must be multiples of 8");
   OI_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_stream: operands must be 16-byte aligned");
   OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
              "gemm_stream: cluster size %d", cluster_size);
+  OI_REQUIRE(!silu_mul || N % BM == 0, "gemm_stream: the fused activation needs N %% 128 == 0 (N=%d)", N);
   const int num_kb = (K + BK - 1) / BK;
   OI_REQUIRE((cluster_size - 1) * ((num_kb + cluster_size - 1) / cluster_size) < num_kb,
              "gemm_stream: %d slices leave one without a k block (K=%d)", cluster_size, K);
   cudaStream_t s = (cudaStream_t)stream;
-#define OI_STREAM(BN_)                                                                                     \
-  do {                                                                                                     \
-    if (out_dtype == OI_BF16) return launch<BN_, bf16>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
-    if (out_dtype == OI_F32) return launch<BN_, float>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
+#define OI_STREAM(BN_)                                                                                            \
+  do {                                                                                                            \
+    if (out_dtype == OI_BF16 && silu_mul) return launch<BN_, bf16, true>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s);  \
+    if (out_dtype == OI_BF16) return launch<BN_, bf16, false>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
+    if (out_dtype == OI_F32 && silu_mul) return launch<BN_, float, true>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s);  \
+    if (out_dtype == OI_F32) return launch<BN_, float, false>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
   } while (0)
   if (M <= 16) OI_STREAM(16);
   else if (M <= 32) OI_STREAM(32);

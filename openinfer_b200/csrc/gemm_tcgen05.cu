@@ -137,8 +137,9 @@ struct Smem {
 // Persistent: CTA b works on tiles b, b + gridDim.x, ... (row tiles fastest, so CTAs that run at the
 // same time share W tiles through L2). The accumulator is double buffered in tensor memory
 // (2 x BN columns): while the epilogue warps drain tile i, the MMA warp already fills tile i + 1.
-// kSiluMul: W holds, per tile of BN rows, BN/2 gate rows followed by the BN/2 up rows of the same
-// indices; the epilogue writes silu(gate) * up, [M, N/2] with row stride ldc, instead of the product.
+// kSiluMul: W's rows come in blocks of 64 gate rows followed by the 64 up rows of the same indices
+// (two such pairs per tile of 256); the epilogue writes silu(gate) * up, [M, N/2] with row stride
+// ldc, instead of the product.
 template <int BN, int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -244,22 +245,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
       if constexpr (kSiluMul) {
+        // the tile's columns: [64 gate | their 64 up] twice; output columns n0 / 2 + 64 * half + c
         const int n_out = N / 2, o0 = n0 / 2;
 #pragma unroll 1
-        for (int c = 0; c < BN / 2; c += 32) {
+        for (int cc = 0; cc < BN / 2; cc += 32) {
+          const int half = cc / 64, c = cc % 64;
           unsigned g[32], u[32];
-          tmem_ld32(tmem_acc + (unsigned)c, g);
-          tmem_ld32(tmem_acc + (unsigned)(BN / 2 + c), u);
+          tmem_ld32(tmem_acc + (unsigned)(half * 128 + c), g);
+          tmem_ld32(tmem_acc + (unsigned)(half * 128 + 64 + c), u);
           tmem_ld_wait();
           if (row < M) {
-            TOut* dst = C + (size_t)row * ldc + o0 + c;
+            TOut* dst = C + (size_t)row * ldc + o0 + cc;
             float a[32];
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const float gg = __uint_as_float(g[e]);
               a[e] = gg / (1.f + __expf(-gg)) * __uint_as_float(u[e]);
             }
-            if (o0 + c + 32 <= n_out && (((uintptr_t)dst) & 15) == 0 && sizeof(TOut) == 2) {
+            if (o0 + cc + 32 <= n_out && (((uintptr_t)dst) & 15) == 0 && sizeof(TOut) == 2) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
                 uint4 o;
@@ -270,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               }
             } else {
               for (int e = 0; e < 32; ++e)
-                if (o0 + c + e < n_out) dst[e] = from_f32<TOut>(a[e]);
+                if (o0 + cc + e < n_out) dst[e] = from_f32<TOut>(a[e]);
             }
           }
         }
@@ -393,8 +396,8 @@ int launch(void* C, long long ldc, const void* A, long long lda, const void* W, 
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw; C: [M, N] bfloat16 or
 // float32, row stride ldc. K and the row strides must be multiples of 8 elements and the bases
 // 16-byte aligned (TMA). tile_n: 256 or 128.
-// silu_mul != 0 (tile_n 256, bfloat16 out, N a multiple of 256): W's rows come in blocks of 128 gate
-// rows followed by their 128 up rows, and C is [M, N / 2] = silu(gate) * up.
+// silu_mul != 0 (tile_n 256, bfloat16 out, N a multiple of 256): W's rows come in blocks of 64 gate
+// rows followed by their 64 up rows, and C is [M, N / 2] = silu(gate) * up.
 OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W,
                            long long ldw, int M, int N, int K, int tile_n, int silu_mul, void* stream) {
   OI_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);

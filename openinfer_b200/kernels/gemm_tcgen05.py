@@ -10,7 +10,7 @@ from . import lib as _lib
 from .lib import KernelError
 
 
-ACT_BLOCK = 128   # gate rows per tile half of the fused gate/up product
+ACT_BLOCK = 64    # the fused gate/up matrix: blocks of 64 gate rows followed by the 64 up rows of the same indices
 
 
 def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -39,7 +39,8 @@ def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256)
 
 def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """out[M, I] = silu(x Wg^T) * (x Wu^T) in one kernel. ``w_gate_up`` is [2 I, K] with rows in blocks
-    of 128 gate rows followed by the 128 up rows of the same indices (I a multiple of 128)."""
+    of 64 gate rows followed by the 64 up rows of the same indices (I a multiple of 128: a tile of the
+    kernel holds two such pairs)."""
     M, K = x.shape
     N = w_gate_up.shape[0]
     if N % (2 * ACT_BLOCK) or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or not takes(out, x, w_gate_up):

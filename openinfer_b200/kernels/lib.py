@@ -34,7 +34,7 @@ _SIGNATURES = {
     "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05_status": [ctypes.POINTER(c_int)],
-    "oi_gemm_stream": [P, I, L, P, L, P, L, I, I, I, I, P],
+    "oi_gemm_stream": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_set_pdl": [I],
     "oi_gemm_stream_status": [ctypes.POINTER(c_int)],
     "oi_attention_mma": [P, I, P, I, P, P, L, I, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P, P, I, I, P],

@@ -70,10 +70,10 @@ def _operands_ok(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
     return not (x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16)
 
 
-def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
+def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool = False) -> bool:
     """The tcgen05 weight-streaming kernel, when it takes the shape."""
     M, N, K = x.shape[0], w.shape[0], w.shape[1]
-    if K % 8 or not _operands_ok(out, x, w):
+    if K % 8 or not _operands_ok(out, x, w) or (silu_mul and N % 128):
         return False
     c = stream_cluster_size(N, K, _sm_count(x.device))
     if _FORCE_C:
@@ -83,9 +83,21 @@ def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
         c //= 2
     L = _lib.load()
     _lib.check(L.oi_gemm_stream(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c,
+                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c, 1 if silu_mul else 0,
                                 torch.cuda.current_stream().cuda_stream), "gemm_stream")
     return True
+
+
+def gate_up_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
+    """silu(x Wg^T) * (x Wu^T) for up to 16 rows of x in ONE weight-streaming kernel, or None when it
+    does not take the operands. ``w_gate_up`` [2 I, K]: blocks of 64 gate rows followed by the 64 up
+    rows of the same indices."""
+    M = x.shape[0]
+    if (DECODE_GEMM != "stream" or not 0 < M <= DECODE_MAX_ROWS or x.dtype != torch.bfloat16
+            or w_gate_up.dtype != torch.bfloat16):
+        return None
+    act = torch.empty((M, w_gate_up.shape[0] // 2), dtype=x.dtype, device=x.device)
+    return act if _stream(act, x, w_gate_up, silu_mul=True) else None
 
 
 def stream_status() -> int:

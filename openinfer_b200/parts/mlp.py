@@ -11,7 +11,7 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import gemm_tcgen05
-from ..kernels.linear import linear, linear_silu_mul
+from ..kernels.linear import gate_up_silu_mul, linear, linear_silu_mul
 
 # rows from which the gate/up product with the activation in its epilogue is used (prompt portions)
 FUSED_MIN_ROWS = 128
@@ -43,8 +43,8 @@ class GatedMlp(FeedForward):
             raise ValueError("gate_proj and up_proj must be stored in one dtype to be fused")
         inter = self.spec.intermediate_size
         # Rows of the fused matrix: blocks of `block` gate rows followed by the up rows of the same
-        # indices. With block = 128 a 256-row tile of the tensor-core product holds a gate block and
-        # its up block side by side, and the activation is formed in that kernel's epilogue.
+        # indices. With block = 64 a 128-row tile of the tensor-core products holds a gate block and
+        # its up block side by side, and the activation is formed in those kernels' epilogues.
         self.block = gemm_tcgen05.ACT_BLOCK if (g.dtype == torch.bfloat16 and inter % gemm_tcgen05.ACT_BLOCK == 0) else inter
         nb = inter // self.block
         self.w_gate_up = torch.stack([g.view(nb, self.block, -1), u.view(nb, self.block, -1)], dim=1).reshape(2 * inter, -1).contiguous()
@@ -52,10 +52,15 @@ class GatedMlp(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         inter = self.spec.intermediate_size
-        if (self.block == gemm_tcgen05.ACT_BLOCK and x.shape[0] >= FUSED_MIN_ROWS and x.dtype == torch.bfloat16):
-            act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
-            if gemm_tcgen05.takes(act, x, self.w_gate_up):
-                gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up)
-                return linear(act, self.w_down)
+        if self.block == gemm_tcgen05.ACT_BLOCK and x.dtype == torch.bfloat16:
+            if x.shape[0] >= FUSED_MIN_ROWS and inter % (2 * gemm_tcgen05.ACT_BLOCK) == 0:
+                act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
+                if gemm_tcgen05.takes(act, x, self.w_gate_up):
+                    gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up)
+                    return linear(act, self.w_down)
+            else:
+                act = gate_up_silu_mul(x, self.w_gate_up)     # decode: the weight stream forms the activation
+                if act is not None:
+                    return linear(act, self.w_down)
         gate_up = linear(x, self.w_gate_up)
         return linear_silu_mul(gate_up, self.w_down, self.block)

@@ -508,7 +508,7 @@ def test_gemm_stream(M, N, K):
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
             klib.check(L.oi_gemm_stream(out.data_ptr(), 1 if out_dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c,
+                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c, 0,
                                         torch.cuda.current_stream().cuda_stream), "gemm_stream")
             tol_ = 2e-2 * ref.abs().max().item() if out_dtype == torch.bfloat16 else 2e-4 * ref.abs().max().item()
             err = (out.double() - ref).abs().max().item()
@@ -531,9 +531,9 @@ def test_gemm_stream_refuses_bad_operands():
     stream = torch.cuda.current_stream().cuda_stream
     # two slices of a single k block, 129 rows of x, a misaligned weight
     for args in [(4, 128, 64, 2), (129, 128, 64, 1)]:
-        rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), *args, stream)
+        rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), *args, 0, stream)
         assert rc != 0 and b"gemm_stream" in L.oi_last_error()
-    rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr() + 2, w.stride(0), 4, 127, 64, 1, stream)
+    rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr() + 2, w.stride(0), 4, 127, 64, 1, 0, stream)
     assert rc != 0 and b"aligned" in L.oi_last_error()
 
 
@@ -578,20 +578,48 @@ def test_gemm_tcgen05(M, N, K, tile_n):
 
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 384, 200), (2048, 1024, 512)])
 def test_gemm_tcgen05_with_activation_in_the_epilogue(M, I, K):
-    """silu(x Wg^T) * (x Wu^T) from one kernel, gate and up rows interleaved in blocks of 128."""
+    """silu(x Wg^T) * (x Wu^T) from one kernel, gate and up rows interleaved in blocks of 64."""
     from openinfer_b200.kernels import gemm_tcgen05 as g
     torch.manual_seed(M + I)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     wg = (torch.randn(I, K, device=DEV) * 0.1).to(torch.bfloat16)
     wu = (torch.randn(I, K, device=DEV) * 0.1).to(torch.bfloat16)
-    nb = I // 128
-    w = torch.stack([wg.view(nb, 128, K), wu.view(nb, 128, K)], dim=1).reshape(2 * I, K).contiguous()
+    nb = I // g.ACT_BLOCK
+    w = torch.stack([wg.view(nb, g.ACT_BLOCK, K), wu.view(nb, g.ACT_BLOCK, K)], dim=1).reshape(2 * I, K).contiguous()
     out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
     g.gemm_silu_mul(out, x, w)
     assert g.status() == 0
     gg, uu = x.double() @ wg.double().t(), x.double() @ wu.double().t()
     ref = gg / (1 + torch.exp(-gg)) * uu
     assert (out.double() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 64, 64), (8, 192, 520), (16, 12288, 4096), (13, 448, 1000)])
+def test_gemm_stream_with_activation(M, I, K):
+    """The decode gate/up product with silu(gate) * up formed where the K slices are added up."""
+    from openinfer_b200.kernels import gemm_tcgen05 as g
+    from openinfer_b200.kernels import lib as klib
+    from openinfer_b200.kernels import linear as lin
+    torch.manual_seed(M + I)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    wg = (torch.randn(I, K, device=DEV) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(I, K, device=DEV) * 0.05).to(torch.bfloat16)
+    nb = I // g.ACT_BLOCK
+    w = torch.stack([wg.view(nb, g.ACT_BLOCK, K), wu.view(nb, g.ACT_BLOCK, K)], dim=1).reshape(2 * I, K).contiguous()
+    gg, uu = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    ref = gg / (1 + torch.exp(-gg)) * uu
+    L = klib.load()
+    num_kb = -(-K // 64)
+    for c in (1, 2, 4, 8):
+        if (c - 1) * (-(-num_kb // c)) >= num_kb:
+            continue
+        out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+        klib.check(L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
+                                    M, 2 * I, K, c, 1, torch.cuda.current_stream().cuda_stream), "gemm_stream")
+        assert (out.double() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item(), f"{c} slices"
+    assert lin.stream_status() == 0
+    act = lin.gate_up_silu_mul(x, w)
+    assert act is not None and (act.double() - ref).abs().max().item() <= 1.5e-2 * ref.abs().max().item()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
