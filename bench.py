@@ -125,6 +125,9 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--model", default="8b", choices=sorted(MODELS), help="layer sizes (default: the headline 8B)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points and the prefill")
+    ap.add_argument("--timeline", default=None, metavar="FILE",
+                    help="write the start and end of every kernel of one decode step (CUPTI through torch.profiler: kernels "
+                         "overlap under programmatic dependent launch, which a serialising profiler cannot show) and exit")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
@@ -204,6 +207,40 @@ def main() -> int:
         for rid in ids:
             runner.end(rid)
         return ms, launches
+
+    if args.timeline:
+        from torch.profiler import ProfilerActivity, profile
+        ids = [f"p{i}" for i in range(B)]
+        for rid in ids:
+            fake_context(rid, CONTEXT)
+        out_ids = torch.empty(B, dtype=torch.int32, device=dev)
+
+        def one():
+            logits = runner.step([StepEntry(rid, [1], [0]) for rid in ids])
+            ops.argmax(out_ids, logits)
+
+        for _ in range(W):
+            one()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                one()
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                     key=lambda e: e.time_range.start)
+        first = [i for i, e in enumerate(evs) if "embedding" in e.name][-1]   # the last of the three steps
+        evs = evs[first:]
+        t0 = evs[0].time_range.start
+        with open(args.timeline, "w") as f:
+            f.write("start_us end_us us_after_the_end_of_everything_before kernel\n")
+            done = 0.0
+            for e in evs:
+                a, b = e.time_range.start - t0, e.time_range.end - t0
+                f.write(f"{a:9.1f} {b:9.1f} {b - max(done, a) if b > done else 0.0:7.1f}  {e.name[:60]}\n")
+                done = max(done, b)
+        print(json.dumps({"timeline": args.timeline, "batch": B, "layers": config.num_hidden_layers,
+                          "kernels": len(evs), "step_us": round(done, 1)}))
+        return 0
 
     if args.profile:
         if args.profile == "decode":
