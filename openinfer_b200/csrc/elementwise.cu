@@ -67,6 +67,25 @@ OI_API int oi_embedding(void* out, int out_dtype, const void* table, int table_d
 //   row_idx != null : output row r reads x[row_idx[r]] (+ delta[row_idx[r]], not stored): the rows
 //                   whose logits are wanted.
 //   out[r] = round( x * rsqrt(mean(x^2) + eps) * (w_offset + w) )
+// ids[i] = from[src[i]] where src[i] >= 0: token ids that the previous step drew and the host has not
+// seen yet (indices outside `from` leave the id alone; the host checks them before the launch).
+__global__ void gather_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ from,
+                                     int n, int n_from) {
+  pdl_start();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int j = src[i];
+  if (j >= 0 && j < n_from) ids[i] = from[j];
+}
+
+OI_API int oi_gather_tokens(int* ids, const int* src, const int* from, int n, int n_from, void* stream) {
+  OI_REQUIRE(n >= 0 && n_from >= 0, "gather_tokens: bad sizes");
+  if (n == 0) return OI_OK;
+  oi_launch(gather_tokens_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, ids, src, from, n, n_from);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
 // ---------------------------------------------------------------------------
 template <typename T, bool kCache>
 __global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* __restrict__ delta,

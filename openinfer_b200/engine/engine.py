@@ -37,20 +37,41 @@ class RunnerExecutor(Executor):
     def free_pages(self) -> int:
         return self.runner.cache.min_free_pages()
 
+    supports_lookahead = True
+
     def execute(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int) -> Dict[Hashable, int]:
+        return self.collect(self.launch(prefill, decode, step_seed))
+
+    def launch(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int, previous=None):
+        """Start one batch on the GPU. Returns (request ids of the sampled rows, their pending tokens)."""
         entries, rows = [], []
         for p in prefill:
             entries.append(StepEntry(p.request_id, p.tokens, [len(p.tokens) - 1] if p.is_last else []))
             if p.is_last:
                 rows.append(p)
+        feed = None
         for d in decode:
-            entries.append(StepEntry(d.request_id, [d.token], [0]))
+            if d.token is None:
+                # the token comes from the batch launched before this one, which the host has not read yet
+                if previous is None or d.request_id not in previous[2]:
+                    raise ValueError(f"request {d.request_id!r} has a token in flight but no batch that draws it")
+                feed = previous[1].device
+                entries.append(StepEntry(d.request_id, [0], [0], token_from=previous[2][d.request_id]))
+            else:
+                entries.append(StepEntry(d.request_id, [d.token], [0]))
             rows.append(d)
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, device_tokens=feed)
+        ids = [r.request_id for r in rows]
         if not rows:
+            return ids, None, {}
+        pending = self.sampler.select_async(logits, [r.sampling for r in rows], [r.step_index for r in rows], step_seed)
+        return ids, pending, {rid: i for i, rid in enumerate(ids)}
+
+    def collect(self, handle) -> Dict[Hashable, int]:
+        ids, pending, _ = handle
+        if pending is None:
             return {}
-        tokens = self.sampler.select(logits, [r.sampling for r in rows], [r.step_index for r in rows], step_seed)
-        return {r.request_id: t for r, t in zip(rows, tokens)}
+        return dict(zip(ids, pending.result()))
 
     def drop(self, request_id: Hashable) -> None:
         self.runner.end(request_id)
@@ -79,7 +100,7 @@ class LLM:
                  kv_cache_memory_margin_mib: int = DEFAULT_KV_MARGIN_MIB,
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
-                 cuda_graph: bool = True, runner: Optional[ModelRunner] = None) -> None:
+                 cuda_graph: bool = True, lookahead: bool = True, runner: Optional[ModelRunner] = None) -> None:
         device = f"cuda:{device_ordinal}"
         weights_seed = None
         if runner is not None:
@@ -109,7 +130,8 @@ class LLM:
         max_context = self.runner.spec.max_positions or (1 << 30)
         self.scheduler = Scheduler(
             self.executor, max_context_tokens=max_context, stop_token_ids=self.runner.spec.stop_token_ids,
-            max_prefill_tokens=max_prefill_tokens, max_decode_batch=max_decode_batch, seed=engine_seed)
+            max_prefill_tokens=max_prefill_tokens, max_decode_batch=max_decode_batch, seed=engine_seed,
+            lookahead=lookahead)
         self._next_id = 0
 
     # ---- step-wise use: submit requests, then call step() until has_work() is false
@@ -121,7 +143,9 @@ class LLM:
         return rid
 
     def step(self) -> List[Event]:
-        """One scheduler iteration: host tokens in, one batch on the GPU, sampled tokens out."""
+        """One scheduler iteration: host tokens in, one batch on the GPU, sampled tokens out. With
+        ``lookahead`` (the default) the batch launched by this call is collected by the next one: its
+        events arrive one call later, and the GPU runs on while the host reads and plans."""
         return self.scheduler.step()
 
     def has_work(self) -> bool:

@@ -19,6 +19,7 @@ from ..cache.manager import RELEASED, CacheManager
 from ..cache.pool import OutOfPages
 from ..config.base import load_config, resolve_architecture
 from ..kernels import lib as kernel_lib
+from ..kernels import ops
 from ..parts.model import Model
 from ..weights.loader import load_tensors
 from ..weights.random import random_tensors
@@ -34,6 +35,8 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()   # places among ``tokens`` whose logits are asked for
+    token_from: Optional[int] = None   # a single token that is not known to the host yet: element
+                                       # ``token_from`` of the ``device_tokens`` given to step()
 
 
 def _dtype_of(name) -> torch.dtype:
@@ -151,15 +154,24 @@ class ModelRunner:
                     f"request {e.request_id!r}: {held + n} positions exceed max_position_embeddings {max_pos}")
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits [wanted rows, vocab] on the device, rows in
         the order of the entries and of each entry's ``want`` (None when nothing is wanted).
+        ``device_tokens`` (int32, on the device): where entries with ``token_from`` take their token.
 
         Raises ``OutOfPages`` with nothing changed if the cache cannot hold the new rows."""
         entries = list(entries)
         if not entries:
             return None
         self.validate(entries)
+        self._device_tokens = device_tokens
+        if any(e.token_from is not None for e in entries):
+            if device_tokens is None or device_tokens.dtype != torch.int32 or not device_tokens.is_cuda:
+                raise StepError("entries with token_from need int32 device_tokens")
+            for e in entries:
+                if e.token_from is not None and (len(e.tokens) != 1 or not 0 <= e.token_from < device_tokens.numel()):
+                    raise StepError(f"request {e.request_id!r}: token_from {e.token_from} needs one token and an index "
+                                    f"below {device_tokens.numel()}")
         cache = self.cache
         opened, reserved = [], []
         try:
@@ -200,13 +212,19 @@ class ModelRunner:
         if self.cache.has(request_id):
             self.cache.close(request_id)
 
+    def _take_device_tokens(self, meta: torch.Tensor, sections: Dict[str, int], T: int, entries) -> None:
+        """Rows whose token the host does not know yet get it from the tensor given to step()."""
+        if any(e.token_from is not None for e in entries):
+            ops.gather_tokens(meta[sections["token_ids"]: sections["token_ids"] + T],
+                              meta[sections["token_src"]: sections["token_src"] + T], self._device_tokens)
+
     # ------------------------------------------------------------------ metadata
     @staticmethod
     def _layout(T: int, B: int, max_pages: int, G: int, n_want: int):
         """Sections of the packed int32 metadata buffer (each starts on a 16-byte boundary)."""
         sections: Dict[str, int] = {}
         off = 0
-        for name, size in (("token_ids", T), ("positions", T), ("token_req", T), ("cu_seqlens", B + 1),
+        for name, size in (("token_ids", T), ("token_src", T), ("positions", T), ("token_req", T), ("cu_seqlens", B + 1),
                            ("state_slots", B)):
             sections[name] = off
             off += _align4(size)
@@ -231,9 +249,11 @@ class ModelRunner:
             return host[sections[name]: sections[name] + size]
 
         tok, pos, req = view("token_ids", T), view("positions", T), view("token_req", T)
+        src = view("token_src", T)
         cu = view("cu_seqlens", B + 1)
         slots_host = view("state_slots", B)
         tok[:] = 0
+        src[:] = -1
         pos[:] = 0
         req[:] = -1
         slots_host[:] = 0
@@ -244,6 +264,8 @@ class ModelRunner:
             tok[row: row + n] = np.asarray(e.tokens, dtype=np.int32)
             pos[row: row + n] = np.arange(starts[b], starts[b] + n, dtype=np.int32)
             req[row: row + n] = b
+            if e.token_from is not None:
+                src[row] = e.token_from
             cu[b] = row
             slots_host[b] = cache.state_slot(e.request_id)
             want_rows.extend(row + int(w) for w in e.want)
@@ -304,6 +326,7 @@ class ModelRunner:
         if n_want:
             host[sections["want"]: sections["want"] + n_want] = np.asarray(want_rows, dtype=np.int32)
         dev = self._stage(host)
+        self._take_device_tokens(dev, sections, T, entries)
         slots = [cache.state_slot(e.request_id) for e in entries]
         ctx = self._context(dev, sections, T, B, max_pages, q_lens, starts, kv_lens, slots)
         row_idx = dev[sections["want"]: sections["want"] + n_want] if n_want else None
@@ -388,6 +411,7 @@ class ModelRunner:
         meta.copy_(self._staging[:n], non_blocking=True)
         self._staging_event = torch.cuda.Event()
         self._staging_event.record()
+        self._take_device_tokens(meta, sections, bucket, entries)
         graph.replay()
         kernel_lib.launches += recorded
         if not want_rows:

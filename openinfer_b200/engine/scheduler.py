@@ -21,6 +21,15 @@ Decisions follow the reference's scheduler (pegainfer-qwen3/src/scheduler.rs):
   smaller than reported), every request the step touched ends with an error and is
   dropped, and the scheduler goes on with the rest (scheduler.rs:1354-1378).
 
+One step ahead (not in the reference, whose loop waits for every step's tokens): with an executor
+that can ``launch`` a batch and ``collect`` its tokens later, ``step()`` launches batch n + 1 BEFORE it
+collects batch n. A decoding request's next input is then "the token batch n draws for it", which
+stays on the device, so the GPU goes from one step into the next while the host reads tokens, resolves
+stops and plans. What the host cannot know in time is a stop token: a request that batch n ends with a
+stop token has already been given a row in batch n + 1; that row's result is thrown away (its cache
+pages are free for reuse at once: work on the device is ordered). Ends by length are known in advance
+and get no such row. Events therefore arrive one call later; the tokens are the same.
+
 The scheduler is host code only: it talks to an *executor* (the model runner plus
 sampler, or a fake in tests).
 """
@@ -67,7 +76,7 @@ class PrefillItem:
 @dataclasses.dataclass
 class DecodeItem:
     request_id: Hashable
-    token: int                # the last generated token, fed back
+    token: Optional[int]      # the last generated token, fed back; None: the one the batch in flight draws for it
     sampling: SamplingParams = SamplingParams()
     step_index: int = 0
 
@@ -89,6 +98,17 @@ class Executor:
     def drop(self, request_id: Hashable) -> None:
         raise NotImplementedError
 
+    # Optional, for running one step ahead: launch() starts a batch and returns a handle; a decode item
+    # whose token is None takes the token that the batch of ``previous`` (a handle not collected yet)
+    # draws for the same request. collect() waits for a launched batch and returns its tokens.
+    supports_lookahead = False
+
+    def launch(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int, previous=None):
+        raise NotImplementedError
+
+    def collect(self, handle) -> Dict[Hashable, int]:
+        raise NotImplementedError
+
 
 @dataclasses.dataclass
 class _Pending:
@@ -102,6 +122,14 @@ class _Active:
     req: Request
     generated: List[int]
     last_token: int
+    inflight: int = 0       # tokens drawn for it by batches that are launched and not collected yet
+    ended: bool = False
+
+
+@dataclasses.dataclass
+class _Launched:
+    handle: object
+    rows: List[_Active]     # who gets a token from this batch
 
 
 def lifetime_pages(prompt_len: int, max_tokens: int, page_size: int) -> int:
@@ -117,7 +145,8 @@ def pages_for(tokens: int, page_size: int) -> int:
 class Scheduler:
     def __init__(self, executor: Executor, *, max_context_tokens: int, stop_token_ids: Sequence[int] = (),
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
-                 max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, seed: int = DEFAULT_ENGINE_SEED) -> None:
+                 max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, seed: int = DEFAULT_ENGINE_SEED,
+                 lookahead: Optional[bool] = None) -> None:
         if max_prefill_tokens <= 0 or max_decode_batch <= 0:
             raise ValueError("max_prefill_tokens and max_decode_batch must be positive")
         self.executor = executor
@@ -131,13 +160,18 @@ class Scheduler:
         self.prefilling: List[_Pending] = []
         self.active: List[_Active] = []
         self.steps = 0
+        can = bool(getattr(executor, "supports_lookahead", False))
+        if lookahead and not can:
+            raise ValueError("this executor cannot run one step ahead")
+        self.lookahead = can if lookahead is None else bool(lookahead)
+        self._inflight: Optional[_Launched] = None
 
     # ------------------------------------------------------------------ public
     def submit(self, req: Request) -> None:
         self.deferred.append(req)
 
     def has_work(self) -> bool:
-        return bool(self.deferred or self.prefilling or self.active)
+        return bool(self.deferred or self.prefilling or self.active or self._inflight is not None)
 
     def load(self) -> Dict[str, int]:
         """Snapshot like the reference's LoadSnapshot (scheduler.rs:513-526)."""
@@ -150,7 +184,7 @@ class Scheduler:
         P = self.page_size
         fut = 0
         for a in self.active:
-            held = len(a.req.prompt_tokens) + len(a.generated) - 1  # the last token has no keys yet
+            held = len(a.req.prompt_tokens) + len(a.generated) + a.inflight - 1  # the last token has no keys yet
             fut += max(0, lifetime_pages(len(a.req.prompt_tokens), a.req.max_tokens, P) - pages_for(held, P))
         for p in self.prefilling:
             fut += max(0, lifetime_pages(len(p.req.prompt_tokens), p.req.max_tokens, P) - pages_for(p.done, P))
@@ -198,6 +232,8 @@ class Scheduler:
     # ------------------------------------------------------------------ one iteration
     def step(self) -> List[Event]:
         """Admit, build one batch, run it, resolve. Returns this iteration's events."""
+        if self.lookahead:
+            return self._step_ahead()
         events = self._admit()
         taken = self._take_prefill()
         decoding = list(self.active)
@@ -239,6 +275,75 @@ class Scheduler:
         self.prefilling = unfinished + self.prefilling  # back to the front (effects.rs:318-406)
         return events
 
+    # ------------------------------------------------------------------ one iteration, one step ahead
+    def _step_ahead(self) -> List[Event]:
+        """Launch the next batch, then collect the one launched by the previous call."""
+        events = self._admit()
+        previous = self._inflight
+        self._inflight, failed = self._launch_next(previous)
+        if previous is not None:
+            try:
+                tokens = self.executor.collect(previous.handle)
+            except Exception as e:
+                self._fail(previous.rows, e, events)
+                tokens = None
+            for a in previous.rows:
+                a.inflight -= 1
+                if tokens is not None and not a.ended:   # ended meanwhile (a stop token one step earlier): the row is void
+                    self._resolve(a, tokens[a.req.request_id], events)
+        if failed is not None:   # the launch failed: everyone it touched fails, after what was in flight has arrived
+            e, taken, decoding = failed
+            for p in taken:
+                events.append(Event(p.req.request_id, "error", reason=f"{type(e).__name__}: {e}"))
+                self.executor.drop(p.req.request_id)
+            self._fail(decoding, e, events)
+        return events
+
+    def _launch_next(self, previous: Optional[_Launched]):
+        taken = self._take_prefill()
+        # who decodes: everyone who is still alive once the tokens in flight have arrived (a stop token
+        # among those cannot be known yet)
+        decoding = [a for a in self.active if len(a.generated) + a.inflight < max(1, a.req.max_tokens)]
+        if not taken and not decoding:
+            return None, None
+        prefill_items = [
+            PrefillItem(p.req.request_id, p.req.prompt_tokens[p.done: p.done + p.step_chunk],
+                        is_last=p.done + p.step_chunk == len(p.req.prompt_tokens),
+                        sampling=p.req.sampling, step_index=0)
+            for p in taken]
+        decode_items = [DecodeItem(a.req.request_id, a.last_token if a.inflight == 0 else None, a.req.sampling,
+                                   len(a.generated) + a.inflight) for a in decoding]
+        step_seed = self.rng.getrandbits(64)
+        self.steps += 1
+        try:
+            handle = self.executor.launch(prefill_items, decode_items, step_seed,
+                                          previous.handle if previous is not None else None)
+        except Exception as e:
+            return None, (e, taken, decoding)
+        rows = list(decoding)
+        unfinished: List[_Pending] = []
+        for p in taken:
+            p.done += p.step_chunk
+            if p.done < len(p.req.prompt_tokens):
+                unfinished.append(p)
+                continue
+            a = _Active(p.req, [], -1)
+            self.active.append(a)
+            rows.append(a)
+        self.prefilling = unfinished + self.prefilling
+        for a in rows:
+            a.inflight += 1
+        return _Launched(handle, rows), None
+
+    def _fail(self, rows: List[_Active], e: Exception, events: List[Event]) -> None:
+        for a in rows:
+            if a.ended:
+                continue
+            a.ended = True
+            events.append(Event(a.req.request_id, "error", reason=f"{type(e).__name__}: {e}"))
+            self.executor.drop(a.req.request_id)
+        self.active = [x for x in self.active if not x.ended]
+
     def _resolve(self, a: _Active, token: int, events: List[Event]) -> None:
         req = a.req
         if token in self.stop_token_ids and not req.sampling.ignore_eos:
@@ -252,6 +357,7 @@ class Scheduler:
 
     def _finish(self, a: _Active, events: List[Event], reason: str) -> None:
         events.append(Event(a.req.request_id, "finished", reason=reason))
+        a.ended = True
         self.executor.drop(a.req.request_id)
         self.active = [x for x in self.active if x is not a]
 

@@ -57,6 +57,20 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> torc
     return out
 
 
+def gather_tokens(ids: torch.Tensor, src: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """ids[i] = tokens[src[i]] wherever src[i] >= 0 (all int32, on the device)."""
+    _cuda(ids, src, tokens)
+    _i32(ids, "gather_tokens ids")
+    _i32(src, "gather_tokens src")
+    _i32(tokens, "gather_tokens tokens")
+    if ids.numel() != src.numel() or not (ids.is_contiguous() and src.is_contiguous() and tokens.is_contiguous()):
+        raise KernelError("gather_tokens: ids and src must be contiguous and of one length")
+    L = _lib.load()
+    _lib.check(L.oi_gather_tokens(ids.data_ptr(), src.data_ptr(), tokens.data_ptr(), ids.numel(), tokens.numel(),
+                                  _stream()), "gather_tokens")
+    return ids
+
+
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, *,
             delta: Optional[torch.Tensor] = None, row_idx: Optional[torch.Tensor] = None,
             weight_offset: float = 0.0) -> torch.Tensor:

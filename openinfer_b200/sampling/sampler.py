@@ -17,19 +17,46 @@ from ..kernels import ops
 from .params import SamplingParams, mix_seed, uniform_from
 
 
+class PendingTokens:
+    """Token ids chosen on the device and on their way to the host (a copy into pinned memory
+    and an event behind it); ``device`` may feed the next step before the host has looked."""
+
+    def __init__(self, device: Optional[torch.Tensor], host: Optional[torch.Tensor], event) -> None:
+        self.device, self._host, self._event = device, host, event
+
+    def result(self) -> List[int]:
+        if self.device is None:
+            return []
+        self._event.synchronize()
+        return [int(t) for t in self._host.tolist()]
+
+
 class Sampler:
     def __init__(self, vocab_size: int, device: torch.device) -> None:
         self.vocab_size = vocab_size
         self.device = torch.device(device)
         self._probs: Optional[torch.Tensor] = None
+        self._pinned: List[torch.Tensor] = []   # a small ring of pinned buffers for the copies to the host
+        self._turn = 0
+
+    def _host_buffer(self, n: int) -> torch.Tensor:
+        if not self._pinned or self._pinned[0].numel() < n:
+            self._pinned = [torch.empty(max(256, 2 * n), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._turn = (self._turn + 1) % len(self._pinned)
+        return self._pinned[self._turn][:n]
 
     def select(self, logits: torch.Tensor, params: Sequence[SamplingParams], steps: Sequence[int],
                step_seed: int) -> List[int]:
         """``logits`` float32 [rows, vocab]; ``steps[i]`` is row i's request-local step
         (how many tokens that request has drawn so far). Returns one token id per row."""
+        return self.select_async(logits, params, steps, step_seed).result()
+
+    def select_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], steps: Sequence[int],
+                     step_seed: int) -> PendingTokens:
+        """As ``select``, without waiting: the ids stay on the device and travel to the host behind an event."""
         n = len(params)
         if n == 0:
-            return []
+            return PendingTokens(None, None, None)
         if logits.shape[0] != n or logits.shape[1] != self.vocab_size:
             raise ValueError(f"logits {tuple(logits.shape)} do not match {n} rows of vocab {self.vocab_size}")
         out = torch.empty(n, dtype=torch.int32, device=self.device)
@@ -60,4 +87,8 @@ class Sampler:
                 out = picked
             else:
                 out[torch.tensor(sampled, device=self.device)] = picked
-        return [int(t) for t in out.cpu().tolist()]
+        host = self._host_buffer(n)
+        host.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(out, host, event)

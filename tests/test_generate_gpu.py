@@ -94,6 +94,30 @@ def test_stop_tokens_and_rejection(folders, tmp_path):
     assert res[1].finish_reason == "rejected:context_length" and res[1].token_ids == []
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_step_ahead_gives_the_tokens_of_waiting_for_every_step(folders, dtype):
+    """The engine launches step n + 1 before it has read step n's tokens (they are fed on the device);
+    the generated ids are those of the loop that waits, stop tokens, ends by length and prompts cut
+    into portions beside decoding included, and every page comes back."""
+    from openinfer_b200 import LLM
+    cfg, _ = plain.read_model_folder(folders["B"])
+    rng = random.Random(5)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 9, 33, 70, 4)]
+    max_tokens = [12, 1, 7, 20, 16]
+    outs = []
+    for ahead in (False, True):
+        llm = LLM(folders["B"], dtype=dtype, max_cache_tokens=1024, max_prefill_tokens=13, lookahead=ahead)
+        assert llm.scheduler.lookahead == ahead
+        free = llm.generate(prompts, max_tokens=max_tokens)
+        # make some token that the longest request draws in mid-course a stop token
+        llm.scheduler.stop_token_ids = {free[3][9]}
+        res = llm.generate_detailed(prompts, max_tokens=max_tokens)
+        outs.append((free, [(r.token_ids, r.finish_reason) for r in res]))
+        assert llm.runner.cache.min_free_pages() == llm.runner.cache.num_pages and not llm.has_work()
+    assert outs[0] == outs[1]
+    assert outs[1][1][3][1] == "stop" and len(outs[1][1][3][0]) <= 9
+
+
 def test_command_line(folders):
     cfg, w = plain.read_model_folder(folders["A"])
     want = plain.greedy_generate(cfg, w, [7, 8, 9], 5)

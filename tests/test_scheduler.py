@@ -213,3 +213,91 @@ def test_per_step_seed_is_reproducible():
         s.submit(Request("a", [1], max_tokens=3))
         s.run()
     assert seeds[:3] == seeds[3:] and len(set(seeds[:3])) == 3
+
+
+# ---------------------------------------------------------------------------
+# one step ahead: batch n + 1 is launched before batch n's tokens are read
+# ---------------------------------------------------------------------------
+class AheadExecutor(FakeExecutor):
+    """The fake with launch/collect: a decode item without a token takes the one the batch before
+    drew for it. Keeps at most one batch uncollected, as the scheduler promises."""
+
+    supports_lookahead = True
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.uncollected = 0
+
+    def launch(self, prefill, decode, step_seed, previous=None):
+        assert self.uncollected <= 1, "two batches were in flight before this launch"
+        resolved = []
+        for d in decode:
+            if d.token is None:
+                assert previous is not None and d.request_id in previous, "a token in flight that nobody draws"
+                resolved.append(DecodeItem(d.request_id, previous[d.request_id], d.sampling, d.step_index))
+            else:
+                resolved.append(d)
+        out = self.execute(prefill, resolved, step_seed)
+        self.uncollected += 1
+        return out
+
+    def collect(self, handle):
+        self.uncollected -= 1
+        return handle
+
+
+def run_both(make_requests, **kw):
+    results = []
+    for cls in (FakeExecutor, AheadExecutor):
+        ex = cls(**kw.get("ex", {}))
+        s = sched(ex, **kw.get("sched", {}))
+        assert s.lookahead == (cls is AheadExecutor)
+        for r in make_requests():
+            s.submit(r)
+        results.append((collect(s.run()), ex))
+    return results
+
+
+def test_one_step_ahead_gives_the_same_tokens_and_ends():
+    def reqs():
+        return [Request("a", [1, 2, 3], max_tokens=6), Request("b", list(range(10, 30)), max_tokens=1),
+                Request("c", [50], max_tokens=3), Request("d", [7, 8], max_tokens=40)]
+    (sync, ex0), (ahead, ex1) = run_both(reqs, sched={"max_prefill_tokens": 8, "stop_token_ids": [20]})
+    assert sync == ahead
+    assert sync[1]["d"] == ("finished", "stop") and sync[1]["a"] == ("finished", "length")
+    assert ex1.used() == 0 and sorted(ex1.dropped) == sorted(ex0.dropped)
+    # d drew its stop token while it already had a row in the next batch: one row more, thrown away
+    rows_of_d = [sum("d" in dec for _, dec in ex.batches) for ex in (ex0, ex1)]
+    assert rows_of_d[1] == rows_of_d[0] + 1 and ex1.uncollected == 0
+    # a, b and c end by length, which is known in advance: no row more
+    for r in "ac":
+        assert sum(r in dec for _, dec in ex0.batches) == sum(r in dec for _, dec in ex1.batches)
+
+
+def test_one_step_ahead_never_launches_a_row_past_max_tokens():
+    ex = AheadExecutor(total_pages=4, page_size=4)   # room for exactly prompt + max_tokens
+    s = sched(ex)
+    s.submit(Request("a", list(range(8)), max_tokens=8))
+    toks, fin = collect(s.run())
+    assert len(toks["a"]) == 8 and fin["a"] == ("finished", "length")
+    assert all(len(d) <= 1 for _, d in ex.batches)
+
+
+def test_one_step_ahead_failed_launch_fails_who_it_touched():
+    ex = AheadExecutor(fail_on_step=3)
+    s = sched(ex)
+    s.submit(Request("a", [1, 2, 3], max_tokens=10))
+    events = s.run()
+    toks, fin = collect(events)
+    assert fin["a"][0] == "error" and "injected failure" in fin["a"][1]
+    assert toks["a"] == [4, 5, 6]       # the three batches before the failing one were collected
+    assert ex.dropped == ["a"] and not s.has_work()
+    s.submit(Request("b", [1], max_tokens=2))
+    toks, fin = collect(s.run())
+    assert toks["b"] == [2, 3] and fin["b"] == ("finished", "length")
+
+
+def test_one_step_ahead_is_refused_without_an_executor_for_it():
+    with pytest.raises(ValueError):
+        sched(FakeExecutor(), lookahead=True)
+    assert not sched(AheadExecutor(), lookahead=False).lookahead
