@@ -1,7 +1,7 @@
 """Each part alone against its plain statement, and the generality of the assembly: a
 window, a layer that reads another layer's cache, a layer named twice in the run order, and
-a toy mixer with state of its own that is defined here, registered, built and stepped
-without touching the package."""
+a toy mixer with state of its own, a toy feed-forward with routing and a toy position encoding
+that are defined here, registered, built and stepped without touching the package."""
 import dataclasses
 import math
 import random
@@ -272,4 +272,146 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     again = runner.step([StepEntry("c", a, list(range(len(a))))])
     assert_close(again, plain_forward(a), "float32", "toy request c in a reused slot")
     runner.end("b"); runner.end("c")
+    runner.cache.check()
+
+
+# ---------------------------------------------------------------------------
+# a toy feed-forward with routing and a toy position encoding, defined here: one model mixes them
+# with the package's own parts, layer by layer, without a change to the package
+# ---------------------------------------------------------------------------
+@dataclasses.dataclass(frozen=True)
+class RoutedToySpec:
+    kind: str = "toy_routed"
+    hidden_size: int = 0
+    inner: int = 0
+    experts: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
+class HalvedPositionSpec:
+    kind: str = "toy_halved_rope"
+    rotary_dim: int = 0
+    theta: float = 100.0
+    max_positions: int = 0
+
+
+def _register_toy_ffn_and_position():
+    from openinfer_b200.parts import ParamInfo
+    from openinfer_b200.parts.base import FeedForward, PositionEncoding
+    from openinfer_b200.parts.registry import register_feed_forward, register_position_encoding
+
+    @register_feed_forward("toy_routed")
+    class RoutedToy(FeedForward):
+        """Every row goes to the ONE expert its router logit (float32) is largest for:
+        y = gate_e * relu(x W1_e^T) W2_e^T. torch ops: a test double, not a product kernel."""
+
+        def parameters(self):
+            s = self.spec
+            return {"router.weight": ParamInfo((s.experts, s.hidden_size)),
+                    "w1": ParamInfo((s.experts * s.inner, s.hidden_size)),
+                    "w2": ParamInfo((s.experts * s.hidden_size, s.inner))}
+
+        def load(self, tensors):
+            s = self.spec
+            self.router = tensors["router.weight"]
+            self.w1 = tensors["w1"].view(s.experts, s.inner, s.hidden_size)
+            self.w2 = tensors["w2"].view(s.experts, s.hidden_size, s.inner)
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.router.float().t()
+            prob = torch.softmax(logits, -1)
+            top = prob.argmax(-1)
+            out = torch.zeros_like(x, dtype=torch.float32)
+            for e in range(self.spec.experts):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel():
+                    hmid = torch.relu(x[rows].float() @ self.w1[e].float().t())
+                    out[rows] = prob[rows, e, None] * (hmid @ self.w2[e].float().t())
+            return out.to(x.dtype)
+
+    @register_position_encoding("toy_halved_rope")
+    class HalvedRope(PositionEncoding):
+        """Rotation by HALF the position: angle = (pos / 2) * theta^(-2i / rotary_dim). Only the table differs."""
+
+        def rotation_tables(self, device):
+            s = self.spec
+            half = s.rotary_dim // 2
+            inv = 1.0 / torch.pow(torch.tensor(float(s.theta)), torch.arange(half, dtype=torch.float32) * 2.0 / s.rotary_dim)
+            ang = (torch.arange(s.max_positions, dtype=torch.float32) / 2.0)[:, None] * inv[None, :]
+            return torch.cos(ang).contiguous().to(device), torch.sin(ang).contiguous().to(device)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_toy_position_encoding(dtype_name):
+    from openinfer_b200.engine.runner import StepEntry
+    from openinfer_b200.parts.spec import AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NormSpec
+    _register_toy_ffn_and_position()
+    dtype = torch.float32 if dtype_name == "float32" else torch.bfloat16
+    hidden, vocab, nq, nkv, hd, rot = 40, 37, 4, 2, 16, 8
+    norm = NormSpec("rms", hidden, 1e-5)
+    toy_attn = AttentionSpec(hidden_size=hidden, num_heads=nq, num_kv_heads=nkv, head_dim=hd, softmax_scale=0.3,
+                             position=HalvedPositionSpec(rotary_dim=rot, theta=100.0, max_positions=128), qk_norm=None)
+    usual = _mini_spec(layers=1, hidden=hidden, nq=nq, nkv=nkv, hd=hd, inter=72, vocab=vocab).blocks[0]
+    toy_block = BlockSpec(name="T.", mixer=toy_attn, feed_forward=RoutedToySpec(hidden_size=hidden, inner=24, experts=3),
+                          input_norm=norm, post_norm=norm)
+    spec = ModelSpec(vocab_size=vocab, hidden_size=hidden, blocks=(toy_block, usual), order=(0, 1), final_norm=norm,
+                     embedding_name="emb", final_norm_name="fn.", head_name="head", max_positions=128)
+    w = _random_tensors(spec, 9)
+    assert {"T.mlp.router.weight", "T.mlp.w1", "T.mlp.w2"} <= set(w)
+    w["T.mlp.router.weight"] = w["T.mlp.router.weight"] * 40     # clear routing decisions, all experts in use
+    runner = _runner(spec, dtype, w)
+
+    def plain_forward(toks):
+        wf = {k: v.float() for k, v in w.items()}
+        T = len(toks)
+        pos = torch.arange(T)
+        h = plain.embedding(torch.tensor(toks), wf["emb"])
+        # the toy layer: attention with the halved rotation over the first `rot` dims, no q/k norm
+        x = plain.rms_norm(h, wf["T.input_layernorm.weight"], 1e-5)
+        inv = 1.0 / torch.pow(torch.tensor(100.0), torch.arange(rot // 2, dtype=torch.float32) * 2.0 / rot)
+        ang = (pos.float() / 2.0)[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        q = plain.linear(x, wf["T.self_attn.q_proj.weight"]).view(T, nq, hd)
+        k = plain.linear(x, wf["T.self_attn.k_proj.weight"]).view(T, nkv, hd)
+        v = plain.linear(x, wf["T.self_attn.v_proj.weight"]).view(T, nkv, hd)
+        q = torch.cat([plain.apply_rope(q[..., :rot], cos, sin), q[..., rot:]], -1)
+        k = torch.cat([plain.apply_rope(k[..., :rot], cos, sin), k[..., rot:]], -1)
+        h = h + plain.linear(plain.causal_attention(q, k, v, 0.3).reshape(T, -1), wf["T.self_attn.o_proj.weight"])
+        x = plain.rms_norm(h, wf["T.post_attention_layernorm.weight"], 1e-5)
+        prob = torch.softmax(x @ wf["T.mlp.router.weight"].t(), -1)
+        top = prob.argmax(-1)
+        w1 = wf["T.mlp.w1"].view(3, 24, hidden)
+        w2 = wf["T.mlp.w2"].view(3, hidden, 24)
+        y = torch.stack([prob[t, top[t]] * (torch.relu(x[t] @ w1[top[t]].t()) @ w2[top[t]].t()) for t in range(T)])
+        assert len(set(top.tolist())) >= 2, "the test wants rows on different experts"
+        h = h + y
+        # the usual layer on top
+        p = "L0."
+        m = usual.mixer
+        x = plain.rms_norm(h, wf[p + "input_layernorm.weight"], 1e-5)
+        cos, sin = plain.rope_tables(hd, 777.0, pos)
+        q = plain.apply_rope(plain.rms_norm(plain.linear(x, wf[p + "self_attn.q_proj.weight"]).view(T, nq, hd), wf[p + "self_attn.q_norm.weight"], 1e-5), cos, sin)
+        k = plain.apply_rope(plain.rms_norm(plain.linear(x, wf[p + "self_attn.k_proj.weight"]).view(T, nkv, hd), wf[p + "self_attn.k_norm.weight"], 1e-5), cos, sin)
+        v = plain.linear(x, wf[p + "self_attn.v_proj.weight"]).view(T, nkv, hd)
+        h = h + plain.linear(plain.causal_attention(q, k, v, m.softmax_scale).reshape(T, -1), wf[p + "self_attn.o_proj.weight"])
+        h = h + plain.swiglu(plain.rms_norm(h, wf[p + "post_attention_layernorm.weight"], 1e-5), wf, p + "mlp.")
+        return plain.linear(plain.rms_norm(h, wf["fn.weight"], 1e-5), wf["head"])
+
+    rng = random.Random(4)
+    a = [rng.randrange(vocab) for _ in range(21)]
+    b = [rng.randrange(vocab) for _ in range(9)]
+    got_a = [runner.step([StepEntry("a", a[:7], list(range(7)))])]
+    both = runner.step([StepEntry("b", b, list(range(9))), StepEntry("a", a[7:8], [0])])
+    got_b = both[:9]
+    got_a.append(both[9:])
+    got_a.append(runner.step([StepEntry("a", a[8:], list(range(13)))]))
+    if dtype_name == "float32":
+        assert_close(torch.cat(got_a), plain_forward(a), dtype_name, "toy routed model, request a")
+        assert_close(got_b, plain_forward(b), dtype_name, "toy routed model, request b")
+    else:
+        # bfloat16 rounding may send a row near a tie to another expert: compare where float32 routing is clear
+        ref = plain_forward(a)
+        err = (torch.cat(got_a).float().cpu() - ref).abs().max(dim=1).values / ref.abs().max()
+        assert (err < 0.05).float().mean() >= 0.8, f"rows within 5 %: {(err < 0.05).float().mean():.2f}"
+    runner.end("a"); runner.end("b")
     runner.cache.check()
