@@ -32,9 +32,7 @@
 // Math as the other attention kernels: s = (q . k) / sqrt(hd) for keys j <= pos (and j > pos - window),
 // softmax in float32 with exp2 and the scale folded in, o = sum p v
 // (pegainfer-kernels/csrc/shared/paged_attention.cu:439-567).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -43,7 +41,6 @@ constexpr int kRows = 128;          // query rows per CTA
 constexpr int kKeys = 64;           // keys per tile
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 __device__ int g_attn_error = 0;
 
@@ -62,113 +59,21 @@ struct Params {
   int out_row_stride;
 };
 
-// ---- PTX wrappers (see gemm_tcgen05.cu for the same set) ---------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
+using namespace tc;
+
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
-  unsigned long long t0 = 0;
-  for (unsigned i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if ((i & 255u) == 255u) {
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) break;
-    }
-  }
-  *abort_flag = 1;
-  atomicCAS(&g_attn_error, 0, code);
-  return false;
+  return tc::mbar_wait(bar, parity, abort_flag, &g_attn_error, code);
 }
-__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+__device__ __forceinline__ void tc_fence_before() { tc::fence_before(); }
+__device__ __forceinline__ void tc_fence_after() { tc::fence_after(); }
+__device__ __forceinline__ unsigned long long desc_k_major(unsigned smem_addr) { return tc::desc_k_major_sw128(smem_addr); }
+__device__ __forceinline__ unsigned long long desc_mn_major(unsigned smem_addr, unsigned lbo_bytes) {
+  return tc::desc_mn_major_sw128(smem_addr, lbo_bytes);
 }
-__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long desc_a, unsigned long long desc_b,
-                                          unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
-}
-
-// K-major operand, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart (Q, K, P tiles).
-__device__ __forceinline__ unsigned long long desc_k_major(unsigned smem_addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
-  d |= (unsigned long long)1 << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= (unsigned long long)1 << 46;
-  d |= (unsigned long long)2 << 61;
-  return d;
-}
-// MN-major operand (V as it lies in its page: a row = one key, 64 head dims = 128 bytes): 8 keys form a
-// 1024-byte group (stride byte offset), the second 64 head dims start `lbo_bytes` further on
-// (leading byte offset).
-__device__ __forceinline__ unsigned long long desc_mn_major(unsigned smem_addr, unsigned lbo_bytes) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
-  d |= (unsigned long long)(lbo_bytes >> 4) << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= (unsigned long long)1 << 46;
-  d |= (unsigned long long)2 << 61;
-  return d;
 }
 
 // shared memory map (bytes from a 1024-aligned base)
@@ -487,21 +392,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
 }  // namespace
 
 // Prompt tiles of 128 query rows; items as for oi_attention_mma with rows_per_cta 128 and no key
@@ -521,7 +411,7 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
                  (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0 && (uintptr_t)out % 16 == 0,
              "attention_tcgen05: misaligned operands");
   if (num_items == 0 || tokens == 0) return OI_OK;
-  EncodeTiledFn enc = encode_fn();
+  tc::EncodeTiledFn enc = tc::encode_fn();
   OI_REQUIRE(enc != nullptr, "attention_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
   const int group = nq / nkv;
   const int box_keys = page_size < kKeys ? page_size : kKeys;

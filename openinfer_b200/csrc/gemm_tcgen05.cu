@@ -19,110 +19,24 @@
 //
 // This is the hand-written counterpart of the library call the reference makes for every projection
 // (pegainfer-kernels/csrc/shared/linear.cu:312-362: bf16 in, float32 accumulate, row-major weight).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a wait gives up after two seconds
 
 __device__ int g_gemm_error = 0;       // set to a non-zero code when a bounded wait ran out
 
-// ------------------------------------------------------------------------------------------------
-// PTX wrappers
-// ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+using namespace tc;
 
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false (and raises the abort flag) when it ran out or another role aborted.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
-  unsigned long long t0 = 0;
-  for (unsigned i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if ((i & 255u) == 255u) {          // look at the clock now and then
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) break;
-    }
-  }
-  *abort_flag = 1;
-  atomicCAS(&g_gemm_error, 0, code);
-  return false;
+  return tc::mbar_wait(bar, parity, abort_flag, &g_gemm_error, code);
 }
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_c, unsigned long long desc_a, unsigned long long desc_b,
-                                          unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The barrier gets one arrival when every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
-// swizzle (what TMA writes): start address, stride between 8-row groups = 1024 bytes, version 1,
-// layout type 2 (128-byte swizzle). The leading-dimension offset is not used by this layout.
-__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);        // bits [0, 14)
-  d |= (unsigned long long)1 << 16;                              // leading byte offset (ignored), bits [16, 30)
-  d |= (unsigned long long)(1024 >> 4) << 32;                    // stride byte offset, bits [32, 46)
-  d |= (unsigned long long)1 << 46;                              // descriptor version, bits [46, 48)
-  d |= (unsigned long long)2 << 61;                              // layout type: SWIZZLE_128B
-  return d;
-}
+__device__ __forceinline__ void tc_fence_before() { tc::fence_before(); }
+__device__ __forceinline__ void tc_fence_after() { tc::fence_after(); }
+__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr) { return tc::desc_k_major_sw128(smem_addr); }
 
 template <int BN, int kStages>
 struct Smem {
@@ -332,46 +246,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// rows x K bfloat16 matrix with row stride ld (elements); tiles of box_rows x 64, 128-byte swizzle,
-// zeros outside the matrix
-int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  OI_REQUIRE(fn != nullptr, "gemm_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  OI_REQUIRE(r == CUDA_SUCCESS, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return OI_OK;
-}
-
 template <int BN, int kStages, typename TOut, bool kSiluMul = false>
 int launch(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
            cudaStream_t s) {
   CUtensorMap ma, mb;
-  int rc = make_map(&ma, A, M, K, lda, BM);
-  if (rc) return rc;
-  rc = make_map(&mb, W, N, K, ldw, BN);
-  if (rc) return rc;
+  int rc = tc::make_map_2d_bf16(&ma, A, M, K, lda, BM);
+  OI_REQUIRE(rc == 0, "gemm_tcgen05: tensor map for A failed (%d; -1: cuTensorMapEncodeTiled is not available)", rc);
+  rc = tc::make_map_2d_bf16(&mb, W, N, K, ldw, BN);
+  OI_REQUIRE(rc == 0, "gemm_tcgen05: tensor map for W failed (%d)", rc);
   auto kernel = gemm_tcgen05_kernel<BN, kStages, TOut, kSiluMul>;
   constexpr int smem = Smem<BN, kStages>::kTotal;
   static bool configured = false;

@@ -55,6 +55,16 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(unsigned dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
 // The same with an L2 cache policy (from createpolicy) for data that is read once.
 __device__ __forceinline__ void tma_load_2d_hint(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar,
                                                  unsigned long long policy) {
@@ -101,6 +111,18 @@ __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
+// 32 consecutive float32 columns of this thread's lane of tensor memory
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
@@ -113,6 +135,19 @@ __device__ __forceinline__ unsigned long long desc_k_major_sw128(unsigned smem_a
   d |= (unsigned long long)(1024 >> 4) << 32;                    // stride byte offset, bits [32, 46)
   d |= (unsigned long long)1 << 46;                              // descriptor version, bits [46, 48)
   d |= (unsigned long long)2 << 61;                              // layout type: SWIZZLE_128B
+  return d;
+}
+// MN-major operand of 128-byte rows with the 128-byte swizzle (a tile as it lies in memory with the
+// non-contracted dimension contiguous, e.g. V[key][head dim] for P V): 8 rows along K form a 1024-byte
+// group (stride byte offset); the next 64 elements of the MN dimension start `lbo_bytes` further on
+// (leading byte offset).
+__device__ __forceinline__ unsigned long long desc_mn_major_sw128(unsigned smem_addr, unsigned lbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
+  d |= (unsigned long long)(lbo_bytes >> 4) << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
   return d;
 }
 // Instruction descriptor of kind::f16 with bfloat16 A and B (both K-major), float32 D, shape M x N.
