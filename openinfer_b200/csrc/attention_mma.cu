@@ -38,6 +38,12 @@ struct AttnParams {
   int window;              // 0 = none
   float* part_o; float* part_lse; int max_splits;  // scratch for split items
   int merge_in_kernel;     // decode kernel: the CTAs of a row form a cluster and merge their slices themselves
+  // decode kernel, fuse_rope != 0: `q` is the raw fused projection [rows, (nq + 2 nkv) * hd]; the per-head
+  // q/k norm, the rotation and the write of the step's key and value into their page happen in the kernel
+  int fuse_rope, write_kv;
+  const void* q_norm_w; const void* k_norm_w; int norm_dtype; float eps, w_offset;
+  const float* cos_tab; const float* sin_tab; int rot_half, max_pos;
+  const int* positions; const int* slots;
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
@@ -449,6 +455,50 @@ __device__ __forceinline__ void load_kv_tile16(bf16* k_smem, bf16* v_smem, const
   }
 }
 
+// One head of the fused projection, by one warp: per-head RMSNorm (weights optional), rotate-half of the
+// pairs (d, d + rot_half) with the position's cos/sin row, dims beyond 2 * rot_half only normalised;
+// float32 arithmetic, one rounding at the store. The formulas of qk_norm_rope_kv_bf16x2_kernel (rope_kv.cu).
+// A lane owns the element pair (2 lane, 2 lane + 1) of the first rotary half and its partner pair in the
+// second (head_dim <= 128: at most 32 such pairs); its cos/sin values and norm weights (wa, wb, with the
+// offset added) are fetched by the caller ahead of time.
+__device__ __forceinline__ void warp_norm_rope_head(const bf16* __restrict__ src, bf16* __restrict__ dst, int hd,
+                                                    const void* w, int norm_dtype, float eps, float w_offset, float2 wa,
+                                                    float2 wb, float2 c, float2 sn, int rot_half, int lane) {
+  const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
+  __nv_bfloat162* dst2 = reinterpret_cast<__nv_bfloat162*>(dst);
+  const int npairs = hd / 2, rot_pairs = rot_half / 2;
+  const bool mine = lane < rot_pairs;
+  float2 x = make_float2(0.f, 0.f), y = x;
+  if (mine) {
+    x = __bfloat1622float2(src2[lane]);
+    y = __bfloat1622float2(src2[lane + rot_pairs]);
+  }
+  float inv = 1.f;
+  if (w) {
+    float ss = x.x * x.x + x.y * x.y + y.x * y.x + y.y * y.y;
+    for (int pr = 2 * rot_pairs + lane; pr < npairs; pr += 32) {
+      const float2 t = __bfloat1622float2(src2[pr]);
+      ss += t.x * t.x + t.y * t.y;
+    }
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)hd + eps);
+    x.x *= inv * wa.x; x.y *= inv * wa.y;
+    y.x *= inv * wb.x; y.y *= inv * wb.y;
+  }
+  if (mine) {
+    dst2[lane] = __floats2bfloat162_rn(x.x * c.x - y.x * sn.x, x.y * c.y - y.y * sn.y);
+    dst2[lane + rot_pairs] = __floats2bfloat162_rn(x.x * sn.x + y.x * c.x, x.y * sn.y + y.y * c.y);
+  }
+  for (int pr = 2 * rot_pairs + lane; pr < npairs; pr += 32) {
+    float2 t = __bfloat1622float2(src2[pr]);
+    if (w) {
+      t.x *= inv * (w_offset + load_as_f32(w, norm_dtype, 2 * pr));
+      t.y *= inv * (w_offset + load_as_f32(w, norm_dtype, 2 * pr + 1));
+    }
+    dst2[pr] = __floats2bfloat162_rn(t.x, t.y);
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attention_decode_kernel(const AttnParams p) {
@@ -517,7 +567,39 @@ attention_decode_kernel(const AttnParams p) {
   if (split_ok) {
     for (; primed < kDecStages - 1 && ld_t != span_tiles - 1; ++primed) issue_next();
   }
+  // fuse_rope: this lane's cos/sin values and norm weights do not depend on the step's kernels either
+  float2 rc = make_float2(1.f, 1.f), rs = make_float2(0.f, 0.f);
+  float2 wqa = rc, wqb = rc, wka = rc, wkb = rc;
+  const bool owns_last_tile = split_ok && t_begin < t_end && t_end == span_tiles;
+  if (p.fuse_rope && lane < p.rot_half / 2) {
+    int rpos = p.positions[row_q];
+    rpos = rpos < 0 ? 0 : (rpos >= p.max_pos ? p.max_pos - 1 : rpos);
+    rc = reinterpret_cast<const float2*>(p.cos_tab + (size_t)rpos * p.rot_half)[lane];
+    rs = reinterpret_cast<const float2*>(p.sin_tab + (size_t)rpos * p.rot_half)[lane];
+    if (p.q_norm_w) {
+      wqa = make_float2(p.w_offset + load_as_f32(p.q_norm_w, p.norm_dtype, 2 * lane), p.w_offset + load_as_f32(p.q_norm_w, p.norm_dtype, 2 * lane + 1));
+      wqb = make_float2(p.w_offset + load_as_f32(p.q_norm_w, p.norm_dtype, 2 * lane + p.rot_half),
+                        p.w_offset + load_as_f32(p.q_norm_w, p.norm_dtype, 2 * lane + p.rot_half + 1));
+    }
+    if (p.k_norm_w && p.write_kv && owns_last_tile) {
+      wka = make_float2(p.w_offset + load_as_f32(p.k_norm_w, p.norm_dtype, 2 * lane), p.w_offset + load_as_f32(p.k_norm_w, p.norm_dtype, 2 * lane + 1));
+      wkb = make_float2(p.w_offset + load_as_f32(p.k_norm_w, p.norm_dtype, 2 * lane + p.rot_half),
+                        p.w_offset + load_as_f32(p.k_norm_w, p.norm_dtype, 2 * lane + p.rot_half + 1));
+    }
+  }
   pdl_wait();
+  // ---- with fuse_rope: this kv head's query heads are normalised and rotated into shared memory (every CTA of
+  // the row does its own copy), and the warp that owns the row's last tile normalises and rotates the step's
+  // key and stores it, and the value, into their page before it requests that tile
+  const bf16* q_src = p.q + (size_t)row_q * p.q_row_stride + (size_t)(kvh * group) * HD;   // [group][HD]
+  if (p.fuse_rope) {
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw + (size_t)kDecWarps * kDecStages * 2 * kDecKeys * HD * sizeof(bf16));
+    for (int r = warp; r < group; r += kDecWarps)
+      warp_norm_rope_head(q_src + (size_t)r * HD, q_s + r * HD, HD, p.q_norm_w, p.norm_dtype, p.eps, p.w_offset, wqa, wqb,
+                          rc, rs, p.rot_half, lane);
+    __syncthreads();
+    q_src = q_s;
+  }
   // ---- Q fragments: rows are the `group` query heads of this kv head (rows >= group are zero)
   constexpr int kSteps = HD / 16;
   const int r_lo = lane >> 2;                     // rows r_lo and r_lo + 8
@@ -531,7 +613,7 @@ attention_decode_kernel(const AttnParams p) {
         const int r = r_lo + 8 * i;
         unsigned a = 0, b = 0;
         if (r < group && split_ok) {
-          const bf16* qp = p.q + (size_t)row_q * p.q_row_stride + (size_t)(kvh * group + r) * HD + ks * 16 + col;
+          const bf16* qp = q_src + (size_t)r * HD + ks * 16 + col;
           a = *reinterpret_cast<const unsigned*>(qp);
           b = *reinterpret_cast<const unsigned*>(qp + 8);
         }
@@ -539,6 +621,20 @@ attention_decode_kernel(const AttnParams p) {
         qf[ks][i + 2] = b;
       }
     }
+  }
+  if (p.fuse_rope && p.write_kv && owns_last_tile) {
+    const int slot = p.slots[row_q];
+    if (slot >= 0) {    // a padding row stores nothing
+      const size_t off = (size_t)(slot / p.page_size) * p.page_stride + (size_t)(slot % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
+      const bf16* row = p.q + (size_t)row_q * p.q_row_stride;
+      warp_norm_rope_head(row + (size_t)(p.nq + kvh) * HD, const_cast<bf16*>(p.k_cache) + off, HD, p.k_norm_w, p.norm_dtype,
+                          p.eps, p.w_offset, wka, wkb, rc, rs, p.rot_half, lane);
+      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(row + (size_t)(p.nq + p.nkv + kvh) * HD);
+      __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(const_cast<bf16*>(p.v_cache) + off);
+      for (int pr = lane; pr < HD / 2; pr += 32) d2[pr] = v2[pr];
+      __threadfence();   // the tile copy below reads these rows back from global memory
+    }
+    __syncwarp();
   }
   if (split_ok) {
     for (; primed < kDecStages - 1; ++primed) issue_next();
@@ -775,7 +871,8 @@ int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens
 
 template <int HD>
 int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
-  constexpr int smem = kDecWarps * kDecStages * 2 * kDecKeys * HD * (int)sizeof(bf16);
+  // the warps' rings, and room for the rotated query heads of one kv head (fuse_rope)
+  constexpr int smem = (kDecWarps * kDecStages * 2 * kDecKeys + 16) * HD * (int)sizeof(bf16);
   static bool configured = false;
   if (!configured) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -798,19 +895,19 @@ int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int
 
 }  // namespace
 
-// Decode rows only (requests that bring one token): items are (request, 0, first slice, nsplits),
-// one CTA per four consecutive slices, every item with nsplits == max_splits. With
-// merge_in_kernel != 0 (max_splits a multiple of 4, at most 32; the items of a request adjacent
-// and in slice order) the max_splits / 4 CTAs of a row run as a thread-block cluster and merge their
-// slices through distributed shared memory; part_o, part_lse and row_splits are not used. Otherwise
-// every listed request's row is merged by a second kernel from scratch in global memory, so
-// row_splits[row] must be nsplits (>= 2) for those rows and <= 1 for all others.
-OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
-                               const void* v_cache, long long page_stride, int page_size, const int* block_table,
-                               int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
-                               int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
-                               float scale, int window, float* part_o, float* part_lse, int max_splits,
-                               int merge_in_kernel, void* stream) {
+namespace {
+struct RopeArgs {
+  const void* q_norm_w; const void* k_norm_w; int norm_dtype; float eps, w_offset;
+  const float* cos_tab; const float* sin_tab; int rot_half, max_pos;
+  const int* positions; const int* slots; int write_kv;
+};
+
+int decode_entry(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                 const void* v_cache, long long page_stride, int page_size, const int* block_table,
+                 int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                 int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
+                 float scale, int window, float* part_o, float* part_lse, int max_splits,
+                 int merge_in_kernel, const RopeArgs* rope, void* stream) {
   OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_decode: head_dim %d not covered (32, 64 or 128)", hd);
   OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16, "attention_decode: group %d/%d not covered (<= 16)", nq, nkv);
   OI_REQUIRE(q_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_decode: misaligned strides");
@@ -837,10 +934,61 @@ OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int o
   p.window = window;
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
   p.merge_in_kernel = merge_in_kernel ? 1 : 0;
+  p.fuse_rope = 0;
+  if (rope) {
+    OI_REQUIRE(rope->rot_half > 0 && rope->rot_half % 2 == 0 && 2 * rope->rot_half <= hd && rope->cos_tab && rope->sin_tab &&
+                   rope->max_pos > 0 && rope->positions,
+               "attention_decode: rotation tables, positions and an even rotary half <= head_dim / 2 are needed (half %d)", rope->rot_half);
+    OI_REQUIRE(!rope->write_kv || rope->slots, "attention_decode: cache write without slots");
+    OI_REQUIRE((rope->q_norm_w == nullptr) == (rope->k_norm_w == nullptr) || !rope->write_kv,
+               "attention_decode: q and k norm weights come together");
+    p.fuse_rope = 1; p.write_kv = rope->write_kv ? 1 : 0;
+    p.q_norm_w = rope->q_norm_w; p.k_norm_w = rope->k_norm_w; p.norm_dtype = rope->norm_dtype;
+    p.eps = rope->eps; p.w_offset = rope->w_offset;
+    p.cos_tab = rope->cos_tab; p.sin_tab = rope->sin_tab; p.rot_half = rope->rot_half; p.max_pos = rope->max_pos;
+    p.positions = rope->positions; p.slots = rope->slots;
+  }
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 32) return launch_decode<32>(p, num_items, row_splits, tokens, s);
   if (hd == 64) return launch_decode<64>(p, num_items, row_splits, tokens, s);
   return launch_decode<128>(p, num_items, row_splits, tokens, s);
+}
+}  // namespace
+
+// Decode rows only (requests that bring one token): items are (request, 0, first slice, nsplits),
+// one CTA per four consecutive slices, every item with nsplits == max_splits. With
+// merge_in_kernel != 0 (max_splits a multiple of 4, at most 32; the items of a request adjacent
+// and in slice order) the max_splits / 4 CTAs of a row run as a thread-block cluster and merge their
+// slices through distributed shared memory; part_o, part_lse and row_splits are not used. Otherwise
+// every listed request's row is merged by a second kernel from scratch in global memory, so
+// row_splits[row] must be nsplits (>= 2) for those rows and <= 1 for all others.
+OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                               const void* v_cache, long long page_stride, int page_size, const int* block_table,
+                               int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                               int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
+                               float scale, int window, float* part_o, float* part_lse, int max_splits,
+                               int merge_in_kernel, void* stream) {
+  return decode_entry(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, block_table, bt_stride,
+                      cu_seqlens, kv_lens, items, num_items, row_splits, tokens, nq, nkv, hd, scale, window, part_o, part_lse,
+                      max_splits, merge_in_kernel, nullptr, stream);
+}
+
+// The same with the per-head q/k norm, the rotation and the write of the step's key and value fused in:
+// `qkv` is the raw fused projection [rows, >= (nq + 2 nkv) * hd] (only the nq query heads when write_kv
+// is 0: a call that reads another call's cache), norm weights [hd] of norm_dtype or null, cos/sin float32
+// [max_pos, rot_half], positions and slots int32 [rows] (a slot < 0 stores nothing). q is not written back.
+OI_API int oi_attention_decode_rope(const void* qkv, int q_row_stride, void* out, int out_row_stride, void* k_cache,
+                                    void* v_cache, long long page_stride, int page_size, const int* block_table,
+                                    int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                                    int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
+                                    float scale, int window, float* part_o, float* part_lse, int max_splits,
+                                    int merge_in_kernel, const void* q_norm_w, const void* k_norm_w, int norm_dtype,
+                                    float eps, float w_offset, const float* cos_tab, const float* sin_tab, int rot_half,
+                                    int max_pos, const int* positions, const int* slots, int write_kv, void* stream) {
+  RopeArgs r{q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab, sin_tab, rot_half, max_pos, positions, slots, write_kv};
+  return decode_entry(qkv, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, block_table, bt_stride,
+                      cu_seqlens, kv_lens, items, num_items, row_splits, tokens, nq, nkv, hd, scale, window, part_o, part_lse,
+                      max_splits, merge_in_kernel, &r, stream);
 }
 
 // items: int32 [num_items, 4] = (request, first token of the tile, split, nsplits), planned by the
@@ -874,6 +1022,7 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
   p.window = window;
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
   p.merge_in_kernel = 0;
+  p.fuse_rope = 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
   if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);

@@ -668,3 +668,59 @@ def test_qk_norm_rope_kv_write_many_tokens(nq, nkv, hd, rot):
     untouched = torch.ones(pages * P, dtype=torch.bool)
     untouched[slots[ok].long()] = False
     assert flat[:, untouched].abs().sum() == 0
+
+
+@pytest.mark.parametrize("nq,nkv,hd,rot,P,norm", [(32, 8, 128, 128, 16, True), (6, 2, 64, 32, 8, True), (4, 1, 32, 32, 16, False),
+                                                  (16, 1, 128, 64, 32, True)])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_attention_decode_with_norm_rotation_and_cache_write_fused(nq, nkv, hd, rot, P, norm, write_kv):
+    """A step of single tokens: the decode kernel takes the raw projection, normalises and rotates q and k
+    and stores k and v itself. Same outputs and same cache as the rotation kernel followed by attention."""
+    from openinfer_b200.kernels import attention as A
+    from openinfer_b200.kernels import ops
+    from openinfer_b200.parts.position import RotaryEncoding
+    from openinfer_b200.parts.spec import PositionSpec
+    torch.manual_seed(nq * 7 + hd)
+    kv_lens = [1, 16, 17, 33, 100, 257, 640]
+    B = len(kv_lens)
+    pages = [-(-kv // P) for kv in kv_lens]
+    total = sum(pages) + 3
+    perm = torch.randperm(total).tolist()
+    bt = torch.zeros(B, max(pages), dtype=torch.int32)
+    at = 0
+    for b in range(B):
+        bt[b, : pages[b]] = torch.tensor(perm[at: at + pages[b]])
+        at += pages[b]
+    cache0 = (torch.randn(total, 2, P, nkv, hd, device=DEV) * 0.7).to(torch.bfloat16)
+    qkv0 = torch.randn(B, (nq + 2 * nkv) * hd, device=DEV).to(torch.bfloat16)
+    cos, sin = RotaryEncoding(PositionSpec("rope", rot, 5000.0, 1024)).rotation_tables(torch.device(DEV))
+    qw = (1 + 0.1 * torch.randn(hd, device=DEV)).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, device=DEV)).to(torch.bfloat16) if norm else None
+    positions = torch.tensor([kv - 1 for kv in kv_lens], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(bt[b, (kv - 1) // P]) * P + (kv - 1) % P for b, kv in enumerate(kv_lens)], dtype=torch.int32, device=DEV)
+    slots[2] = -1 if not write_kv else slots[2]      # (only meaningful without the write: stays unused)
+    scale = 1.0 / math.sqrt(hd)
+    results = []
+    for fused in (False, True):
+        cache, qkv = cache0.clone(), qkv0.clone()
+        out = torch.full((B, nq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ctx = _FakeCtx([1] * B, kv_lens, P)
+        grp = _FakeGroup(bt.to(DEV), kv_lens)
+        k_c, v_c = cache[:, 0], cache[:, 1]
+        if fused:
+            assert A.decode_takes_rope(qkv, ctx, grp, nq, nkv, hd, None, cos, qw, cache.stride(0))   # a grid of one wave
+            rope = A.RopeFusion(qw, kw, 1e-6, 0.0, cos, sin, positions, slots, write_kv)
+            A.paged_attention(qkv, out, k_c, v_c, cache.stride(0), ctx, grp, nq, nkv, hd, scale, None, rope=rope)
+            assert torch.equal(qkv, qkv0), "the fused kernel leaves the projection as it is"
+        else:
+            ops.qk_norm_rope_kv(qkv, nq, nkv, hd, q_norm_w=qw, k_norm_w=kw, eps=1e-6, weight_offset=0.0, cos=cos, sin=sin,
+                                positions=positions, slots=slots, k_cache=k_c, v_cache=v_c, page_stride=cache.stride(0),
+                                page_size=P, write_kv=write_kv)
+            assert A.attention_mma(qkv[:, : nq * hd], out, k_c, v_c, cache.stride(0), ctx, grp, nq, nkv, hd, scale, None)
+        results.append((out.float(), cache.float()))
+    (o0, c0), (o1, c1) = results
+    assert torch.isfinite(o1).all()
+    assert (c0 - c1).abs().max().item() <= 1e-2 * c0.abs().max().item(), "the cache after the step"
+    if not write_kv:
+        assert torch.equal(c1, cache0.float()), "nothing is stored when the call reads another call's cache"
+    assert (o0 - o1).abs().max().item() <= 2e-2, f"outputs differ by {(o0 - o1).abs().max().item()}"
