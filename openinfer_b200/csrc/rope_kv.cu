@@ -179,6 +179,106 @@ __global__ void qk_norm_rope_kv_bf16x2_kernel(
   }
 }
 
+// bfloat16, full rotation (rotary_dim == head_dim), head_dim 32 / 64 / 128, everything 16-byte aligned:
+// a lane moves EIGHT neighbouring elements of the first half of a head and their partners in the second
+// half with 16-byte accesses, so HD / 16 lanes cover a head and a warp handles 512 / HD heads of one token
+// at once; a block of four warps takes 2048 / HD consecutive heads. Many independent 16-byte loads per
+// lane (row, cos, sin, weights) are in flight before anything is used: prompt-sized launches run at the
+// speed of memory instead of the latency of 4-byte accesses.
+template <int HD, typename TW>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_vec_kernel(bf16* __restrict__ qkv, int row_stride, int nq, int nkv, const TW* __restrict__ q_norm_w,
+                           const TW* __restrict__ k_norm_w, float eps, float w_offset, const float* __restrict__ cos_tab,
+                           const float* __restrict__ sin_tab, int max_pos, const int* __restrict__ positions,
+                           const int* __restrict__ slots, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                           long long page_stride, int page_size, int heads_total) {
+  pdl_start();
+  constexpr int kHalf = HD / 2;
+  constexpr int kLanes = HD / 16;            // lanes per head
+  constexpr int kHeadsPerWarp = 32 / kLanes;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int token = blockIdx.x;
+  const int head = (blockIdx.y * 4 + warp) * kHeadsPerWarp + lane / kLanes;
+  const int sub = lane % kLanes;             // elements [8 sub, 8 sub + 8) of each half
+  const bool live = head < heads_total;
+  const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
+  int pos = positions[token];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+  const int slot = slots ? slots[token] : -1;
+  bf16* src = qkv + (size_t)token * row_stride + (size_t)head * HD;
+  bf16* dst = src;   // q: in place
+  bool store = live;
+  if (live && kind != 0) {
+    store = slot >= 0;   // a padding row stores nothing
+    const int kvh = kind == 1 ? head - nq : head - nq - nkv;
+    if (store)
+      dst = (kind == 1 ? k_cache : v_cache) + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * nkv * HD +
+            (size_t)kvh * HD;
+  }
+  uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
+  if (live) {
+    ra = *reinterpret_cast<const uint4*>(src + sub * 8);
+    rb = *reinterpret_cast<const uint4*>(src + kHalf + sub * 8);
+  }
+  if (live && kind == 2) {
+    if (store) {
+      *reinterpret_cast<uint4*>(dst + sub * 8) = ra;
+      *reinterpret_cast<uint4*>(dst + kHalf + sub * 8) = rb;
+    }
+  }
+  // all lanes stay for the shuffles below
+  const TW* w = kind == 0 ? q_norm_w : k_norm_w;
+  const bool rotate = live && kind != 2;
+  float c[8], sn[8], wa[8], wb[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { c[e] = 1.f; sn[e] = 0.f; wa[e] = 1.f; wb[e] = 1.f; }
+  if (rotate) {
+    const float4* c4 = reinterpret_cast<const float4*>(cos_tab + (size_t)pos * kHalf + sub * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_tab + (size_t)pos * kHalf + sub * 8);
+    const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    if (w) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        wa[e] = w_offset + to_f32(w[sub * 8 + e]);
+        wb[e] = w_offset + to_f32(w[kHalf + sub * 8 + e]);
+      }
+    }
+  }
+  float a[8], b[8];
+  {
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&ra);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&rb);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(a2[e]), y = __bfloat1622float2(b2[e]);
+      a[2 * e] = x.x; a[2 * e + 1] = x.y; b[2 * e] = y.x; b[2 * e + 1] = y.y;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
+#pragma unroll
+  for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!rotate || !store) return;
+  if (w) {
+    const float inv = rsqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { a[e] *= inv * wa[e]; b[e] *= inv * wb[e]; }
+  }
+  uint4 oa, ob;
+  __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+  __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    oa2[e] = __floats2bfloat162_rn(a[2 * e] * c[2 * e] - b[2 * e] * sn[2 * e], a[2 * e + 1] * c[2 * e + 1] - b[2 * e + 1] * sn[2 * e + 1]);
+    ob2[e] = __floats2bfloat162_rn(a[2 * e] * sn[2 * e] + b[2 * e] * c[2 * e], a[2 * e + 1] * sn[2 * e + 1] + b[2 * e + 1] * c[2 * e + 1]);
+  }
+  *reinterpret_cast<uint4*>(dst + sub * 8) = oa;
+  *reinterpret_cast<uint4*>(dst + kHalf + sub * 8) = ob;
+}
+
 // write_kv = 0: only the nq query heads are processed (a mixer that reads another layer's cache).
 OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, int nq, int nkv, int hd,
                               const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
@@ -201,6 +301,23 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
         (float*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
         sin_tab, rot_half, max_pos, positions, slots, (float*)k_cache, (float*)v_cache, page_stride,
         page_size, heads_total, tokens);
+  } else if (dtype == OI_BF16 && 2 * rot_half == hd && (hd == 32 || hd == 64 || hd == 128) && row_stride % 8 == 0 &&
+             (uintptr_t)qkv % 16 == 0 && page_stride % 8 == 0 && (uintptr_t)cos_tab % 16 == 0 && (uintptr_t)sin_tab % 16 == 0 &&
+             (!write_kv || ((uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0)) &&
+             ((!q_norm_w && !k_norm_w) || norm_dtype == OI_BF16 || norm_dtype == OI_F32)) {
+    // the 16-byte path: full rotation, aligned operands
+    const int heads_per_block = 4 * (512 / hd);
+    const dim3 grid(tokens, (heads_total + heads_per_block - 1) / heads_per_block);
+#define OI_ROPE_VEC(HD_, TW_)                                                                                        \
+  oi_launch(qk_norm_rope_kv_vec_kernel<HD_, TW_>, grid, 128, 0, s, (bf16*)qkv, row_stride, nq, nkv, (const TW_*)q_norm_w, \
+            (const TW_*)k_norm_w, eps, w_offset, cos_tab, sin_tab, max_pos, positions, slots, (bf16*)k_cache,         \
+            (bf16*)v_cache, page_stride, page_size, heads_total)
+    if (norm_dtype == OI_BF16) {
+      if (hd == 128) OI_ROPE_VEC(128, bf16); else if (hd == 64) OI_ROPE_VEC(64, bf16); else OI_ROPE_VEC(32, bf16);
+    } else {
+      if (hd == 128) OI_ROPE_VEC(128, float); else if (hd == 64) OI_ROPE_VEC(64, float); else OI_ROPE_VEC(32, float);
+    }
+#undef OI_ROPE_VEC
   } else if (dtype == OI_BF16 && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 && tokens <= 2147483647 &&
              (uintptr_t)qkv % 4 == 0 && page_stride % 2 == 0 && (!write_kv || ((uintptr_t)k_cache % 4 == 0 && (uintptr_t)v_cache % 4 == 0)) &&
              (uintptr_t)cos_tab % 8 == 0 && (uintptr_t)sin_tab % 8 == 0) {
