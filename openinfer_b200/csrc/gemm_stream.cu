@@ -14,8 +14,10 @@
 //              the producer, and commits the accumulator once at the end;
 //   warps 2-5  read the accumulator (tcgen05.ld, one weight row per thread) and either store it
 //              (c = 1) or leave it as a float32 partial in shared memory.
-// With c > 1 the partials are added up through distributed shared memory in rank order (CTA r adds
-// rows [r * 128 / c, ...) of the tile over all ranks), so the result does not depend on timing.
+// With c > 1 every CTA deposits its partial sums of a row in the shared memory of the CTA that owns the
+// row (CTA r owns rows [r * 128 / c, ...) of the tile), through distributed shared memory; after ONE
+// cluster barrier each CTA adds up what it was given, in rank order, so the result does not depend on
+// timing, and nobody reads remote memory after the barrier (no second barrier before leaving).
 // Two CTAs fit on an SM (<= 112 KB of stages each). Every mbarrier wait is bounded (two seconds): a
 // wait that runs out sets an error word and a flag that ends all roles of the CTA, which still
 // joins its cluster's barriers, frees its tensor memory and returns. No load uses cluster multicast.
@@ -41,12 +43,16 @@ struct Layout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (112 * 1024) / kStageBytes;            // 6, 5, 4, 3 for BN 16, 32, 64, 128
-  static constexpr int kBarOffset = kStages * kStageBytes;              // full[kStages], empty[kStages], acc_full
+  // where the other CTAs of a cluster deposit their partial sums: a region of its own, because they may
+  // do so while this CTA still streams (up to 32 tokens; more tokens run without clusters)
+  static constexpr int kRecvBytes = BN <= 32 ? BN * BM * 4 : 0;
+  static constexpr int kStages = (112 * 1024 - kRecvBytes) / kStageBytes;   // 5, 4, 4, 3 for BN 16, 32, 64, 128
+  static constexpr int kRecvOffset = kStages * kStageBytes;
+  static constexpr int kBarOffset = kRecvOffset + kRecvBytes;           // full[kStages], empty[kStages], acc_full
   static constexpr int kNumBars = 2 * kStages + 1;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
-  static_assert(BN * BM * 4 <= kBarOffset, "the partial sums reuse the stages");
+  static_assert(BN * BM * 4 <= kStages * kStageBytes, "without a cluster the partial sums reuse the stages");
 };
 
 // kSiluMul: W's rows come in blocks of 64 gate rows followed by the 64 up rows of the same indices, so a
@@ -69,7 +75,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const unsigned acc_full = bar_base + 8u * (2 * kStages);
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* part = reinterpret_cast<float*>(smem);        // [token][128 rows], written when the stages are drained
+  // partial sums [K slice][token][rows of this CTA's share]: in the region of its own when a cluster adds
+  // up, else over the drained stages
+  float* recv = reinterpret_cast<float*>(gridDim.x > 1 ? smem + L::kRecvOffset : smem);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = blockIdx.x, csize = gridDim.x;
@@ -100,6 +108,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   tc::fence_after();
   const unsigned tmem_base = *tmem_slot;
+  if (csize > 1) tc::cluster_arrive();   // phase 0: "this CTA runs"; waited for before anyone writes into it
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -172,8 +181,23 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (c0 + e < M) out[(size_t)(c0 + e) * ldc + n] = from_f32<TOut>(__uint_as_float(v[e]));
         }
       } else {
+        // Deposit this row's partial sums with the CTA that adds the row up. Rows are shared out evenly:
+        // CTA j takes rows [j * 128 / c, ...) (with the activation: gate rows [j * 64 / c, ...) and, behind
+        // them in its buffer, the up rows of the same indices).
+        const int share = BM / csize;                       // values per (slice, token) in a CTA's buffer
+        int owner, local;
+        if (kSiluMul) {
+          const int idx = row & (BM / 2 - 1), per = BM / 2 / csize;
+          owner = idx / per;
+          local = (row >= BM / 2 ? per : 0) + idx % per;
+        } else {
+          owner = row / share;
+          local = row % share;
+        }
+        if (c0 == 0 && csize > 1) tc::cluster_wait();       // phase 0: every CTA of the cluster runs
+        float* dst = (csize > 1 ? cg::this_cluster().map_shared_rank(recv, owner) : recv) + (size_t)(rank * BN + c0) * share + local;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) part[(c0 + e) * BM + row] = __uint_as_float(v[e]);
+        for (int e = 0; e < 16; ++e) dst[e * share] = __uint_as_float(v[e]);
       }
     }
   }
@@ -181,24 +205,27 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   // ------------------------------------------------------------------ sum over the K slices, teardown
   tc::fence_before();
   if (csize > 1 || kSiluMul) {
-    cg::cluster_group cluster = cg::this_cluster();
-    if (csize > 1) cluster.sync(); else __syncthreads();
+    if (csize > 1) {
+      if (warp < 2) tc::cluster_wait();   // the read-out warps waited before their first deposit
+      tc::cluster_arrive();               // phase 1: this CTA's deposits are made ...
+      tc::cluster_wait();                 // ... and so are everybody's; nothing remote is touched after this
+    } else {
+      __syncthreads();
+    }
     constexpr int kOutRows = kSiluMul ? BM / 2 : BM;   // output columns per tile
+    const int share = BM / csize;
     const int rows_mine = kOutRows / csize;
-    const int row_lo = rank * rows_mine;
-    const int n_out = kSiluMul ? N / 2 : N, o0 = kSiluMul ? n0 / 2 : n0;
+    const int n_out = kSiluMul ? N / 2 : N, o0 = (kSiluMul ? n0 / 2 : n0) + rank * rows_mine;
     for (int i = threadIdx.x; i < M * rows_mine; i += kThreads) {
-      const int m = i / rows_mine, row = row_lo + (i - m * rows_mine);
+      const int m = i / rows_mine, l = i - m * rows_mine;
       float sum = 0.f, up = 0.f;
-      for (int q = 0; q < csize; ++q) {
-        const float* remote = csize > 1 ? cluster.map_shared_rank(part, q) : part;
-        sum += remote[m * BM + row];
-        if (kSiluMul) up += remote[m * BM + BM / 2 + row];
+      for (int q = 0; q < csize; ++q) {                // slice order: the result does not depend on timing
+        sum += recv[(size_t)(q * BN + m) * share + l];
+        if (kSiluMul) up += recv[(size_t)(q * BN + m) * share + rows_mine + l];
       }
       if (kSiluMul) sum = sum / (1.f + __expf(-sum)) * up;
-      if (o0 + row < n_out) out[(size_t)m * ldc + o0 + row] = from_f32<TOut>(sum);
+      if (o0 + l < n_out) out[(size_t)m * ldc + o0 + l] = from_f32<TOut>(sum);
     }
-    if (csize > 1) cluster.sync();   // nobody leaves while its shared memory may still be read
   } else {
     __syncthreads();
   }
@@ -251,6 +278,7 @@ OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x
   OI_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_stream: operands must be 16-byte aligned");
   OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
              "gemm_stream: cluster size %d", cluster_size);
+  OI_REQUIRE(cluster_size == 1 || M <= 32, "gemm_stream: clusters take up to 32 rows of x (M=%d)", M);
   OI_REQUIRE(!silu_mul || N % BM == 0, "gemm_stream: the fused activation needs N %% 128 == 0 (N=%d)", N);
   const int num_kb = (K + BK - 1) / BK;
   OI_REQUIRE((cluster_size - 1) * ((num_kb + cluster_size - 1) / cluster_size) < num_kb,

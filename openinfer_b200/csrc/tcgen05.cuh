@@ -102,6 +102,11 @@ __device__ __forceinline__ void umma_commit(unsigned bar) {
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
+// The cluster's hardware barrier in two halves (every thread of every CTA arrives once per phase and
+// waits before it arrives again): work between the halves hides the barrier's latency.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+
 // 16 consecutive float32 columns of this thread's lane of tensor memory
 __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
   asm volatile(

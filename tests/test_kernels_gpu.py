@@ -503,7 +503,7 @@ def test_gemm_stream(M, N, K):
     L = klib.load()
     num_kb = -(-K // 64)
     for c in (1, 2, 4, 8):
-        if (c - 1) * (-(-num_kb // c)) >= num_kb:     # a slice without a k block: refused by the entry point
+        if (c - 1) * (-(-num_kb // c)) >= num_kb or (c > 1 and M > 32):   # refused by the entry point
             continue
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
@@ -529,8 +529,8 @@ def test_gemm_stream_refuses_bad_operands():
     w = torch.zeros(128, 64, device=DEV, dtype=torch.bfloat16)
     out = torch.zeros(4, 128, device=DEV, dtype=torch.bfloat16)
     stream = torch.cuda.current_stream().cuda_stream
-    # two slices of a single k block, 129 rows of x, a misaligned weight
-    for args in [(4, 128, 64, 2), (129, 128, 64, 1)]:
+    # two slices of a single k block, 129 rows of x, a cluster for more than 32 rows, a misaligned weight
+    for args in [(4, 128, 64, 2), (129, 128, 64, 1), (40, 128, 256, 2)]:
         rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), *args, 0, stream)
         assert rc != 0 and b"gemm_stream" in L.oi_last_error()
     rc = L.oi_gemm_stream(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr() + 2, w.stride(0), 4, 127, 64, 1, 0, stream)
