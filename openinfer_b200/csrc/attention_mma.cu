@@ -37,7 +37,8 @@ struct AttnParams {
   float scale_log2;        // softmax scale * log2(e)
   int window;              // 0 = none
   float* part_o; float* part_lse; int max_splits;  // scratch for split items
-  int merge_in_kernel;     // decode kernel: the CTAs of a row form a cluster and merge their slices themselves
+  int merge_in_kernel;     // decode kernel: the CTAs of a row form a cluster and merge their slices themselves:
+                           // 1 by reading each other's shared memory, 2 by depositing partials with the merging CTA
   // decode kernel, fuse_rope != 0: `q` is the raw fused projection [rows, (nq + 2 nkv) * hd]; the per-head
   // q/k norm, the rotation and the write of the step's key and value into their page happen in the kernel
   int fuse_rope, write_kv;
@@ -503,6 +504,8 @@ template <int HD>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attention_decode_kernel(const AttnParams p) {
   pdl_trigger();
+  const bool deposit = p.merge_in_kernel == 2 && gridDim.x > 0 && p.max_splits > kDecWarps;   // a cluster that pushes
+  if (deposit) asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");   // phase 0: "this CTA runs"
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // [warp][stage][K | V][16][HD]
@@ -733,6 +736,57 @@ attention_decode_kernel(const AttnParams p) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
   }
   const int col = (lane & 3) * 2;
+  if (deposit) {
+    // The CTAs of this (request, kv head) are one cluster. Output idx = head * HD + dim of the row belongs to
+    // CTA (idx / 128) % csize. Every warp deposits its normalised partial with the owners of its outputs
+    // (their receive buffer [pass][slice][128], behind the rings: a CTA may still be streaming when others
+    // deposit) and its log-sum-exps with everyone; after ONE cluster barrier each CTA merges what it was
+    // given, in slice order (the formula of attention_merge_kernel), and nobody touches remote memory again.
+    cg::cluster_group cluster = cg::this_cluster();
+    const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    float* const recv_o = reinterpret_cast<float*>(smem_raw + (size_t)(kDecWarps * kDecStages * 2 * kDecKeys + 16) * HD * sizeof(bf16));
+    const int passes = (group * HD + 128 * csize - 1) / (128 * csize);
+    float* const recv_lse = recv_o + (size_t)passes * nsplits * 128;    // [slice][16]
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // phase 0: every CTA of the cluster runs
+    if (split < nsplits) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = r_lo + 8 * i;
+        if (r >= group) continue;
+        const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+#pragma unroll
+        for (int j = 0; j < kOTiles; ++j) {
+          const int idx = r * HD + j * 8 + col;
+          const int blk = idx >> 7;                      // which block of 128 outputs
+          float* dst = cluster.map_shared_rank(recv_o, blk % csize) + ((size_t)(blk / csize) * nsplits + split) * 128 + (idx & 127);
+          *reinterpret_cast<float2*>(dst) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+        }
+        if ((lane & 3) == 0) {
+          const float lse = l[i] > 0.f ? m[i] + log2f(l[i]) : -INFINITY;
+          for (int q = 0; q < csize; ++q) cluster.map_shared_rank(recv_lse, q)[split * 16 + r] = lse;
+        }
+      }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    for (int pass = 0; pass < passes; ++pass) {
+      const int idx = (pass * csize + rank) * 128 + threadIdx.x;
+      if (idx >= group * HD) break;
+      const int r = idx / HD, d = idx - r * HD;
+      float mx = -INFINITY;
+      for (int sl = 0; sl < nsplits; ++sl) mx = fmaxf(mx, recv_lse[sl * 16 + r]);
+      float acc = 0.f, wsum = 0.f;
+      for (int sl = 0; sl < nsplits; ++sl) {
+        const float lse = recv_lse[sl * 16 + r];
+        const float w = lse == -INFINITY ? 0.f : exp2f(lse - mx);
+        wsum += w;
+        acc += w * recv_o[((size_t)pass * nsplits + sl) * 128 + threadIdx.x];
+      }
+      p.out[(size_t)row_q * p.out_row_stride + (size_t)(kvh * group + r) * HD + d] =
+          __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+    }
+    return;
+  }
   if (p.merge_in_kernel) {
     // The CTAs of this (request, kv head) are one cluster. Every warp leaves its normalised partial
     // [group][HD] and log-sum-exps [group] in its own drained ring; then CTA r of the cluster merges
@@ -871,8 +925,10 @@ int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens
 
 template <int HD>
 int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
-  // the warps' rings, and room for the rotated query heads of one kv head (fuse_rope)
-  constexpr int smem = (kDecWarps * kDecStages * 2 * kDecKeys + 16) * HD * (int)sizeof(bf16);
+  // the warps' rings, room for the rotated query heads of one kv head (fuse_rope), and the receive buffer
+  // of the merge by deposit
+  constexpr int kRecvMax = 12 * 1024;
+  constexpr int smem = (kDecWarps * kDecStages * 2 * kDecKeys + 16) * HD * (int)sizeof(bf16) + kRecvMax;
   static bool configured = false;
   if (!configured) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -880,7 +936,12 @@ int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int
   }
   dim3 grid(num_items, p.nkv);
   if (p.merge_in_kernel) {
-    oi_launch_cluster(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, p.max_splits / kDecWarps, p);
+    // deposit when the receive buffer fits: [passes][slices][128] floats and [slices][16] log-sum-exps
+    const int csize = p.max_splits / kDecWarps;
+    const int passes = (p.group * HD + 128 * csize - 1) / (128 * csize);
+    AttnParams q = p;
+    q.merge_in_kernel = (csize > 1 && (passes * p.max_splits * 128 + p.max_splits * 16) * 4 <= kRecvMax) ? 2 : 1;
+    oi_launch_cluster(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, csize, q);
     OI_CHECK_LAUNCH();
     return OI_OK;
   }
