@@ -126,22 +126,28 @@ template <int VPT>
 __global__ void rmsnorm_bf16_vec_kernel(bf16* __restrict__ out, bf16* __restrict__ x, const bf16* __restrict__ delta,
                                         const bf16* __restrict__ w, const int* __restrict__ row_idx, int hidden,
                                         float eps, float w_offset) {
-  pdl_start();
+  pdl_trigger();
   __shared__ float red[32];
   const int r = blockIdx.x;
-  const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
   const int nvec = hidden / 8;
-  uint4* xr = reinterpret_cast<uint4*>(x + src * hidden);
-  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + src * hidden) : nullptr;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
   uint4 xv[VPT], dv[VPT], wv[VPT];
+  // the norm weight does not depend on the kernels ahead on the stream: fetched before waiting for them
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int v = threadIdx.x + k * blockDim.x;
+    if (v < nvec) wv[k] = wr[v];
+  }
+  pdl_wait();
+  const size_t src = row_idx ? (size_t)row_idx[r] : (size_t)r;
+  uint4* xr = reinterpret_cast<uint4*>(x + src * hidden);
+  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + src * hidden) : nullptr;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
     const int v = threadIdx.x + k * blockDim.x;
     if (v < nvec) {
       xv[k] = xr[v];
       if (dr) dv[k] = dr[v];
-      wv[k] = wr[v];
     }
   }
   float vals[VPT][8];

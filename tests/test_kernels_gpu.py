@@ -724,3 +724,47 @@ def test_attention_decode_with_norm_rotation_and_cache_write_fused(nq, nkv, hd, 
     if not write_kv:
         assert torch.equal(c1, cache0.float()), "nothing is stored when the call reads another call's cache"
     assert (o0 - o1).abs().max().item() <= 2e-2, f"outputs differ by {(o0 - o1).abs().max().item()}"
+
+
+@pytest.mark.parametrize("nq,nkv,hd,P", [(8, 2, 128, 16), (4, 1, 128, 64), (6, 2, 32, 16), (4, 4, 64, 8)])
+@pytest.mark.parametrize("rows", [1, 40])
+def test_tensor_core_attention_finds_one_far_key_and_respects_the_window(nq, nkv, hd, P, rows):
+    """The tuned kernels (decode rows: rows = 1; prompt tiles, tcgen05 where head_dim is 128: rows = 40):
+    ONE key among 700 is made to stand out for every query row; the output must be that key's value
+    wherever it lies (first key, edges of pages and of 64-key tiles, the last visible key). With a window
+    that just excludes it, it must not be seen at all."""
+    from openinfer_b200.kernels import attention as A
+    torch.manual_seed(hd + rows)
+    S = 700
+    scale = 1.0 / math.sqrt(hd)
+    n_pages = -(-S // P) + 4
+    order = torch.randperm(n_pages).tolist()
+    bt = torch.tensor([order[: -(-S // P)]], dtype=torch.int32, device=DEV)
+    first_row_pos = S - rows
+    for far in (0, P - 1, P, 63, 64, 65, 127, 128, 383, 384, first_row_pos - 1, first_row_pos):
+        direction = torch.randn(hd)
+        direction /= direction.norm()
+        # a window of S - 1 - far keys: the last row (position S - 1) just misses `far`, the rows before it see it
+        for window in (None, S - 1 - far if far < first_row_pos else None):
+            k = torch.randn(S, nkv, hd) * 0.1
+            v = torch.randn(S, nkv, hd)
+            k[far] = direction * 12.0
+            cache = _paged(k, v, P, order, torch.bfloat16, n_pages).to(DEV)
+            q = (direction * 12.0 * math.sqrt(hd) / 2).repeat(rows, nq, 1).to(torch.bfloat16)
+            qd = q.view(rows, -1).to(DEV)
+            out = torch.full((rows, nq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+            ctx = _FakeCtx([rows], [S], P)
+            grp = _FakeGroup(bt, [S])
+            assert A.attention_mma(qd, out, cache[:, 0, 0], cache[:, 0, 1], cache.stride(0), ctx, grp, nq, nkv, hd, scale, window)
+            assert A.tcgen05_status() == 0
+            got = out.float().cpu().view(rows, nq, hd)
+            want = v[far].to(torch.bfloat16).float()     # [nkv, hd]
+            if window is None:
+                for r in range(rows):
+                    for h in range(nq):
+                        assert torch.allclose(got[r, h], want[h // (nq // nkv)], atol=3e-2), f"far key {far}: row {r}, head {h}"
+            else:
+                # the window of the LAST row ends just after `far`: that row must not see it; row 0 still does
+                assert not torch.allclose(got[rows - 1, 0], want[0], atol=0.2), f"key {far} seen outside a window of {window}"
+                if rows > 1:
+                    assert torch.allclose(got[0, 0], want[0], atol=3e-2), f"key {far} not seen by row 0 inside a window of {window}"
