@@ -9,8 +9,8 @@
 // stream; here the caller supplies one uniform number per row (made from the request's own seed
 // and step, so a row's draw does not depend on its place in the batch) and the kernel walks the
 // cumulative distribution in vocabulary order. Thresholds are found by bisection on the bit
-// pattern of the (non-negative) probabilities, so no sort and no scratch beyond one float per
-// vocabulary entry and row.
+// pattern of the (non-negative) probabilities, over the few thousand largest of them where that
+// suffices (see sample_kernel), so no sort and no scratch beyond one float per vocabulary entry and row.
 #include "common.cuh"
 
 namespace {
@@ -104,10 +104,10 @@ __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restri
 }
 
 // count and mass of { p >= thr } over one row (p >= 0, compared as bit patterns)
-__device__ __forceinline__ void count_mass(const float* __restrict__ p, int vocab, unsigned thr_bits,
+__device__ __forceinline__ void count_mass(const float* __restrict__ p, int n, unsigned thr_bits,
                                            unsigned floor_bits, float* red, int& count, float& mass) {
   float c = 0.f, m = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = p[i];
     const unsigned b = __float_as_uint(v);
     if (b >= thr_bits && b >= floor_bits) { c += 1.f; m += v; }
@@ -118,59 +118,202 @@ __device__ __forceinline__ void count_mass(const float* __restrict__ p, int voca
   mass = m;
 }
 
+// The same over the candidate list in shared memory, whose ORDER differs from run to run (it is filled
+// through an atomic counter): the mass is added up in 2^-39 fixed point, where addition is associative,
+// so the result does not depend on the order.
+__device__ __forceinline__ void count_mass_list(const float* p, int n, unsigned thr_bits, unsigned floor_bits,
+                                                unsigned long long* red64, int& count, float& mass) {
+  unsigned long long acc = 0;     // mass in units of 2^-39 (at most 4096 values <= 1.0: at most 2^51)
+  int c = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = p[i];
+    const unsigned b = __float_as_uint(v);
+    if (b >= thr_bits && b >= floor_bits) {
+      acc += (unsigned long long)(v * 549755813888.f);
+      ++c;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red64[warp] = acc + ((unsigned long long)c << 52);     // count above the mass bits
+  __syncthreads();
+  acc = 0;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) acc += red64[w];
+  count = (int)(acc >> 52);
+  mass = (float)(acc & ((1ull << 52) - 1)) * (1.f / 549755813888.f);
+}
+
+template <bool kList>
+__device__ __forceinline__ void count_mass_any(const float* p, int n, unsigned thr_bits, unsigned floor_bits, float* red,
+                                               unsigned long long* red64, int& count, float& mass) {
+  if (kList) count_mass_list(p, n, thr_bits, floor_bits, red64, count, mass);
+  else count_mass(p, n, thr_bits, floor_bits, red, count, mass);
+}
+
+// largest t (as a bit pattern) with count{ p >= t } >= k: the k-th largest value of p[0, n)
+template <bool kList>
+__device__ __forceinline__ unsigned kth_largest_bits(const float* p, int n, int k, float* red, unsigned long long* red64) {
+  unsigned cur = 0;
+  for (int b = 30; b >= 0; --b) {
+    const unsigned cand = cur | (1u << b);
+    int cnt; float mass;
+    count_mass_any<kList>(p, n, cand, 0u, red, red64, cnt, mass);
+    if (cnt >= k) cur = cand;
+  }
+  return cur;
+}
+// largest t with mass{ p >= max(t, floor) } >= need
+template <bool kList>
+__device__ __forceinline__ unsigned mass_threshold_bits(const float* p, int n, unsigned floor_bits, float need, float* red,
+                                                        unsigned long long* red64) {
+  unsigned cur = 0;
+  for (int b = 30; b >= 0; --b) {
+    const unsigned cand = cur | (1u << b);
+    int cnt; float mass;
+    count_mass_any<kList>(p, n, cand, floor_bits, red, red64, cnt, mass);
+    if (cnt > 0 && mass >= need) cur = cand;
+  }
+  return cur;
+}
+
+constexpr int kSampleThreads = 1024;
+constexpr int kListCap = 4096;       // candidates kept in shared memory for the threshold searches
+constexpr int kExpBins = 128;        // exponents of values in [0, 1]
+
 // One block per row. probs: scratch [rows, vocab] float32.
-__global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
-                              float* __restrict__ probs, int vocab, const float* __restrict__ temperature,
-                              const int* __restrict__ top_k, const float* __restrict__ top_p,
-                              const float* __restrict__ min_p, const float* __restrict__ uniform) {
+//
+// After the softmax numerators e = exp((x - max) / T) are written (p_max = 1), a histogram over their
+// binary exponents tells how many values, and how much mass, lie at or above every power of two. The
+// largest values, down to the power of two at which more than kListCap would qualify, are copied
+// into shared memory; when the k-th largest value / the top-p mass lies inside that list (the usual
+// case: a peaked distribution) the threshold searches bisect over the list instead of the whole
+// vocabulary. Otherwise (a flat distribution) they scan the vocabulary as before: same thresholds,
+// more passes.
+__global__ void __launch_bounds__(kSampleThreads)
+sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
+              float* __restrict__ probs, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const float* __restrict__ uniform) {
   pdl_start();
   __shared__ float red[32];
-  __shared__ float chunk_sum[1024];
-  __shared__ int picked;
+  __shared__ float chunk_sum[kSampleThreads];
+  __shared__ float list[kListCap];
+  __shared__ unsigned long long red64[32];
+  __shared__ int hist_cnt[kExpBins];
+  __shared__ int picked, list_n, cut_exp;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   float* p = probs + (size_t)r * vocab;
   const float inv_t = 1.f / temperature[r];
+  const int tid = threadIdx.x;
+  const int k_req = top_k[r];
+  const bool want_list = (k_req > 0 && k_req < vocab) || top_p[r] < 1.f;   // a threshold search will follow
+  const bool vec = (vocab % 4 == 0) && (((uintptr_t)row) % 16 == 0) && (((uintptr_t)p) % 16 == 0);
 
+  for (int i = tid; i < kExpBins; i += kSampleThreads) hist_cnt[i] = 0;
+  if (tid == 0) { list_n = 0; picked = -1; }
+  // ---- maximum
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, row[i]);
-  mx = block_max(mx, red);
-  float z = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float e = expf((row[i] - mx) * inv_t);
-    p[i] = e;
-    z += e;
+  if (vec) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+    for (int i = tid; i < vocab / 4; i += kSampleThreads) {
+      const float4 v = row4[i];
+      mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
+  } else {
+    for (int i = tid; i < vocab; i += kSampleThreads) mx = fmaxf(mx, row[i]);
   }
-  z = block_sum(z, red);  // also orders the writes of p before the reads below (barriers inside)
+  mx = block_max(mx, red);
+  // ---- numerators, their sum, and the histogram over exponents (how many values per power of two)
+  float z = 0.f;
+  auto note = [&](float e) {
+    z += e;
+    if (!want_list) return;
+    const int bin = (int)(__float_as_uint(e) >> 23);     // e in [0, 1]: 0 .. 127
+    // lanes of a warp that hit the same bin count together: one atomic per distinct bin and warp
+    const unsigned peers = __match_any_sync(__activemask(), bin);
+    if ((int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&hist_cnt[bin], __popc(peers));
+  };
+  if (vec) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    float4* p4 = reinterpret_cast<float4*>(p);
+#pragma unroll 2
+    for (int i = tid; i < vocab / 4; i += kSampleThreads) {
+      const float4 v = row4[i];
+      float4 e;
+      e.x = expf((v.x - mx) * inv_t); e.y = expf((v.y - mx) * inv_t);
+      e.z = expf((v.z - mx) * inv_t); e.w = expf((v.w - mx) * inv_t);
+      p4[i] = e;
+      note(e.x); note(e.y); note(e.z); note(e.w);
+    }
+  } else {
+    for (int i = tid; i < vocab; i += kSampleThreads) {
+      const float e = expf((row[i] - mx) * inv_t);
+      p[i] = e;
+      note(e);
+    }
+  }
+  z = block_sum(z, red);  // also orders the writes of p and of the histogram before the reads below
   // p holds unnormalised e in [0, 1]; p_max = 1. Thresholds are scale-free.
+
+  // ---- the candidate list: every value at or above 2^(cut_exp - 127)
+  if (tid == 0) {
+    int total = 0, e = kExpBins;
+    if (want_list)
+      while (e > 0 && total + hist_cnt[e - 1] <= kListCap) { --e; total += hist_cnt[e]; }
+    cut_exp = e;    // bins [e, 128) are in the list; e == 128: not even the top bin fits (no list)
+  }
+  __syncthreads();
+  const unsigned cut_bits = (unsigned)cut_exp << 23;
+  const bool have_list = cut_exp < kExpBins;
+  if (have_list) {
+    auto take = [&](float v) {
+      if (__float_as_uint(v) >= cut_bits) list[atomicAdd(&list_n, 1)] = v;
+    };
+    if (vec) {
+      const float4* p4 = reinterpret_cast<const float4*>(p);
+#pragma unroll 4
+      for (int i = tid; i < vocab / 4; i += kSampleThreads) {
+        const float4 v = p4[i];
+        take(v.x); take(v.y); take(v.z); take(v.w);
+      }
+    } else {
+      for (int i = tid; i < vocab; i += kSampleThreads) take(p[i]);
+    }
+  }
+  __syncthreads();
+  const int ln = have_list ? list_n : 0;
 
   unsigned floor_bits = 0;  // running lower bound of kept values (bit pattern)
   float kept_mass = z;
-  int k = top_k[r];
+  const int k = k_req;
   if (k > 0 && k < vocab) {
-    // largest t with count(p >= t) >= k: the k-th largest value
-    unsigned cur = 0;
-    for (int b = 30; b >= 0; --b) {
-      const unsigned cand = cur | (1u << b);
-      int cnt; float mass;
-      count_mass(p, vocab, cand, 0u, red, cnt, mass);
-      if (cnt >= k) cur = cand;
-    }
-    floor_bits = cur;
+    // the k-th largest value: among the list's values when it holds at least k (it holds the largest ones)
     int cnt;
-    count_mass(p, vocab, floor_bits, 0u, red, cnt, kept_mass);
+    if (k <= ln) {
+      floor_bits = kth_largest_bits<true>(list, ln, k, red, red64);
+      count_mass_list(list, ln, floor_bits, 0u, red64, cnt, kept_mass);
+    } else {
+      floor_bits = kth_largest_bits<false>(p, vocab, k, red, red64);
+      count_mass(p, vocab, floor_bits, 0u, red, cnt, kept_mass);
+    }
   }
   const float tp = top_p[r];
   if (tp < 1.f) {
-    // largest t with mass(p >= t, kept) >= top_p * kept_mass
+    // largest t with mass(p >= t, kept) >= top_p * kept_mass. When the kept values that the list holds
+    // already reach that mass, t is at or above the list's cut and every value >= t is in the list.
     const float need = tp * kept_mass;
-    unsigned cur = 0;
-    for (int b = 30; b >= 0; --b) {
-      const unsigned cand = cur | (1u << b);
-      int cnt; float mass;
-      count_mass(p, vocab, cand, floor_bits, red, cnt, mass);  // counts p >= max(cand, floor)
-      if (cnt > 0 && mass >= need) cur = cand;
-    }
+    int cnt; float in_list;
+    count_mass_list(list, ln, floor_bits, 0u, red64, cnt, in_list);
+    unsigned cur;
+    if (ln > 0 && cnt > 0 && in_list >= need) cur = mass_threshold_bits<true>(list, ln, floor_bits, need, red, red64);
+    else cur = mass_threshold_bits<false>(p, vocab, floor_bits, need, red, red64);
     if (cur > floor_bits) floor_bits = cur;
   }
   const float mp = min_p[r];
@@ -180,43 +323,110 @@ __global__ void sample_kernel(int* __restrict__ out, const float* __restrict__ l
   }
 
   // inverse CDF in vocabulary order: thread t owns a contiguous chunk
-  const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
-  const int lo = threadIdx.x * chunk, hi = min(vocab, lo + chunk);
+  const int chunk = ((vocab + kSampleThreads - 1) / kSampleThreads + 3) & ~3;   // a multiple of 4: 16-byte loads
+  const int lo = min(vocab, tid * chunk), hi = min(vocab, lo + chunk);
   float local = 0.f;
-  for (int i = lo; i < hi; ++i) {
-    const float v = p[i];
-    if (__float_as_uint(v) >= floor_bits) local += v;
-  }
-  chunk_sum[threadIdx.x] = local;
-  if (threadIdx.x == 0) picked = -1;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float total = 0.f;
-    for (int t = 0; t < blockDim.x; ++t) total += chunk_sum[t];
-    const float target = uniform[r] * total;
-    float run = 0.f;
-    int owner = -1, last_nonempty = -1;
-    for (int t = 0; t < blockDim.x; ++t) {
-      if (chunk_sum[t] > 0.f) last_nonempty = t;
-      if (owner < 0 && chunk_sum[t] > 0.f && run + chunk_sum[t] > target) { owner = t; break; }
-      run += chunk_sum[t];
-    }
-    if (owner < 0) { owner = last_nonempty; run -= chunk_sum[owner]; }  // rounding at the very end
-    // walk the owner's chunk
-    const int clo = owner * chunk, chi = min(vocab, clo + chunk);
-    int pick = -1, last_kept = -1;
-    for (int i = clo; i < chi; ++i) {
-      const float v = p[i];
-      if (__float_as_uint(v) >= floor_bits && v > 0.f) {
-        last_kept = i;
-        run += v;
-        if (run > target) { pick = i; break; }
+  {
+    int i = lo;
+    if (vec) {
+      for (; i + 4 <= hi; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p + i);
+        if (__float_as_uint(v.x) >= floor_bits) local += v.x;
+        if (__float_as_uint(v.y) >= floor_bits) local += v.y;
+        if (__float_as_uint(v.z) >= floor_bits) local += v.z;
+        if (__float_as_uint(v.w) >= floor_bits) local += v.w;
       }
     }
-    picked = pick >= 0 ? pick : last_kept;
+    for (; i < hi; ++i) {
+      const float v = p[i];
+      if (__float_as_uint(v) >= floor_bits) local += v;
+    }
+  }
+  chunk_sum[tid] = local;
+  __syncthreads();
+  if (tid < 32) {
+    // warp 0 walks the cumulative distribution: lane l owns chunk sums [32 l, 32 l + 32), then the owning
+    // chunk's values are shared out among the lanes in the same way. The first kept value at which the
+    // running sum exceeds u * total is drawn; rounding at the very end falls back to the last kept value.
+    const int lane = tid;
+    float mine = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < 32; ++t) mine += chunk_sum[lane * 32 + t];
+    float incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const float total = __shfl_sync(0xffffffffu, incl, 31);
+    const float target = uniform[r] * total;
+    float run = incl - mine;
+    int found = -1, last_nonempty = -1;
+    for (int t = 0; t < 32; ++t) {
+      const float c = chunk_sum[lane * 32 + t];
+      if (c > 0.f) {
+        last_nonempty = lane * 32 + t;
+        if (found < 0 && run + c > target) found = lane * 32 + t;
+      }
+      if (found < 0) run += c;
+    }
+    const unsigned who = __ballot_sync(0xffffffffu, found >= 0);
+    int owner, src_lane;
+    if (who) {
+      src_lane = __ffs(who) - 1;
+      owner = __shfl_sync(0xffffffffu, found, src_lane);
+    } else {   // rounding at the very end: the last chunk that holds anything, entered with the sum before it
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) last_nonempty = max(last_nonempty, __shfl_xor_sync(0xffffffffu, last_nonempty, o));
+      owner = last_nonempty < 0 ? 0 : last_nonempty;   // (nothing kept cannot happen: the largest value always is)
+      src_lane = owner >> 5;
+      if (lane == src_lane) {
+        run = incl - mine;
+        for (int t = lane * 32; t < owner; ++t) run += chunk_sum[t];
+      }
+    }
+    float before = __shfl_sync(0xffffffffu, run, src_lane);    // cumulative sum in front of the owning chunk
+    // the owning chunk: lane l takes its values [per l, per l + per)
+    const int clo = min(vocab, owner * chunk), chi = min(vocab, clo + chunk);
+    const int per = (chunk + 31) / 32;
+    float vals[8];
+    float lsum = 0.f;
+    const int l0 = clo + lane * per;
+    for (int e = 0; e < 8; ++e) {
+      const int i = l0 + e;
+      float v = (e < per && i < chi) ? p[i] : 0.f;
+      if (!(__float_as_uint(v) >= floor_bits && v > 0.f)) v = 0.f;
+      vals[e] = v;
+      lsum += v;
+    }
+    float lincl = lsum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, lincl, o);
+      if (lane >= o) lincl += up;
+    }
+    float lrun = before + lincl - lsum;
+    int pick = -1, last_kept = -1;
+    for (int e = 0; e < 8; ++e) {
+      if (vals[e] > 0.f) {
+        last_kept = l0 + e;
+        lrun += vals[e];
+        if (pick < 0 && lrun > target) pick = l0 + e;
+      }
+    }
+    const unsigned got = __ballot_sync(0xffffffffu, pick >= 0);
+    int result;
+    if (got) {
+      result = __shfl_sync(0xffffffffu, pick, __ffs(got) - 1);
+    } else {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) last_kept = max(last_kept, __shfl_xor_sync(0xffffffffu, last_kept, o));
+      result = last_kept < 0 ? 0 : last_kept;
+    }
+    if (lane == 0) picked = result;
   }
   __syncthreads();
-  if (threadIdx.x == 0) out[r] = picked;
+  if (tid == 0) out[r] = picked;
 }
 
 }  // namespace
@@ -250,8 +460,9 @@ OI_API int oi_sample(int* out, const float* logits, long long row_stride, float*
                      const float* uniform, void* stream) {
   OI_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   OI_REQUIRE(probs != nullptr, "sample: scratch missing");
+  OI_REQUIRE(vocab <= 8 * 32 * kSampleThreads, "sample: vocabulary %d beyond %d", vocab, 8 * 32 * kSampleThreads);
   if (rows == 0) return OI_OK;
-  oi_launch(sample_kernel, rows, 1024, 0, (cudaStream_t)stream, out, logits, row_stride, probs, vocab, temperature,
+  oi_launch(sample_kernel, rows, kSampleThreads, 0, (cudaStream_t)stream, out, logits, row_stride, probs, vocab, temperature,
                                                          top_k, top_p, min_p, uniform);
   OI_CHECK_LAUNCH();
   return OI_OK;

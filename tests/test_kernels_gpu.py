@@ -283,7 +283,7 @@ def test_argmax_ties_and_odd_vocab():
         assert out3.tolist() == torch.argmax(wide, dim=-1).tolist()
 
 
-@pytest.mark.parametrize("vocab", [50, 384, 5000])
+@pytest.mark.parametrize("vocab", [50, 384, 5000, 30001])
 def test_sample_matches_plain_distribution(vocab):
     """The kept set and the drawn token follow the plain statement of temperature / top-k /
     top-p / min-p, for uniform numbers across [0, 1)."""
@@ -293,6 +293,14 @@ def test_sample_matches_plain_distribution(vocab):
                 (1.0, -1, 1.0, 0.1), (0.9, 10, 0.95, 0.05), (1.0, -1, 0.01, 0.0)]
     us = [0.0, 0.001, 0.25, 0.5, 0.75, 0.999, 0.9999999]
     logits = torch.randn(len(settings), vocab) * 2.0
+    if vocab > 5000:
+        # more values than the kernel's shared-memory list of candidates holds: peaked rows find their thresholds
+        # in the list, the flat ones (spread 0.05) must fall back to scanning the vocabulary; rows 1 and 5 get
+        # many exact ties at the top
+        logits[2] *= 0.025
+        logits[3] *= 0.025
+        logits[1, :6000] = 9.0
+        logits[5, ::3] = 7.0
     for u in us:
         rows = len(settings)
         out = torch.empty(rows, dtype=torch.int32, device=DEV)
