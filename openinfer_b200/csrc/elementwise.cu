@@ -86,6 +86,36 @@ OI_API int oi_gather_tokens(int* ids, const int* src, const int* from, int n, in
   return OI_OK;
 }
 
+// dst[i] = src[i] for a few thousand 32-bit words, by a kernel: `src` or `dst` may be PINNED HOST memory
+// (which the device reads and writes directly), so that a step's metadata reaches the device, and its
+// drawn tokens the host, in the stream's kernel order without a copy-engine operation in between. With
+// ids_off >= 0 the words [ids_off, ids_off + n_ids) are token ids, and those whose source index
+// (the words at src_off) is >= 0 are taken from `from` instead (see oi_gather_tokens).
+__global__ void copy_words_kernel(int* __restrict__ dst, const int* __restrict__ src, int n, int ids_off, int src_off,
+                                  int n_ids, const int* __restrict__ from, int n_from) {
+  pdl_start();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    int v = src[i];
+    if (ids_off >= 0 && i >= ids_off && i < ids_off + n_ids) {
+      const int j = src[src_off + (i - ids_off)];
+      if (j >= 0 && j < n_from) v = from[j];
+    }
+    dst[i] = v;
+  }
+}
+
+OI_API int oi_copy_words(int* dst, const int* src, int n, int ids_off, int src_off, int n_ids, const int* from, int n_from,
+                         void* stream) {
+  OI_REQUIRE(n >= 0 && (ids_off < 0 || (src_off >= 0 && n_ids >= 0 && ids_off + n_ids <= n && src_off + n_ids <= n)),
+             "copy_words: bad sizes");
+  OI_REQUIRE(ids_off < 0 || n_from == 0 || from != nullptr, "copy_words: token source missing");
+  if (n == 0) return OI_OK;
+  const int blocks = (n + 255) / 256 > 64 ? 64 : (n + 255) / 256;
+  oi_launch(copy_words_kernel, blocks, 256, 0, (cudaStream_t)stream, dst, src, n, ids_off, src_off, n_ids, from, n_from);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
 // ---------------------------------------------------------------------------
 template <typename T, bool kCache>
 __global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* __restrict__ delta,

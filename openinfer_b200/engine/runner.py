@@ -58,8 +58,10 @@ class ModelRunner:
         self.cache = cache
         self.device = torch.device(device)
         self.spec = model.spec
-        self._staging: Optional[torch.Tensor] = None
-        self._staging_event: Optional[torch.cuda.Event] = None
+        self._staging: List[torch.Tensor] = []
+        self._staging_events: List[Optional[torch.cuda.Event]] = []
+        self._staging_turn = 0
+        self._device_tokens: Optional[torch.Tensor] = None
         self.steps_run = 0
         self.cuda_graph = False          # record decode-only steps as CUDA graphs and replay them
         self.max_graph_batch = 256
@@ -116,21 +118,35 @@ class ModelRunner:
         return cls.build(config, None, dtype=dtype, device=device, folder=folder, **kw)
 
     # ------------------------------------------------------------------ helpers
-    def _stage(self, host: np.ndarray) -> torch.Tensor:
-        """Host int32 array -> device tensor through a pinned staging buffer, one copy."""
+    def _pinned(self, host: np.ndarray) -> torch.Tensor:
+        """The step's metadata in pinned host memory (a ring of buffers, so that the host can write the
+        next step's while the device has not read this one's yet)."""
         n = host.size
-        if self._staging is None or self._staging.numel() < n:
-            self._staging = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
-            self._staging_event = None
-        if self._staging_event is not None:
-            self._staging_event.synchronize()  # the previous step's copy has left the buffer
-        self._staging[:n].numpy()[:] = host
+        if not self._staging or self._staging[0].numel() < n:
+            if self._staging:
+                torch.cuda.current_stream().synchronize()   # kernels in flight may still read the old buffers
+            self._staging = [torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+            self._staging_events = [None] * 4
+            self._staging_turn = 0
+        self._staging_turn = (self._staging_turn + 1) % len(self._staging)
+        event = self._staging_events[self._staging_turn]
+        if event is not None:
+            event.synchronize()   # the step that used this buffer four steps ago has read it
+        buf = self._staging[self._staging_turn]
+        buf[:n].numpy()[:] = host
         self._staging_last_bytes = n * 4
-        dev = torch.empty(n, dtype=torch.int32, device=self.device)
-        dev.copy_(self._staging[:n], non_blocking=True)
-        self._staging_event = torch.cuda.Event()
-        self._staging_event.record()
-        return dev
+        return buf
+
+    def _upload(self, dev: torch.Tensor, host: np.ndarray, sections: Dict[str, int], T: int, entries) -> None:
+        """Metadata to the device by a KERNEL that reads the pinned buffer (no copy-engine operation between
+        the steps' kernels); the same kernel puts in the token ids that the host does not know yet."""
+        buf = self._pinned(host)
+        feed = any(e.token_from is not None for e in entries)
+        ops.copy_words(dev, buf, host.size, ids_off=sections["token_ids"] if feed else -1, src_off=sections["token_src"],
+                       n_ids=T if feed else 0, tokens=self._device_tokens if feed else None)
+        event = torch.cuda.Event()
+        event.record()
+        self._staging_events[self._staging_turn] = event
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
         vocab, max_pos = self.spec.vocab_size, self.spec.max_positions
@@ -211,12 +227,6 @@ class ModelRunner:
         """The request is finished: its pages and state slot go back to the pools."""
         if self.cache.has(request_id):
             self.cache.close(request_id)
-
-    def _take_device_tokens(self, meta: torch.Tensor, sections: Dict[str, int], T: int, entries) -> None:
-        """Rows whose token the host does not know yet get it from the tensor given to step()."""
-        if any(e.token_from is not None for e in entries):
-            ops.gather_tokens(meta[sections["token_ids"]: sections["token_ids"] + T],
-                              meta[sections["token_src"]: sections["token_src"] + T], self._device_tokens)
 
     # ------------------------------------------------------------------ metadata
     @staticmethod
@@ -325,8 +335,8 @@ class ModelRunner:
         want_rows = self._fill(host, sections, entries, starts, T, B, max_pages)
         if n_want:
             host[sections["want"]: sections["want"] + n_want] = np.asarray(want_rows, dtype=np.int32)
-        dev = self._stage(host)
-        self._take_device_tokens(dev, sections, T, entries)
+        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        self._upload(dev, host, sections, T, entries)
         slots = [cache.state_slot(e.request_id) for e in entries]
         ctx = self._context(dev, sections, T, B, max_pages, q_lens, starts, kv_lens, slots)
         row_idx = dev[sections["want"]: sections["want"] + n_want] if n_want else None
@@ -400,18 +410,7 @@ class ModelRunner:
         host = np.zeros(total, dtype=np.int32)
         want_rows = self._fill(host, sections, entries, starts, bucket, bucket, cap)
         host[sections["want"]: sections["want"] + bucket] = np.arange(bucket, dtype=np.int32)
-        n = host.size
-        if self._staging is None or self._staging.numel() < n:
-            self._staging = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
-            self._staging_event = None
-        if self._staging_event is not None:
-            self._staging_event.synchronize()
-        self._staging[:n].numpy()[:] = host
-        self._staging_last_bytes = n * 4
-        meta.copy_(self._staging[:n], non_blocking=True)
-        self._staging_event = torch.cuda.Event()
-        self._staging_event.record()
-        self._take_device_tokens(meta, sections, bucket, entries)
+        self._upload(meta, host, sections, bucket, entries)
         graph.replay()
         kernel_lib.launches += recorded
         if not want_rows:

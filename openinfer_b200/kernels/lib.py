@@ -24,6 +24,7 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 _SIGNATURES = {
     "oi_embedding": [P, I, P, I, P, I, I, I, P],
     "oi_gather_tokens": [P, P, P, I, I, P],
+    "oi_copy_words": [P, P, I, I, I, I, P, I, P],
     "oi_rmsnorm": [P, P, P, I, P, I, P, I, I, F, F, P],
     "oi_add_inplace": [P, P, I, L, P],
     "oi_silu_mul": [P, P, I, I, I, I, P],

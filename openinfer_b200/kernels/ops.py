@@ -71,6 +71,22 @@ def gather_tokens(ids: torch.Tensor, src: torch.Tensor, tokens: torch.Tensor) ->
     return ids
 
 
+def copy_words(dst: torch.Tensor, src: torch.Tensor, n: int, *, ids_off: int = -1, src_off: int = 0, n_ids: int = 0,
+               tokens: Optional[torch.Tensor] = None) -> None:
+    """dst[:n] = src[:n] (int32) by a kernel; one of the two may be pinned host memory, which the device
+    reads or writes directly. With ``ids_off >= 0`` the words [ids_off, ids_off + n_ids) are token ids:
+    where the source index at ``src_off`` is >= 0 the id comes from ``tokens`` (int32, on the device)."""
+    for t, what in ((dst, "dst"), (src, "src")):
+        if t.dtype != torch.int32 or not t.is_contiguous() or t.numel() < n or not (t.is_cuda or t.is_pinned()):
+            raise KernelError(f"copy_words: {what} must be contiguous int32 of at least {n} words, on the device or pinned")
+    if tokens is not None:
+        _cuda(tokens)
+        _i32(tokens, "copy_words tokens")
+    L = _lib.load()
+    _lib.check(L.oi_copy_words(dst.data_ptr(), src.data_ptr(), int(n), int(ids_off), int(src_off), int(n_ids),
+                               _ptr(tokens), 0 if tokens is None else tokens.numel(), _stream()), "copy_words")
+
+
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, *,
             delta: Optional[torch.Tensor] = None, row_idx: Optional[torch.Tensor] = None,
             weight_offset: float = 0.0) -> torch.Tensor:

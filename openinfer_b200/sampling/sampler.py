@@ -88,7 +88,7 @@ class Sampler:
             else:
                 out[torch.tensor(sampled, device=self.device)] = picked
         host = self._host_buffer(n)
-        host.copy_(out, non_blocking=True)
+        ops.copy_words(host, out, n)     # a kernel writes the ids into pinned host memory: no copy-engine operation
         event = torch.cuda.Event()
         event.record()
         return PendingTokens(out, host, event)
