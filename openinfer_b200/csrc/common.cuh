@@ -63,6 +63,9 @@ typedef __nv_bfloat16 bf16;
 // kernel writes or reads-then-overwrites is touched before that wait, so the memory effects stay
 // in stream order; what overlaps is the launch latency, the prologues, and in the weight-streaming
 // products the first loads of the (never written) weights, which they request before waiting.
+// What a kernel may read before its wait must have been written before the step's kernels began: the
+// step's metadata is put in place by a kernel that does NOT trigger early (copy_words_kernel), so
+// everything behind it starts after it has finished; keys and values of earlier steps lie behind that fence too.
 // A kernel launched without the attribute (oi_set_pdl(0), or after a library kernel) sees both
 // instructions as no-ops.
 // ---------------------------------------------------------------------------------------------

@@ -71,7 +71,7 @@ OI_API int oi_embedding(void* out, int out_dtype, const void* table, int table_d
 // seen yet (indices outside `from` leave the id alone; the host checks them before the launch).
 __global__ void gather_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ from,
                                      int n, int n_from) {
-  pdl_start();
+  pdl_wait();   // no early trigger: see copy_words_kernel
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int j = src[i];
@@ -93,7 +93,10 @@ OI_API int oi_gather_tokens(int* ids, const int* src, const int* from, int n, in
 // (the words at src_off) is >= 0 are taken from `from` instead (see oi_gather_tokens).
 __global__ void copy_words_kernel(int* __restrict__ dst, const int* __restrict__ src, int n, int ids_off, int src_off,
                                   int n_ids, const int* __restrict__ from, int n_from) {
-  pdl_start();
+  // No early trigger here: what this kernel writes (a step's lengths, block tables, positions) is read by
+  // later kernels BEFORE their own wait, so nothing after it may start until it has finished. It is the
+  // fence between two steps.
+  pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     int v = src[i];
     if (ids_off >= 0 && i >= ids_off && i < ids_off + n_ids) {
