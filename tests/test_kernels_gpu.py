@@ -776,3 +776,27 @@ def test_tensor_core_attention_finds_one_far_key_and_respects_the_window(nq, nkv
                 assert not torch.allclose(got[rows - 1, 0], want[0], atol=0.2), f"key {far} seen outside a window of {window}"
                 if rows > 1:
                     assert torch.allclose(got[0, 0], want[0], atol=3e-2), f"key {far} not seen by row 0 inside a window of {window}"
+
+
+def test_copy_words_between_pinned_host_memory_and_the_device():
+    """A step's metadata goes to the device, and the drawn tokens come back, by a kernel that reads or
+    writes pinned host memory; token ids that the host does not know yet are put in on the way."""
+    from openinfer_b200.kernels import ops
+    n, ids_off, src_off, n_ids = 300, 8, 40, 20
+    host = torch.arange(n, dtype=torch.int32).pin_memory()
+    host[src_off: src_off + n_ids] = -1
+    host[src_off + 3] = 2          # id 3 comes from tokens[2], id 7 from tokens[0]
+    host[src_off + 7] = 0
+    host[src_off + 9] = 99         # outside the tokens: left alone
+    tokens = torch.tensor([1000, 1001, 1002], dtype=torch.int32, device=DEV)
+    dev = torch.full((n + 5,), -7, dtype=torch.int32, device=DEV)
+    ops.copy_words(dev, host, n, ids_off=ids_off, src_off=src_off, n_ids=n_ids, tokens=tokens)
+    want = host.clone()
+    want[ids_off + 3], want[ids_off + 7] = 1002, 1000
+    assert torch.equal(dev[:n].cpu(), want) and bool((dev[n:] == -7).all())
+    back = torch.zeros(n, dtype=torch.int32).pin_memory()
+    ops.copy_words(back, dev, n)
+    torch.cuda.synchronize()
+    assert torch.equal(back, want)
+    with pytest.raises(Exception):
+        ops.copy_words(dev, torch.zeros(n, dtype=torch.int32), n)      # pageable host memory is refused

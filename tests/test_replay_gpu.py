@@ -119,3 +119,30 @@ def test_decode_steps_replayed_as_cuda_graphs(folders, workloads, name, dtype):
         assert runner._graphs, "no step went through a graph"
         _check(got, ref, dtype, f"graphs {name}/{dtype}/{mode}")
         runner.cache.check()
+
+
+def test_without_programmatic_dependent_launch(folders, workloads):
+    """Every kernel is launched so that it may start under its predecessor and waits before touching
+    what that one writes; with the attribute switched off (plain stream order) the logits are the same
+    bit for bit, with and without recorded graphs."""
+    from openinfer_b200.kernels import lib as klib
+    name = "A"
+    cfg, reqs, ref = workloads[name]
+    biggest = max(round64(len(t)) for t in reqs.values())
+    steps = trace_mixed(reqs, biggest + 192, seed=3)
+    L = klib.load()
+    outs = {}
+    try:
+        for pdl in (1, 0):
+            for graphs in (False, True):
+                klib.check(L.oi_set_pdl(pdl), "set_pdl")
+                runner = _runner(folders[name], "bfloat16", biggest + 192, page_size=16, cuda_graph=graphs)
+                outs[(pdl, graphs)] = replay_in_process(runner, steps)
+    finally:
+        klib.check(L.oi_set_pdl(1), "set_pdl")
+    for graphs in (False, True):
+        a, b = outs[(1, graphs)], outs[(0, graphs)]
+        assert a.keys() == b.keys()
+        for k in a:
+            assert torch.equal(torch.as_tensor(a[k]), torch.as_tensor(b[k])), f"step {k} differs without the attribute (graphs {graphs})"
+    _check(outs[(1, True)], ref, "bfloat16", "with dependent launches")
