@@ -64,7 +64,8 @@ MAX_SPLITS = 16            # slices of a prompt tile's keys
 MIN_TILES_PER_SPLIT = 2    # such a slice is at least 128 keys long
 DECODE_WARPS = 4           # slices of a decode row per CTA (one per warp)
 DECODE_CTAS_PER_SM = 2
-DECODE_MAX_SPLITS = 64
+DECODE_MAX_SPLITS = 32     # 8 CTAs of 4 slices: what a cluster merges in the kernel (batch 1 at context 2048: 313 tok/s
+                           # against 299 with 64 slices and the second kernel)
 DECODE_MERGE_IN_KERNEL_MAX_SPLITS = 32   # up to 8 CTAs of a row form a cluster and merge their slices themselves
 DECODE_MIN_KEYS_PER_SPLIT = 32
 DECODE_MAX_GROUP = 16

@@ -432,11 +432,14 @@ def test_attention_mma_mixed_batch(nq, nkv, hd, P, window, tcgen05, monkeypatch)
 
 @pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 128), (6, 2, 32), (8, 1, 64)])
 @pytest.mark.parametrize("window", [None, 200])
-def test_attention_mma_split_kv_decode(nq, nkv, hd, window):
+def test_attention_mma_split_kv_decode(nq, nkv, hd, window, monkeypatch):
     """Decode rows whose keys are cut into slices and merged; contexts around tile edges."""
+    from openinfer_b200.kernels import attention as A
     kv_lens = [1, 63, 64, 65, 127, 128, 129, 700, 1025]
     long = kv_lens + [2100]
+    monkeypatch.setattr(A, "DECODE_MAX_SPLITS", 64)     # more slices than the planner uses: the second kernel merges
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(long), long, force_splits="max")
+    monkeypatch.setattr(A, "DECODE_MAX_SPLITS", 32)
     # the decode kernel, 64 slices: too many CTAs per row for a cluster, merged by the second kernel
     assert plan.num_decode_items and plan.max_splits == 64 and not plan.num_tile_items and not plan.decode_merge_in_kernel
     plan = _mma_case(nq, nkv, hd, 16, window, [1] * len(kv_lens), kv_lens)
