@@ -27,13 +27,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# BASELINE configs[2]: Qwen3-8B sizes
+# the headline configuration: Qwen3-8B sizes
 QWEN3_8B = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
     num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
     vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
     max_position_embeddings=4096)
-# BASELINE configs[3] and [4]: the other two Qwen3 sizes (selected with --model)
+# the other two Qwen3 sizes of the reference's benchmarks (selected with --model)
 QWEN3_06B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
                  intermediate_size=3072, tie_word_embeddings=True)
 QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
