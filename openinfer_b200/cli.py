@@ -48,7 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
     eng.add_argument("--kv-page-size", type=int, default=16, help="tokens per cache page")
     eng.add_argument("--num-pages", type=int, default=None, help="size the cache pool explicitly (pages)")
     eng.add_argument("--no-prefix-cache", action="store_true",
-                     help="accepted for compatibility: this engine keeps no prefix cache")
+                     help="do not share registered prompt pages between requests")
     gen = ap.add_argument_group("generation")
     gen.add_argument("--prompt-ids", action="append", default=[],
                      help="comma-separated token ids of one prompt (repeatable)")
@@ -102,7 +102,8 @@ def main(argv: Optional[List[str]] = None) -> int:
               device_ordinal=args.device_ordinal, kv_page_size=args.kv_page_size, num_pages=args.num_pages,
               gpu_memory_utilization=args.gpu_memory_utilization,
               kv_cache_memory_margin_mib=args.kv_cache_memory_margin_mib,
-              max_prefill_tokens=args.max_prefill_tokens, cuda_graph=args.cuda_graph)
+              max_prefill_tokens=args.max_prefill_tokens, cuda_graph=args.cuda_graph,
+              prefix_cache=not args.no_prefix_cache)
     sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
                         seed=args.sampling_seed, ignore_eos=args.ignore_eos)
     for i, r in enumerate(llm.generate_detailed(prompts, sp, args.max_tokens)):

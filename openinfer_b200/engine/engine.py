@@ -76,6 +76,9 @@ class RunnerExecutor(Executor):
     def drop(self, request_id: Hashable) -> None:
         self.runner.end(request_id)
 
+    def begin(self, request_id: Hashable, prompt_tokens: Sequence[int]) -> int:
+        return self.runner.begin(request_id, prompt_tokens)
+
 
 @dataclasses.dataclass
 class GenerationResult:
@@ -100,7 +103,8 @@ class LLM:
                  kv_cache_memory_margin_mib: int = DEFAULT_KV_MARGIN_MIB,
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
-                 cuda_graph: bool = True, lookahead: bool = True, runner: Optional[ModelRunner] = None) -> None:
+                 cuda_graph: bool = True, lookahead: bool = True, prefix_cache: bool = True,
+                 runner: Optional[ModelRunner] = None) -> None:
         device = f"cuda:{device_ordinal}"
         weights_seed = None
         if runner is not None:
@@ -119,11 +123,12 @@ class LLM:
 
             self.runner, _ = pages_from_memory_budget(
                 config, weights_seed, model_path, dtype, device, kv_page_size, gpu_memory_utilization,
-                kv_cache_memory_margin_mib, max_prefill_tokens)
+                kv_cache_memory_margin_mib, max_prefill_tokens, prefix_cache=prefix_cache)
         else:
             self.runner = ModelRunner.build(
                 config, weights_seed, dtype=dtype, device=device, page_size=kv_page_size, num_pages=num_pages,
-                max_tokens=max_cache_tokens, max_requests=max_decode_batch, folder=model_path)
+                max_tokens=max_cache_tokens, max_requests=max_decode_batch, folder=model_path,
+                prefix_cache=prefix_cache)
         self.runner.cuda_graph = cuda_graph
         self.config = config
         self.executor = RunnerExecutor(self.runner)

@@ -14,7 +14,7 @@ from .runner import ModelRunner, StepEntry, _dtype_of
 
 
 def pages_from_memory_budget(config, weights_seed, folder, dtype, device, page_size: int,
-                             utilization: float, margin_mib: int, max_prefill_tokens: int):
+                             utilization: float, margin_mib: int, max_prefill_tokens: int, prefix_cache: bool = False):
     """Build the runner with a pool sized from free memory. Returns (runner, num_pages)."""
     if not (0.0 < utilization <= 1.0):
         raise ValueError(f"gpu_memory_utilization must be in (0, 1], got {utilization}")
@@ -45,7 +45,7 @@ def pages_from_memory_budget(config, weights_seed, folder, dtype, device, page_s
     model = runner.model
     del runner
     torch.cuda.empty_cache()
-    cache = CacheManager(page_size=page_size)
+    cache = CacheManager(page_size=page_size, prefix_cache=prefix_cache)
     model.bind_cache(cache)
     cache.allocate(int(num_pages), 256, device=dev, dtype=tdtype)
     return ModelRunner(model, cache, dev), int(num_pages)

@@ -73,7 +73,7 @@ class ModelRunner:
     @classmethod
     def build(cls, config, tensors_or_seed, dtype="bfloat16", device="cuda:0", *, page_size: int = 16,
               num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
-              max_requests: int = 256, folder: Optional[str] = None) -> "ModelRunner":
+              max_requests: int = 256, folder: Optional[str] = None, prefix_cache: bool = False) -> "ModelRunner":
         """Assemble model + cache on the device.
 
         ``tensors_or_seed``: None to load ``folder``'s safetensors, or an int seed for
@@ -103,7 +103,7 @@ class ModelRunner:
             tensors = random_tensors(expected, int(tensors_or_seed), dtype=dtype, device=device)
         model.load(tensors, device)
         del tensors
-        cache = CacheManager(page_size=page_size)
+        cache = CacheManager(page_size=page_size, prefix_cache=prefix_cache)
         model.bind_cache(cache)
         if num_pages is None:
             if max_tokens is None:
@@ -218,10 +218,16 @@ class ModelRunner:
             for rid in opened:
                 cache.close(rid)
             raise
-        for rid in reserved:
-            cache.commit(rid)
+        for e in entries:     # token ids the host knows let the prefix cache register full pages of them
+            cache.commit(e.request_id, tokens=None if e.token_from is not None else e.tokens)
         self.steps_run += 1
         return logits
+
+    def begin(self, request_id: Hashable, prompt_tokens: Sequence[int]) -> int:
+        """Open a request ahead of its first step and let it share registered pages that match the front
+        of its prompt (the prefix cache). Returns how many prompt tokens are already in the cache: the first
+        step of the request brings the tokens behind them."""
+        return self.cache.begin(request_id, [int(t) for t in prompt_tokens])
 
     def end(self, request_id: Hashable) -> None:
         """The request is finished: its pages and state slot go back to the pools."""

@@ -12,6 +12,9 @@ Decisions follow the reference's scheduler (pegainfer-qwen3/src/scheduler.rs):
   no swapping. A request that cannot fit now stays deferred (later, smaller requests may
   pass it); one that could never fit, or whose prompt + max_tokens exceeds the context
   limit, is rejected at once;
+* an admitted request is announced to the executor (``begin``), which may answer that the front of its
+  prompt is in the cache already (the reference's prefix cache, on by default there); its portions then
+  start behind that;
 * every step forwards at most ``max_prefill_tokens`` prompt tokens in total, taken from the
   front of ``prefilling`` (scheduler.rs:145-179), beside one token of every active request
   (plan.rs:56-87): prompt portions always ride along with decoding;
@@ -97,6 +100,11 @@ class Executor:
 
     def drop(self, request_id: Hashable) -> None:
         raise NotImplementedError
+
+    def begin(self, request_id: Hashable, prompt_tokens: Sequence[int]) -> int:
+        """A request has been admitted. Returns how many tokens at the front of its prompt are in the
+        cache already (a prefix cache; 0 without one): its portions start behind them."""
+        return 0
 
     # Optional, for running one step ahead: launch() starts a batch and returns a handle; a decode item
     # whose token is None takes the token that the batch of ``previous`` (a handle not collected yet)
@@ -210,7 +218,12 @@ class Scheduler:
             if need <= budget and slots > 0:
                 budget -= need
                 slots -= 1
-                self.prefilling.append(_Pending(req))
+                try:
+                    cached = int(self.executor.begin(req.request_id, req.prompt_tokens))
+                except Exception as e:
+                    events.append(Event(req.request_id, "error", reason=f"{type(e).__name__}: {e}"))
+                    continue
+                self.prefilling.append(_Pending(req, done=min(max(cached, 0), n - 1)))
             else:
                 still.append(req)
         self.deferred = still

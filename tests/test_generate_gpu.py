@@ -141,3 +141,32 @@ def test_no_cpu_path(folders):
     from openinfer_b200.kernels import KernelError
     with pytest.raises(KernelError, match="no CPU path"):
         ModelRunner.from_folder(folders["A"], device="cpu", max_tokens=64)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_cache_gives_the_same_tokens_and_is_used(folders, dtype):
+    """Requests whose prompts share a front reuse its pages (registered when the first of them was computed);
+    the generated ids are those of an engine without the prefix cache, and every page comes back."""
+    from openinfer_b200 import LLM
+    cfg, _ = plain.read_model_folder(folders["B"])
+    rng = random.Random(9)
+    stem = random_tokens(rng, 50, cfg["vocab_size"])
+    prompts = [stem + random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 7, 20)] + [stem[:33], stem, random_tokens(rng, 9, cfg["vocab_size"])]
+    outs = []
+    for on in (False, True):
+        llm = LLM(folders["B"], dtype=dtype, max_cache_tokens=2048, max_prefill_tokens=24, kv_page_size=16, prefix_cache=on)
+        first = llm.generate(prompts[:1], max_tokens=6)            # computes and registers the stem's three full pages
+        rest = llm.generate(prompts[1:], max_tokens=6)             # five more requests at once
+        again = llm.generate(prompts[:1], max_tokens=6)
+        outs.append((first, rest, again))
+        hits = llm.runner.cache.prefix_hits
+        # stem + n shares 48 tokens; stem[:33] 32; stem itself 48; the unrelated prompt none; the repeat 48
+        assert hits == ((48 + 48 + 32 + 48 + 0 + 48) if on else 0), hits
+        assert llm.runner.cache.min_free_pages() == llm.runner.cache.num_pages and not llm.has_work()
+        llm.runner.cache.check()
+    if dtype == "float32":
+        assert outs[0] == outs[1]
+    else:
+        same = sum(a == b for a, b in zip(sum(outs[0], []), sum(outs[1], [])))
+        assert same >= len(sum(outs[0], [])) - 1       # bfloat16: a near-tie may fall the other way
+    assert outs[1][0] == outs[1][2]

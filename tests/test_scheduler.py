@@ -301,3 +301,21 @@ def test_one_step_ahead_is_refused_without_an_executor_for_it():
     with pytest.raises(ValueError):
         sched(FakeExecutor(), lookahead=True)
     assert not sched(AheadExecutor(), lookahead=False).lookahead
+
+
+def test_portions_start_behind_what_the_executor_already_has():
+    """An executor with a prefix cache answers `begin` with the tokens it already holds."""
+    class Prefixed(FakeExecutor):
+        def begin(self, rid, prompt):
+            n = 8 if list(prompt[:8]) == list(range(8)) else 0
+            self.tokens[rid] = n
+            return n
+
+    ex = Prefixed()
+    s = sched(ex, max_prefill_tokens=5)
+    s.submit(Request("a", list(range(12)), max_tokens=2))     # 8 cached: portions of 4 tokens in all
+    s.submit(Request("b", [9, 9, 9], max_tokens=1))
+    toks, fin = collect(s.run())
+    assert ex.batches[0][0] == [("a", 4, True), ("b", 1, False)]
+    assert toks["a"] == [12, 13] and fin["a"] == ("finished", "length") and toks["b"] == [10]
+    assert ex.used() == 0
