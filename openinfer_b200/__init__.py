@@ -15,6 +15,7 @@ _LAZY = {
     "LLM": ("openinfer_b200.engine.engine", "LLM"),
     "generate": ("openinfer_b200.engine.engine", "generate"),
     "SamplingParams": ("openinfer_b200.sampling.params", "SamplingParams"),
+    "TokenLogprob": ("openinfer_b200.sampling.params", "TokenLogprob"),
     "ModelRunner": ("openinfer_b200.engine.runner", "ModelRunner"),
     "StepEntry": ("openinfer_b200.engine.runner", "StepEntry"),
     "load_config": ("openinfer_b200.config.base", "load_config"),

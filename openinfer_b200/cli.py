@@ -60,6 +60,8 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--min-p", type=float, default=0.0)
     gen.add_argument("--sampling-seed", type=int, default=None, help="per-request sampling seed")
     gen.add_argument("--ignore-eos", action="store_true")
+    gen.add_argument("--logprobs", type=int, default=0, help="report each token's log-probability and this many top ones")
+    gen.add_argument("--echo", action="store_true", help="with --logprobs: also the prompt tokens' log-probabilities")
     return ap
 
 
@@ -106,6 +108,14 @@ def main(argv: Optional[List[str]] = None) -> int:
               prefix_cache=not args.no_prefix_cache)
     sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
                         seed=args.sampling_seed, ignore_eos=args.ignore_eos)
-    for i, r in enumerate(llm.generate_detailed(prompts, sp, args.max_tokens)):
-        print(json.dumps({"prompt": i, "token_ids": r.token_ids, "finish_reason": r.finish_reason}), flush=True)
+    def lp(entry):
+        return None if entry is None else {"logprob": entry.logprob, "top_logprobs": entry.top_logprobs}
+
+    for i, r in enumerate(llm.generate_detailed(prompts, sp, args.max_tokens, logprobs=args.logprobs, echo=args.echo)):
+        line = {"prompt": i, "token_ids": r.token_ids, "finish_reason": r.finish_reason}
+        if r.logprobs is not None:
+            line["logprobs"] = [lp(e) for e in r.logprobs]
+        if r.prompt_logprobs is not None:
+            line["prompt_logprobs"] = [lp(e) for e in r.prompt_logprobs]
+        print(json.dumps(line), flush=True)
     return 0

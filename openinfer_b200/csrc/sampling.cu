@@ -429,6 +429,73 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   if (tid == 0) out[r] = picked;
 }
 
+// Log-probabilities for requests that ask for them: for each listed row of the logits, the log-softmax
+// value of the picked token and the `k` largest entries (id and log-probability, in descending order of
+// the raw logits, ties to the lowest id, so that rounding of the subtraction cannot change the order).
+// The log-sum-exp is accumulated in double precision (a 150k-wide sum loses digits in float32). As the
+// reference's host routine (pegainfer-sample/src/lib.rs:305-358), on the device.
+constexpr int kLogprobThreads = 512;
+
+__global__ void __launch_bounds__(kLogprobThreads)
+token_logprob_kernel(const float* __restrict__ logits, long long row_stride, int vocab, const int* __restrict__ rows,
+                     const int* __restrict__ picked, const int* __restrict__ ks, int k_max, float* __restrict__ out_lp,
+                     float* __restrict__ top_vals, int* __restrict__ top_ids) {
+  pdl_start();
+  __shared__ float red[32];
+  __shared__ double redd[32];
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)rows[r] * row_stride;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float mx = -INFINITY;
+  for (int i = tid; i < vocab; i += kLogprobThreads) mx = fmaxf(mx, row[i]);
+  mx = block_max(mx, red);
+  double sum = 0.0;
+  for (int i = tid; i < vocab; i += kLogprobThreads) sum += (double)expf(row[i] - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) redd[warp] = sum;
+  __syncthreads();
+  sum = 0.0;
+  for (int w = 0; w < kLogprobThreads / 32; ++w) sum += redd[w];
+  const float lse = mx + (float)log(sum);
+  if (tid == 0) {
+    int pk = picked[r];
+    pk = pk < 0 ? 0 : (pk >= vocab ? vocab - 1 : pk);
+    out_lp[r] = row[pk] - lse;
+  }
+  int k = ks[r];
+  k = k < k_max ? k : k_max;
+  k = k < vocab ? k : vocab;
+  ArgPair last{INFINITY, -1};     // everything comes after this in the order (value descending, id ascending)
+  for (int j = 0; j < k; ++j) {
+    ArgPair best{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < vocab; i += kLogprobThreads) {
+      const float v = row[i];
+      if (v == v && (v < last.v || (v == last.v && i > last.i))) best = better(best, ArgPair{v, i});
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = better(best, other);
+    }
+    __syncthreads();
+    if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+    __syncthreads();
+    ArgPair b{sv[0], si[0]};
+    for (int w = 1; w < kLogprobThreads / 32; ++w) b = better(b, ArgPair{sv[w], si[w]});
+    if (tid == 0) {
+      const bool found = b.i != 0x7fffffff;
+      top_ids[(size_t)r * k_max + j] = found ? b.i : -1;
+      top_vals[(size_t)r * k_max + j] = found ? b.v - lse : -INFINITY;
+    }
+    last = b;
+  }
+  if (tid == 0)
+    for (int j = k; j < k_max; ++j) { top_ids[(size_t)r * k_max + j] = -1; top_vals[(size_t)r * k_max + j] = -INFINITY; }
+}
+
 }  // namespace
 
 // Number of float/int pairs of scratch per row that oi_argmax wants for this vocabulary.
@@ -464,6 +531,20 @@ OI_API int oi_sample(int* out, const float* logits, long long row_stride, float*
   if (rows == 0) return OI_OK;
   oi_launch(sample_kernel, rows, kSampleThreads, 0, (cudaStream_t)stream, out, logits, row_stride, probs, vocab, temperature,
                                                          top_k, top_p, min_p, uniform);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// For n listed rows of float32 logits: out_lp[i] = log-softmax of token picked[i] (ids on the device: they
+// may come straight from the sampler), and the ks[i] <= k_max largest entries of the row into
+// top_ids / top_vals [n, k_max] (unused places: -1 / -inf).
+OI_API int oi_token_logprobs(const float* logits, long long row_stride, int vocab, const int* rows, const int* picked,
+                             const int* ks, int n, int k_max, float* out_lp, float* top_vals, int* top_ids, void* stream) {
+  OI_REQUIRE(n >= 0 && vocab > 0 && row_stride >= vocab && k_max >= 0, "token_logprobs: bad sizes");
+  OI_REQUIRE(k_max == 0 || (top_vals && top_ids), "token_logprobs: outputs missing");
+  if (n == 0) return OI_OK;
+  oi_launch(token_logprob_kernel, n, kLogprobThreads, 0, (cudaStream_t)stream, logits, row_stride, vocab, rows, picked, ks,
+            k_max, out_lp, top_vals, top_ids);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

@@ -14,7 +14,8 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 import torch
 
 from ..config.base import ModelConfig, load_config
-from ..sampling.params import SamplingParams
+from ..kernels import ops
+from ..sampling.params import SamplingParams, TokenLogprob
 from ..sampling.sampler import Sampler
 from .runner import ModelRunner, StepEntry
 from .scheduler import (DEFAULT_ENGINE_SEED, DEFAULT_MAX_DECODE_BATCH, DEFAULT_MAX_PREFILL_TOKENS, DecodeItem,
@@ -33,6 +34,7 @@ class RunnerExecutor(Executor):
         self.page_size = runner.cache.page_size
         self.total_pages = runner.cache.num_pages
         self.sampler = Sampler(runner.spec.vocab_size, runner.device)
+        self.last_logprobs: Dict[Hashable, dict] = {}
 
     def free_pages(self) -> int:
         return self.runner.cache.min_free_pages()
@@ -43,12 +45,27 @@ class RunnerExecutor(Executor):
         return self.collect(self.launch(prefill, decode, step_seed))
 
     def launch(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int, previous=None):
-        """Start one batch on the GPU. Returns (request ids of the sampled rows, their pending tokens)."""
+        """Start one batch on the GPU. Returns (request ids of the sampled rows, their pending tokens,
+        request id -> place among the sampled rows, pending log-probabilities or None)."""
         entries, rows = [], []
+        sample_at: List[int] = []       # which row of the returned logits each sampled row is
+        echo: List[tuple] = []          # (request id, first prompt position, first logits row, targets, top-k)
+        at = 0                          # logits rows so far
         for p in prefill:
-            entries.append(StepEntry(p.request_id, p.tokens, [len(p.tokens) - 1] if p.is_last else []))
-            if p.is_last:
-                rows.append(p)
+            n = len(p.tokens)
+            if p.targets is not None:   # prompt log-probabilities: the logits of every position of the portion
+                entries.append(StepEntry(p.request_id, p.tokens, list(range(n))))
+                echo.append((p.request_id, p.first_position, at, list(p.targets), p.logprobs))
+                if p.is_last:
+                    sample_at.append(at + n - 1)
+                    rows.append(p)
+                at += n
+            else:
+                entries.append(StepEntry(p.request_id, p.tokens, [n - 1] if p.is_last else []))
+                if p.is_last:
+                    sample_at.append(at)
+                    rows.append(p)
+                    at += 1
         feed = None
         for d in decode:
             if d.token is None:
@@ -59,19 +76,59 @@ class RunnerExecutor(Executor):
                 entries.append(StepEntry(d.request_id, [0], [0], token_from=previous[2][d.request_id]))
             else:
                 entries.append(StepEntry(d.request_id, [d.token], [0]))
+            sample_at.append(at)
             rows.append(d)
+            at += 1
         logits = self.runner.step(entries, device_tokens=feed)
         ids = [r.request_id for r in rows]
-        if not rows:
-            return ids, None, {}
-        pending = self.sampler.select_async(logits, [r.sampling for r in rows], [r.step_index for r in rows], step_seed)
-        return ids, pending, {rid: i for i, rid in enumerate(ids)}
+        pending = None
+        if rows:
+            picked_rows = logits if sample_at == list(range(logits.shape[0])) else \
+                logits[torch.tensor(sample_at, device=logits.device)]
+            pending = self.sampler.select_async(picked_rows, [r.sampling for r in rows], [r.step_index for r in rows], step_seed)
+        lp = self._launch_logprobs(logits, rows, sample_at, pending, echo)
+        return ids, pending, {rid: i for i, rid in enumerate(ids)}, lp
+
+    def _launch_logprobs(self, logits, rows, sample_at, pending, echo):
+        """One kernel for every log-probability the batch's requests asked for: of the drawn tokens (ids still
+        on the device) and, for echo, of the prompt's tokens. Returns what collect() needs, or None."""
+        want_tok = [(i, r) for i, r in enumerate(rows) if r.logprobs > 0]
+        if not want_tok and not echo:
+            return None
+        dev = logits.device
+        lrows = [sample_at[i] for i, _ in want_tok]
+        ks = [r.logprobs for _, r in want_tok]
+        picked = pending.device[torch.tensor([i for i, _ in want_tok], device=dev)].to(torch.int32) if want_tok else \
+            torch.empty(0, dtype=torch.int32, device=dev)
+        spans = []
+        for rid, first_pos, row0, targets, k in echo:
+            spans.append((rid, first_pos, len(lrows), len(targets)))
+            lrows.extend(range(row0, row0 + len(targets)))
+            ks.extend([k] * len(targets))
+            picked = torch.cat([picked, torch.tensor(targets, dtype=torch.int32, device=dev)])
+        k_max = max(ks) if ks else 0
+        lpv, vals, tids = ops.token_logprobs(logits, torch.tensor(lrows, dtype=torch.int32, device=dev), picked,
+                                             torch.tensor(ks, dtype=torch.int32, device=dev), k_max)
+        return [r.request_id for _, r in want_tok], spans, ks, lpv, vals, tids
 
     def collect(self, handle) -> Dict[Hashable, int]:
-        ids, pending, _ = handle
-        if pending is None:
-            return {}
-        return dict(zip(ids, pending.result()))
+        ids, pending, _, lp = handle
+        self.last_logprobs = {}
+        tokens = dict(zip(ids, pending.result())) if pending is not None else {}
+        if lp is not None:
+            tok_ids, spans, ks, lpv, vals, tids = lp
+            lpv, vals, tids = lpv.cpu().tolist(), vals.cpu().tolist(), tids.cpu().tolist()
+
+            def entry(i):
+                return TokenLogprob(lpv[i], [(tids[i][j], vals[i][j]) for j in range(ks[i]) if tids[i][j] >= 0])
+
+            for i, rid in enumerate(tok_ids):
+                self.last_logprobs.setdefault(rid, {})["token"] = entry(i)
+            for rid, first_pos, at, n in spans:
+                got = [entry(at + j) for j in range(n)]
+                # position 0 of the prompt has nothing in front of it
+                self.last_logprobs.setdefault(rid, {})["prompt"] = ([None] if first_pos == 0 else []) + got
+        return tokens
 
     def drop(self, request_id: Hashable) -> None:
         self.runner.end(request_id)
@@ -85,6 +142,8 @@ class GenerationResult:
     request_id: Hashable
     token_ids: List[int]
     finish_reason: str   # "stop" | "length" | "rejected:<why>" | "error:<message>"
+    logprobs: Optional[List[Optional[TokenLogprob]]] = None          # one per generated token, when asked for
+    prompt_logprobs: Optional[List[Optional[TokenLogprob]]] = None   # one per prompt token (None for the first), with echo
 
 
 class LLM:
@@ -141,10 +200,11 @@ class LLM:
 
     # ---- step-wise use: submit requests, then call step() until has_work() is false
     def submit(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None,
-               max_tokens: int = 16) -> Hashable:
+               max_tokens: int = 16, logprobs: int = 0, echo: bool = False) -> Hashable:
         rid = self._next_id
         self._next_id += 1
-        self.scheduler.submit(Request(rid, list(prompt_token_ids), int(max_tokens), sampling_params or SamplingParams()))
+        self.scheduler.submit(Request(rid, list(prompt_token_ids), int(max_tokens), sampling_params or SamplingParams(),
+                                      int(logprobs), bool(echo)))
         return rid
 
     def step(self) -> List[Event]:
@@ -158,7 +218,11 @@ class LLM:
 
     def generate_detailed(self, prompt_token_ids: Sequence[Sequence[int]],
                           sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
-                          max_tokens: Union[int, Sequence[int]] = 16) -> List[GenerationResult]:
+                          max_tokens: Union[int, Sequence[int]] = 16, logprobs: int = 0,
+                          echo: bool = False) -> List[GenerationResult]:
+        """``logprobs`` = k > 0: every generated token comes with its log-probability and the k most likely
+        tokens' (raw logits, no temperature); with ``echo`` also the prompt's tokens (the reference's request
+        options of the same names, pegainfer-frontend/src/engine.rs:67-95)."""
         n = len(prompt_token_ids)
         if sampling_params is None:
             sampling_params = SamplingParams()
@@ -171,14 +235,21 @@ class LLM:
             rid = self._next_id
             self._next_id += 1
             ids.append(rid)
-            self.scheduler.submit(Request(rid, list(prompt_token_ids[i]), int(mt[i]), sp[i]))
-        out: Dict[Hashable, GenerationResult] = {rid: GenerationResult(rid, [], "") for rid in ids}
+            self.scheduler.submit(Request(rid, list(prompt_token_ids[i]), int(mt[i]), sp[i], int(logprobs), bool(echo)))
+        out: Dict[Hashable, GenerationResult] = {
+            rid: GenerationResult(rid, [], "", [] if logprobs > 0 else None, [] if (logprobs > 0 and echo) else None)
+            for rid in ids}
         for ev in self.scheduler.run():
             r = out.get(ev.request_id)
             if r is None:
                 continue
             if ev.kind == "token":
                 r.token_ids.append(ev.token)
+                if r.logprobs is not None:
+                    r.logprobs.append(ev.logprob)
+            elif ev.kind == "prompt_logprobs":
+                if r.prompt_logprobs is not None:
+                    r.prompt_logprobs.extend(ev.prompt_logprobs)
             elif ev.kind == "finished":
                 r.finish_reason = ev.reason
             elif ev.kind in ("rejected", "error"):

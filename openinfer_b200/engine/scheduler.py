@@ -42,7 +42,7 @@ import dataclasses
 import random
 from typing import Dict, Hashable, List, Optional, Sequence
 
-from ..sampling.params import SamplingParams
+from ..sampling.params import SamplingParams, TokenLogprob
 
 DEFAULT_MAX_PREFILL_TOKENS = 1024   # scheduler.rs:1170
 DEFAULT_MAX_DECODE_BATCH = 256      # batch_decode_buffers.rs:25-28
@@ -55,16 +55,21 @@ class Request:
     prompt_tokens: Sequence[int]
     max_tokens: int = 16
     sampling: SamplingParams = SamplingParams()
+    logprobs: int = 0      # how many top log-probabilities to report beside each token's own (0: none)
+    echo: bool = False     # with logprobs > 0: also the log-probabilities of the prompt's tokens
 
 
 @dataclasses.dataclass
 class Event:
-    """What the scheduler reports: kind is "token", "finished", "rejected" or "error"."""
+    """What the scheduler reports: kind is "token", "finished", "rejected", "error" or "prompt_logprobs"."""
 
     request_id: Hashable
     kind: str
     token: Optional[int] = None
     reason: str = ""   # finished: "stop" | "length"; rejected: "context_length" | "kv_budget" | "empty_prompt"; error: message
+    logprob: Optional[TokenLogprob] = None              # with kind "token", when the request asked for logprobs
+    prompt_logprobs: Optional[List[Optional[TokenLogprob]]] = None   # with kind "prompt_logprobs": one per prompt
+                                                                      # position of a portion (None: the very first)
 
 
 @dataclasses.dataclass
@@ -74,6 +79,11 @@ class PrefillItem:
     is_last: bool             # the portion ends the prompt: its last row is sampled
     sampling: SamplingParams = SamplingParams()
     step_index: int = 0       # request-local count of tokens drawn so far
+    logprobs: int = 0
+    # echo with logprobs: the prompt token that follows each token of the portion (one fewer than tokens on
+    # the last portion, whose last row is sampled); None otherwise
+    targets: Optional[Sequence[int]] = None
+    first_position: int = 0   # position of tokens[0] in the prompt
 
 
 @dataclasses.dataclass
@@ -82,6 +92,7 @@ class DecodeItem:
     token: Optional[int]      # the last generated token, fed back; None: the one the batch in flight draws for it
     sampling: SamplingParams = SamplingParams()
     step_index: int = 0
+    logprobs: int = 0
 
 
 class Executor:
@@ -116,6 +127,10 @@ class Executor:
 
     def collect(self, handle) -> Dict[Hashable, int]:
         raise NotImplementedError
+
+    # After execute() / collect(): what the batch's requests asked for beside tokens.
+    # request id -> {"token": TokenLogprob, "prompt": [TokenLogprob or None, ...]} (either may be missing)
+    last_logprobs: Dict[Hashable, dict] = {}
 
 
 @dataclasses.dataclass
@@ -219,7 +234,8 @@ class Scheduler:
                 budget -= need
                 slots -= 1
                 try:
-                    cached = int(self.executor.begin(req.request_id, req.prompt_tokens))
+                    # prompt log-probabilities need the logits of every prompt position: nothing is taken from a prefix cache
+                    cached = 0 if (req.echo and req.logprobs > 0) else int(self.executor.begin(req.request_id, req.prompt_tokens))
                 except Exception as e:
                     events.append(Event(req.request_id, "error", reason=f"{type(e).__name__}: {e}"))
                     continue
@@ -242,6 +258,15 @@ class Scheduler:
             taken.append(self.prefilling.pop(i))
         return taken
 
+    def _prefill_item(self, p: "_Pending") -> PrefillItem:
+        req = p.req
+        lo, hi = p.done, p.done + p.step_chunk
+        targets = None
+        if req.echo and req.logprobs > 0:
+            targets = req.prompt_tokens[lo + 1: hi + 1]      # the last portion has one target fewer than tokens
+        return PrefillItem(req.request_id, req.prompt_tokens[lo:hi], is_last=hi == len(req.prompt_tokens),
+                           sampling=req.sampling, step_index=0, logprobs=req.logprobs, targets=targets, first_position=lo)
+
     # ------------------------------------------------------------------ one iteration
     def step(self) -> List[Event]:
         """Admit, build one batch, run it, resolve. Returns this iteration's events."""
@@ -252,12 +277,8 @@ class Scheduler:
         decoding = list(self.active)
         if not taken and not decoding:
             return events
-        prefill_items = [
-            PrefillItem(p.req.request_id, p.req.prompt_tokens[p.done: p.done + p.step_chunk],
-                        is_last=p.done + p.step_chunk == len(p.req.prompt_tokens),
-                        sampling=p.req.sampling, step_index=0)
-            for p in taken]
-        decode_items = [DecodeItem(a.req.request_id, a.last_token, a.req.sampling, len(a.generated))
+        prefill_items = [self._prefill_item(p) for p in taken]
+        decode_items = [DecodeItem(a.req.request_id, a.last_token, a.req.sampling, len(a.generated), a.req.logprobs)
                         for a in decoding]
         step_seed = self.rng.getrandbits(64)
         self.steps += 1
@@ -273,9 +294,11 @@ class Scheduler:
             self.active = []
             return events
 
+        extra = getattr(self.executor, "last_logprobs", None) or {}
+        self._report_prompt_logprobs(extra, events)
         # decode rows first (they are older), then the requests whose prompt just ended
         for a in decoding:
-            self._resolve(a, tokens[a.req.request_id], events)
+            self._resolve(a, tokens[a.req.request_id], events, extra.get(a.req.request_id, {}).get("token"))
         unfinished: List[_Pending] = []
         for p in taken:
             p.done += p.step_chunk
@@ -284,7 +307,7 @@ class Scheduler:
                 continue
             a = _Active(p.req, [], -1)
             self.active.append(a)
-            self._resolve(a, tokens[p.req.request_id], events)
+            self._resolve(a, tokens[p.req.request_id], events, extra.get(p.req.request_id, {}).get("token"))
         self.prefilling = unfinished + self.prefilling  # back to the front (effects.rs:318-406)
         return events
 
@@ -300,10 +323,12 @@ class Scheduler:
             except Exception as e:
                 self._fail(previous.rows, e, events)
                 tokens = None
+            extra = (getattr(self.executor, "last_logprobs", None) or {}) if tokens is not None else {}
+            self._report_prompt_logprobs(extra, events)
             for a in previous.rows:
                 a.inflight -= 1
                 if tokens is not None and not a.ended:   # ended meanwhile (a stop token one step earlier): the row is void
-                    self._resolve(a, tokens[a.req.request_id], events)
+                    self._resolve(a, tokens[a.req.request_id], events, extra.get(a.req.request_id, {}).get("token"))
         if failed is not None:   # the launch failed: everyone it touched fails, after what was in flight has arrived
             e, taken, decoding = failed
             for p in taken:
@@ -319,13 +344,9 @@ class Scheduler:
         decoding = [a for a in self.active if len(a.generated) + a.inflight < max(1, a.req.max_tokens)]
         if not taken and not decoding:
             return None, None
-        prefill_items = [
-            PrefillItem(p.req.request_id, p.req.prompt_tokens[p.done: p.done + p.step_chunk],
-                        is_last=p.done + p.step_chunk == len(p.req.prompt_tokens),
-                        sampling=p.req.sampling, step_index=0)
-            for p in taken]
+        prefill_items = [self._prefill_item(p) for p in taken]
         decode_items = [DecodeItem(a.req.request_id, a.last_token if a.inflight == 0 else None, a.req.sampling,
-                                   len(a.generated) + a.inflight) for a in decoding]
+                                   len(a.generated) + a.inflight, a.req.logprobs) for a in decoding]
         step_seed = self.rng.getrandbits(64)
         self.steps += 1
         try:
@@ -357,14 +378,20 @@ class Scheduler:
             self.executor.drop(a.req.request_id)
         self.active = [x for x in self.active if not x.ended]
 
-    def _resolve(self, a: _Active, token: int, events: List[Event]) -> None:
+    @staticmethod
+    def _report_prompt_logprobs(extra: Dict[Hashable, dict], events: List[Event]) -> None:
+        for rid, what in extra.items():
+            if what.get("prompt") is not None:
+                events.append(Event(rid, "prompt_logprobs", prompt_logprobs=what["prompt"]))
+
+    def _resolve(self, a: _Active, token: int, events: List[Event], logprob: Optional[TokenLogprob] = None) -> None:
         req = a.req
         if token in self.stop_token_ids and not req.sampling.ignore_eos:
             self._finish(a, events, "stop")
             return
         a.generated.append(token)
         a.last_token = token
-        events.append(Event(req.request_id, "token", token=token))
+        events.append(Event(req.request_id, "token", token=token, logprob=logprob))
         if len(a.generated) >= max(1, req.max_tokens):
             self._finish(a, events, "length")
 

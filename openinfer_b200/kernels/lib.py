@@ -32,6 +32,7 @@ _SIGNATURES = {
     "oi_attention_generic": [P, I, P, I, I, P, P, L, I, P, I, P, P, I, I, I, I, F, I, P],
     "oi_gemm_generic": [P, I, P, I, P, I, I, I, I, L, L, L, P],
     "oi_argmax": [P, P, I, I, L, P, P, P],
+    "oi_token_logprobs": [P, L, I, P, P, P, I, I, P, P, P, P],
     "oi_sample": [P, P, L, P, I, I, P, P, P, P, P, P],
     "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05": [P, I, L, P, L, P, L, I, I, I, I, I, P],

@@ -234,6 +234,26 @@ def argmax(out: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def token_logprobs(logits: torch.Tensor, rows: torch.Tensor, picked: torch.Tensor, ks: torch.Tensor, k_max: int):
+    """For the listed rows of float32 ``logits``: (log-softmax of ``picked[i]``, the ``ks[i]`` largest
+    log-probabilities [n, k_max], their ids [n, k_max]; unused places -inf / -1). All index tensors int32
+    on the device."""
+    _cuda(logits, rows, picked, ks)
+    for t, what in ((rows, "rows"), (picked, "picked"), (ks, "ks")):
+        _i32(t, f"token_logprobs {what}")
+    n = rows.numel()
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or picked.numel() != n or ks.numel() != n:
+        raise KernelError("token_logprobs: logits must be float32 rows; rows, picked and ks of one length")
+    lp = torch.empty(n, dtype=torch.float32, device=logits.device)
+    vals = torch.empty((n, max(k_max, 1)), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((n, max(k_max, 1)), dtype=torch.int32, device=logits.device)
+    L = _lib.load()
+    _lib.check(L.oi_token_logprobs(logits.data_ptr(), logits.stride(0), logits.shape[1], rows.data_ptr(), picked.data_ptr(),
+                                   ks.data_ptr(), n, int(k_max), lp.data_ptr(), vals.data_ptr(), ids.data_ptr(), _stream()),
+               "token_logprobs")
+    return lp, vals[:, :k_max], ids[:, :k_max]
+
+
 def sample(out: torch.Tensor, logits: torch.Tensor, probs_scratch: torch.Tensor, temperature: torch.Tensor,
            top_k: torch.Tensor, top_p: torch.Tensor, min_p: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
     """One token per row from softmax(logits / temperature) after top-k, top-p and min-p,

@@ -1,4 +1,4 @@
 """Sampling: parameters and the batched selector."""
-from .params import SamplingParams, mix_seed, uniform_from
+from .params import SamplingParams, TokenLogprob, mix_seed, uniform_from
 
-__all__ = ["SamplingParams", "mix_seed", "uniform_from"]
+__all__ = ["SamplingParams", "TokenLogprob", "mix_seed", "uniform_from"]

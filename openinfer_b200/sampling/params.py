@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
-from typing import Optional
+from typing import List, Optional, Tuple
 
 GREEDY_TEMPERATURE = 1e-5  # below this the temperature -> 0 limit (argmax) is taken
 
@@ -34,6 +34,15 @@ class SamplingParams:
         """Also greedy when top_p <= 1/vocab: only the argmax is in the nucleus
         (pegainfer-sample/src/lib.rs:297-303)."""
         return self.is_greedy() or (vocab_size > 0 and self.top_p <= 1.0 / vocab_size)
+
+
+@dataclasses.dataclass
+class TokenLogprob:
+    """log-softmax (of the raw logits, no temperature) of a token, and the request's top-k
+    (id, log-probability) pairs in descending order (pegainfer-frontend/src/engine.rs:55-58)."""
+
+    logprob: float
+    top_logprobs: List[Tuple[int, float]] = dataclasses.field(default_factory=list)
 
 
 def mix_seed(seed: int, step: int) -> int:

@@ -170,3 +170,35 @@ def test_prefix_cache_gives_the_same_tokens_and_is_used(folders, dtype):
         same = sum(a == b for a, b in zip(sum(outs[0], []), sum(outs[1], [])))
         assert same >= len(sum(outs[0], [])) - 1       # bfloat16: a near-tie may fall the other way
     assert outs[1][0] == outs[1][2]
+
+
+@pytest.mark.parametrize("lookahead", [True, False])
+def test_logprobs_and_echo(folders, lookahead):
+    """The request options `logprobs` and `echo` of the reference: each generated token with its log-probability
+    and the k most likely tokens, and with echo the same for the prompt's tokens, portions and decoding mixed."""
+    from openinfer_b200 import LLM
+    cfg, w = plain.read_model_folder(folders["A"])
+    rng = random.Random(3)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (9, 30, 4)]
+    llm = LLM(folders["A"], dtype="float32", max_cache_tokens=1024, max_prefill_tokens=7, kv_page_size=8, lookahead=lookahead)
+    res = llm.generate_detailed(prompts, max_tokens=5, logprobs=3, echo=True)
+    plain_tokens = llm.generate(prompts, max_tokens=5)
+    for p, r, toks in zip(prompts, res, plain_tokens):
+        assert r.token_ids == toks and r.finish_reason == "length"
+        full = torch.log_softmax(plain.forward_logits(cfg, w, p + r.token_ids).double(), dim=-1)
+        assert len(r.logprobs) == 5 and len(r.prompt_logprobs) == len(p) and r.prompt_logprobs[0] is None
+        for t in range(1, len(p)):          # the prompt: token t under the distribution after t - 1
+            e = r.prompt_logprobs[t]
+            assert abs(e.logprob - float(full[t - 1, p[t]])) < 1e-3
+            assert [i for i, _ in e.top_logprobs] == torch.topk(full[t - 1], 3).indices.tolist()
+        for j, e in enumerate(r.logprobs):  # generated token j under the distribution after what precedes it
+            at = len(p) - 1 + j
+            assert abs(e.logprob - float(full[at, r.token_ids[j]])) < 1e-3
+            assert e.top_logprobs[0][0] == r.token_ids[j]        # greedy: the drawn token is the most likely one
+            assert all(abs(v - float(full[at, i])) < 1e-3 for i, v in e.top_logprobs)
+    # without echo only the generated tokens carry log-probabilities; without logprobs nothing does
+    r = llm.generate_detailed(prompts[:1], max_tokens=3, logprobs=2)[0]
+    assert r.prompt_logprobs is None and len(r.logprobs) == 3 and len(r.logprobs[0].top_logprobs) == 2
+    r = llm.generate_detailed(prompts[:1], max_tokens=3)[0]
+    assert r.logprobs is None and r.prompt_logprobs is None
+    assert llm.runner.cache.min_free_pages() == llm.runner.cache.num_pages

@@ -803,3 +803,28 @@ def test_copy_words_between_pinned_host_memory_and_the_device():
     assert torch.equal(back, want)
     with pytest.raises(Exception):
         ops.copy_words(dev, torch.zeros(n, dtype=torch.int32), n)      # pageable host memory is refused
+
+
+@pytest.mark.parametrize("vocab", [37, 5000, 151936])
+def test_token_logprobs(vocab):
+    """log-softmax of a picked token and the k most likely ones, ties to the lowest id
+    (pegainfer-sample/src/lib.rs:305-358), for rows listed out of a larger logits tensor."""
+    from openinfer_b200.kernels import ops
+    torch.manual_seed(vocab)
+    logits = torch.randn(6, vocab) * 3
+    logits[2, 5] = logits[2, 11] = logits[2].max() + 1.0        # a tie at the top: id 5 comes first
+    logits[4] = 0.25                                             # all equal: ids 0, 1, 2, ...
+    rows = [4, 0, 2, 2, 5]
+    picked = [3, 7, 11, 0, vocab - 1]
+    ks = [4, 0, 3, 1, 5]
+    lp, vals, ids = ops.token_logprobs(logits.to(DEV), torch.tensor(rows, dtype=torch.int32, device=DEV),
+                                       torch.tensor(picked, dtype=torch.int32, device=DEV),
+                                       torch.tensor(ks, dtype=torch.int32, device=DEV), 5)
+    lp, vals, ids = lp.cpu(), vals.cpu(), ids.cpu()
+    ref = torch.log_softmax(logits.double(), dim=-1)
+    for i, (r, p, k) in enumerate(zip(rows, picked, ks)):
+        assert abs(float(lp[i]) - float(ref[r, p])) < 2e-4
+        order = sorted(range(vocab), key=lambda j: (-float(logits[r, j]), j))[:k]
+        assert ids[i, :k].tolist() == order, f"row {r}: top-{k} ids"
+        assert torch.allclose(vals[i, :k].double(), ref[r, order], atol=2e-4)
+        assert (ids[i, k:] == -1).all() and bool(torch.isinf(vals[i, k:]).all())
