@@ -125,6 +125,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--model", default="8b", choices=sorted(MODELS), help="layer sizes (default: the headline 8B)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points and the prefill")
+    ap.add_argument("--batch-invariant", action="store_true",
+                    help="measure under the batch-invariant numeric policy (one product kernel, fixed key slices)")
     ap.add_argument("--timeline", default=None, metavar="FILE",
                     help="write the start and end of every kernel of one decode step (CUPTI through torch.profiler: kernels "
                          "overlap under programmatic dependent launch, which a serialising profiler cannot show) and exit")
@@ -153,6 +155,9 @@ def main() -> int:
     from openinfer_b200.kernels import ops
     from openinfer_b200.sampling.params import SamplingParams
 
+    if args.batch_invariant:
+        from openinfer_b200.kernels import policy
+        policy.set_batch_invariant(True)
     peaks, peaks_src = read_peaks()
     model_name, model_cfg = MODELS[args.model]
     cfg_dict = dict(model_cfg)
@@ -321,6 +326,8 @@ def main() -> int:
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
     }
+    if args.batch_invariant:
+        out["config"]["batch_invariant"] = True
 
     if not args.skip_points:
         points = {}

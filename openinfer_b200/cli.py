@@ -47,6 +47,8 @@ def build_parser() -> argparse.ArgumentParser:
                      help="memory left free beside the cache pool")
     eng.add_argument("--kv-page-size", type=int, default=16, help="tokens per cache page")
     eng.add_argument("--num-pages", type=int, default=None, help="size the cache pool explicitly (pages)")
+    eng.add_argument("--batch-invariant", action="store_true",
+                     help="a request's results do not depend, bit for bit, on what it is batched with (slower)")
     eng.add_argument("--no-prefix-cache", action="store_true",
                      help="do not share registered prompt pages between requests")
     gen = ap.add_argument_group("generation")
@@ -105,7 +107,7 @@ def main(argv: Optional[List[str]] = None) -> int:
               gpu_memory_utilization=args.gpu_memory_utilization,
               kv_cache_memory_margin_mib=args.kv_cache_memory_margin_mib,
               max_prefill_tokens=args.max_prefill_tokens, cuda_graph=args.cuda_graph,
-              prefix_cache=not args.no_prefix_cache)
+              prefix_cache=not args.no_prefix_cache, batch_invariant=True if args.batch_invariant else None)
     sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
                         seed=args.sampling_seed, ignore_eos=args.ignore_eos)
     def lp(entry):

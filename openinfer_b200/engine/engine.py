@@ -163,7 +163,11 @@ class LLM:
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
                  cuda_graph: bool = True, lookahead: bool = True, prefix_cache: bool = True,
-                 runner: Optional[ModelRunner] = None) -> None:
+                 batch_invariant: Optional[bool] = None, runner: Optional[ModelRunner] = None) -> None:
+        from ..kernels import policy
+        if batch_invariant is not None:
+            policy.set_batch_invariant(batch_invariant)   # process-wide: which kernels take which step shapes
+        batch_invariant = policy.batch_invariant()
         device = f"cuda:{device_ordinal}"
         weights_seed = None
         if runner is not None:
@@ -195,7 +199,7 @@ class LLM:
         self.scheduler = Scheduler(
             self.executor, max_context_tokens=max_context, stop_token_ids=self.runner.spec.stop_token_ids,
             max_prefill_tokens=max_prefill_tokens, max_decode_batch=max_decode_batch, seed=engine_seed,
-            lookahead=lookahead)
+            lookahead=lookahead, batch_invariant=batch_invariant)
         self._next_id = 0
 
     # ---- step-wise use: submit requests, then call step() until has_work() is false

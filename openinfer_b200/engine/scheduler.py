@@ -169,7 +169,7 @@ class Scheduler:
     def __init__(self, executor: Executor, *, max_context_tokens: int, stop_token_ids: Sequence[int] = (),
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, seed: int = DEFAULT_ENGINE_SEED,
-                 lookahead: Optional[bool] = None) -> None:
+                 lookahead: Optional[bool] = None, batch_invariant: bool = False) -> None:
         if max_prefill_tokens <= 0 or max_decode_batch <= 0:
             raise ValueError("max_prefill_tokens and max_decode_batch must be positive")
         self.executor = executor
@@ -179,6 +179,10 @@ class Scheduler:
         self.max_prefill_tokens = max_prefill_tokens
         self.max_decode_batch = max_decode_batch
         self.rng = random.Random(seed)
+        # request-local portions (the reference's --batch-invariant, scheduler.rs:137-179): a request takes
+        # min(what is left of its prompt, max_prefill_tokens) whole or waits, so where its prompt is cut
+        # depends on its own length only
+        self.batch_invariant = bool(batch_invariant)
         self.deferred: List[Request] = []
         self.prefilling: List[_Pending] = []
         self.active: List[_Active] = []
@@ -252,7 +256,14 @@ class Scheduler:
         i = 0
         while i < len(self.prefilling) and budget > 0:
             p = self.prefilling[i]
-            chunk = min(len(p.req.prompt_tokens) - p.done, budget)
+            left = len(p.req.prompt_tokens) - p.done
+            if self.batch_invariant:
+                chunk = min(left, self.max_prefill_tokens)
+                if chunk > budget:      # whole or not at all: a later, shorter request may still fit
+                    i += 1
+                    continue
+            else:
+                chunk = min(left, budget)
             p.step_chunk = chunk
             budget -= chunk
             taken.append(self.prefilling.pop(i))

@@ -49,6 +49,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p  # noqa: E402
 import numpy as np  # noqa: E402
 
 from . import lib as _lib  # noqa: E402
+from . import policy  # noqa: E402
 
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 
@@ -111,6 +112,8 @@ class AttentionPlan:
 def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int]) -> int:
     """Slices per decode row: as many as fill the GPU once (two CTAs of four slices per SM), a
     multiple of four, each at least 32 keys long when the lengths are known."""
+    if policy.batch_invariant():
+        return policy.INVARIANT_DECODE_SPLITS      # the same cutting whatever else is in the step
     pairs = max(1, num_rows * nkv)
     ns = DECODE_WARPS * max(1, (DECODE_CTAS_PER_SM * sm_count) // pairs)
     ns = min(ns, DECODE_MAX_SPLITS)
@@ -121,6 +124,8 @@ def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[i
 
 def tile_rows(q_lens, group: int, decode_kernel: bool = True) -> int:
     """Query rows per tile: 128 when some prompt portion fills such a tile, else 64."""
+    if policy.batch_invariant():
+        return ROWS_PER_CTA_LARGE
     big = [n for n in q_lens if not (decode_kernel and n == 1 and group <= DECODE_MAX_GROUP)]
     if group <= ROWS_PER_CTA and any(n * group >= ROWS_PER_CTA_LARGE for n in big):
         return ROWS_PER_CTA_LARGE
@@ -163,7 +168,7 @@ def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_
             row_splits[starts[b]] = ns
             decode_items.extend((b, 0, s0, ns) for s0 in range(0, ns, DECODE_WARPS))
     want = 1
-    if tiles and not decode_reqs and len(tiles) * nkv < 2 * sm_count:
+    if tiles and not decode_reqs and len(tiles) * nkv < 2 * sm_count and not policy.batch_invariant():
         want = min(MAX_SPLITS, -(-2 * sm_count // (len(tiles) * nkv)))
     tile_items = []
     tile_split = False
@@ -191,7 +196,7 @@ def plan_items_static_decode(num_requests: int, group: int, nkv: int, sm_count: 
                            dtype=np.int32).reshape(-1, 4)
         return empty, items, np.full(num_requests, ns, dtype=np.int32), ns, False
     ns = 1
-    if num_requests * nkv < 2 * sm_count:
+    if num_requests * nkv < 2 * sm_count and not policy.batch_invariant():
         ns = min(MAX_SPLITS, -(-2 * sm_count // (num_requests * nkv)))
     items = np.asarray([(b, 0, s, ns) for b in range(num_requests) for s in range(ns)], dtype=np.int32).reshape(-1, 4)
     return items, empty, np.full(num_requests, ns, dtype=np.int32), ns, ns > 1
@@ -202,7 +207,7 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
     plan = ctx.scratch.get(key)
     if plan is None:
         if getattr(ctx, "static_decode", False):
-            rows = ROWS_PER_CTA if group <= ROWS_PER_CTA else ROWS_PER_CTA_LARGE
+            rows = ROWS_PER_CTA if (group <= ROWS_PER_CTA and not policy.batch_invariant()) else ROWS_PER_CTA_LARGE
             t_items, d_items, row_splits, max_splits, tile_split = plan_items_static_decode(
                 ctx.num_requests, group, nkv, _sm_count(device))
         else:
@@ -249,6 +254,8 @@ def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd:
     """Whether this step's attention is the decode kernel alone (every request brings one token) and
     that kernel can take the norm, rotation and cache write into itself."""
     if not FUSE_ROPE_IN_DECODE or cos is None or qkv.dtype != torch.bfloat16 or hd not in (32, 64, 128):
+        return False
+    if policy.batch_invariant():
         return False
     if nq // nkv > DECODE_MAX_GROUP or qkv.stride(0) % 2 or page_stride % 8 or qkv.data_ptr() % 4:
         return False

@@ -18,8 +18,9 @@ from typing import Callable, Optional
 
 import torch
 
+from . import gemm_tcgen05 as _tc
 from . import lib as _lib
-from . import ops
+from . import ops, policy
 
 # which hand-written kernel takes the decode products: "stream" (tcgen05), "skinny" (mma.sync), "library"
 DECODE_GEMM = _os.environ.get("OI_DECODE_GEMM", "stream")
@@ -96,6 +97,8 @@ def gate_up_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch
     does not take the operands. ``w_gate_up`` [2 I, K]: blocks of 64 gate rows followed by the 64 up
     rows of the same indices."""
     M = x.shape[0]
+    if policy.batch_invariant():
+        return None
     if (DECODE_GEMM != "stream" or not 0 < M <= DECODE_MAX_ROWS or x.dtype != torch.bfloat16
             or w_gate_up.dtype != torch.bfloat16):
         return None
@@ -167,6 +170,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if M == 0:
         return out
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        if policy.batch_invariant():
+            # one kernel for every step shape: a row's sums are formed in the same order whatever else is in the step
+            if not _tc.takes(out, x, w):
+                raise ops.KernelError("linear: batch-invariant products need 16-byte aligned bfloat16 operands with K % 8 == 0")
+            _tc.gemm(out, x, w, 256)
+            return out
         if _bf16_gemm is not None and _bf16_gemm(out, x, w):
             return out
         if M <= DECODE_MAX_ROWS:

@@ -1,0 +1,29 @@
+"""Numeric policy: whether a request's results may depend, at rounding level, on what else is in the batch.
+
+By default the kernels are chosen for speed by the shape of the whole step: the streaming product up to
+32 rows and the library beyond, more or fewer key slices per decode row depending on how many rows there
+are, tiles of 64 or 128 query rows, the rotation inside or in front of the attention kernel. Every choice
+computes the same thing in float32 but may round differently, so a request's logits agree between batches
+only "beyond rounding".
+
+With ``set_batch_invariant(True)`` (the reference's ``--batch-invariant``, pegainfer-qwen3/src/lib.rs:419-443:
+request-local prompt portions, pinned product algorithm, request-local key slices) every choice depends on
+the request alone: all bfloat16 products go through ONE kernel (gemm_tcgen05: a row's dot products are formed
+in the same order whatever else is in the step), decode rows always get 16 key slices, prompt tiles are
+never cut and always hold 128 query rows, the rotation kernel always runs on its own. Together with
+request-local portions in the scheduler a request's logits are then the same BIT FOR BIT whatever it is batched
+with. It costs speed, mostly in decode (the product kernel is built for prompt-sized steps).
+"""
+from __future__ import annotations
+
+_BATCH_INVARIANT = False
+INVARIANT_DECODE_SPLITS = 16
+
+
+def set_batch_invariant(on: bool) -> None:
+    global _BATCH_INVARIANT
+    _BATCH_INVARIANT = bool(on)
+
+
+def batch_invariant() -> bool:
+    return _BATCH_INVARIANT

@@ -10,7 +10,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import gemm_tcgen05
+from ..kernels import gemm_tcgen05, policy
 from ..kernels.linear import gate_up_silu_mul, linear, linear_silu_mul
 
 # rows from which the gate/up product with the activation in its epilogue is used (prompt portions)
@@ -53,7 +53,7 @@ class GatedMlp(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         inter = self.spec.intermediate_size
         if self.block == gemm_tcgen05.ACT_BLOCK and x.dtype == torch.bfloat16:
-            if x.shape[0] >= FUSED_MIN_ROWS and inter % (2 * gemm_tcgen05.ACT_BLOCK) == 0:
+            if (x.shape[0] >= FUSED_MIN_ROWS or policy.batch_invariant()) and inter % (2 * gemm_tcgen05.ACT_BLOCK) == 0:
                 act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
                 if gemm_tcgen05.takes(act, x, self.w_gate_up):
                     gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up)

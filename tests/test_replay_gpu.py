@@ -146,3 +146,59 @@ def test_without_programmatic_dependent_launch(folders, workloads):
         for k in a:
             assert torch.equal(torch.as_tensor(a[k]), torch.as_tensor(b[k])), f"step {k} differs without the attribute (graphs {graphs})"
     _check(outs[(1, True)], ref, "bfloat16", "with dependent launches")
+
+
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_batch_invariant_mode_is_bitwise(folders, workloads, name):
+    """With the batch-invariant numeric policy a request's logits are the same BIT FOR BIT whether it runs
+    alone or beside others (prompt portions of its own fixed size, then single tokens), in bfloat16, with
+    recorded graphs for the decode steps; and they still agree with the plain implementation."""
+    from openinfer_b200.engine.runner import StepEntry
+    from openinfer_b200.kernels import policy
+    cfg, reqs, ref = workloads[name]          # C: head 64 (mma.sync tiles); E: head 128 (tcgen05 tiles, fused gate/up)
+    C = 16 if name == "C" else 96            # request-local portion size
+    tail = 6                                 # tokens at the end of every request that are fed one by one
+    reqs = {r: t for r, t in reqs.items() if len(t) > tail}
+    ids = list(reqs)[:4]
+
+    def schedule(group):
+        """Steps for the requests of `group` running together: request-local portions, then single tokens."""
+        at = {r: 0 for r in group}
+        steps = []
+        while any(at[r] < len(reqs[r]) for r in group):
+            entries = []
+            for r in group:
+                n = len(reqs[r])
+                if at[r] >= n:
+                    continue
+                take = min(C, n - tail - at[r]) if at[r] < n - tail else 1
+                entries.append((r, reqs[r][at[r]: at[r] + take]))
+                at[r] += take
+            steps.append(entries)
+        return steps
+
+    def run(group):
+        runner = _runner(folders[name], "bfloat16", sum(round64(len(reqs[r])) for r in group) + 64, page_size=16, cuda_graph=True)
+        rows = {r: [] for r in group}
+        for entries in schedule(group):
+            logits = runner.step([StepEntry(r, toks, list(range(len(toks)))) for r, toks in entries])
+            at = 0
+            for r, toks in entries:
+                rows[r].append(logits[at: at + len(toks)].float().cpu())
+                at += len(toks)
+        for r in group:
+            runner.end(r)
+        return {r: torch.cat(v) for r, v in rows.items()}
+
+    policy.set_batch_invariant(True)
+    try:
+        together = run(ids)
+        alone = {r: run([r])[r] for r in ids}
+        pair = run(ids[1:3])
+    finally:
+        policy.set_batch_invariant(False)
+    for r in ids:
+        assert torch.equal(together[r], alone[r]), f"request {r}: logits differ between running alone and with three others"
+    for r in ids[1:3]:
+        assert torch.equal(pair[r], alone[r]), f"request {r}: logits differ in a batch of two"
+    _check({r: together[r] for r in ids}, {r: ref[r] for r in ids}, "bfloat16", "batch-invariant policy")

@@ -319,3 +319,25 @@ def test_portions_start_behind_what_the_executor_already_has():
     assert ex.batches[0][0] == [("a", 4, True), ("b", 1, False)]
     assert toks["a"] == [12, 13] and fin["a"] == ("finished", "length") and toks["b"] == [10]
     assert ex.used() == 0
+
+
+def test_request_local_portions_take_whole_or_wait():
+    """With batch_invariant a request takes min(left, max_prefill_tokens) whole or not at all, so where its
+    prompt is cut depends on its own length only (and a later, shorter request may pass a waiting one)."""
+    def cuts(batch_invariant, others):
+        ex = FakeExecutor(total_pages=200)
+        s = sched(ex, max_prefill_tokens=8, batch_invariant=batch_invariant)
+        if others:
+            s.submit(Request("x", list(range(5)), max_tokens=1))
+        s.submit(Request("a", list(range(20)), max_tokens=1))
+        if others:
+            s.submit(Request("y", list(range(3)), max_tokens=1))
+        s.run()
+        return [n for pre, _ in ex.batches for rid, n, _ in pre if rid == "a"], ex.batches
+
+    alone, _ = cuts(True, False)
+    with_others, batches = cuts(True, True)
+    assert alone == with_others == [8, 8, 4]
+    # step 0: x takes 5, a's 8 do not fit and wait, y's 3 fit behind
+    assert batches[0][0] == [("x", 5, True), ("y", 3, True)]
+    assert cuts(False, True)[0] != alone          # the default fills the budget: a is cut by what x left over
