@@ -283,7 +283,7 @@ def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nk
     if rope is not None and (plan.num_tile_items or not plan.num_decode_items):
         return False
     L = _lib.load()
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = _lib.current_stream()
     bt = group_step.block_table
     po = 0 if plan.part_o is None else plan.part_o.data_ptr()
     pl = 0 if plan.part_lse is None else plan.part_lse.data_ptr()

@@ -33,7 +33,7 @@ def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256)
     L = _lib.load()
     _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                  x.stride(0), w.data_ptr(), w.stride(0), M, N, K, tile_n, 0,
-                                 torch.cuda.current_stream().cuda_stream), "gemm_tcgen05")
+                                 _lib.current_stream()), "gemm_tcgen05")
     return out
 
 
@@ -47,7 +47,7 @@ def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor) -
         raise KernelError(f"gemm_silu_mul: operands not accepted: x={tuple(x.shape)} w={tuple(w_gate_up.shape)} out={tuple(out.shape)}")
     L = _lib.load()
     _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w_gate_up.data_ptr(),
-                                 w_gate_up.stride(0), M, N, K, 256, 1, torch.cuda.current_stream().cuda_stream),
+                                 w_gate_up.stride(0), M, N, K, 256, 1, _lib.current_stream()),
                "gemm_tcgen05 (fused activation)")
     return out
 

@@ -105,6 +105,20 @@ def _declare_optional(lib) -> None:
 # number of entry-point calls that launched work (read by the benchmark)
 launches = 0
 
+try:    # the raw handle of the current stream without building a Stream object (about ten times faster)
+    from torch._C import _cuda_getCurrentRawStream as _raw_stream
+    from torch._C import _cuda_getDevice as _raw_device
+except Exception:   # pragma: no cover - a torch without the private entry points
+    _raw_stream = _raw_device = None
+
+
+def current_stream() -> int:
+    """The CUDA stream handle that torch's current stream of the current device stands for."""
+    if _raw_stream is not None:
+        return _raw_stream(_raw_device())
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
 
 def check(code: int, what: str) -> None:
     global launches

@@ -88,7 +88,7 @@ def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool 
     L = _lib.load()
     _lib.check(L.oi_gemm_stream(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c, 1 if silu_mul else 0,
-                                torch.cuda.current_stream().cuda_stream), "gemm_stream")
+                                _lib.current_stream()), "gemm_stream")
     return True
 
 
@@ -140,7 +140,7 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) 
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                 x.stride(0), w.data_ptr(), w.stride(0), M, N, K, int(silu_mul), c,
-                                torch.cuda.current_stream().cuda_stream), "gemm_skinny")
+                                _lib.current_stream()), "gemm_skinny")
     return True
 
 

@@ -36,7 +36,7 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _lib.current_stream()
 
 
 def _i32(t: Optional[torch.Tensor], what: str) -> None:
