@@ -828,3 +828,11 @@ def test_token_logprobs(vocab):
         assert ids[i, :k].tolist() == order, f"row {r}: top-{k} ids"
         assert torch.allclose(vals[i, :k].double(), ref[r, order], atol=2e-4)
         assert (ids[i, k:] == -1).all() and bool(torch.isinf(vals[i, k:]).all())
+
+
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (4, 1, 64)])
+def test_attention_mma_long_contexts(nq, nkv, hd):
+    """Thousands of keys: a 1,500-token portion over a 1,500-token prefix (many query tiles, up to 47 key tiles
+    each, block-table rounds of the TMA producer), and decode rows at 5,000 and 3,001 keys (32 key slices)."""
+    plan = _mma_case(nq, nkv, hd, 16, None, [1500, 1, 1, 300], [3000, 5000, 3001, 300], seed=3)
+    assert plan.num_tile_items and plan.num_decode_items
