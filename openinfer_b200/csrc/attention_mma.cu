@@ -385,8 +385,15 @@ attention_mma_kernel(const AttnParams p) {
 // Decode rows (one query token per request): every WARP owns one slice of a request's keys for
 // one kv head, with a private ring of 16-key K/V tiles in shared memory filled by cp.async. No
 // block-wide barrier: a warp waits only for its own copies, so several tiles per warp are in
-// flight all the time, which is what a bandwidth-bound gather over pages needs. Each warp writes
-// a normalised partial output and its log-sum-exp; attention_merge_kernel combines the slices.
+// flight all the time, which is what a bandwidth-bound gather over pages needs. Each warp ends with
+// a normalised partial output and its log-sum-exp. The CTAs of a row (up to 8: 32 slices) run as a
+// thread-block cluster and merge the slices themselves through distributed shared memory (partials
+// deposited with the merging CTA behind one cluster barrier, or read from each other's shared memory
+// when the receive buffer would not fit); with more slices the partials go to scratch in global
+// memory and attention_merge_kernel combines them. The tiles of earlier steps' keys are requested
+// before the kernel waits for its predecessor on the stream (programmatic dependent launch), and on
+// request the kernel also does the per-head q/k norm, the rotation and the write of the step's key
+// and value (fuse_rope), which otherwise take a kernel of their own in front of it.
 // ---------------------------------------------------------------------------
 constexpr int kDecWarps = 4;
 constexpr int kDecKeys = 16;     // keys per tile

@@ -37,7 +37,7 @@ TINY_D = dict(
     tie_word_embeddings=False, max_position_embeddings=1024)
 # Real head geometry at reduced depth and vocabulary: head 128 with a group of 2, an intermediate size
 # that is a multiple of 128: the shapes the tcgen05 kernels (products, fused gate/up, prompt attention),
-# the skinny decode products and the split decode attention take in the engine.
+# the streaming decode products and the split decode attention take in the engine.
 TINY_E = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3",
     num_hidden_layers=2, hidden_size=512, num_attention_heads=8, num_key_value_heads=4, head_dim=128,
