@@ -202,3 +202,46 @@ def test_batch_invariant_mode_is_bitwise(folders, workloads, name):
     for r in ids[1:3]:
         assert torch.equal(pair[r], alone[r]), f"request {r}: logits differ in a batch of two"
     _check({r: together[r] for r in ids}, {r: ref[r] for r in ids}, "bfloat16", "batch-invariant policy")
+
+
+def test_real_layer_sizes_bfloat16_against_float32():
+    """Qwen3-8B layer sizes (hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary 151936) with two
+    layers and random weights: the bfloat16 engine (streaming products with clusters of 4 and 8, gate/up with
+    the activation, decode attention with rotation and merge inside, recorded graphs) against the float32
+    engine on the same weights, prompts in portions and then tokens one by one, three requests."""
+    from openinfer_b200.config.base import resolve_architecture
+    from openinfer_b200.engine.runner import ModelRunner, StepEntry
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=4096,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
+               rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+    config = resolve_architecture(cfg).config_cls.from_dict(cfg)
+    rng = random.Random(1)
+    prompts = {r: [rng.randrange(151936) for _ in range(n)] for r, n in (("a", 150), ("b", 37), ("c", 260))}
+    outs = {}
+    feed = {}
+    for dtype in ("float32", "bfloat16"):
+        runner = ModelRunner.build(config, 7, dtype=dtype, device="cuda:0", page_size=16, max_tokens=1024, max_requests=8)
+        runner.cuda_graph = dtype == "bfloat16"
+        rows = {r: [] for r in prompts}
+        # the prompts in two portions each, together; then 6 tokens one by one (the float32 run's argmax is fed to both)
+        for part in range(2):
+            entries = []
+            for r, p in prompts.items():
+                cut = len(p) // 2
+                toks = p[:cut] if part == 0 else p[cut:]
+                entries.append(StepEntry(r, toks, [len(toks) - 1]))
+            logits = runner.step(entries)
+            for i, r in enumerate(prompts):
+                rows[r].append(logits[i].float().cpu())
+        for step in range(6):
+            if dtype == "float32":
+                feed[step] = {r: int(rows[r][-1].argmax()) for r in prompts}
+            logits = runner.step([StepEntry(r, [feed[step][r]], [0]) for r in prompts])
+            for i, r in enumerate(prompts):
+                rows[r].append(logits[i].float().cpu())
+        outs[dtype] = {r: torch.stack(v) for r, v in rows.items()}
+        if dtype == "bfloat16":
+            assert runner._graphs, "the single-token steps did not go through a graph"
+        del runner
+        torch.cuda.empty_cache()
+    _check(outs["bfloat16"], outs["float32"], "bfloat16", "real layer sizes")
