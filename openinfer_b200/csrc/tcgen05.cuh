@@ -107,6 +107,85 @@ __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::aft
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 
+// ---- a pair of CTAs (a cluster of two) working as one tensor-core unit (cta_group::2) ----------
+// The CTA with the even rank issues the products for both; each CTA holds its half of the rows of A
+// and of B in its own shared memory and its half of the accumulator's rows in its own tensor memory.
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+// the address, in the cluster's shared window, of the same location in the CTA of rank `rank`
+__device__ __forceinline__ unsigned map_to_rank(unsigned smem_addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// arrival on a barrier anywhere in the cluster (address from map_to_rank)
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// mbar_wait for a barrier that threads of the other CTA arrive on
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_word, int code) {
+  unsigned long long t0 = 0;
+  for (unsigned i = 0;; ++i) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((i & 255u) == 255u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(error_word, 0, code);
+  return false;
+}
+// A tile load into this CTA's shared memory whose bytes are counted on a barrier that may lie in the
+// pair's other CTA (`bar_cluster` from map_to_rank). The data goes to this CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster) : "memory");
+}
+// Tensor memory of both CTAs at once: the same warp of each CTA executes these, with the same arguments.
+__device__ __forceinline__ void tmem_alloc_pair(unsigned dst_smem, unsigned cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned taddr, unsigned cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+// One product of the pair: M (256) rows of A and N rows of B split in halves over the two CTAs, the
+// descriptors naming the same shared-memory offsets in both. Issued by one thread of the even CTA.
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_c, unsigned long long desc_a, unsigned long long desc_b,
+                                               unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// One arrival on the barrier at this offset in every CTA of `cta_mask` when the pair's products
+// issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(unsigned bar, unsigned short cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+      ::"r"(bar), "h"(cta_mask) : "memory");
+}
+
 // 16 consecutive float32 columns of this thread's lane of tensor memory
 __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
   asm volatile(

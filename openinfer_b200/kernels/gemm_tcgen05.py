@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_longlong, c_void_p
 
 import torch
@@ -22,8 +23,26 @@ def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+PAIR = 0          # tile_n value that selects 256 x 256 tiles computed by pairs of CTAs (cta_group::2)
+PAIR_MIN_ROWS = 129   # from this many rows the pair's 256-row tiles are used for prompt portions
+# Which kernel takes the plain projections of prompt portions: "library" or "pair" (this file's).
+# Measured on B200 at 2,048 rows (us, library / pair / one CTA per tile): QKV 6144 x 4096: 72 / 76 / 84;
+# O 4096 x 4096: 49 / 51 / 51; down 4096 x 12288: 136 / 148 / 165; gate|up 24576 x 4096: 279 / 285 / 313
+# (and 285 includes the activation, which costs the library path a further 32 us kernel). The pair's
+# main loop runs at about 89 % of the library's rate per SM: its stage of 32 KB per 512 tensor-core
+# cycles keeps the shared memory busy with 64 + 64 bytes per cycle, where the library's 256 x 256 tile
+# per CTA needs 48 + 48.
+PREFILL_GEMM = os.environ.get("OI_PREFILL_GEMM", "library")
+
+
+def portion_tile(rows: int) -> int:
+    """The tile a prompt portion of ``rows`` tokens is computed with."""
+    return PAIR if rows >= PAIR_MIN_ROWS else 256
+
+
 def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
-    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (float32 accumulation in TMEM)."""
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (float32 accumulation in TMEM).
+    ``tile_n``: 256 or 128 columns per 128-row tile of one CTA, or ``PAIR``."""
     if not (x.is_cuda and w.is_cuda and out.is_cuda):
         raise KernelError("gemm_tcgen05: operands must be on a CUDA device; this package has no CPU path")
     M, K = x.shape
@@ -31,13 +50,23 @@ def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256)
     if w.shape[1] != K or out.shape != (M, N) or not takes(out, x, w):
         raise KernelError(f"gemm_tcgen05: operands not accepted: x={tuple(x.shape)} w={tuple(w.shape)} out={tuple(out.shape)}")
     L = _lib.load()
+    if tile_n == PAIR:
+        return _pair(L, out, x, w, 0)
     _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
                                  x.stride(0), w.data_ptr(), w.stride(0), M, N, K, tile_n, 0,
                                  _lib.current_stream()), "gemm_tcgen05")
     return out
 
 
-def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def _pair(L, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) -> torch.Tensor:
+    M, K = x.shape
+    _lib.check(L.oi_gemm_tcgen05_pair(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
+                                      x.stride(0), w.data_ptr(), w.stride(0), M, w.shape[0], K, silu_mul,
+                                      _lib.current_stream()), "gemm_tcgen05_pair")
+    return out
+
+
+def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
     """out[M, I] = silu(x Wg^T) * (x Wu^T) in one kernel. ``w_gate_up`` is [2 I, K] with rows in blocks
     of 64 gate rows followed by the 64 up rows of the same indices (I a multiple of 128: a tile of the
     kernel holds two such pairs)."""
@@ -46,8 +75,10 @@ def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor) -
     if N % (2 * ACT_BLOCK) or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or not takes(out, x, w_gate_up):
         raise KernelError(f"gemm_silu_mul: operands not accepted: x={tuple(x.shape)} w={tuple(w_gate_up.shape)} out={tuple(out.shape)}")
     L = _lib.load()
+    if tile_n == PAIR:
+        return _pair(L, out, x, w_gate_up, 1)
     _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w_gate_up.data_ptr(),
-                                 w_gate_up.stride(0), M, N, K, 256, 1, _lib.current_stream()),
+                                 w_gate_up.stride(0), M, N, K, tile_n, 1, _lib.current_stream()),
                "gemm_tcgen05 (fused activation)")
     return out
 

@@ -36,6 +36,7 @@ _SIGNATURES = {
     "oi_sample": [P, P, L, P, I, I, P, P, P, P, P, P],
     "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05": [P, I, L, P, L, P, L, I, I, I, I, I, P],
+    "oi_gemm_tcgen05_pair": [P, I, L, P, L, P, L, I, I, I, I, P],
     "oi_gemm_tcgen05_status": [ctypes.POINTER(c_int)],
     "oi_gemm_stream": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_set_pdl": [I],

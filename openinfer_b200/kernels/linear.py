@@ -183,6 +183,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
                 return out
             if DECODE_GEMM in ("stream", "skinny") and _skinny(out, x, w, 0):
                 return out
+        if M >= _tc.PAIR_MIN_ROWS and _tc.PREFILL_GEMM == "pair" and _tc.takes(out, x, w):
+            _tc.gemm(out, x, w, _tc.PAIR)
+            return out
         if out_dtype == torch.bfloat16:
             torch.mm(x, w.t(), out=out)
         else:

@@ -562,11 +562,13 @@ def test_gemm_skinny_with_fused_activation(M, N, K):
     assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
 
 
-@pytest.mark.parametrize("tile_n", [256, 128])
+@pytest.mark.parametrize("tile_n", [256, 128, 0])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 4096), (300, 520, 1000), (2048, 1024, 512),
-                                   (17, 100, 72), (129, 257, 8)])
+                                   (17, 100, 72), (129, 257, 8), (2048, 5120, 192), (600, 1100, 2048), (2048, 2560, 1536)])
 def test_gemm_tcgen05(M, N, K, tile_n):
-    """The tcgen05 / TMEM / TMA product against float64: whole tiles, ragged edges in M, N and K."""
+    """The tcgen05 / TMEM / TMA product against float64: whole tiles, ragged edges in M, N and K; tiles of
+    one CTA (tile_n columns) and 256 x 256 tiles of a pair of CTAs (0). (2048, 5120, 192) and (2048, 2560, 1536)
+    give every pair of CTAs more than one tile, so both accumulators and every stage are used again."""
     from openinfer_b200.kernels import gemm_tcgen05 as g
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -587,8 +589,9 @@ def test_gemm_tcgen05(M, N, K, tile_n):
     assert (out.double() - big[:, :K].double() @ w.double().t()).abs().max().item() <= 1e-4 * scale
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 384, 200), (2048, 1024, 512)])
-def test_gemm_tcgen05_with_activation_in_the_epilogue(M, I, K):
+@pytest.mark.parametrize("tile_n", [256, 0])
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 384, 200), (2048, 1024, 512), (520, 640, 2048), (2048, 1280, 1536)])
+def test_gemm_tcgen05_with_activation_in_the_epilogue(M, I, K, tile_n):
     """silu(x Wg^T) * (x Wu^T) from one kernel, gate and up rows interleaved in blocks of 64."""
     from openinfer_b200.kernels import gemm_tcgen05 as g
     torch.manual_seed(M + I)
@@ -598,7 +601,7 @@ def test_gemm_tcgen05_with_activation_in_the_epilogue(M, I, K):
     nb = I // g.ACT_BLOCK
     w = torch.stack([wg.view(nb, g.ACT_BLOCK, K), wu.view(nb, g.ACT_BLOCK, K)], dim=1).reshape(2 * I, K).contiguous()
     out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
-    g.gemm_silu_mul(out, x, w)
+    g.gemm_silu_mul(out, x, w, tile_n)
     assert g.status() == 0
     gg, uu = x.double() @ wg.double().t(), x.double() @ wu.double().t()
     ref = gg / (1 + torch.exp(-gg)) * uu
