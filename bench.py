@@ -115,12 +115,14 @@ class ClockSampler:
 
 
 def main() -> int:
+    global CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--model", default="8b", choices=sorted(MODELS), help="layer sizes (default: the headline 8B)")
@@ -134,6 +136,7 @@ def main() -> int:
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
     args = ap.parse_args()
+    CONTEXT = args.context
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -164,10 +167,16 @@ def main() -> int:
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
+    cfg_dict["max_position_embeddings"] = max(cfg_dict["max_position_embeddings"],
+                                              CONTEXT + args.steps + args.warmup + max(args.batch, 8) * -(-CONTEXT // PREFILL_TOKENS) + 128)
     config = resolve_architecture(cfg_dict).config_cls.from_dict(cfg_dict)
     K, W, B = args.steps, args.warmup, args.batch
     max_batch = B if args.skip_points else max(B, 64)
-    per_req = CONTEXT + K + W + max(B, 8) + 16 + 2 * PAGE
+    # Through the entry point the requests' prompts are computed one portion a step, and a request that has its
+    # prompt decodes while the others' are still computed: it must not finish before all of them decode.
+    e2e_prompt_steps = max(B, 8) * -(-CONTEXT // PREFILL_TOKENS)
+    e2e_new_tokens = W + K + e2e_prompt_steps + 8
+    per_req = CONTEXT + e2e_new_tokens + 16 + 2 * PAGE
     pool_tokens = max_batch * per_req + PREFILL_TOKENS + 64
     dev = torch.device("cuda:0")
     runner = ModelRunner.build(config, 0, dtype=args.dtype, device=dev, page_size=PAGE,
@@ -288,11 +297,17 @@ def main() -> int:
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks_src}
 
     # end to end through the Python entry point: host token ids in and out every step
-    llm = LLM(config=config, runner=runner, max_prefill_tokens=2048, max_decode_batch=max_batch)
+    llm = LLM(config=config, runner=runner, max_prefill_tokens=PREFILL_TOKENS, max_decode_batch=max_batch)
     for i in range(B):
-        llm.submit([rng.randrange(vocab) for _ in range(CONTEXT)], SamplingParams(ignore_eos=True), W + K + B + 8)
-    while len(llm.scheduler.active) < B:
-        llm.step()
+        llm.submit([rng.randrange(vocab) for _ in range(CONTEXT)], SamplingParams(ignore_eos=True), e2e_new_tokens)
+    for _ in range(e2e_prompt_steps + 8):
+        if len(llm.scheduler.active) == B:
+            break
+        for ev in llm.step():
+            if ev.kind in ("error", "rejected"):
+                raise RuntimeError(f"bench: request {ev.request_id} {ev.kind}: {ev.reason}")
+    if len(llm.scheduler.active) != B:
+        raise RuntimeError(f"bench: only {len(llm.scheduler.active)} of {B} requests decode after their prompts")
     for _ in range(W):
         llm.step()
     torch.cuda.synchronize()
@@ -310,7 +325,7 @@ def main() -> int:
     e2e["h2d_bytes_per_step"] = int(runner._staging_last_bytes) if hasattr(runner, "_staging_last_bytes") else None
 
     out = {
-        "metric": f"decode tokens/s ({model_name}, random weights, batch {B}, context 2048)",
+        "metric": f"decode tokens/s ({model_name}, random weights, batch {B}, context {CONTEXT})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic (random weights, uniform random token ids)",
