@@ -202,3 +202,52 @@ def test_logprobs_and_echo(folders, lookahead):
     r = llm.generate_detailed(prompts[:1], max_tokens=3)[0]
     assert r.logprobs is None and r.prompt_logprobs is None
     assert llm.runner.cache.min_free_pages() == llm.runner.cache.num_pages
+
+
+@pytest.mark.parametrize("lookahead", [True, False])
+def test_many_requests_arriving_over_time_with_few_pages(folders, lookahead):
+    """Thirty requests of random lengths (some sharing a front, so the prefix cache lends pages) arrive while
+    others run, in a pool that holds about five of them: requests wait for pages, pages are used again many
+    times, prompts are cut into portions beside decoded tokens. In float32 every request gets the tokens it
+    gets alone in a fresh engine, a third of them are also checked against the plain implementation, and
+    in the end every page is back."""
+    from openinfer_b200 import LLM
+    cfg, w = plain.read_model_folder(folders["B"])
+    rng = random.Random(31 + int(lookahead))
+    stem = random_tokens(rng, 40, cfg["vocab_size"])
+    reqs = []
+    for i in range(30):
+        body = random_tokens(rng, rng.choice([1, 2, 5, 17, 30, 63, 90]), cfg["vocab_size"])
+        prompt = (stem[: rng.choice([16, 32, 40])] + body) if i % 3 == 0 else body
+        reqs.append((prompt, rng.randint(1, 20)))
+    llm = LLM(folders["B"], dtype="float32", max_cache_tokens=640, max_prefill_tokens=24, max_decode_batch=6,
+              kv_page_size=16, lookahead=lookahead, prefix_cache=True)
+    got = {}
+    reasons = {}
+    ids = []
+    waiting = list(reqs)
+    steps = 0
+    while waiting or llm.has_work():
+        for _ in range(rng.randint(0, 3)):          # zero to three arrivals before every step
+            if waiting:
+                prompt, n_new = waiting.pop(0)
+                ids.append(llm.submit(prompt, max_tokens=n_new))
+        for ev in llm.step():
+            assert ev.kind in ("token", "finished"), (ev.kind, ev.reason)
+            if ev.kind == "token":
+                got.setdefault(ev.request_id, []).append(ev.token)
+            else:
+                reasons[ev.request_id] = ev.reason
+        steps += 1
+        assert steps < 5000
+    assert len(ids) == 30 and set(reasons) == set(ids)
+    cache = llm.runner.cache
+    cache.check()
+    assert cache.min_free_pages() == cache.num_pages
+    assert cache.prefix_hits > 0
+    solo = LLM(folders["B"], dtype="float32", max_cache_tokens=640, prefix_cache=False, runner=None)
+    for k, (rid, (prompt, n_new)) in enumerate(zip(ids, reqs)):
+        assert len(got[rid]) == n_new and reasons[rid] == "length"
+        assert got[rid] == solo.generate([prompt], max_tokens=n_new)[0], f"request {k}"
+        if k % 3 == 1:
+            assert got[rid] == plain.greedy_generate(cfg, w, prompt, n_new), f"request {k} against the plain implementation"
