@@ -245,3 +245,27 @@ def test_real_layer_sizes_bfloat16_against_float32():
         del runner
         torch.cuda.empty_cache()
     _check(outs["bfloat16"], outs["float32"], "bfloat16", "real layer sizes")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd,nq,nkv,hidden", [(48, 4, 2, 80), (80, 6, 3, 144), (96, 2, 1, 176), (112, 5, 5, 208),
+                                               (144, 3, 1, 96), (256, 2, 2, 112)])
+def test_head_sizes_in_steps_of_16(tmp_path, dtype, hd, nq, nkv, hidden):
+    """Head sizes that no tuned kernel covers (48 ... 256), with widths that are no power of two and groups of
+    1, 2, 3: the engine takes them through its general kernels. Two requests, mixed with so few pages that they
+    are used again, against the plain implementation."""
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=hidden,
+               num_attention_heads=nq, num_key_value_heads=nkv, head_dim=hd, intermediate_size=hidden + 40,
+               vocab_size=257, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=bool(hd % 32),
+               max_position_embeddings=512)
+    folder = make_model_folder(str(tmp_path / "m"), cfg, hd)
+    pcfg, w = plain.read_model_folder(folder)
+    rng = random.Random(hd)
+    reqs = {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate((70, 45, 100))}
+    ref = {rid: plain.forward_logits(pcfg, w, toks) for rid, toks in reqs.items()}
+    max_tokens = 128 + 128
+    steps = trace_mixed(reqs, max_tokens, seed=hd)
+    runner = _runner(folder, dtype, max_tokens, page_size=16)
+    _check(replay_in_process(runner, steps), ref, dtype, f"head {hd}/{dtype}")
+    runner.cache.check()
+    assert runner.cache.min_free_pages() == runner.cache.num_pages
