@@ -8,7 +8,7 @@
 // index (csrc/shared/argmax.cu:15-18). The reference draws by rejection sampling with a philox
 // stream; here the caller supplies one uniform number per row (made from the request's own seed
 // and step, so a row's draw does not depend on its place in the batch) and the kernel walks the
-// cumulative distribution in vocabulary order. Thresholds are found by bisection on the bit
+// cumulative distribution in vocabulary order. Thresholds are found by radix selection on the bit
 // pattern of the (non-negative) probabilities, over the few thousand largest of them where that
 // suffices (see sample_kernel), so no sort and no scratch beyond one float per vocabulary entry and row.
 #include "common.cuh"
@@ -103,24 +103,12 @@ __global__ void argmax_final_kernel(int* __restrict__ out, const float* __restri
   if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
 }
 
-// count and mass of { p >= thr } over one row (p >= 0, compared as bit patterns)
-__device__ __forceinline__ void count_mass(const float* __restrict__ p, int n, unsigned thr_bits,
-                                           unsigned floor_bits, float* red, int& count, float& mass) {
-  float c = 0.f, m = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = p[i];
-    const unsigned b = __float_as_uint(v);
-    if (b >= thr_bits && b >= floor_bits) { c += 1.f; m += v; }
-  }
-  c = block_sum(c, red);
-  m = block_sum(m, red);
-  count = (int)(c + 0.5f);
-  mass = m;
-}
+constexpr int kRadixBins = 2048;
+constexpr float kFixedScale = 549755813888.f;    // 2^39: masses of list values are added up in this fixed point
 
-// The same over the candidate list in shared memory, whose ORDER differs from run to run (it is filled
-// through an atomic counter): the mass is added up in 2^-39 fixed point, where addition is associative,
-// so the result does not depend on the order.
+// Count and mass of { p >= thr, p >= floor } over the candidate list in shared memory (p >= 0, compared as
+// bit patterns). The list's ORDER differs from run to run (it is filled through an atomic counter): the mass
+// is added up in 2^-39 fixed point, where addition is associative, so the result does not depend on the order.
 __device__ __forceinline__ void count_mass_list(const float* p, int n, unsigned thr_bits, unsigned floor_bits,
                                                 unsigned long long* red64, int& count, float& mass) {
   unsigned long long acc = 0;     // mass in units of 2^-39 (at most 4096 values <= 1.0: at most 2^51)
@@ -129,7 +117,7 @@ __device__ __forceinline__ void count_mass_list(const float* p, int n, unsigned 
     const float v = p[i];
     const unsigned b = __float_as_uint(v);
     if (b >= thr_bits && b >= floor_bits) {
-      acc += (unsigned long long)(v * 549755813888.f);
+      acc += (unsigned long long)(v * kFixedScale);
       ++c;
     }
   }
@@ -145,55 +133,113 @@ __device__ __forceinline__ void count_mass_list(const float* p, int n, unsigned 
   acc = 0;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) acc += red64[w];
   count = (int)(acc >> 52);
-  mass = (float)(acc & ((1ull << 52) - 1)) * (1.f / 549755813888.f);
+  mass = (float)(acc & ((1ull << 52) - 1)) * (1.f / kFixedScale);
 }
 
-template <bool kList>
-__device__ __forceinline__ void count_mass_any(const float* p, int n, unsigned thr_bits, unsigned floor_bits, float* red,
-                                               unsigned long long* red64, int& count, float& mass) {
-  if (kList) count_mass_list(p, n, thr_bits, floor_bits, red64, count, mass);
-  else count_mass(p, n, thr_bits, floor_bits, red, count, mass);
+// Thresholds by radix selection over n non-negative values (the candidate list, or the whole row when the
+// list does not reach far enough): three rounds (11 + 11 + 9 bits of the pattern, from the top), each a
+// histogram of the still undecided values over the round's digit (count and fixed-point mass per bin, shared-
+// memory atomics) and a scan of the bins from the top for the largest digit at which the condition still
+// holds. Sums are integers (2^-39 fixed point), so neither the order of the values nor that of the atomics
+// changes the result. by_mass: largest t with mass{ v >= max(t, floor) } >= need (and at least one such
+// v); else largest t with count{ v >= t } >= k. kept_count / kept_mass: of { v >= max(t, floor) }.
+__device__ __forceinline__ bool radix_holds(int cnt, unsigned long long mass, bool by_mass, int k, float need) {
+  if (!by_mass) return cnt >= k;
+  return cnt > 0 && (float)mass * (1.f / kFixedScale) >= need;
 }
-
-// largest t (as a bit pattern) with count{ p >= t } >= k: the k-th largest value of p[0, n)
-template <bool kList>
-__device__ __forceinline__ unsigned kth_largest_bits(const float* p, int n, int k, float* red, unsigned long long* red64) {
-  unsigned cur = 0;
-  for (int b = 30; b >= 0; --b) {
-    const unsigned cand = cur | (1u << b);
-    int cnt; float mass;
-    count_mass_any<kList>(p, n, cand, 0u, red, red64, cnt, mass);
-    if (cnt >= k) cur = cand;
+struct RadixScratch {
+  unsigned long long mass[kRadixBins];
+  int count[kRadixBins];
+  unsigned long long warp_mass[32];
+  int warp_count[32];
+  unsigned long long above_mass;
+  int above_count;
+  int digit;
+};
+__device__ __forceinline__ unsigned radix_threshold(const float* v_in, int n, unsigned floor_bits, bool by_mass, int k,
+                                                    float need, RadixScratch& sc, int& kept_count, float& kept_mass) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  unsigned prefix = 0;
+  unsigned long long above_m = 0;                // mass and count of the values above the prefix's range
+  int above_c = 0;
+  int decided = 31;                              // bits [decided, 31) of the threshold are fixed
+#pragma unroll 1
+  for (int round = 0; round < 3; ++round) {
+    const int width = round == 2 ? 9 : 11, shift = decided - width, nb = 1 << width;
+    for (int i = tid; i < nb; i += blockDim.x) { sc.mass[i] = 0; sc.count[i] = 0; }
+    if (tid == 0) sc.digit = -1;
+    __syncthreads();
+    for (int i = tid; i < n; i += blockDim.x) {
+      const float v = v_in[i];
+      const unsigned b = __float_as_uint(v);
+      if (b >= floor_bits && (b >> decided) == (prefix >> decided)) {
+        const int d = (int)((b >> shift) & (unsigned)(nb - 1));
+        atomicAdd(&sc.mass[d], (unsigned long long)(v * kFixedScale));
+        atomicAdd(&sc.count[d], 1);
+      }
+    }
+    __syncthreads();
+    // suffix sums over the digits, two bins per thread (thread t: digits 2t, 2t + 1)
+    const bool has = 2 * tid < nb;
+    const unsigned long long m0 = has ? sc.mass[2 * tid] : 0, m1 = has ? sc.mass[2 * tid + 1] : 0;
+    const int c0 = has ? sc.count[2 * tid] : 0, c1 = has ? sc.count[2 * tid + 1] : 0;
+    unsigned long long sm = m0 + m1;             // become the sums over this and all later threads' bins
+    int scn = c0 + c1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long dm = __shfl_down_sync(0xffffffffu, sm, o);
+      const int dc = __shfl_down_sync(0xffffffffu, scn, o);
+      if (lane + o < 32) { sm += dm; scn += dc; }
+    }
+    if (lane == 0) { sc.warp_mass[warp] = sm; sc.warp_count[warp] = scn; }
+    __syncthreads();
+    unsigned long long later_m = above_m;
+    int later_c = above_c;
+    for (int w = warp + 1; w < nwarps; ++w) { later_m += sc.warp_mass[w]; later_c += sc.warp_count[w]; }
+    const unsigned long long from1_m = later_m + sm - m0;   // everything at or above digit 2t + 1
+    const int from1_c = later_c + scn - c0;
+    const unsigned long long from0_m = from1_m + m0;        // ... digit 2t
+    const int from0_c = from1_c + c0;
+    if (has) {
+      int best = -1;
+      if (radix_holds(from1_c, from1_m, by_mass, k, need)) best = 2 * tid + 1;
+      else if (radix_holds(from0_c, from0_m, by_mass, k, need)) best = 2 * tid;
+      if (best >= 0) atomicMax(&sc.digit, best);
+    }
+    __syncthreads();
+    const int digit = sc.digit < 0 ? 0 : sc.digit;          // nothing holds (the callers rule it out): digit 0
+    if (has && (digit >> 1) == tid) {                       // what lies above the chosen digit
+      sc.above_mass = (digit & 1) ? from1_m - m1 : from0_m - m0;
+      sc.above_count = (digit & 1) ? from1_c - c1 : from0_c - c0;
+    }
+    __syncthreads();
+    above_m = sc.above_mass;
+    above_c = sc.above_count;
+    prefix |= (unsigned)digit << shift;
+    decided = shift;
   }
-  return cur;
-}
-// largest t with mass{ p >= max(t, floor) } >= need
-template <bool kList>
-__device__ __forceinline__ unsigned mass_threshold_bits(const float* p, int n, unsigned floor_bits, float need, float* red,
-                                                        unsigned long long* red64) {
-  unsigned cur = 0;
-  for (int b = 30; b >= 0; --b) {
-    const unsigned cand = cur | (1u << b);
-    int cnt; float mass;
-    count_mass_any<kList>(p, n, cand, floor_bits, red, red64, cnt, mass);
-    if (cnt > 0 && mass >= need) cur = cand;
-  }
-  return cur;
+  // { v >= max(prefix, floor) }: what lies above the last digit plus that digit's bin (still in the scratch)
+  const int last = (int)(prefix & ((1u << 9) - 1));
+  kept_count = above_c + sc.count[last];
+  kept_mass = (float)(above_m + sc.mass[last]) * (1.f / kFixedScale);
+  __syncthreads();                                          // before the scratch is used again
+  return prefix;
 }
 
 constexpr int kSampleThreads = 1024;
 constexpr int kListCap = 4096;       // candidates kept in shared memory for the threshold searches
 constexpr int kExpBins = 128;        // exponents of values in [0, 1]
+constexpr int kCountedOneIn = 8;     // the exponent histogram counts one value in eight
 
 // One block per row. probs: scratch [rows, vocab] float32.
 //
-// After the softmax numerators e = exp((x - max) / T) are written (p_max = 1), a histogram over their
-// binary exponents tells how many values, and how much mass, lie at or above every power of two. The
-// largest values, down to the power of two at which more than kListCap would qualify, are copied
-// into shared memory; when the k-th largest value / the top-p mass lies inside that list (the usual
-// case: a peaked distribution) the threshold searches bisect over the list instead of the whole
-// vocabulary. Otherwise (a flat distribution) they scan the vocabulary as before: same thresholds,
-// more passes.
+// After the softmax numerators e = exp((x - max) / T) are written (p_max = 1), a histogram over the
+// binary exponents of one value in eight estimates how many values lie at or above every power of two.
+// The largest values, down to the power of two at which about half of kListCap qualify, are copied
+// into shared memory (a list that overflows all the same is not used); when the k-th largest value /
+// the top-p mass lies inside that list (the usual case: a peaked distribution) the threshold searches
+// run over the list instead of the whole vocabulary. Otherwise (a flat distribution) they run over
+// the vocabulary: same thresholds, three more passes each.
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
               float* __restrict__ probs, int vocab, const float* __restrict__ temperature,
@@ -205,6 +251,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   __shared__ float list[kListCap];
   __shared__ unsigned long long red64[32];
   __shared__ int hist_cnt[kExpBins];
+  __shared__ RadixScratch radix;
   __shared__ int picked, list_n, cut_exp;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
@@ -215,8 +262,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   const bool want_list = (k_req > 0 && k_req < vocab) || top_p[r] < 1.f;   // a threshold search will follow
   const bool vec = (vocab % 4 == 0) && (((uintptr_t)row) % 16 == 0) && (((uintptr_t)p) % 16 == 0);
 
-  for (int i = tid; i < kExpBins; i += kSampleThreads) hist_cnt[i] = 0;
+  static_assert(kRadixBins * 2 == (kSampleThreads / 32) * kExpBins, "one histogram per warp in the radix bins' words");
+  for (int i = tid; i < kRadixBins * 2; i += kSampleThreads) reinterpret_cast<int*>(radix.mass)[i] = 0;
   if (tid == 0) { list_n = 0; picked = -1; }
+  __syncthreads();
   // ---- maximum
   float mx = -INFINITY;
   if (vec) {
@@ -232,63 +281,87 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   mx = block_max(mx, red);
   // ---- numerators, their sum, and the histogram over exponents (how many values per power of two)
   float z = 0.f;
-  auto note = [&](float e) {
+  // every warp counts into a histogram of its own (in the words that the radix selection uses later), so
+  // the atomics of different warps never meet; the warps' histograms are added up below
+  int* const warp_hist = reinterpret_cast<int*>(radix.mass) + (tid >> 5) * kExpBins;
+  // Only every eighth value is counted: the histogram just has to place the list's cut so that the list
+  // neither overflows nor comes out needlessly short, and the thresholds found do not depend on the cut.
+  auto note = [&](float e, bool counted) {
     z += e;
-    if (!want_list) return;
-    const int bin = (int)(__float_as_uint(e) >> 23);     // e in [0, 1]: 0 .. 127
-    // lanes of a warp that hit the same bin count together: one atomic per distinct bin and warp
-    const unsigned peers = __match_any_sync(__activemask(), bin);
-    if ((int)(__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(&hist_cnt[bin], __popc(peers));
+    if (counted) atomicAdd(&warp_hist[__float_as_uint(e) >> 23], 1);       // e in [0, 1]: exponent 0 .. 127
   };
   if (vec) {
     const float4* row4 = reinterpret_cast<const float4*>(row);
     float4* p4 = reinterpret_cast<float4*>(p);
+    bool even = true;
 #pragma unroll 2
-    for (int i = tid; i < vocab / 4; i += kSampleThreads) {
+    for (int i = tid; i < vocab / 4; i += kSampleThreads, even = !even) {
       const float4 v = row4[i];
       float4 e;
       e.x = expf((v.x - mx) * inv_t); e.y = expf((v.y - mx) * inv_t);
       e.z = expf((v.z - mx) * inv_t); e.w = expf((v.w - mx) * inv_t);
       p4[i] = e;
-      note(e.x); note(e.y); note(e.z); note(e.w);
+      note(e.x, want_list && even); note(e.y, false); note(e.z, false); note(e.w, false);
     }
   } else {
-    for (int i = tid; i < vocab; i += kSampleThreads) {
+    int it = 0;
+    for (int i = tid; i < vocab; i += kSampleThreads, ++it) {
       const float e = expf((row[i] - mx) * inv_t);
       p[i] = e;
-      note(e);
+      note(e, want_list && (it & 7) == 0);
     }
   }
-  z = block_sum(z, red);  // also orders the writes of p and of the histogram before the reads below
+  z = block_sum(z, red);  // also orders the writes of p and of the histograms before the reads below
+  if (want_list && tid < kExpBins) {
+    int c = 0;
+    for (int w = 0; w < kSampleThreads / 32; ++w) c += reinterpret_cast<int*>(radix.mass)[w * kExpBins + tid];
+    hist_cnt[tid] = c;
+  }
+  __syncthreads();
   // p holds unnormalised e in [0, 1]; p_max = 1. Thresholds are scale-free.
 
   // ---- the candidate list: every value at or above 2^(cut_exp - 127)
   if (tid == 0) {
     int total = 0, e = kExpBins;
     if (want_list)
-      while (e > 0 && total + hist_cnt[e - 1] <= kListCap) { --e; total += hist_cnt[e]; }
+      while (e > 0 && total + kCountedOneIn * hist_cnt[e - 1] <= kListCap / 2) { --e; total += kCountedOneIn * hist_cnt[e]; }
     cut_exp = e;    // bins [e, 128) are in the list; e == 128: not even the top bin fits (no list)
   }
   __syncthreads();
   const unsigned cut_bits = (unsigned)cut_exp << 23;
   const bool have_list = cut_exp < kExpBins;
   if (have_list) {
-    auto take = [&](float v) {
-      if (__float_as_uint(v) >= cut_bits) list[atomicAdd(&list_n, 1)] = v;
+    // one atomic per warp and round: the lanes that take a value share out the places among themselves
+    const unsigned lane = tid & 31, below = (1u << lane) - 1u;
+    auto take = [&](float v, bool valid) {
+      const bool mine = valid && __float_as_uint(v) >= cut_bits;
+      const unsigned takers = __ballot_sync(0xffffffffu, mine);
+      if (takers == 0) return;
+      int base = 0;
+      if (lane == (unsigned)(__ffs(takers) - 1)) base = atomicAdd(&list_n, __popc(takers));
+      base = __shfl_sync(0xffffffffu, base, __ffs(takers) - 1);
+      const int at = base + __popc(takers & below);
+      if (mine && at < kListCap) list[at] = v;      // the estimate was off by more than a factor of two: see below
     };
     if (vec) {
       const float4* p4 = reinterpret_cast<const float4*>(p);
-#pragma unroll 4
-      for (int i = tid; i < vocab / 4; i += kSampleThreads) {
-        const float4 v = p4[i];
-        take(v.x); take(v.y); take(v.z); take(v.w);
+      const int n4 = vocab / 4, rounds = (n4 + kSampleThreads - 1) / kSampleThreads;
+      for (int it = 0; it < rounds; ++it) {
+        const int i = it * kSampleThreads + tid;
+        const bool valid = i < n4;
+        const float4 v = valid ? p4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        take(v.x, valid); take(v.y, valid); take(v.z, valid); take(v.w, valid);
       }
     } else {
-      for (int i = tid; i < vocab; i += kSampleThreads) take(p[i]);
+      const int rounds = (vocab + kSampleThreads - 1) / kSampleThreads;
+      for (int it = 0; it < rounds; ++it) {
+        const int i = it * kSampleThreads + tid;
+        take(i < vocab ? p[i] : 0.f, i < vocab);
+      }
     }
   }
   __syncthreads();
-  const int ln = have_list ? list_n : 0;
+  const int ln = (have_list && list_n <= kListCap) ? list_n : 0;   // an overflowed list is not used at all
 
   unsigned floor_bits = 0;  // running lower bound of kept values (bit pattern)
   float kept_mass = z;
@@ -296,24 +369,19 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   if (k > 0 && k < vocab) {
     // the k-th largest value: among the list's values when it holds at least k (it holds the largest ones)
     int cnt;
-    if (k <= ln) {
-      floor_bits = kth_largest_bits<true>(list, ln, k, red, red64);
-      count_mass_list(list, ln, floor_bits, 0u, red64, cnt, kept_mass);
-    } else {
-      floor_bits = kth_largest_bits<false>(p, vocab, k, red, red64);
-      count_mass(p, vocab, floor_bits, 0u, red, cnt, kept_mass);
-    }
+    if (k <= ln) floor_bits = radix_threshold(list, ln, 0u, false, k, 0.f, radix, cnt, kept_mass);
+    else floor_bits = radix_threshold(p, vocab, 0u, false, k, 0.f, radix, cnt, kept_mass);
   }
   const float tp = top_p[r];
   if (tp < 1.f) {
     // largest t with mass(p >= t, kept) >= top_p * kept_mass. When the kept values that the list holds
     // already reach that mass, t is at or above the list's cut and every value >= t is in the list.
     const float need = tp * kept_mass;
-    int cnt; float in_list;
+    int cnt; float in_list, m;
     count_mass_list(list, ln, floor_bits, 0u, red64, cnt, in_list);
     unsigned cur;
-    if (ln > 0 && cnt > 0 && in_list >= need) cur = mass_threshold_bits<true>(list, ln, floor_bits, need, red, red64);
-    else cur = mass_threshold_bits<false>(p, vocab, floor_bits, need, red, red64);
+    if (ln > 0 && cnt > 0 && in_list >= need) cur = radix_threshold(list, ln, floor_bits, true, 0, need, radix, cnt, m);
+    else cur = radix_threshold(p, vocab, floor_bits, true, 0, need, radix, cnt, m);
     if (cur > floor_bits) floor_bits = cur;
   }
   const float mp = min_p[r];

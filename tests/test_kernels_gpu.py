@@ -318,6 +318,35 @@ def test_sample_matches_plain_distribution(vocab):
             assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, f"setting {settings[r]} u={u}: token {tok} covers [{lo}, {float(cdf[tok])}]"
 
 
+def test_sample_when_the_estimate_of_the_candidate_list_is_wrong():
+    """The kernel places the cut of its shared-memory list from a histogram of one value in eight (the first of
+    every other group of four per thread). 5,000 equal large values at places that are never counted make that
+    estimate miss them all: the list overflows, is dropped, and the thresholds come from the whole row."""
+    from openinfer_b200.kernels import ops
+    torch.manual_seed(5)
+    vocab = 151936
+    settings = [(1.0, 10, 1.0, 0.0), (1.0, -1, 0.5, 0.0), (0.8, 7000, 0.9, 0.0)]
+    logits = torch.randn(len(settings), vocab) * 0.01
+    hot = torch.arange(vocab)[torch.arange(vocab) % 4 == 1][:5000]
+    logits[:, hot] = 5.0
+    logits[2, hot[:100]] = 6.0
+    rows = len(settings)
+    for u in (0.0, 0.3, 0.77, 0.9999):
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        scratch = torch.empty(rows * vocab, device=DEV)
+        ops.sample(out, logits.to(DEV), scratch,
+                   torch.tensor([s[0] for s in settings], device=DEV), torch.tensor([max(s[1], 0) for s in settings], dtype=torch.int32, device=DEV),
+                   torch.tensor([s[2] for s in settings], device=DEV), torch.tensor([s[3] for s in settings], device=DEV),
+                   torch.full((rows,), u, device=DEV))
+        for r, (t, k, p, mp) in enumerate(settings):
+            dist = plain.sampling_distribution(logits[r], t, k, p, mp)
+            tok = int(out[r])
+            assert dist[tok] > 0, f"setting {settings[r]} u={u}: token {tok} is outside the kept set"
+            cdf = torch.cumsum(dist.double(), 0)
+            lo = float(cdf[tok] - dist[tok])
+            assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, f"setting {settings[r]} u={u}: token {tok} covers [{lo}, {float(cdf[tok])}]"
+
+
 # ---------------------------------------------------------------------------
 # the tensor-core attention kernel (bfloat16; prompt tiles and split-KV decode)
 # ---------------------------------------------------------------------------
