@@ -11,6 +11,8 @@
 // cumulative distribution in vocabulary order. Thresholds are found by radix selection on the bit
 // pattern of the (non-negative) probabilities, over the few thousand largest of them where that
 // suffices (see sample_kernel), so no sort and no scratch beyond one float per vocabulary entry and row.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace {
@@ -230,6 +232,7 @@ constexpr int kSampleThreads = 1024;
 constexpr int kListCap = 4096;       // candidates kept in shared memory for the threshold searches
 constexpr int kExpBins = 128;        // exponents of values in [0, 1]
 constexpr int kCountedOneIn = 8;     // the exponent histogram counts one value in eight
+constexpr int kNoAnswer = -1;        // written for a row that the cluster kernel leaves to sample_kernel
 
 // One block per row. probs: scratch [rows, vocab] float32.
 //
@@ -244,8 +247,9 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride,
               float* __restrict__ probs, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
-              const float* __restrict__ min_p, const float* __restrict__ uniform) {
+              const float* __restrict__ min_p, const float* __restrict__ uniform, int only_unanswered) {
   pdl_start();
+  if (only_unanswered && out[blockIdx.x] != kNoAnswer) return;    // the cluster kernel has drawn this row's token
   __shared__ float red[32];
   __shared__ float chunk_sum[kSampleThreads];
   __shared__ float list[kListCap];
@@ -497,6 +501,246 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long long
   if (tid == 0) out[r] = picked;
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same selection by a thread-block cluster of kRowCtas CTAs per row, for rows that can be read 16
+// bytes at a time. One block per row is bound by what one SM can pull from L2 (three passes over 600 KB
+// for a 152k vocabulary, and a scratch row written and read back); here every CTA owns an eighth of the
+// row and every thread 32 consecutive values of it, which stay in registers from the one load to the
+// draw. The CTAs exchange through distributed shared memory, behind the cluster's barrier: their maxima;
+// their sums and exponent histograms; their candidates, appended to the list of the CTA of rank 0, which
+// alone searches the thresholds and sends them back; their kept masses, after which the CTA that holds
+// the target of the inverse CDF walks to it. Sums over CTAs are formed in rank order by everyone, so
+// all CTAs agree and a seeded draw is reproducible. A row whose thresholds the list does not hold (a
+// flat distribution, or a list that overflowed) is left to sample_kernel: the cluster writes -1 for it.
+constexpr int kRowCtas = 8;
+constexpr int kOwn4 = 8;             // float4 per thread: 32 values
+
+struct RowExchange {                 // what the CTAs of a row write into one another's shared memory
+  float max_of[kRowCtas];
+  float sum_of[kRowCtas];
+  float mass_of[kRowCtas];
+  int hist_of[kRowCtas][kExpBins];
+  unsigned floor_bits;               // from rank 0, with ...
+  int answered;                      // ... 1, or 0 when the list did not hold the thresholds
+  int list_n;                        // rank 0's counts
+  float list[kListCap];              // rank 0's is filled
+};
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, long long row_stride, int vocab,
+                      const float* __restrict__ temperature, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p, const float* __restrict__ min_p,
+                      const float* __restrict__ uniform) {
+  pdl_start();
+  // "this CTA runs": waited for before the first write into another CTA's shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float red[32];
+  __shared__ unsigned long long red64[32];
+  __shared__ RowExchange ex;
+  __shared__ RadixScratch radix;
+  __shared__ int cut_exp, first_tid, last_tid;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rank = (int)cluster.block_rank();
+  const int r = blockIdx.x / kRowCtas;
+  const float4* row4 = reinterpret_cast<const float4*>(logits + (size_t)r * row_stride);
+  const int n4 = vocab / 4, per4 = (n4 + kRowCtas - 1) / kRowCtas;
+  const int lo4 = rank * per4, hi4 = min(n4, lo4 + per4);
+  const int mine4 = lo4 + tid * kOwn4;           // this thread's values: float4 [mine4, mine4 + kOwn4) below hi4
+  const float inv_t = 1.f / temperature[r];
+  const int k_req = top_k[r];
+  const float tp = top_p[r];
+  const bool want_list = (k_req > 0 && k_req < vocab) || tp < 1.f;
+
+  for (int i = tid; i < kRadixBins * 2; i += kSampleThreads) reinterpret_cast<int*>(radix.mass)[i] = 0;
+  if (tid == 0) { ex.list_n = 0; ex.answered = 1; ex.floor_bits = 0; }
+
+  // ---- the one load, and the maximum
+  float4 x[kOwn4];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kOwn4; ++j) {
+    const bool valid = mine4 + j < hi4;
+    x[j] = valid ? row4[mine4 + j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    mx = fmaxf(fmaxf(mx, fmaxf(x[j].x, x[j].y)), fmaxf(x[j].z, x[j].w));
+  }
+  mx = block_max(mx, red);
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");        // 0: every CTA of the row runs
+  if (tid < kRowCtas) *cluster.map_shared_rank(&ex.max_of[rank], tid) = mx;
+  cluster.sync();                                // 1: the maxima
+  float gmax = ex.max_of[0];
+#pragma unroll
+  for (int c = 1; c < kRowCtas; ++c) gmax = fmaxf(gmax, ex.max_of[c]);
+
+  // ---- numerators (kept in the registers), their sum, the histogram over exponents of one value in eight
+  int* const warp_hist = reinterpret_cast<int*>(radix.mass) + warp * kExpBins;
+  float z = 0.f;
+#pragma unroll
+  for (int j = 0; j < kOwn4; ++j) {
+    float4 e;
+    e.x = expf((x[j].x - gmax) * inv_t); e.y = expf((x[j].y - gmax) * inv_t);     // exp(-inf) = 0 beyond the slice
+    e.z = expf((x[j].z - gmax) * inv_t); e.w = expf((x[j].w - gmax) * inv_t);
+    x[j] = e;
+    z += (e.x + e.y) + (e.z + e.w);
+    if (want_list && (j & 1) == 0 && mine4 + j < hi4) atomicAdd(&warp_hist[__float_as_uint(e.x) >> 23], 1);
+  }
+  z = block_sum(z, red);                         // also orders the histograms before the reads below
+  if (tid < kRowCtas) *cluster.map_shared_rank(&ex.sum_of[rank], tid) = z;
+  if (want_list && tid < kExpBins) {
+    int c = 0;
+    for (int w = 0; w < kSampleThreads / 32; ++w) c += reinterpret_cast<int*>(radix.mass)[w * kExpBins + tid];
+    for (int to = 0; to < kRowCtas; ++to) *cluster.map_shared_rank(&ex.hist_of[rank][tid], to) = c;
+  }
+  cluster.sync();                                // 2: sums and histograms
+  float ztot = 0.f;
+#pragma unroll
+  for (int c = 0; c < kRowCtas; ++c) ztot += ex.sum_of[c];
+
+  unsigned floor_bits = 0;                       // running lower bound of kept values (bit pattern)
+  if (want_list) {
+    // ---- the candidate list, in the CTA of rank 0: every value at or above 2^(cut_exp - 127)
+    if (tid == 0) {
+      int total = 0, e = kExpBins;
+      while (e > 0) {
+        int c = 0;
+        for (int q = 0; q < kRowCtas; ++q) c += ex.hist_of[q][e - 1];
+        if (total + kCountedOneIn * c > kListCap / 2) break;
+        --e;
+        total += kCountedOneIn * c;
+      }
+      cut_exp = e;                               // the same in every CTA: all add the same counts
+    }
+    __syncthreads();
+    const unsigned cut_bits = (unsigned)cut_exp << 23;
+    if (cut_exp < kExpBins) {
+      int* const n_at_0 = cluster.map_shared_rank(&ex.list_n, 0);
+      float* const list_at_0 = cluster.map_shared_rank(&ex.list[0], 0);
+      const unsigned below = (1u << lane) - 1u;
+      auto take = [&](float v) {
+        const bool mine = __float_as_uint(v) >= cut_bits;     // values beyond the slice are 0: never taken (cut_bits > 0 ...
+        const unsigned takers = __ballot_sync(0xffffffffu, mine && v > 0.f);   // ... unless the cut is at the bottom)
+        if (takers == 0) return;
+        int base = 0;
+        if (lane == __ffs(takers) - 1) base = atomicAdd(n_at_0, __popc(takers));
+        base = __shfl_sync(0xffffffffu, base, __ffs(takers) - 1);
+        const int at = base + __popc(takers & below);
+        if (mine && v > 0.f && at < kListCap) list_at_0[at] = v;
+      };
+#pragma unroll
+      for (int j = 0; j < kOwn4; ++j) { take(x[j].x); take(x[j].y); take(x[j].z); take(x[j].w); }
+    }
+    cluster.sync();                              // 3: the list is complete
+    if (rank == 0) {
+      const int ln = (cut_exp < kExpBins && ex.list_n <= kListCap) ? ex.list_n : 0;
+      bool ok = true;
+      float kept_mass = ztot;
+      if (k_req > 0 && k_req < vocab) {
+        int cnt;
+        if (k_req <= ln) floor_bits = radix_threshold(ex.list, ln, 0u, false, k_req, 0.f, radix, cnt, kept_mass);
+        else ok = false;
+      }
+      if (ok && tp < 1.f) {
+        const float need = tp * kept_mass;
+        int cnt; float in_list, m;
+        count_mass_list(ex.list, ln, floor_bits, 0u, red64, cnt, in_list);
+        if (ln > 0 && cnt > 0 && in_list >= need) {
+          const unsigned cur = radix_threshold(ex.list, ln, floor_bits, true, 0, need, radix, cnt, m);
+          if (cur > floor_bits) floor_bits = cur;
+        } else {
+          ok = false;
+        }
+      }
+      if (tid < kRowCtas) {
+        *cluster.map_shared_rank(&ex.floor_bits, tid) = floor_bits;
+        *cluster.map_shared_rank(&ex.answered, tid) = ok ? 1 : 0;
+      }
+    }
+    cluster.sync();                              // 4: the thresholds
+    floor_bits = ex.floor_bits;
+    if (!ex.answered) {                          // nobody touches anybody's shared memory after this barrier
+      if (rank == 0 && tid == 0) out[r] = kNoAnswer;
+      return;
+    }
+  }
+  const float mp = min_p[r];
+  if (mp > 0.f && __float_as_uint(mp) > floor_bits) floor_bits = __float_as_uint(mp);   // p_max = 1 in this scale
+
+  // ---- inverse CDF in vocabulary order: thread t of CTA c owns values [32 (1024 c' + t), +32) of the row
+  float own = 0.f;
+#pragma unroll
+  for (int j = 0; j < kOwn4; ++j) {
+    if (__float_as_uint(x[j].x) >= floor_bits) own += x[j].x;
+    if (__float_as_uint(x[j].y) >= floor_bits) own += x[j].y;
+    if (__float_as_uint(x[j].z) >= floor_bits) own += x[j].z;
+    if (__float_as_uint(x[j].w) >= floor_bits) own += x[j].w;
+  }
+  // what the threads before this one hold (warp scan, then the warps before this one)
+  float incl = own;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  __syncthreads();                               // red is free again
+  if (lane == 31) red[warp] = incl;
+  if (tid == 0) { first_tid = kSampleThreads; last_tid = -1; }
+  __syncthreads();
+  float before = 0.f, cta_mass = 0.f;
+  for (int w = 0; w < kSampleThreads / 32; ++w) {
+    if (w < warp) before += red[w];
+    cta_mass += red[w];
+  }
+  before += incl - own;
+  if (tid < kRowCtas) *cluster.map_shared_rank(&ex.mass_of[rank], tid) = cta_mass;
+  cluster.sync();                                // 5: the kept masses; no remote access after this
+  float total = 0.f, offset = 0.f;
+#pragma unroll
+  for (int c = 0; c < kRowCtas; ++c) {
+    if (c < rank) offset += ex.mass_of[c];
+    total += ex.mass_of[c];
+  }
+  const float target = uniform[r] * total;
+  // the CTA that holds the target: the first whose range ends beyond it; rounding at the very end falls to
+  // the last CTA that keeps anything
+  int owner = -1, last_with_mass = -1;
+  {
+    float run = 0.f;
+    for (int c = 0; c < kRowCtas; ++c) {
+      const float m = ex.mass_of[c];
+      if (m > 0.f) {
+        last_with_mass = c;
+        if (owner < 0 && run + m > target) owner = c;
+      }
+      run += m;
+    }
+    if (owner < 0) owner = last_with_mass < 0 ? 0 : last_with_mass;
+  }
+  if (rank != owner) return;
+  if (own > 0.f) {
+    atomicMax(&last_tid, tid);
+    if (offset + before + own > target) atomicMin(&first_tid, tid);
+  }
+  __syncthreads();
+  const int chosen = first_tid < kSampleThreads ? first_tid : last_tid;    // (nothing kept cannot happen: the largest value always is)
+  if (tid != (chosen < 0 ? 0 : chosen)) return;
+  float run = offset + before;
+  int pick = -1, last_kept = -1;
+#pragma unroll
+  for (int j = 0; j < kOwn4; ++j) {
+    const float v[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (__float_as_uint(v[e]) >= floor_bits && v[e] > 0.f) {
+        last_kept = 4 * (mine4 + j) + e;
+        run += v[e];
+        if (pick < 0 && run > target) pick = last_kept;
+      }
+    }
+  }
+  out[r] = pick >= 0 ? pick : (last_kept >= 0 ? last_kept : 0);
+}
+
 // Log-probabilities for requests that ask for them: for each listed row of the logits, the log-softmax
 // value of the picked token and the `k` largest entries (id and log-probability, in descending order of
 // the raw logits, ties to the lowest id, so that rounding of the subtraction cannot change the order).
@@ -588,6 +832,10 @@ OI_API int oi_argmax(int* out, const float* logits, int rows, int vocab, long lo
   return OI_OK;
 }
 
+static int g_sample_no_clusters = 0;
+// 1: every row goes to the kernel of one block per row (for tests and comparisons)
+OI_API int oi_sample_use_clusters(int on) { g_sample_no_clusters = on ? 0 : 1; return OI_OK; }
+
 // Per-row parameter arrays live on the device. `probs` is caller-provided scratch of
 // rows * vocab floats. temperature must be > 0 (greedy rows go to oi_argmax).
 OI_API int oi_sample(int* out, const float* logits, long long row_stride, float* probs, int rows, int vocab,
@@ -597,8 +845,18 @@ OI_API int oi_sample(int* out, const float* logits, long long row_stride, float*
   OI_REQUIRE(probs != nullptr, "sample: scratch missing");
   OI_REQUIRE(vocab <= 8 * 32 * kSampleThreads, "sample: vocabulary %d beyond %d", vocab, 8 * 32 * kSampleThreads);
   if (rows == 0) return OI_OK;
-  oi_launch(sample_kernel, rows, kSampleThreads, 0, (cudaStream_t)stream, out, logits, row_stride, probs, vocab, temperature,
-                                                         top_k, top_p, min_p, uniform);
+  cudaStream_t s = (cudaStream_t)stream;
+  // rows that can be read 16 bytes at a time go to the clusters first; what they leave unanswered, and every
+  // other shape, to the kernel of one block per row
+  const bool clusters = vocab % 4 == 0 && row_stride % 4 == 0 && ((uintptr_t)logits) % 16 == 0 &&
+                        vocab <= kRowCtas * kSampleThreads * kOwn4 * 4 && !g_sample_no_clusters;
+  if (clusters) {
+    oi_launch_cluster(sample_cluster_kernel, rows * kRowCtas, kSampleThreads, 0, s, kRowCtas, out, logits, row_stride, vocab,
+                      temperature, top_k, top_p, min_p, uniform);
+    OI_CHECK_LAUNCH();
+  }
+  oi_launch(sample_kernel, rows, kSampleThreads, 0, s, out, logits, row_stride, probs, vocab, temperature, top_k, top_p, min_p,
+            uniform, clusters ? 1 : 0);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "oi_argmax": [P, P, I, I, L, P, P, P],
     "oi_token_logprobs": [P, L, I, P, P, P, I, I, P, P, P, P],
     "oi_sample": [P, P, L, P, I, I, P, P, P, P, P, P],
+    "oi_sample_use_clusters": [I],
     "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05_pair": [P, I, L, P, L, P, L, I, I, I, I, P],

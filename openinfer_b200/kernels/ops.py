@@ -254,6 +254,12 @@ def token_logprobs(logits: torch.Tensor, rows: torch.Tensor, picked: torch.Tenso
     return lp, vals[:, :k_max], ids[:, :k_max]
 
 
+def sample_use_clusters(on: bool) -> None:
+    """Whether rows that can be read 16 bytes at a time are sampled by a cluster of CTAs per row (the default) or
+    every row by one block (what the clusters leave unanswered always is)."""
+    _lib.check(_lib.load().oi_sample_use_clusters(1 if on else 0), "sample_use_clusters")
+
+
 def sample(out: torch.Tensor, logits: torch.Tensor, probs_scratch: torch.Tensor, temperature: torch.Tensor,
            top_k: torch.Tensor, top_p: torch.Tensor, min_p: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
     """One token per row from softmax(logits / temperature) after top-k, top-p and min-p,

@@ -283,10 +283,20 @@ def test_argmax_ties_and_odd_vocab():
         assert out3.tolist() == torch.argmax(wide, dim=-1).tolist()
 
 
-@pytest.mark.parametrize("vocab", [50, 384, 5000, 30001])
-def test_sample_matches_plain_distribution(vocab):
+@pytest.fixture(params=[True, False], ids=["clusters", "one-block"])
+def sample_clusters(request):
+    """Both ways through the sampler: a cluster of CTAs per row where the row allows it, and one block per row."""
+    from openinfer_b200.kernels import ops
+    ops.sample_use_clusters(request.param)
+    yield request.param
+    ops.sample_use_clusters(True)
+
+
+@pytest.mark.parametrize("vocab", [50, 52, 384, 5000, 30001, 30004])
+def test_sample_matches_plain_distribution(vocab, sample_clusters):
     """The kept set and the drawn token follow the plain statement of temperature / top-k /
-    top-p / min-p, for uniform numbers across [0, 1)."""
+    top-p / min-p, for uniform numbers across [0, 1). Vocabularies that are multiples of 4 go to the
+    clusters (30004: the flat rows are then left to the one-block kernel), the others to one block."""
     from openinfer_b200.kernels import ops
     torch.manual_seed(vocab)
     settings = [(0.8, -1, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (0.7, -1, 0.9, 0.0), (1.3, 20, 0.8, 0.0),
@@ -318,7 +328,7 @@ def test_sample_matches_plain_distribution(vocab):
             assert lo - 1e-4 <= u <= float(cdf[tok]) + 1e-4, f"setting {settings[r]} u={u}: token {tok} covers [{lo}, {float(cdf[tok])}]"
 
 
-def test_sample_when_the_estimate_of_the_candidate_list_is_wrong():
+def test_sample_when_the_estimate_of_the_candidate_list_is_wrong(sample_clusters):
     """The kernel places the cut of its shared-memory list from a histogram of one value in eight (the first of
     every other group of four per thread). 5,000 equal large values at places that are never counted make that
     estimate miss them all: the list overflows, is dropped, and the thresholds come from the whole row."""
