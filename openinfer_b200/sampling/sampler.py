@@ -38,12 +38,26 @@ class Sampler:
         self._probs: Optional[torch.Tensor] = None
         self._pinned: List[torch.Tensor] = []   # a small ring of pinned buffers for the copies to the host
         self._turn = 0
+        # the rows' parameters travel the other way through a ring of pinned buffers too: a kernel reads them
+        # into one device buffer, so the host never waits for the stream (a copy from pageable memory does)
+        self._param_pinned: List[torch.Tensor] = []
+        self._param_turn = 0
+        self._param_dev: Optional[torch.Tensor] = None
 
     def _host_buffer(self, n: int) -> torch.Tensor:
         if not self._pinned or self._pinned[0].numel() < n:
             self._pinned = [torch.empty(max(256, 2 * n), dtype=torch.int32, pin_memory=True) for _ in range(4)]
         self._turn = (self._turn + 1) % len(self._pinned)
         return self._pinned[self._turn][:n]
+
+    def _param_buffers(self, words: int):
+        if not self._param_pinned or self._param_pinned[0].numel() < words:
+            torch.cuda.current_stream().synchronize()     # nothing reads the old buffers any more
+            size = max(1024, 2 * words)
+            self._param_pinned = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+            self._param_dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        self._param_turn = (self._param_turn + 1) % len(self._param_pinned)
+        return self._param_pinned[self._param_turn], self._param_dev
 
     def select(self, logits: torch.Tensor, params: Sequence[SamplingParams], steps: Sequence[int],
                step_seed: int) -> List[int]:
@@ -65,8 +79,12 @@ class Sampler:
             ops.argmax(out, logits)  # every row; sampled rows are overwritten below
         if sampled:
             k = len(sampled)
-            host = np.zeros((5, k), dtype=np.float32)
-            topk = np.zeros(k, dtype=np.int32)
+            # [temperature | top_p | min_p | uniform] as float32 bit patterns, then top_k and the rows' numbers
+            pinned, dev = self._param_buffers(6 * k)
+            words = pinned.numpy()
+            host = words[: 4 * k].view(np.float32).reshape(4, k)
+            topk = words[4 * k: 5 * k]
+            which = words[5 * k: 6 * k]
             for j, i in enumerate(sampled):
                 p = params[i]
                 host[0, j] = p.temperature
@@ -75,18 +93,20 @@ class Sampler:
                 host[3, j] = (uniform_from(p.seed, steps[i]) if p.seed is not None
                               else uniform_from(mix_seed(step_seed, i), steps[i]))
                 topk[j] = p.top_k if 0 < p.top_k < self.vocab_size else 0
-            fl = torch.from_numpy(host).to(self.device)
-            tk = torch.from_numpy(topk).to(self.device)
-            rows = logits if k == n else logits[torch.tensor(sampled, device=self.device)]
+                which[j] = i
+            ops.copy_words(dev, pinned, 6 * k)
+            fl = dev[: 4 * k].view(torch.float32).view(4, k)
+            tk = dev[4 * k: 5 * k]
+            idx = dev[5 * k: 6 * k]
+            rows = logits if k == n else logits.index_select(0, idx)
             if self._probs is None or self._probs.numel() < k * self.vocab_size:
                 self._probs = torch.empty(k * self.vocab_size, dtype=torch.float32, device=self.device)
             picked = torch.empty(k, dtype=torch.int32, device=self.device)
-            ops.sample(picked, rows.contiguous(), self._probs, fl[0].contiguous(), tk, fl[1].contiguous(),
-                       fl[2].contiguous(), fl[3].contiguous())
+            ops.sample(picked, rows.contiguous(), self._probs, fl[0], tk, fl[1], fl[2], fl[3])
             if k == n:
                 out = picked
             else:
-                out[torch.tensor(sampled, device=self.device)] = picked
+                out.index_copy_(0, idx, picked)
         host = self._host_buffer(n)
         ops.copy_words(host, out, n)     # a kernel writes the ids into pinned host memory: no copy-engine operation
         event = torch.cuda.Event()
