@@ -24,7 +24,7 @@ def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 PAIR = 0          # tile_n value that selects 256 x 256 tiles computed by pairs of CTAs (cta_group::2)
-PAIR_MIN_ROWS = 129   # from this many rows the pair's 256-row tiles are used for prompt portions
+PAIR_MIN_ROWS = int(os.environ.get("OI_PAIR_MIN_ROWS", "129"))   # from this many rows the pair's 256-row tiles are used for prompt portions
 # Which kernel takes the plain projections of prompt portions: "library" or "pair" (this file's).
 # Measured on B200 at 2,048 rows (us, library / pair / one CTA per tile): QKV 6144 x 4096: 72 / 76 / 84;
 # O 4096 x 4096: 49 / 51 / 51; down 4096 x 12288: 136 / 148 / 165; gate|up 24576 x 4096: 279 / 285 / 313
