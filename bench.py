@@ -114,6 +114,60 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+def sampler_mode(args, torch, ops, vocab: int) -> int:
+    """The sampling kernels alone on rows whose few dozen largest logits stand out, as a trained model's do."""
+    dev = torch.device("cuda:0")
+    rows = args.batch
+    torch.manual_seed(0)
+    logits = torch.randn(rows, vocab, device=dev) * 3
+    logits[:, :40] += torch.linspace(16, 6, 40, device=dev)
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    scratch = torch.empty(rows * vocab, device=dev)
+    settings = {"temperature": (0.8, 0, 1.0, 0.0), "top_k": (0.8, 20, 1.0, 0.0), "top_p": (0.8, 0, 0.9, 0.0),
+                "top_k_top_p": (0.6, 20, 0.95, 0.0), "top_k_top_p_min_p": (0.8, 50, 0.9, 0.05)}
+
+    def tensors(t, k, p, mp):
+        return (torch.full((rows,), t, device=dev), torch.full((rows,), k, dtype=torch.int32, device=dev),
+                torch.full((rows,), p, device=dev), torch.full((rows,), mp, device=dev), torch.full((rows,), 0.37, device=dev))
+
+    if args.profile == "sampler":
+        T, K, P, MP, U = tensors(*settings["top_k_top_p"])
+        for i in range(args.warmup + 1):
+            if i == args.warmup:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
+            ops.sample(out, logits, scratch, T, K, P, MP, U)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled": "sampler", "rows": rows, "vocab": vocab}))
+        return 0
+    result = {}
+    for clusters in (True, False):
+        ops.sample_use_clusters(clusters)
+        for name, setting in settings.items():
+            T, K, P, MP, U = tensors(*setting)
+            for _ in range(3):
+                ops.sample(out, logits, scratch, T, K, P, MP, U)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(10):
+                    ops.sample(out, logits, scratch, T, K, P, MP, U)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            result[("clusters/" if clusters else "one_block/") + name] = round(e0.elapsed_time(e1) / 50 * 1000, 1)
+    ops.sample_use_clusters(True)
+    print(json.dumps({"sampler_us_per_call": result, "rows": rows, "vocab": vocab,
+                      "note": "temperature, top_k, top_p, min_p per setting: " + json.dumps(settings)}))
+    return 0
+
+
 def main() -> int:
     global CONTEXT
     ap = argparse.ArgumentParser()
@@ -132,7 +186,10 @@ def main() -> int:
     ap.add_argument("--timeline", default=None, metavar="FILE",
                     help="write the start and end of every kernel of one decode step (CUPTI through torch.profiler: kernels "
                          "overlap under programmatic dependent launch, which a serialising profiler cannot show) and exit")
-    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--sampler", action="store_true",
+                    help="time the sampling kernels alone (vocabulary of the model, --batch rows, recorded into a CUDA "
+                         "graph): one JSON line of microseconds per call and setting, then exit")
+    ap.add_argument("--profile", choices=["decode", "prefill", "sampler"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
     args = ap.parse_args()
@@ -161,6 +218,8 @@ def main() -> int:
     if args.batch_invariant:
         from openinfer_b200.kernels import policy
         policy.set_batch_invariant(True)
+    if args.sampler or args.profile == "sampler":
+        return sampler_mode(args, torch, ops, MODELS[args.model][1]["vocab_size"])
     peaks, peaks_src = read_peaks()
     model_name, model_cfg = MODELS[args.model]
     cfg_dict = dict(model_cfg)
