@@ -47,11 +47,11 @@ TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), 
 
 # Stated tolerances (never widened to make a cutting pass; every cutting uses the same).
 #  float32: both sides sum in float32 in different orders; logits are O(1).
-F32_ATOL, F32_RTOL = 2e-5, 2e-4
+F32_ATOL, F32_RTOL = 1e-5, 5e-5       # measured: up to 4e-6 absolute on logits up to 2.4
 #  bfloat16: activations are rounded to 8 bits of mantissa between kernels; the bound is
 #  relative to the largest logit of the reference.
-BF16_MAX_REL = 0.04
-BF16_MEAN_REL = 0.006
+BF16_MAX_REL = 0.02          # measured on the five tiny configurations: 0.2 % to 0.8 %
+BF16_MEAN_REL = 0.003        # measured: 0.04 % to 0.13 %
 
 
 def make_model_folder(path: str, cfg: dict, seed: int) -> str:
