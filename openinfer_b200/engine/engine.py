@@ -24,6 +24,8 @@ from .scheduler import (DEFAULT_ENGINE_SEED, DEFAULT_MAX_DECODE_BATCH, DEFAULT_M
 DEFAULT_GPU_MEMORY_UTILIZATION = 0.90   # pegainfer-qwen3/src/weights.rs:31-36
 DEFAULT_KV_MARGIN_MIB = 150
 DEFAULT_KV_PAGE_SIZE = 16
+# rows of a mixed step are made a multiple of the widest row tile of the prompt products (256: a pair of CTAs)
+DEFAULT_ROW_ALIGNMENT = 256
 
 
 class RunnerExecutor(Executor):
@@ -163,7 +165,8 @@ class LLM:
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
                  cuda_graph: bool = True, lookahead: bool = True, prefix_cache: bool = True,
-                 batch_invariant: Optional[bool] = None, runner: Optional[ModelRunner] = None) -> None:
+                 batch_invariant: Optional[bool] = None, runner: Optional[ModelRunner] = None,
+                 row_alignment: int = DEFAULT_ROW_ALIGNMENT) -> None:
         from ..kernels import policy
         if batch_invariant is not None:
             policy.set_batch_invariant(batch_invariant)   # process-wide: which kernels take which step shapes
@@ -199,7 +202,7 @@ class LLM:
         self.scheduler = Scheduler(
             self.executor, max_context_tokens=max_context, stop_token_ids=self.runner.spec.stop_token_ids,
             max_prefill_tokens=max_prefill_tokens, max_decode_batch=max_decode_batch, seed=engine_seed,
-            lookahead=lookahead, batch_invariant=batch_invariant)
+            lookahead=lookahead, batch_invariant=batch_invariant, row_alignment=row_alignment)
         self._next_id = 0
 
     # ---- step-wise use: submit requests, then call step() until has_work() is false

@@ -169,7 +169,7 @@ class Scheduler:
     def __init__(self, executor: Executor, *, max_context_tokens: int, stop_token_ids: Sequence[int] = (),
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, seed: int = DEFAULT_ENGINE_SEED,
-                 lookahead: Optional[bool] = None, batch_invariant: bool = False) -> None:
+                 lookahead: Optional[bool] = None, batch_invariant: bool = False, row_alignment: int = 1) -> None:
         if max_prefill_tokens <= 0 or max_decode_batch <= 0:
             raise ValueError("max_prefill_tokens and max_decode_batch must be positive")
         self.executor = executor
@@ -183,6 +183,9 @@ class Scheduler:
         # min(what is left of its prompt, max_prefill_tokens) whole or waits, so where its prompt is cut
         # depends on its own length only
         self.batch_invariant = bool(batch_invariant)
+        # A prompt that the token budget cuts anyway is cut so that the step's rows (portions + decoded
+        # tokens) are a multiple of this: the products' row tiles are then all full. 1: no such trimming.
+        self.row_alignment = max(1, int(row_alignment))
         self.deferred: List[Request] = []
         self.prefilling: List[_Pending] = []
         self.active: List[_Active] = []
@@ -250,7 +253,8 @@ class Scheduler:
         return events
 
     # ------------------------------------------------------------------ portions
-    def _take_prefill(self) -> List[_Pending]:
+    def _take_prefill(self, other_rows: int = 0) -> List[_Pending]:
+        """The prompt portions of the next step; ``other_rows``: the rows that decoding requests add to it."""
         budget = self.max_prefill_tokens
         taken: List[_Pending] = []
         i = 0
@@ -267,6 +271,14 @@ class Scheduler:
             p.step_chunk = chunk
             budget -= chunk
             taken.append(self.prefilling.pop(i))
+        if taken and self.row_alignment > 1 and not self.batch_invariant:
+            last = taken[-1]
+            rows = other_rows + sum(p.step_chunk for p in taken)
+            over = rows % self.row_alignment
+            # only a prompt that is cut here anyway gives up tokens, and only if whole tiles remain
+            if (over and last.step_chunk < len(last.req.prompt_tokens) - last.done and rows > self.row_alignment
+                    and last.step_chunk > over):
+                last.step_chunk -= over
         return taken
 
     def _prefill_item(self, p: "_Pending") -> PrefillItem:
@@ -284,8 +296,8 @@ class Scheduler:
         if self.lookahead:
             return self._step_ahead()
         events = self._admit()
-        taken = self._take_prefill()
         decoding = list(self.active)
+        taken = self._take_prefill(len(decoding))
         if not taken and not decoding:
             return events
         prefill_items = [self._prefill_item(p) for p in taken]
@@ -349,10 +361,10 @@ class Scheduler:
         return events
 
     def _launch_next(self, previous: Optional[_Launched]):
-        taken = self._take_prefill()
         # who decodes: everyone who is still alive once the tokens in flight have arrived (a stop token
         # among those cannot be known yet)
         decoding = [a for a in self.active if len(a.generated) + a.inflight < max(1, a.req.max_tokens)]
+        taken = self._take_prefill(len(decoding))
         if not taken and not decoding:
             return None, None
         prefill_items = [self._prefill_item(p) for p in taken]

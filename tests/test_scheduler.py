@@ -341,3 +341,36 @@ def test_request_local_portions_take_whole_or_wait():
     # step 0: x takes 5, a's 8 do not fit and wait, y's 3 fit behind
     assert batches[0][0] == [("x", 5, True), ("y", 3, True)]
     assert cuts(False, True)[0] != alone          # the default fills the budget: a is cut by what x left over
+
+
+def test_a_cut_portion_fills_whole_row_tiles():
+    """With a row alignment, a prompt that the budget cuts anyway gives up as many tokens as make the step's
+    rows (portions + decoded tokens) a multiple of it; a prompt that ends in the step is never shortened."""
+    ex = FakeExecutor(total_pages=4000, page_size=4)
+    s = sched(ex, max_prefill_tokens=64, row_alignment=16, lookahead=False, max_context_tokens=100000)
+    for rid, n in (("a", 5), ("b", 7), ("c", 9)):
+        s.submit(Request(rid, list(range(n)), 50, SamplingParams()))
+    s.step()                                        # 21 prompt tokens end here: nothing to trim
+    assert [x[1] for x in ex.batches[-1][0]] == [5, 7, 9]
+    s.submit(Request("long", list(range(300)), 4, SamplingParams()))
+    s.step()                                        # 3 decoded tokens + a cut of 64 -> 61 (64 rows)
+    pre, dec = ex.batches[-1]
+    assert len(dec) == 3 and [x[1] for x in pre] == [61]
+    s.step()
+    assert [x[1] for x in ex.batches[-1][0]] == [61]
+    # without alignment the budget is filled
+    ex2 = FakeExecutor(total_pages=4000, page_size=4)
+    s2 = sched(ex2, max_prefill_tokens=64, lookahead=False, max_context_tokens=100000)
+    s2.submit(Request("a", list(range(5)), 50, SamplingParams()))
+    s2.step()
+    s2.submit(Request("long", list(range(300)), 4, SamplingParams()))
+    s2.step()
+    assert [x[1] for x in ex2.batches[-1][0]] == [64]
+    # the last portion of a prompt is taken whole even if it leaves a ragged tile
+    ex3 = FakeExecutor(total_pages=4000, page_size=4)
+    s3 = sched(ex3, max_prefill_tokens=64, row_alignment=16, lookahead=False, max_context_tokens=100000)
+    s3.submit(Request("a", list(range(5)), 50, SamplingParams()))
+    s3.step()
+    s3.submit(Request("p", list(range(40)), 4, SamplingParams()))
+    s3.step()
+    assert [x[1] for x in ex3.batches[-1][0]] == [40]
