@@ -419,7 +419,7 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
     if force_splits:
         old = A.plan_items
 
-        def forced(ql, kl, group, nkv_, window_, sm, decode_kernel=True, rows_per_cta=None):
+        def forced(ql, kl, group, nkv_, window_, sm, decode_kernel=True, rows_per_cta=None, whole_tiles_kernel=False):
             if force_splits == "tiles":     # decode rows through the tile kernel, cut into slices
                 return old(ql, kl, group, nkv_, window_, 10 ** 6, decode_kernel=False, rows_per_cta=rows_per_cta)
             if force_splits == "tiles_whole":
@@ -503,6 +503,16 @@ def test_attention_mma_split_prompt_portion():
 
 def test_attention_mma_plan():
     from openinfer_b200.kernels.attention import plan_items
+    # a kernel that takes whole tiles only stands ready: 32 tiles x 8 kv heads (less than two CTAs per SM) stay
+    # whole; two tiles over a long prefix (a quarter of the SMs at most) are still cut
+    _, _, _, mx, cut = plan_items([1024], [1024], group=4, nkv=8, window=None, sm_count=148, rows_per_cta=128,
+                                  whole_tiles_kernel=True)
+    assert not cut and mx == 1
+    _, _, _, mx, cut = plan_items([1024], [1024], group=4, nkv=8, window=None, sm_count=148, rows_per_cta=128)
+    assert cut and mx > 1
+    _, _, _, mx, cut = plan_items([64], [9000], group=4, nkv=8, window=None, sm_count=148, rows_per_cta=128,
+                                  whole_tiles_kernel=True)
+    assert cut and mx > 1
     tiles, dec, row_splits, mx, tile_split = plan_items([40, 1], [100, 513], group=4, nkv=8, window=None, sm_count=148)
     # 40 tokens x group 4 fill a 128-row tile: 32 tokens per tile, 2 whole tiles;
     # the decode row: 513 keys -> 16 slices of >= 32 keys, 4 per CTA
