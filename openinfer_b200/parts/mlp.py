@@ -56,7 +56,7 @@ class GatedMlp(FeedForward):
             if (x.shape[0] >= FUSED_MIN_ROWS or policy.batch_invariant()) and inter % (2 * gemm_tcgen05.ACT_BLOCK) == 0:
                 act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
                 if gemm_tcgen05.takes(act, x, self.w_gate_up):
-                    tile = 256 if policy.batch_invariant() else gemm_tcgen05.portion_tile(x.shape[0])
+                    tile = 256 if policy.batch_invariant() else gemm_tcgen05.portion_tile(x.shape[0], x.shape[1])
                     gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up, tile)
                     return linear(act, self.w_down)
             else:
