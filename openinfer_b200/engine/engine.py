@@ -41,6 +41,9 @@ class RunnerExecutor(Executor):
     def free_pages(self) -> int:
         return self.runner.cache.min_free_pages()
 
+    def free_slots(self) -> int:
+        return self.runner.cache.slot_pool.free_count
+
     supports_lookahead = True
 
     def execute(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int) -> Dict[Hashable, int]:
@@ -166,7 +169,7 @@ class LLM:
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
                  cuda_graph: bool = True, lookahead: bool = True, prefix_cache: bool = True,
                  batch_invariant: Optional[bool] = None, runner: Optional[ModelRunner] = None,
-                 row_alignment: int = DEFAULT_ROW_ALIGNMENT) -> None:
+                 row_alignment: int = DEFAULT_ROW_ALIGNMENT, strict_weights: bool = False) -> None:
         from ..kernels import policy
         if batch_invariant is not None:
             policy.set_batch_invariant(batch_invariant)   # process-wide: which kernels take which step shapes
@@ -189,12 +192,13 @@ class LLM:
 
             self.runner, _ = pages_from_memory_budget(
                 config, weights_seed, model_path, dtype, device, kv_page_size, gpu_memory_utilization,
-                kv_cache_memory_margin_mib, max_prefill_tokens, prefix_cache=prefix_cache)
+                kv_cache_memory_margin_mib, max_prefill_tokens, prefix_cache=prefix_cache,
+                max_requests=max_decode_batch, strict_weights=strict_weights)
         else:
             self.runner = ModelRunner.build(
                 config, weights_seed, dtype=dtype, device=device, page_size=kv_page_size, num_pages=num_pages,
                 max_tokens=max_cache_tokens, max_requests=max_decode_batch, folder=model_path,
-                prefix_cache=prefix_cache)
+                prefix_cache=prefix_cache, strict_weights=strict_weights)
         self.runner.cuda_graph = cuda_graph
         self.config = config
         self.executor = RunnerExecutor(self.runner)
@@ -222,6 +226,11 @@ class LLM:
 
     def has_work(self) -> bool:
         return self.scheduler.has_work()
+
+    def cancel(self, request_id: Hashable) -> bool:
+        """Take a submitted request back, in whatever state it is: waiting, in the middle of its prompt, or
+        decoding. Its pages are free at once; no further token of it is reported. False if it is not alive."""
+        return self.scheduler.cancel(request_id) is not None
 
     def generate_detailed(self, prompt_token_ids: Sequence[Sequence[int]],
                           sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,

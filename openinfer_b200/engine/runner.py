@@ -64,21 +64,26 @@ class ModelRunner:
         self._device_tokens: Optional[torch.Tensor] = None
         self.steps_run = 0
         self.cuda_graph = False          # record decode-only steps as CUDA graphs and replay them
-        self.max_graph_batch = 256
+        # the largest batch a recorded step is made for: every request that can be open at once
+        self.max_graph_batch = int(getattr(cache, "max_requests", 0) or 256)
         self._graphs: Dict[tuple, tuple] = {}
         self._graph_pool = None
         self._graph_safe: Optional[bool] = None
+        self.ignored_tensors: List[str] = []   # names in the model folder that the model did not ask for
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def build(cls, config, tensors_or_seed, dtype="bfloat16", device="cuda:0", *, page_size: int = 16,
               num_pages: Optional[int] = None, max_tokens: Optional[int] = None,
-              max_requests: int = 256, folder: Optional[str] = None, prefix_cache: bool = False) -> "ModelRunner":
+              max_requests: int = 256, folder: Optional[str] = None, prefix_cache: bool = False,
+              strict_weights: bool = False) -> "ModelRunner":
         """Assemble model + cache on the device.
 
         ``tensors_or_seed``: None to load ``folder``'s safetensors, or an int seed for
         random weights drawn on the device. The pool holds ``num_pages`` pages per group,
-        or enough for ``max_tokens`` positions (rounded up to whole pages)."""
+        or enough for ``max_tokens`` positions (rounded up to whole pages). Tensors of the
+        folder that the model does not name are left unread and listed in
+        ``runner.ignored_tensors`` (an error only with ``strict_weights``)."""
         dtype = _dtype_of(dtype)
         device = torch.device(device)
         if device.type != "cuda":
@@ -91,14 +96,19 @@ class ModelRunner:
         # the true 32-bit path must not use a reduced-precision matrix mode anywhere
         torch.backends.cuda.matmul.allow_tf32 = False
         torch.backends.cudnn.allow_tf32 = False
+        # library products of bfloat16 operands add up in float32 throughout, as the reference's do
+        # (cublasGemmEx with CUBLAS_COMPUTE_32F, pegainfer-kernels/csrc/shared/linear.cu:312-362): no
+        # partial sums of a split K rounded to bfloat16
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         entry = resolve_architecture(config.to_dict())
         spec = entry.build_spec(config)
         model = Model(spec, dtype)
         expected = model.expected_tensors()
+        ignored: List[str] = []
         if tensors_or_seed is None:
             if folder is None:
                 raise ValueError("either a folder or a seed is needed")
-            tensors = load_tensors(folder, expected, dtype, device)
+            tensors = load_tensors(folder, expected, dtype, device, strict=strict_weights, ignored=ignored)
         else:
             tensors = random_tensors(expected, int(tensors_or_seed), dtype=dtype, device=device)
         model.load(tensors, device)
@@ -110,7 +120,9 @@ class ModelRunner:
                 raise ValueError("give num_pages or max_tokens")
             num_pages = max(1, -(-int(max_tokens) // page_size))
         cache.allocate(num_pages, max_requests, device=device, dtype=dtype)
-        return cls(model, cache, device)
+        runner = cls(model, cache, device)
+        runner.ignored_tensors = ignored
+        return runner
 
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **kw) -> "ModelRunner":

@@ -66,7 +66,7 @@ class Event:
     request_id: Hashable
     kind: str
     token: Optional[int] = None
-    reason: str = ""   # finished: "stop" | "length"; rejected: "context_length" | "kv_budget" | "empty_prompt"; error: message
+    reason: str = ""   # finished: "stop" | "length" | "cancelled"; rejected: "context_length" | "kv_budget" | "empty_prompt"; error: message
     logprob: Optional[TokenLogprob] = None              # with kind "token", when the request asked for logprobs
     prompt_logprobs: Optional[List[Optional[TokenLogprob]]] = None   # with kind "prompt_logprobs": one per prompt
                                                                       # position of a portion (None: the very first)
@@ -104,6 +104,10 @@ class Executor:
 
     def free_pages(self) -> int:
         raise NotImplementedError
+
+    def free_slots(self) -> Optional[int]:
+        """How many more requests the cache can hold open (per-request state slots); None: no such limit."""
+        return None
 
     def execute(self, prefill: List[PrefillItem], decode: List[DecodeItem], step_seed: int) -> Dict[Hashable, int]:
         """Run one batch; returns the sampled token of every last portion and every decode item."""
@@ -203,6 +207,33 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.deferred or self.prefilling or self.active or self._inflight is not None)
 
+    def cancel(self, request_id: Hashable) -> Optional[Event]:
+        """Take a submitted request back (its client is gone). The reference retires a request as soon as
+        its receiver has hung up and frees its pages at once (scheduler/effects.rs:209-224,
+        pegainfer-qwen3/tests/scheduler_robustness.rs); here the caller says so.
+
+        A request that still waits simply disappears; one whose prompt is being computed, or that decodes,
+        is dropped and its pages, shared prefix pages and state slot go back now. With one step ahead a row
+        of it may be in flight: that row's token is thrown away when it arrives, like the row behind a stop
+        token (work on the device is ordered, so whoever gets the pages next writes them after that row has
+        read them). Returns the event ``finished`` / ``cancelled``, or None if no such request is alive."""
+        for i, req in enumerate(self.deferred):
+            if req.request_id == request_id:
+                del self.deferred[i]
+                return Event(request_id, "finished", reason="cancelled")
+        for i, p in enumerate(self.prefilling):
+            if p.req.request_id == request_id:
+                del self.prefilling[i]
+                self.executor.drop(request_id)
+                return Event(request_id, "finished", reason="cancelled")
+        for a in self.active:
+            if a.req.request_id == request_id and not a.ended:
+                a.ended = True
+                self.executor.drop(request_id)
+                self.active = [x for x in self.active if x is not a]
+                return Event(request_id, "finished", reason="cancelled")
+        return None
+
     def load(self) -> Dict[str, int]:
         """Snapshot like the reference's LoadSnapshot (scheduler.rs:513-526)."""
         return {"kv_used_pages": self.executor.total_pages - self.executor.free_pages(),
@@ -224,6 +255,9 @@ class Scheduler:
         events: List[Event] = []
         budget = max(0, self.executor.free_pages() - self._future_pages())
         slots = max(0, self.max_decode_batch - len(self.active) - len(self.prefilling))
+        open_slots = self.executor.free_slots()
+        if open_slots is not None:      # a request that finds no state slot waits, like one that finds no pages
+            slots = min(slots, max(0, int(open_slots)))
         still: List[Request] = []
         for req in self.deferred:
             n = len(req.prompt_tokens)

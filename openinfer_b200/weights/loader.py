@@ -7,6 +7,14 @@ reference validates its whole plan first (weight_loader.rs:411-439), and ONE err
 everything that is wrong: missing tensors, unexpected tensors, wrong shapes, unusable
 dtypes.
 
+Tensors the model did not ask for are not an error by themselves: the reference looks
+tensors up by name and never reads the rest (pegainfer-core/src/weight_loader.rs:251-269;
+``lm_head.weight`` of a tied model is skipped, pegainfer-qwen3/src/weights/load.rs:85-91),
+and real checkpoints carry such tensors (a tied model that still stores its head, rotary
+``inv_freq`` buffers of older exports). They are reported back (``ignored``), named in the
+error when something else is wrong (a misnamed tensor shows up as one missing and one
+unexpected), and refused on their own only with ``strict=True``.
+
 Storage rules: floating tensors are kept in the model dtype, except that a tensor
 stored in 32-bit stays 32-bit in a bfloat16 model; in a float32 model everything is
 widened (exactly) to float32; integer tensors are kept as int32.
@@ -16,7 +24,7 @@ from __future__ import annotations
 import json
 import os
 import struct
-from typing import Dict, List, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 from safetensors import safe_open
@@ -81,12 +89,13 @@ def _target_dtype(stored: str, integer: bool, model_dtype: torch.dtype):
 
 
 def load_tensors(folder: str, expected: Dict[str, ParamInfo], model_dtype: torch.dtype,
-                 device, strict: bool = True) -> Dict[str, torch.Tensor]:
+                 device, strict: bool = False, ignored: Optional[List[str]] = None) -> Dict[str, torch.Tensor]:
     """Load every expected tensor onto ``device``. Raises one ``WeightError`` that lists all
-    missing tensors, unexpected tensors (when ``strict``), wrong shapes and unusable dtypes."""
+    missing tensors, unexpected tensors, wrong shapes and unusable dtypes. Unexpected tensors
+    alone raise only when ``strict``; otherwise their names are appended to ``ignored``."""
     index = checkpoint_index(folder)
     missing = sorted(n for n in expected if n not in index)
-    unexpected = sorted(n for n in index if n not in expected) if strict else []
+    unexpected = sorted(n for n in index if n not in expected)
     wrong_shape, wrong_dtype = [], []
     for name, info in expected.items():
         if name not in index:
@@ -97,7 +106,7 @@ def load_tensors(folder: str, expected: Dict[str, ParamInfo], model_dtype: torch
         if _target_dtype(stored, info.integer, model_dtype) is None:
             kind = "an integer" if info.integer else "a floating"
             wrong_dtype.append(f"{name}: stored as {stored}, expected {kind} type")
-    if missing or unexpected or wrong_shape or wrong_dtype:
+    if missing or wrong_shape or wrong_dtype or (strict and unexpected):
         lines = [f"{folder}: the checkpoint does not fit the model:"]
         if missing:
             lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
@@ -110,6 +119,8 @@ def load_tensors(folder: str, expected: Dict[str, ParamInfo], model_dtype: torch
             lines.append(f"  wrong dtypes ({len(wrong_dtype)}):")
             lines += [f"    {w}" for w in wrong_dtype]
         raise WeightError("\n".join(lines))
+    if ignored is not None:
+        ignored.extend(unexpected)
 
     by_file: Dict[str, List[str]] = {}
     for name in expected:

@@ -374,3 +374,78 @@ def test_a_cut_portion_fills_whole_row_tiles():
     s3.submit(Request("p", list(range(40)), 4, SamplingParams()))
     s3.step()
     assert [x[1] for x in ex3.batches[-1][0]] == [40]
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_cancel_in_every_state(ahead):
+    """A request is taken back while it waits, in the middle of its prompt, while it decodes and (one step
+    ahead) with a row in flight: it reports `finished / cancelled` once, nothing more of it arrives, its
+    pages come back at once, and the other requests' tokens are what they are without it."""
+    def others():
+        return [Request("keep", [1, 2, 3], max_tokens=8), Request("keep2", [40, 41], max_tokens=5)]
+
+    ex0 = (AheadExecutor if ahead else FakeExecutor)()
+    s0 = sched(ex0, max_prefill_tokens=4)
+    for r in others():
+        s0.submit(r)
+    want, _ = collect(s0.run())
+
+    for state in ("deferred", "prefilling", "decoding", "never"):
+        ex = (AheadExecutor if ahead else FakeExecutor)(total_pages=64, page_size=4)
+        s = sched(ex, max_prefill_tokens=4, max_decode_batch=3 if state != "deferred" else 2)
+        for r in others():
+            s.submit(r)
+        s.submit(Request("gone", list(range(10, 22)), max_tokens=30))
+        events = []
+        if state == "deferred":
+            events += s.step()
+            assert [r.request_id for r in s.deferred] == ["gone"]       # no decode slot for it
+        elif state == "prefilling":
+            while not any(p.req.request_id == "gone" and p.done > 0 for p in s.prefilling):
+                events += s.step()
+        elif state == "decoding":
+            while not any(a.req.request_id == "gone" and (a.generated or a.inflight) for a in s.active):
+                events += s.step()
+            if ahead:
+                assert any(a.req.request_id == "gone" and a.inflight for a in s.active)   # a row of it is in flight
+        ev = s.cancel("gone" if state != "never" else "nobody")
+        if state == "never":
+            assert ev is None
+            ev = s.cancel("gone")
+        assert ev.kind == "finished" and ev.reason == "cancelled"
+        assert s.cancel("gone") is None                        # only once
+        assert ("gone" in ex.tokens) is False                  # its pages are back already
+        n_before = sum(1 for e in events if e.request_id == "gone" and e.kind == "token")
+        rest = s.run()
+        assert not [e for e in rest if e.request_id == "gone"], "a cancelled request reported something"
+        toks, fin = collect(events + rest)
+        assert {k: v for k, v in toks.items() if k != "gone"} == want
+        assert len(toks.get("gone", [])) == n_before
+        assert ex.used() == 0 and not s.has_work()
+        if ahead:
+            assert ex.uncollected == 0
+
+
+def test_state_slots_are_a_limit_of_admission_not_an_error():
+    """When the cache can hold fewer requests open than max_decode_batch allows, the ones that find no slot
+    wait for one (they are not failed)."""
+    class Slotted(FakeExecutor):
+        slots = 2
+
+        def free_slots(self):
+            return self.slots - len(self.tokens)
+
+        def begin(self, rid, prompt):
+            assert self.free_slots() > 0, "admitted without a state slot"
+            self.tokens[rid] = 0
+            return 0
+
+    ex = Slotted()
+    s = sched(ex, max_decode_batch=8)
+    for i in range(5):
+        s.submit(Request(i, [i, i + 1], max_tokens=3))
+    first = s.step()
+    assert len(s.prefilling) + len(s.active) == 2 and len(s.deferred) == 3
+    toks, fin = collect(first + s.run())
+    assert all(fin[i] == ("finished", "length") and len(toks[i]) == 3 for i in range(5))
+    assert max(len(p) + len(d) for p, d in ex.batches) <= 2

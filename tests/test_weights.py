@@ -104,3 +104,27 @@ def test_random_weights_are_deterministic_and_seeded(tmp_path):
     sub = {k: exp[k] for k in list(exp)[:3]}
     s = random_tensors(sub, 5)
     assert all(torch.equal(s[k], a[k]) for k in sub)
+
+
+def test_tensors_nobody_asked_for_are_ignored_unless_strict(tmp_path):
+    """A tied model whose file still stores lm_head.weight, and a file with rotary inv_freq buffers, load:
+    the reference looks tensors up by name and never reads the rest (pegainfer-core/src/weight_loader.rs:251-269,
+    pegainfer-qwen3/src/weights/load.rs:85-91). ``strict`` refuses them; any other fault still names them."""
+    f = make_model_folder(str(tmp_path / "a"), TINY_A, seed=0)
+    before = {n: v.clone() for n, v in load_file(os.path.join(f, "model.safetensors")).items()}  # the file is rewritten below
+
+    def extras(t):
+        t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+        t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    _rewrite(f, extras)
+    exp = expected_tensors(Qwen3Config.from_dict(TINY_A))
+    ignored = []
+    got = load_tensors(f, exp, torch.bfloat16, "cpu", ignored=ignored)
+    assert ignored == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert set(got) == set(exp) and all(torch.equal(got[n], before[n]) for n in exp)
+    with pytest.raises(WeightError, match=r"unexpected tensors \(2\)"):
+        load_tensors(f, exp, torch.bfloat16, "cpu", strict=True)
+    _rewrite(f, lambda t: t.pop("model.norm.weight"))
+    with pytest.raises(WeightError) as e:
+        load_tensors(f, exp, torch.bfloat16, "cpu")
+    assert "missing tensors (1)" in str(e.value) and "unexpected tensors (2)" in str(e.value)
