@@ -43,6 +43,13 @@ TINY_E = dict(
     num_hidden_layers=2, hidden_size=512, num_attention_heads=8, num_key_value_heads=4, head_dim=128,
     intermediate_size=1536, vocab_size=1000, rope_theta=1000000.0, rms_norm_eps=1e-6,
     tie_word_embeddings=True, max_position_embeddings=2048)
+# The shape relations of the smallest real model (head 128, a group of 2, queries twice as wide as the
+# hidden state) at toy width.
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+    intermediate_size=768, vocab_size=700, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, max_position_embeddings=2048)
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 # Stated tolerances (never widened to make a cutting pass; every cutting uses the same).
@@ -176,6 +183,23 @@ def trace_mixed(requests: Dict[str, List[int]], max_tokens: int, seed: int = 0, 
             del live[rid]
         s += 1
     return steps
+
+
+def count_page_handouts(cache) -> Dict[tuple, int]:
+    """From now on, count how often each (group, page id) is handed out by the cache's pools. A page that
+    was handed out twice has been used again after a request gave it back."""
+    counts: Dict[tuple, int] = {}
+    for gi, g in enumerate(cache.groups):
+        inner = g.pool.allocate
+
+        def allocate(n, _inner=inner, _gi=gi):
+            ids = _inner(n)
+            for i in ids:
+                counts[(_gi, i)] = counts.get((_gi, i), 0) + 1
+            return ids
+
+        g.pool.allocate = allocate
+    return counts
 
 
 def replay_in_process(runner, steps: List[dict]) -> Dict[str, torch.Tensor]:

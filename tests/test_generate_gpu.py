@@ -251,3 +251,75 @@ def test_many_requests_arriving_over_time_with_few_pages(folders, lookahead):
         assert got[rid] == solo.generate([prompt], max_tokens=n_new)[0], f"request {k}"
         if k % 3 == 1:
             assert got[rid] == plain.greedy_generate(cfg, w, prompt, n_new), f"request {k} against the plain implementation"
+
+
+def _splitmix(seed: int, step: int) -> int:
+    """SplitMix64 over (seed, step), restated from pegainfer-sample/src/lib.rs:283-288."""
+    m = (1 << 64) - 1
+    z = (seed ^ ((step * 0x9E3779B97F4A7C15) & m)) & m
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+    return z ^ (z >> 31)
+
+
+def _uniform(seed: int, step: int) -> float:
+    return (_splitmix(seed, step) >> 40) / float(1 << 24)     # the top 24 bits: exact in float32
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_sampled_tokens_are_the_plain_draws(folders, ahead):
+    """Configuration B's workload: prompts of 1/9/33/70 tokens in portions of 13 beside decoding, 12 tokens at
+    temperature 0.8 (one request also with top-k and top-p), seeded and unseeded requests mixed, in float32.
+    Every token must be the plain implementation's inverse-CDF pick from the plain distribution at the uniform
+    number that belongs to the draw: SplitMix64(the request's seed, its own count of tokens so far) for a seeded
+    request; for an unseeded one SplitMix64(SplitMix64(the step's seed, its row among the step's sampled rows),
+    its own count), the step's seed being the next 64 bits of Random(engine seed). A draw whose uniform number lies
+    within 1e-4 of an edge of the cumulative distribution is not judged."""
+    from openinfer_b200 import LLM, SamplingParams
+    cfg, w = plain.read_model_folder(folders["B"])
+    rng = random.Random(8)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 9, 33, 70)]
+    params = [SamplingParams(temperature=0.8, seed=1234), SamplingParams(temperature=0.8),
+              SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=77), SamplingParams(temperature=0.8)]
+    n_new = 12
+    engine_seed = 4242
+    llm = LLM(folders["B"], dtype="float32", max_cache_tokens=1024, max_prefill_tokens=13, lookahead=ahead,
+              engine_seed=engine_seed)
+    # which rows each step samples, in the order the executor hands them to the sampler: the requests whose
+    # prompt ends in the step, then the decoding ones (recorded from the scheduler's calls, nothing else)
+    batches = []
+    inner = llm.executor.launch
+
+    def launch(prefill, decode, step_seed, previous=None):
+        batches.append((step_seed, [p.request_id for p in prefill if p.is_last] + [d.request_id for d in decode]))
+        return inner(prefill, decode, step_seed, previous)
+
+    llm.executor.launch = launch
+    got = llm.generate(prompts, params, max_tokens=n_new)
+    seeds = random.Random(engine_seed)
+    drawn = {i: 0 for i in range(4)}
+    where = {}                           # (request, its k-th token) -> (step seed, row)
+    for step_seed, rows in batches:
+        assert step_seed == seeds.getrandbits(64)
+        for row, rid in enumerate(rows):
+            where[(rid, drawn[rid])] = (step_seed, row)
+            drawn[rid] += 1
+    ids = sorted(drawn)
+    judged = 0
+    for i, rid in enumerate(ids):
+        assert len(got[i]) == n_new
+        sp, seq = params[i], list(prompts[i])
+        for k, tok in enumerate(got[i]):
+            logits = plain.forward_logits(cfg, w, seq)[-1]
+            dist = plain.sampling_distribution(logits, sp.temperature, sp.top_k, sp.top_p, sp.min_p)
+            if sp.seed is not None:
+                u = _uniform(sp.seed, k)
+            else:
+                step_seed, row = where[(rid, k)]
+                u = _uniform(_splitmix(step_seed, row), k)
+            edges = torch.cumsum(dist, 0)
+            if float((edges - u).abs().min()) > 1e-4:
+                assert tok == plain.inverse_cdf_pick(dist, u), f"request {i}, token {k}: not the plain draw"
+                judged += 1
+            seq.append(tok)
+    assert judged >= 40

@@ -600,15 +600,19 @@ def test_gemm_stream_refuses_bad_operands():
 @pytest.mark.parametrize("M,N,K", [(1, 96, 224), (8, 4096, 12288), (13, 200, 1536)])
 def test_gemm_skinny_with_fused_activation(M, N, K):
     from openinfer_b200.kernels import linear as lin
-    from openinfer_b200.kernels import ops
     torch.manual_seed(M + N)
     gu = torch.randn(M, 2 * K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
-    act = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
-    ops.silu_mul(act, gu)
+    g, u = gu[:, :K].double(), gu[:, K:].double()       # the reference activation in float64, rounded once like the kernel's
+    act = (g / (1.0 + torch.exp(-g)) * u).to(torch.bfloat16)
     ref = act.double() @ w.double().t()
-    out = lin.linear_silu_mul(gu, w)
-    assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    for fused in (False, True):
+        lin.FUSE_SILU_MUL = fused
+        try:
+            out = lin.linear_silu_mul(gu, w)
+        finally:
+            lin.FUSE_SILU_MUL = False
+        assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item(), f"fused={fused}"
 
 
 @pytest.mark.parametrize("tile_n", [256, 128, 0])

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import (TINY, assert_close, make_model_folder, random_tokens, replay_in_process,
+from helpers import (TINY, assert_close, count_page_handouts, make_model_folder, random_tokens, replay_in_process,
                      replay_trace_run, round64, trace_mixed, trace_portions, trace_tail, trace_whole)
 
 pytestmark = pytest.mark.gpu
@@ -69,9 +69,12 @@ def test_cuttings_match_plain(folders, workloads, name, dtype, mode):
         assert max(len(s["entries"]) for s in steps) >= 2
     page = {"A": 8, "B": 16, "C": 16, "D": 32, "E": 16}[name]
     runner = _runner(folders[name], dtype, max_tokens, page_size=page)
+    handed_out = count_page_handouts(runner.cache)
     got = replay_in_process(runner, steps)
     _check(got, ref, dtype, f"{name}/{dtype}/{mode}")
     runner.cache.check()
+    if mode == "mixed":
+        assert max(handed_out.values()) >= 2, "no page was used again: the pool is too large for this test"
     assert runner.cache.min_free_pages() == runner.cache.num_pages, "pages were not all given back"
     from openinfer_b200.kernels import attention as A, gemm_tcgen05 as G
     assert A.tcgen05_status() == 0 and G.status() == 0, "a bounded wait ran out in a tcgen05 kernel"
@@ -204,23 +207,24 @@ def test_batch_invariant_mode_is_bitwise(folders, workloads, name):
     _check({r: together[r] for r in ids}, {r: ref[r] for r in ids}, "bfloat16", "batch-invariant policy")
 
 
-def test_real_layer_sizes_bfloat16_against_float32():
-    """Qwen3-8B layer sizes (hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary 151936) with two
-    layers and random weights: the bfloat16 engine (streaming products with clusters of 4 and 8, gate/up with
-    the activation, decode attention with rotation and merge inside, recorded graphs) against the float32
-    engine on the same weights, prompts in portions and then tokens one by one, three requests."""
-    from openinfer_b200.config.base import resolve_architecture
+def test_real_layer_sizes_and_vocabulary(tmp_path):
+    """Qwen3-8B layer sizes (hidden 4096, 32/8 heads of 128, intermediate 12288) with the REAL vocabulary
+    of 151,936 entries, two layers, random weights written to a folder: the bfloat16 engine (streaming
+    products with clusters of 4 and 8, gate/up with the activation, decode attention with rotation and merge
+    inside, recorded graphs) against the float32 engine on the same weights, prompts in portions and then
+    tokens one by one, three requests; and the float32 engine against the plain implementation on the shortest
+    request (43 positions: the plain implementation's head alone is 2.5 GB of float32 on the CPU)."""
     from openinfer_b200.engine.runner import ModelRunner, StepEntry
     cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=4096,
                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
-    config = resolve_architecture(cfg).config_cls.from_dict(cfg)
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 7)
     rng = random.Random(1)
     prompts = {r: [rng.randrange(151936) for _ in range(n)] for r, n in (("a", 150), ("b", 37), ("c", 260))}
     outs = {}
     feed = {}
     for dtype in ("float32", "bfloat16"):
-        runner = ModelRunner.build(config, 7, dtype=dtype, device="cuda:0", page_size=16, max_tokens=1024, max_requests=8)
+        runner = ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_size=16, max_tokens=1024, max_requests=8)
         runner.cuda_graph = dtype == "bfloat16"
         rows = {r: [] for r in prompts}
         # the prompts in two portions each, together; then 6 tokens one by one (the float32 run's argmax is fed to both)
@@ -245,6 +249,13 @@ def test_real_layer_sizes_bfloat16_against_float32():
         del runner
         torch.cuda.empty_cache()
     _check(outs["bfloat16"], outs["float32"], "bfloat16", "real layer sizes")
+    pcfg, w = plain.read_model_folder(folder)
+    p = prompts["b"]
+    seq = p + [feed[s]["b"] for s in range(6)]
+    at = [len(p) // 2 - 1, len(p) - 1] + list(range(len(p), len(p) + 6))
+    ref = plain.forward_logits(pcfg, w, seq)[at]
+    assert_close(outs["float32"]["b"], ref, "float32", "real layer sizes and vocabulary, float32 engine against plain")
+    assert_close(outs["bfloat16"]["b"], ref, "bfloat16", "real layer sizes and vocabulary, bfloat16 engine against plain")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
