@@ -27,14 +27,16 @@ from safetensors import safe_open
 # --------------------------------------------------------------------------
 # loading
 # --------------------------------------------------------------------------
-def read_model_folder(folder: str):
-    """config.json as a dict and every tensor of model.safetensors widened to float32."""
+def read_model_folder(folder: str, dtype: torch.dtype = torch.float32):
+    """config.json as a dict and every tensor of model.safetensors widened to float32 (or, for an
+    oracle whose own rounding is out of the picture at real layer widths, to float64: every function
+    below computes in the type of the tensors it is given; rotation angles stay float32 by definition)."""
     with open(os.path.join(folder, "config.json")) as fh:
         cfg = json.load(fh)
     tensors: Dict[str, torch.Tensor] = {}
     with safe_open(os.path.join(folder, "model.safetensors"), framework="pt", device="cpu") as f:
         for name in f.keys():
-            tensors[name] = f.get_tensor(name).to(torch.float32)
+            tensors[name] = f.get_tensor(name).to(dtype)
     return cfg, tensors
 
 

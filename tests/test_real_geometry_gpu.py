@@ -2,12 +2,15 @@
 
 Hidden size, head counts, head size and intermediate size are those of Qwen3-8B, Qwen3-0.6B and
 Qwen3-32B; the depth is 2 layers and the vocabulary is cut to 3,001 entries, because this is a
-correctness test, not a benchmark: the plain implementation runs on the CPU. Mixed steps with up to
+correctness test, not a benchmark: the plain implementation runs on the CPU, here in float64 (sums of
+4,096 to 25,600 float32 terms differ between two correct orders of summation by about as much as the
+float32 tolerance allows, so the oracle's own rounding is taken out of the comparison). Mixed steps with up to
 twelve live requests, nine and more of them decoding at once, so few pages that they are used again,
 decode-only steps replayed as recorded graphs, in float32 and in bfloat16."""
 import random
 
 import pytest
+import torch
 
 import plain_qwen3 as plain
 from helpers import assert_close, count_page_handouts, make_model_folder, random_tokens, replay_in_process, trace_mixed
@@ -31,10 +34,10 @@ LENGTHS = [90, 24, 61, 33, 128, 47, 70, 25, 52, 38, 101, 29, 44, 66]
 def workload(request, tmp_path_factory):
     name = request.param
     folder = make_model_folder(str(tmp_path_factory.mktemp(f"geo{name}")), GEOMETRY[name], seed=len(name))
-    cfg, w = plain.read_model_folder(folder)
+    cfg, w = plain.read_model_folder(folder, dtype=torch.float64)
     rng = random.Random(17)
     reqs = {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(LENGTHS)}
-    ref = {rid: plain.forward_logits(cfg, w, toks) for rid, toks in reqs.items()}
+    ref = {rid: plain.forward_logits(cfg, w, toks).float() for rid, toks in reqs.items()}
     del w
     return name, folder, reqs, ref
 

@@ -249,11 +249,11 @@ def test_real_layer_sizes_and_vocabulary(tmp_path):
         del runner
         torch.cuda.empty_cache()
     _check(outs["bfloat16"], outs["float32"], "bfloat16", "real layer sizes")
-    pcfg, w = plain.read_model_folder(folder)
+    pcfg, w = plain.read_model_folder(folder, dtype=torch.float64)   # an oracle without rounding of its own
     p = prompts["b"]
     seq = p + [feed[s]["b"] for s in range(6)]
     at = [len(p) // 2 - 1, len(p) - 1] + list(range(len(p), len(p) + 6))
-    ref = plain.forward_logits(pcfg, w, seq)[at]
+    ref = plain.forward_logits(pcfg, w, seq)[at].float()
     assert_close(outs["float32"]["b"], ref, "float32", "real layer sizes and vocabulary, float32 engine against plain")
     assert_close(outs["bfloat16"]["b"], ref, "bfloat16", "real layer sizes and vocabulary, bfloat16 engine against plain")
 
