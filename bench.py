@@ -8,8 +8,14 @@ A "step" is one decode step of a batch of 8 requests, each with a 2,048-token co
 engine's step function plus on-device argmax); ``e2e`` is the same through the Python
 entry point ``LLM.step()`` with host token ids in and out every step. The line also
 reports a 2,048-token prefill, the decode step's fraction of the HBM roofline, and decode
-at batch 1 and 64. Prints ONE JSON line. The engine runs on one GPU: for --gpus > 1 it
-says so and exits with 2.
+at batch 1 and 64; then, as flat entries of ``points`` (and once more, grouped, under
+``sizes``), prefills of 8,192 and 32,768 tokens at the headline sizes and the other two
+sizes of the reference's benchmarks, each built, measured and freed in turn: Qwen3-0.6B
+sizes (decode at batch 1/8/64, prefill, and the mixed step of 8 prompt portions of 512
+tokens beside 56 decoding requests, device-timed and through ``LLM.step()``) and Qwen3-32B
+sizes (decode at batch 1/8/64, prefill), each with its own roofline fractions and clock
+sample. Prints ONE JSON line. The engine runs on one GPU: for --gpus > 1 it says so and
+exits with 2.
 """
 from __future__ import annotations
 
@@ -168,6 +174,224 @@ def sampler_mode(args, torch, ops, vocab: int) -> int:
     return 0
 
 
+class Bench:
+    """One model size on the GPU: the runner, its pool, and the measurements taken on it."""
+
+    def __init__(self, torch, mods, cfg_dict, dtype, max_batch, steps_room, context, prefill_room=PREFILL_TOKENS,
+                 layers=None, page=PAGE):
+        self.torch, self.mods = torch, mods
+        cfg_dict = dict(cfg_dict)
+        self.full_layers = cfg_dict["num_hidden_layers"]
+        if layers:
+            cfg_dict["num_hidden_layers"] = layers
+        self.context = context
+        per_req = context + steps_room + 16 + 2 * page
+        cfg_dict["max_position_embeddings"] = max(cfg_dict["max_position_embeddings"], per_req + 128, prefill_room + 128)
+        self.config = mods["resolve_architecture"](cfg_dict).config_cls.from_dict(cfg_dict)
+        self.dtype = dtype
+        self.esize = 2 if dtype == "bfloat16" else 4
+        self.dev = torch.device("cuda:0")
+        pool_tokens = max_batch * per_req + max(prefill_room, 8 * 512) + 64
+        self.runner = mods["ModelRunner"].build(self.config, 0, dtype=dtype, device=self.dev, page_size=page,
+                                                max_tokens=pool_tokens, max_requests=max_batch + 16)
+        self.runner.cuda_graph = True
+        self.cache = self.runner.cache
+        for g in self.cache.groups:  # contexts are not computed but filled: decode reads the same bytes
+            g.tensor.normal_(0.0, 0.5)
+        self.rng = random.Random(0)
+        self.vocab = self.config.vocab_size
+
+    def close(self):
+        import gc
+        self.runner = self.cache = None
+        gc.collect()
+        self.torch.cuda.synchronize()
+        self.torch.cuda.empty_cache()
+
+    def fake_context(self, rid, n):
+        self.cache.open(rid)
+        self.cache.reserve(rid, n)
+        self.cache.commit(rid)
+
+    def decode_run(self, batch, steps, warmup):
+        """Device-timed decode: `steps` steps of `batch` requests at the context length. Returns (ms, launches)."""
+        torch, runner, ops, klib, StepEntry = self.torch, self.runner, self.mods["ops"], self.mods["klib"], self.mods["StepEntry"]
+        ids = [f"b{batch}_{i}" for i in range(batch)]
+        for rid in ids:
+            self.fake_context(rid, self.context)
+        toks = [[self.rng.randrange(self.vocab)] for _ in ids]
+        out = torch.empty(batch, dtype=torch.int32, device=self.dev)
+
+        def one():
+            logits = runner.step([StepEntry(rid, t, [0]) for rid, t in zip(ids, toks)])
+            ops.argmax(out, logits)
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        l0 = klib.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = klib.launches - l0
+        for rid in ids:
+            runner.end(rid)
+        return ms, launches
+
+    def decode_bytes(self, batch, steps, warmup):
+        """What a decode step has to read: every weight it uses once, and the cache of the live requests."""
+        kv_tokens = batch * (self.context + warmup + steps // 2)
+        return self.runner.model.weight_bytes() + kv_tokens * self.cache.bytes_per_token(self.esize)
+
+    def linear_flops_per_token(self):
+        c = self.config
+        return c.num_hidden_layers * 2 * (c.hidden_size * (c.q_dim + 2 * c.kv_dim) + c.q_dim * c.hidden_size
+                                          + 3 * c.hidden_size * c.intermediate_size)
+
+    def prefill_flops(self, T):
+        c = self.config
+        return (T * self.linear_flops_per_token() + c.num_hidden_layers * 4 * c.num_attention_heads * c.head_dim * T * T / 2
+                + 2 * self.vocab * c.hidden_size)
+
+    def prefill_run(self, T, reps=3, warm=3):
+        """One prompt of T tokens in one step, back to back; the median of `reps` after `warm`."""
+        torch, runner, StepEntry = self.torch, self.runner, self.mods["StepEntry"]
+        toks = [self.rng.randrange(self.vocab) for _ in range(T)]
+        times = []
+        for i in range(warm + reps):
+            rid = f"pf{T}_{i}"
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step([StepEntry(rid, toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.end(rid)
+            if i >= warm:
+                times.append(e0.elapsed_time(e1))
+        return statistics.median(times)
+
+    def mixed_flops(self, n_decode, n_portions, portion):
+        c = self.config
+        rows = n_decode + n_portions * portion
+        att = 4 * c.num_attention_heads * c.head_dim * (n_decode * self.context + n_portions * portion * portion / 2)
+        return rows * self.linear_flops_per_token() + c.num_hidden_layers * att + 2 * (n_decode + n_portions) * self.vocab * c.hidden_size
+
+    def mixed_run(self, n_decode, n_portions, portion, steps, warmup):
+        """The general step: `n_portions` prompt portions of `portion` tokens (each the start of a new prompt)
+        beside `n_decode` requests decoding at the context length, one logits row each. Device-timed."""
+        torch, runner, ops, StepEntry = self.torch, self.runner, self.mods["ops"], self.mods["StepEntry"]
+        ids = [f"mx{i}" for i in range(n_decode)]
+        for rid in ids:
+            self.fake_context(rid, self.context)
+        tok = [[self.rng.randrange(self.vocab)] for _ in ids]
+        parts = [[self.rng.randrange(self.vocab) for _ in range(portion)] for _ in range(n_portions)]
+        out = torch.empty(n_decode + n_portions, dtype=torch.int32, device=self.dev)
+
+        def one(i):
+            entries = [StepEntry(rid, t, [0]) for rid, t in zip(ids, tok)]
+            entries += [StepEntry(f"mxp{i}_{j}", p, [portion - 1]) for j, p in enumerate(parts)]
+            ops.argmax(out, runner.step(entries))
+            for j in range(n_portions):
+                runner.end(f"mxp{i}_{j}")
+
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            one(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        for rid in ids:
+            runner.end(rid)
+        return e0.elapsed_time(e1) / steps
+
+    def mixed_e2e(self, n_decode, n_portions, portion, steps, warmup):
+        """The same step through LLM.step(): every call the host submits `n_portions` new prompts of `portion`
+        token ids (one token each to generate) and reads the step's sampled ids. Returns seconds per step."""
+        torch, LLM, SamplingParams = self.torch, self.mods["LLM"], self.mods["SamplingParams"]
+        llm = LLM(config=self.config, runner=self.runner, max_prefill_tokens=max(PREFILL_TOKENS, n_portions * portion),
+                  max_decode_batch=n_decode + 2 * n_portions)
+        long = warmup + steps + 16 + n_decode * -(-self.context // PREFILL_TOKENS)
+        for _ in range(n_decode):
+            llm.submit([self.rng.randrange(self.vocab) for _ in range(self.context)], SamplingParams(ignore_eos=True), long)
+        for _ in range(n_decode * -(-self.context // PREFILL_TOKENS) + 8):
+            if len(llm.scheduler.active) == n_decode and not llm.scheduler.prefilling:
+                break
+            for ev in llm.step():
+                if ev.kind in ("error", "rejected"):
+                    raise RuntimeError(f"bench: request {ev.request_id} {ev.kind}: {ev.reason}")
+        if len(llm.scheduler.active) != n_decode:
+            raise RuntimeError(f"bench: only {len(llm.scheduler.active)} of {n_decode} requests decode after their prompts")
+
+        def one():
+            for _ in range(n_portions):
+                llm.submit([self.rng.randrange(self.vocab) for _ in range(portion)], SamplingParams(ignore_eos=True), 1)
+            return sum(1 for ev in llm.step() if ev.kind == "token")
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n_tok = 0
+        for _ in range(steps):
+            n_tok += one()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        for a in list(llm.scheduler.active) + [p for p in llm.scheduler.prefilling]:
+            llm.cancel(a.req.request_id)
+        while llm.has_work():
+            llm.step()
+        return dt / steps, n_tok / steps
+
+
+def measure_size(torch, mods, key, args, peaks, mixed: bool):
+    """Decode at batch 1/8/64, a 2,048-token prefill and (0.6B) the mixed step at one of the other sizes, with its
+    own clock sample. Returns (flat points, grouped record)."""
+    name, cfg = MODELS[key]
+    steps, warm = max(16, args.steps // 4), max(3, args.warmup // 2)
+    room = 2 * (steps + warm) + 64 * -(-CONTEXT // PREFILL_TOKENS) + 64
+    b = Bench(torch, mods, cfg, args.dtype, 64, room, CONTEXT)
+    sampler = ClockSampler(0)
+    sampler.start()
+    flat, rec = {}, {"model": name, "layers": b.config.num_hidden_layers}
+    try:
+        for batch in (1, 8, 64):
+            ms, _ = b.decode_run(batch, steps, warm)
+            gbs = b.decode_bytes(batch, steps, warm) / (ms * 1e-3) / 1e9
+            flat[f"{key}_decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
+            flat[f"{key}_decode_b{batch}_hbm_frac"] = round(gbs / peaks["hbm_gbs"], 4)
+        pf_ms = b.prefill_run(PREFILL_TOKENS)
+        flat[f"{key}_prefill_{PREFILL_TOKENS}"] = round(PREFILL_TOKENS * 1000.0 / pf_ms, 1)
+        flat[f"{key}_prefill_{PREFILL_TOKENS}_frac"] = round(b.prefill_flops(PREFILL_TOKENS) / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
+        if mixed:
+            nd, npor, por = 56, 8, 512
+            rows = nd + npor * por
+            ms = b.mixed_run(nd, npor, por, steps, warm)
+            flat[f"mixed_{key}"] = round(rows * 1000.0 / ms, 1)
+            flat[f"mixed_{key}_ms"] = round(ms, 3)
+            flat[f"mixed_{key}_frac"] = round(b.mixed_flops(nd, npor, por) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
+            s_step, tok_step = b.mixed_e2e(nd, npor, por, steps, warm)
+            flat[f"mixed_{key}_e2e"] = round(rows / s_step, 1)
+            flat[f"mixed_{key}_e2e_ms"] = round(s_step * 1000, 3)
+            rec["mixed"] = {"rows_per_step": rows, "logit_rows": nd + npor, "sampled_per_step_e2e": round(tok_step, 1),
+                            "what": f"{npor} prompt portions of {por} tokens (each the start of a prompt) beside {nd} "
+                                    f"requests decoding at context {CONTEXT}; tokens/s counts all {rows} rows"}
+    finally:
+        clocks = sampler.stop()
+        b.close()
+    flat[f"{key}_sm_mhz"] = clocks.get("sm_mhz")
+    rec.update({k[len(key) + 1:] if k.startswith(key + "_") else k: v for k, v in flat.items()})
+    rec["clocks"] = clocks
+    return flat, rec
+
+
 def main() -> int:
     global CONTEXT
     ap = argparse.ArgumentParser()
@@ -180,7 +404,13 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--model", default="8b", choices=sorted(MODELS), help="layer sizes (default: the headline 8B)")
-    ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points and the prefill")
+    ap.add_argument("--skip-points", action="store_true", help="skip the batch-1/64 points, the prefills and the other sizes")
+    ap.add_argument("--sizes", default=None,
+                    help="other sizes to measure after the headline one, comma separated (default: 0.6b,32b when the headline "
+                         "is the full 8B model in bfloat16; 'none' to skip)")
+    ap.add_argument("--long-prefill", default=None,
+                    help="further prefill lengths at the headline sizes, comma separated (default 8192,32768 with the "
+                         "full model; 'none' to skip)")
     ap.add_argument("--batch-invariant", action="store_true",
                     help="measure under the batch-invariant numeric policy (one product kernel, fixed key slices)")
     ap.add_argument("--timeline", default=None, metavar="FILE",
@@ -189,7 +419,7 @@ def main() -> int:
     ap.add_argument("--sampler", action="store_true",
                     help="time the sampling kernels alone (vocabulary of the model, --batch rows, recorded into a CUDA "
                          "graph): one JSON line of microseconds per call and setting, then exit")
-    ap.add_argument("--profile", choices=["decode", "prefill", "sampler"], default=None,
+    ap.add_argument("--profile", choices=["decode", "prefill", "mixed", "sampler"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
     args = ap.parse_args()
@@ -215,6 +445,8 @@ def main() -> int:
     from openinfer_b200.kernels import ops
     from openinfer_b200.sampling.params import SamplingParams
 
+    mods = {"resolve_architecture": resolve_architecture, "LLM": LLM, "ModelRunner": ModelRunner, "StepEntry": StepEntry,
+            "klib": klib, "ops": ops, "SamplingParams": SamplingParams}
     if args.batch_invariant:
         from openinfer_b200.kernels import policy
         policy.set_batch_invariant(True)
@@ -222,64 +454,27 @@ def main() -> int:
         return sampler_mode(args, torch, ops, MODELS[args.model][1]["vocab_size"])
     peaks, peaks_src = read_peaks()
     model_name, model_cfg = MODELS[args.model]
-    cfg_dict = dict(model_cfg)
-    full_layers = cfg_dict["num_hidden_layers"]
-    if args.layers:
-        cfg_dict["num_hidden_layers"] = args.layers
-    cfg_dict["max_position_embeddings"] = max(cfg_dict["max_position_embeddings"],
-                                              CONTEXT + args.steps + args.warmup + max(args.batch, 8) * -(-CONTEXT // PREFILL_TOKENS) + 128)
-    config = resolve_architecture(cfg_dict).config_cls.from_dict(cfg_dict)
     K, W, B = args.steps, args.warmup, args.batch
+    headline_full = args.model == "8b" and not args.layers and args.dtype == "bfloat16" and not args.batch_invariant
+    long_prefill = [] if args.skip_points else \
+        ([8192, 32768] if headline_full else []) if args.long_prefill is None else \
+        [int(x) for x in args.long_prefill.split(",") if x and x != "none"]
+    sizes = [] if args.skip_points else \
+        (["0.6b", "32b"] if headline_full else []) if args.sizes is None else \
+        [x for x in args.sizes.split(",") if x and x != "none"]
+    for x in sizes:
+        if x not in MODELS:
+            ap.error(f"--sizes: unknown size {x!r}")
     max_batch = B if args.skip_points else max(B, 64)
     # Through the entry point the requests' prompts are computed one portion a step, and a request that has its
     # prompt decodes while the others' are still computed: it must not finish before all of them decode.
     e2e_prompt_steps = max(B, 8) * -(-CONTEXT // PREFILL_TOKENS)
     e2e_new_tokens = W + K + e2e_prompt_steps + 8
-    per_req = CONTEXT + e2e_new_tokens + 16 + 2 * PAGE
-    pool_tokens = max_batch * per_req + PREFILL_TOKENS + 64
-    dev = torch.device("cuda:0")
-    runner = ModelRunner.build(config, 0, dtype=args.dtype, device=dev, page_size=PAGE,
-                               max_tokens=pool_tokens, max_requests=max_batch + 8)
-    runner.cuda_graph = True
-    cache = runner.cache
-    esize = 2 if args.dtype == "bfloat16" else 4
-    for g in cache.groups:  # contexts are not computed but filled: decode reads the same bytes
-        g.tensor.normal_(0.0, 0.5)
-    rng = random.Random(0)
-    vocab = config.vocab_size
-
-    def fake_context(rid, n):
-        cache.open(rid)
-        cache.reserve(rid, n)
-        cache.commit(rid)
-
-    def decode_run(batch, steps, warmup):
-        """Device-timed decode: `steps` steps of `batch` requests at context CONTEXT."""
-        ids = [f"b{batch}_{i}" for i in range(batch)]
-        for rid in ids:
-            fake_context(rid, CONTEXT)
-        toks = [[rng.randrange(vocab)] for _ in ids]
-        out = torch.empty(batch, dtype=torch.int32, device=dev)
-
-        def one():
-            logits = runner.step([StepEntry(rid, t, [0]) for rid, t in zip(ids, toks)])
-            ops.argmax(out, logits)
-
-        for _ in range(warmup):
-            one()
-        torch.cuda.synchronize()
-        l0 = klib.launches
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            one()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        launches = klib.launches - l0
-        for rid in ids:
-            runner.end(rid)
-        return ms, launches
+    bench = Bench(torch, mods, model_cfg, args.dtype, max_batch, e2e_new_tokens, CONTEXT,
+                  prefill_room=max([PREFILL_TOKENS] + long_prefill), layers=args.layers)
+    runner, config, cache, dev, rng, vocab = bench.runner, bench.config, bench.cache, bench.dev, bench.rng, bench.vocab
+    full_layers = bench.full_layers
+    fake_context = bench.fake_context
 
     if args.timeline:
         from torch.profiler import ProfilerActivity, profile
@@ -329,6 +524,21 @@ def main() -> int:
                 ops.argmax(out_ids, logits)
             torch.cuda.synchronize()
             torch.cuda.profiler.stop()
+        elif args.profile == "mixed":
+            ids = [f"p{i}" for i in range(56)]
+            for rid in ids:
+                fake_context(rid, CONTEXT)
+            parts = [[rng.randrange(vocab) for _ in range(512)] for _ in range(8)]
+            for i in range(W + 1):
+                if i == W:
+                    torch.cuda.synchronize()
+                    torch.cuda.profiler.start()
+                runner.step([StepEntry(rid, [1], [0]) for rid in ids]
+                            + [StepEntry(f"pp{i}_{j}", p, [511]) for j, p in enumerate(parts)])
+                torch.cuda.synchronize()
+                for j in range(8):
+                    runner.end(f"pp{i}_{j}")
+            torch.cuda.profiler.stop()
         else:
             toks = [rng.randrange(vocab) for _ in range(PREFILL_TOKENS)]
             for i in range(W + 1):
@@ -344,13 +554,12 @@ def main() -> int:
 
     sampler = ClockSampler(0)
     sampler.start()
-    ms_step, launches = decode_run(B, K, W)
+    ms_step, launches = bench.decode_run(B, K, W)
     clocks = sampler.stop()
     value = B * 1000.0 / ms_step
 
     # roofline of the decode step: every weight once + the cache of the live requests
-    kv_tokens = B * (CONTEXT + W + K // 2)
-    step_bytes = runner.model.weight_bytes() + kv_tokens * cache.bytes_per_token(esize)
+    step_bytes = bench.decode_bytes(B, K, W)
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "peaks": peaks_src}
@@ -382,7 +591,9 @@ def main() -> int:
            "ms_per_step": round(e2e_s * 1000 / max(K - 1, 1), 4)}
     # bytes of step metadata copied host->device each step (token ids, positions, block tables, ...)
     e2e["h2d_bytes_per_step"] = int(runner._staging_last_bytes) if hasattr(runner, "_staging_last_bytes") else None
+    del llm
 
+    weights_gb = runner.model.weight_bytes() / 1e9
     out = {
         "metric": f"decode tokens/s ({model_name}, random weights, batch {B}, context {CONTEXT})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
@@ -396,7 +607,8 @@ def main() -> int:
             "intermediate": config.intermediate_size, "vocab": config.vocab_size,
             "rope_theta": config.rope_theta, "rms_norm_eps": config.rms_norm_eps, "tied": config.tie_word_embeddings,
             "global_batch": B, "seq_len": CONTEXT, "kv_page": PAGE, "new_tokens": K,
-            "parallelism": "single GPU", "l2": "weights (>15 GB) exceed L2; no flush needed",
+            "parallelism": "single GPU",
+            "l2": f"no flush: a step reads {step_bytes / 1e9:.2f} GB ({weights_gb:.2f} GB of weights), L2 holds 0.126 GB",
         },
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
     }
@@ -407,30 +619,14 @@ def main() -> int:
         points = {}
         for b in (1, 64):
             steps = max(16, K // 2)
-            ms_b, _ = decode_run(b, steps, max(3, W // 2))
+            ms_b, _ = bench.decode_run(b, steps, max(3, W // 2))
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
         out["points"] = points
 
         # prefill of one 2,048-token prompt in one step
-        toks = [rng.randrange(vocab) for _ in range(PREFILL_TOKENS)]
-        times = []
-        for i in range(3 + 3):
-            rid = f"pf{i}"
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            runner.step([StepEntry(rid, toks, [PREFILL_TOKENS - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            runner.end(rid)
-            if i >= 3:
-                times.append(e0.elapsed_time(e1))
-        pf_ms = statistics.median(times)
-        L, H, I = config.num_hidden_layers, config.hidden_size, config.intermediate_size
-        dq, dkv = config.q_dim, config.kv_dim
         T = PREFILL_TOKENS
-        flops = L * (2 * T * H * (dq + 2 * dkv) + 2 * T * dq * H + 2 * T * H * 2 * I + 2 * T * I * H
-                     + 4 * config.num_attention_heads * config.head_dim * T * T / 2) + 2 * vocab * H
+        pf_ms = bench.prefill_run(T)
+        flops = bench.prefill_flops(T)
         peak_tf = peaks["bf16_tflops"] if args.dtype == "bfloat16" else 75.0
         out["prefill"] = {"value": round(T * 1000.0 / pf_ms, 1), "tokens": T, "ms": round(pf_ms, 3),
                           "frac": round(flops / (pf_ms * 1e-3) / (peak_tf * 1e12), 4), "peaks": peaks_src}
@@ -438,6 +634,18 @@ def main() -> int:
             # the step is timed back to back after the decode runs, i.e. under the power cap: also against the
             # library product's SUSTAINED rate (a burst after idle runs this step in 23.6 ms instead of 26.5)
             out["prefill"]["frac_of_sustained"] = round(flops / (pf_ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)
+        for T in long_prefill:
+            ms_t = bench.prefill_run(T, reps=2, warm=1)
+            points[f"prefill_{T}"] = round(T * 1000.0 / ms_t, 1)
+            points[f"prefill_{T}_frac"] = round(bench.prefill_flops(T) / (ms_t * 1e-3) / (peak_tf * 1e12), 4)
+    runner = cache = None
+    bench.close()
+    if sizes:
+        out["sizes"] = {}
+        for key in sizes:
+            flat, rec = measure_size(torch, mods, key, args, peaks, mixed=(key == "0.6b"))
+            out["points"].update(flat)
+            out["sizes"][key] = rec
     print(json.dumps(out))
     return 0
 

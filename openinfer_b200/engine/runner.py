@@ -170,12 +170,13 @@ class ModelRunner:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < vocab):
-                    raise StepError(f"request {e.request_id!r}: token id {t} outside [0, {vocab})")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {e.request_id!r}: wanted place {w} outside its {n} tokens")
+            lo, hi = (min(e.tokens), max(e.tokens)) if n > 1 else (e.tokens[0], e.tokens[0])
+            if not (0 <= int(lo) and int(hi) < vocab):
+                bad = next(t for t in e.tokens if not 0 <= int(t) < vocab)
+                raise StepError(f"request {e.request_id!r}: token id {bad} outside [0, {vocab})")
+            if len(e.want) and not (0 <= int(min(e.want)) and int(max(e.want)) < n):
+                bad = next(w for w in e.want if not 0 <= int(w) < n)
+                raise StepError(f"request {e.request_id!r}: wanted place {bad} outside its {n} tokens")
             held = self.cache.num_tokens(e.request_id) if self.cache.has(e.request_id) else 0
             if max_pos and held + n > max_pos:
                 raise StepError(
