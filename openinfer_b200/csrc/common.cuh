@@ -113,6 +113,16 @@ inline void oi_launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t s
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 
+// Gate activations of a gated feed-forward, act(gate) * up. The codes are part of the C interface.
+#define OI_ACT_NONE 0
+#define OI_ACT_SILU 1        // g * sigmoid(g)
+#define OI_ACT_GELU_TANH 2   // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) = g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
+template <bool kFastExp>
+__device__ __forceinline__ float gate_act(float g, int act) {
+  const float t = act == OI_ACT_GELU_TANH ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+  return g / (1.f + (kFastExp ? __expf(-t) : expf(-t)));
+}
+
 template <typename T>
 __device__ __forceinline__ T from_f32(float x);
 template <>

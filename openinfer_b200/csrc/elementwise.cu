@@ -305,26 +305,53 @@ OI_API int oi_add_inplace(void* x, const void* delta, int dtype, long long n, vo
 }
 
 // ---------------------------------------------------------------------------
-// SiLU * mul on a fused [rows, 2*inter] gate|up buffer: out[r, i] = silu(g_i) * u_i.
+// x = x * scale, then (cap > 0) x = cap * tanh(x / cap): an embedding scale, or the soft cap of logits.
+// float32 math, one rounding.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void scale_cap_kernel(T* __restrict__ x, size_t n, float scale, float cap) {
+  pdl_start();
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = to_f32(x[i]) * scale;
+    if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+    x[i] = from_f32<T>(v);
+  }
+}
+
+OI_API int oi_scale_cap(void* x, int dtype, long long n, float scale, float cap, void* stream) {
+  OI_REQUIRE(n >= 0 && cap >= 0.f, "scale_cap: bad size %lld or cap %f", n, (double)cap);
+  if (n == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+  if (dtype == OI_F32) oi_launch(scale_cap_kernel<float>, blocks, 256, 0, s, (float*)x, (size_t)n, scale, cap);
+  else if (dtype == OI_BF16) oi_launch(scale_cap_kernel<bf16>, blocks, 256, 0, s, (bf16*)x, (size_t)n, scale, cap);
+  else OI_REQUIRE(false, "scale_cap: unknown dtype code %d", dtype);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// ---------------------------------------------------------------------------
+// act * mul on a fused [rows, 2*inter] gate|up buffer: out[r, i] = act(g_i) * u_i, act = SiLU or tanh-GELU.
 // Layout of a row: blocks of `block` gate values followed by the `block` up values of the same
 // indices; block == inter is the plain [all gates | all ups] layout. (A product kernel whose tile
 // holds a gate block and its up block side by side can form the activation in its epilogue.)
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int block, size_t n) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int block, size_t n, int act) {
   pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i - r * inter;
     const size_t gi = r * 2 * inter + (c / block) * 2 * block + (c % block);
     const float g = to_f32(gate_up[gi]);
     const float u = to_f32(gate_up[gi + block]);
-    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    out[i] = from_f32<T>(gate_act<false>(g, act) * u);
   }
 }
 
 // 8 bf16 per thread when inter and block are multiples of 8
 __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up,
-                                       int inter8, int block8, size_t n8) {
+                                       int inter8, int block8, size_t n8, int act) {
   pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter8, c = i - r * inter8;
@@ -339,13 +366,14 @@ __global__ void silu_mul_bf16x8_kernel(uint4* __restrict__ out, const uint4* __r
     for (int k = 0; k < 4; ++k) {
       const float2 g = __bfloat1622float2(g2[k]);
       const float2 u = __bfloat1622float2(u2[k]);
-      o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+      o2[k] = __floats2bfloat162_rn(gate_act<false>(g.x, act) * u.x, gate_act<false>(g.y, act) * u.y);
     }
     out[i] = ov;
   }
 }
 
-OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, int block, void* stream) {
+OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int inter, int block, int act, void* stream) {
+  OI_REQUIRE(act == OI_ACT_SILU || act == OI_ACT_GELU_TANH, "silu_mul: unknown activation code %d", act);
   OI_REQUIRE(rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d inter=%d", rows, inter);
   OI_REQUIRE(block > 0 && inter % block == 0, "silu_mul: block %d does not divide inter %d", block, inter);
   if (rows == 0) return OI_OK;
@@ -354,11 +382,11 @@ OI_API int oi_silu_mul(void* out, const void* gate_up, int dtype, int rows, int 
   if (dtype == OI_BF16 && inter % 8 == 0 && block % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
     const size_t n8 = n / 8;
     const int blocks = (int)((n8 + 255) / 256 > 148 * 16 ? 148 * 16 : (n8 + 255) / 256);
-    oi_launch(silu_mul_bf16x8_kernel, blocks, 256, 0, s, (uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8);
+    oi_launch(silu_mul_bf16x8_kernel, blocks, 256, 0, s, (uint4*)out, (const uint4*)gate_up, inter / 8, block / 8, n8, act);
   } else {
     const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-    if (dtype == OI_F32) oi_launch(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, inter, block, n);
-    else if (dtype == OI_BF16) oi_launch(silu_mul_kernel<bf16>, blocks, 256, 0, s, (bf16*)out, (const bf16*)gate_up, inter, block, n);
+    if (dtype == OI_F32) oi_launch(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, inter, block, n, act);
+    else if (dtype == OI_BF16) oi_launch(silu_mul_kernel<bf16>, blocks, 256, 0, s, (bf16*)out, (const bf16*)gate_up, inter, block, n, act);
     else OI_REQUIRE(false, "silu_mul: unknown dtype code %d", dtype);
   }
   OI_CHECK_LAUNCH();

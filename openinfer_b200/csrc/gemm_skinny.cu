@@ -60,15 +60,13 @@ __device__ __forceinline__ uint4 lds128(unsigned addr) {
   return v;
 }
 
-__device__ __forceinline__ float silu(float g) { return g / (1.f + expf(-g)); }
-
 // NT: token tiles of 8 (M <= 8 * NT). kCluster: CTAs along K add up through distributed shared memory.
 // The weight ring is primed BEFORE waiting for the kernel that produces x (programmatic dependent
 // launch), so the first 40 KB of W per CTA stream in under its tail.
 template <int NT, typename TOut, bool kSiluMul, bool kCluster>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict__ x, long long ldx,
-                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int act_block) {
+                   const bf16* __restrict__ W, long long ldw, int M, int N, int K, int k_slice, int act_block, int act) {
   pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int stride = row_stride_elems(k_slice);                 // elements per token row
@@ -132,7 +130,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, long long ldc, const bf16* __restrict
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 gg = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-            o2[e] = __floats2bfloat162_rn(silu(gg.x) * u.x, silu(gg.y) * u.y);
+            o2[e] = __floats2bfloat162_rn(gate_act<false>(gg.x, act) * u.x, gate_act<false>(gg.y, act) * u.y);
           }
         } else {
           val = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k0 + v * 8);
@@ -219,7 +217,7 @@ size_t smem_bytes(int NT, int k_slice) {
 
 template <int NT, typename TOut, bool kSiluMul>
 int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N,
-           int K, int csize, int act_block, cudaStream_t s) {
+           int K, int csize, int act_block, int act, cudaStream_t s) {
   const int k_slice = K / csize;
   const size_t smem = smem_bytes(NT, k_slice);
   static size_t configured[2] = {0, 0};   // largest dynamic shared memory set so far, per kernel variant
@@ -232,14 +230,14 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
       configured[1] = smem;
     }
     oi_launch_cluster(kernel, grid, kWarps * 32, smem, s, csize, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K,
-                      k_slice, act_block);
+                      k_slice, act_block, act);
   } else {
     auto kernel = gemm_skinny_kernel<NT, TOut, kSiluMul, false>;
     if (smem > configured[0]) {
       OI_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured[0] = smem;
     }
-    oi_launch(kernel, grid, kWarps * 32, smem, s, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, act_block);
+    oi_launch(kernel, grid, kWarps * 32, smem, s, (TOut*)out, ldc, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, k_slice, act_block, act);
   }
   OI_CHECK_LAUNCH();
   return OI_OK;
@@ -249,9 +247,10 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
 
 // silu_mul != 0: x is a fused [M, 2K] gate|up buffer laid out in blocks of `silu_mul` gate values
 // followed by their up values (silu_mul == K: all gates, then all ups) and the activation
-// silu(gate) * up is formed on the fly. cluster_size in {1, 2, 4, 8}: the number of K slices (CTAs per cluster).
+// act(gate) * up (act: OI_ACT_SILU or OI_ACT_GELU_TANH) is formed on the fly. cluster_size in {1, 2, 4, 8}: the number of K slices (CTAs per cluster).
 OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
-                          long long ldw, int M, int N, int K, int silu_mul, int cluster_size, void* stream) {
+                          long long ldw, int M, int N, int K, int silu_mul, int act, int cluster_size, void* stream) {
+  OI_REQUIRE(silu_mul == 0 || act == OI_ACT_SILU || act == OI_ACT_GELU_TANH, "gemm_skinny: unknown activation code %d", act);
   OI_REQUIRE(M >= 1 && M <= 16, "gemm_skinny: M=%d outside 1..16", M);
   OI_REQUIRE(N >= 1 && K >= 32, "gemm_skinny: bad sizes N=%d K=%d", N, K);
   OI_REQUIRE(cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8,
@@ -264,7 +263,7 @@ OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x
   const size_t smem = smem_bytes(NT, K / cluster_size);
   OI_REQUIRE(smem <= 200 * 1024, "gemm_skinny: K slice %d needs %zu bytes of shared memory", K / cluster_size, smem);
   cudaStream_t s = (cudaStream_t)stream;
-#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, silu_mul, s)
+#define OI_SKINNY(NT_, T_, S_) return launch<NT_, T_, S_>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, silu_mul, act, s)
   if (out_dtype == OI_BF16) {
     if (NT == 1) { if (silu_mul) OI_SKINNY(1, bf16, true); else OI_SKINNY(1, bf16, false); }
     else         { if (silu_mul) OI_SKINNY(2, bf16, true); else OI_SKINNY(2, bf16, false); }

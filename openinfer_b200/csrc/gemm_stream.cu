@@ -57,11 +57,11 @@ struct Layout {
 
 // kSiluMul: W's rows come in blocks of 64 gate rows followed by the 64 up rows of the same indices, so a
 // tile holds gate rows in lanes 0-63 of the accumulator and their up rows in lanes 64-127; the result
-// is out[M, N / 2] = silu(gate) * up, formed where the K slices are added up.
+// is out[M, N / 2] = act(gate) * up (act: OI_ACT_SILU or OI_ACT_GELU_TANH), formed where the K slices are added up.
 template <int BN, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                   TOut* __restrict__ out, long long ldc, int M, int N, int num_kb, int kb_per_rank) {
+                   TOut* __restrict__ out, long long ldc, int M, int N, int num_kb, int kb_per_rank, int act) {
   pdl_trigger();   // the next kernel may be scheduled now: it reads nothing of ours before we are done
   using L = Layout<BN>;
   constexpr int kStages = L::kStages;
@@ -223,7 +223,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         sum += recv[(size_t)(q * BN + m) * share + l];
         if (kSiluMul) up += recv[(size_t)(q * BN + m) * share + rows_mine + l];
       }
-      if (kSiluMul) sum = sum / (1.f + __expf(-sum)) * up;
+      if (kSiluMul) sum = gate_act<true>(sum, act) * up;
       if (o0 + l < n_out) out[(size_t)m * ldc + o0 + l] = from_f32<TOut>(sum);
     }
   } else {
@@ -242,7 +242,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 template <int BN, typename TOut, bool kSiluMul>
 int launch(void* out, long long ldc, const void* x, long long ldx, const void* W, long long ldw, int M, int N, int K,
-           int csize, cudaStream_t s) {
+           int csize, int act, cudaStream_t s) {
   using L = Layout<BN>;
   CUtensorMap mw, mx;
   int rc = tc::make_map_2d_bf16(&mw, W, N, K, ldw, BM);
@@ -258,7 +258,7 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
   const int num_kb = (K + BK - 1) / BK;
   const int kb_per_rank = (num_kb + csize - 1) / csize;
   oi_launch_cluster(kernel, dim3(csize, (N + BM - 1) / BM, 1), kThreads, L::kTotal, s, csize, mw, mx, (TOut*)out, ldc, M, N,
-                    num_kb, kb_per_rank);
+                    num_kb, kb_per_rank, act);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -268,10 +268,13 @@ int launch(void* out, long long ldc, const void* x, long long ldx, const void* W
 // x: [M, K] bfloat16 (row stride ldx), W: [N, K] bfloat16 (row stride ldw), out: [M, N] bfloat16 or
 // float32 (row stride ldc), 1 <= M <= 128. K and the row strides of x and W must be multiples of 8
 // elements and their bases 16-byte aligned (TMA). cluster_size in {1, 2, 4, 8}: the number of K
-// slices; it must not exceed the number of 64-wide k blocks. silu_mul != 0 (N a multiple of 128): W's rows
-// come in blocks of 64 gate rows followed by their 64 up rows and out is [M, N / 2] = silu(gate) * up.
+// slices; it must not exceed the number of 64-wide k blocks. act != 0 (OI_ACT_SILU or OI_ACT_GELU_TANH; N a
+// multiple of 128): W's rows come in blocks of 64 gate rows followed by their 64 up rows and out is
+// [M, N / 2] = act(gate) * up.
 OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
-                          long long ldw, int M, int N, int K, int cluster_size, int silu_mul, void* stream) {
+                          long long ldw, int M, int N, int K, int cluster_size, int act, void* stream) {
+  const int silu_mul = act;
+  OI_REQUIRE(act >= OI_ACT_NONE && act <= OI_ACT_GELU_TANH, "gemm_stream: unknown activation code %d", act);
   OI_REQUIRE(M >= 1 && M <= 128, "gemm_stream: M=%d outside 1..128", M);
   OI_REQUIRE(N >= 1 && K >= 8, "gemm_stream: bad sizes N=%d K=%d", N, K);
   OI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_stream: K and row strides must be multiples of 8");
@@ -286,10 +289,10 @@ OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x
   cudaStream_t s = (cudaStream_t)stream;
 #define OI_STREAM(BN_)                                                                                            \
   do {                                                                                                            \
-    if (out_dtype == OI_BF16 && silu_mul) return launch<BN_, bf16, true>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s);  \
-    if (out_dtype == OI_BF16) return launch<BN_, bf16, false>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
-    if (out_dtype == OI_F32 && silu_mul) return launch<BN_, float, true>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s);  \
-    if (out_dtype == OI_F32) return launch<BN_, float, false>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, s); \
+    if (out_dtype == OI_BF16 && silu_mul) return launch<BN_, bf16, true>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, act, s);  \
+    if (out_dtype == OI_BF16) return launch<BN_, bf16, false>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, 0, s); \
+    if (out_dtype == OI_F32 && silu_mul) return launch<BN_, float, true>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, act, s);  \
+    if (out_dtype == OI_F32) return launch<BN_, float, false>(out, ldc, x, ldx, W, ldw, M, N, K, cluster_size, 0, s); \
   } while (0)
   if (M <= 16) OI_STREAM(16);
   else if (M <= 32) OI_STREAM(32);

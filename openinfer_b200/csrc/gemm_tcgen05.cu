@@ -76,7 +76,7 @@ __device__ __forceinline__ void store_32(TOut* dst, const float (&a)[32], int va
 
 template <int BN, typename TOut, bool kSiluMul>
 __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __restrict__ C, long long ldc, int row, int n0,
-                                                  int M, int N) {
+                                                  int M, int N, int act) {
   auto load = [&](int col, float (&a)[32]) {
     unsigned v[32];
     tmem_ld32(tmem_acc + (unsigned)col, v);
@@ -95,7 +95,7 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
       load(half * 128 + 64 + c, u);
       if (row < M) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) g[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
+        for (int e = 0; e < 32; ++e) g[e] = gate_act<true>(g[e], act) * u[e];
         store_32(C + (size_t)row * ldc + o0 + cc, g, n_out - (o0 + cc));
       }
     }
@@ -118,7 +118,7 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
 template <int BN, int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+                    TOut* __restrict__ C, long long ldc, int M, int N, int K, int act) {
   pdl_start();
   using L = Smem<BN, kStages>;
   extern __shared__ unsigned char smem_raw[];
@@ -219,7 +219,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
-      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N);
+      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act);
       // this warp has read its part of the accumulator: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -260,7 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int kStages, typename TOut, bool kSiluMul>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         TOut* __restrict__ C, long long ldc, int M, int N, int K) {
+                         TOut* __restrict__ C, long long ldc, int M, int N, int K, int act) {
   pdl_start();
   constexpr int BN = 256, kPairM = 256;
   using L = Smem<128, kStages>;             // per CTA: 128 rows of A and 128 rows of W per stage
@@ -363,7 +363,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int m0 = (tile % m_tiles) * kPairM + (int)rank * 128, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
-      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N);
+      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty_bar(a), 0));
@@ -389,7 +389,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // ------------------------------------------------------------------------------------------------
 template <int BN, int kStages, typename TOut, bool kSiluMul = false>
 int launch(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
-           cudaStream_t s) {
+           cudaStream_t s, int act = 0) {
   CUtensorMap ma, mb;
   int rc = tc::make_map_2d_bf16(&ma, A, M, K, lda, BM);
   OI_REQUIRE(rc == 0, "gemm_tcgen05: tensor map for A failed (%d; -1: cuTensorMapEncodeTiled is not available)", rc);
@@ -409,14 +409,14 @@ int launch(void* C, long long ldc, const void* A, long long lda, const void* W, 
     OI_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  oi_launch(kernel, tiles < sm_count ? tiles : sm_count, kThreads, smem, s, ma, mb, (TOut*)C, ldc, M, N, K);
+  oi_launch(kernel, tiles < sm_count ? tiles : sm_count, kThreads, smem, s, ma, mb, (TOut*)C, ldc, M, N, K, act);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
 
 template <int kStages, typename TOut, bool kSiluMul = false>
 int launch_pair(void* C, long long ldc, const void* A, long long lda, const void* W, long long ldw, int M, int N, int K,
-                cudaStream_t s) {
+                cudaStream_t s, int act = 0) {
   CUtensorMap ma, mb;
   int rc = tc::make_map_2d_bf16(&ma, A, M, K, lda, 128);
   OI_REQUIRE(rc == 0, "gemm_tcgen05: tensor map for A failed (%d; -1: cuTensorMapEncodeTiled is not available)", rc);
@@ -437,7 +437,7 @@ int launch_pair(void* C, long long ldc, const void* A, long long lda, const void
   }
   const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  oi_launch_cluster(kernel, 2 * pairs, kThreads, smem, s, 2, ma, mb, (TOut*)C, ldc, M, N, K);
+  oi_launch_cluster(kernel, 2 * pairs, kThreads, smem, s, 2, ma, mb, (TOut*)C, ldc, M, N, K, act);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -447,10 +447,12 @@ int launch_pair(void* C, long long ldc, const void* A, long long lda, const void
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw; C: [M, N] bfloat16 or
 // float32, row stride ldc. K and the row strides must be multiples of 8 elements and the bases
 // 16-byte aligned (TMA). tile_n: 256 or 128.
-// silu_mul != 0 (tile_n 256, bfloat16 out, N a multiple of 256): W's rows come in blocks of 64 gate
-// rows followed by their 64 up rows, and C is [M, N / 2] = silu(gate) * up.
+// act != 0 (OI_ACT_SILU or OI_ACT_GELU_TANH; tile_n 256, bfloat16 out, N a multiple of 256): W's rows come in
+// blocks of 64 gate rows followed by their 64 up rows, and C is [M, N / 2] = act(gate) * up.
 OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W,
-                           long long ldw, int M, int N, int K, int tile_n, int silu_mul, void* stream) {
+                           long long ldw, int M, int N, int K, int tile_n, int act, void* stream) {
+  const int silu_mul = act;
+  OI_REQUIRE(act >= OI_ACT_NONE && act <= OI_ACT_GELU_TANH, "gemm_tcgen05: unknown activation code %d", act);
   OI_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
   OI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and row strides must be multiples of 8");
   OI_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tcgen05: operands must be 16-byte aligned");
@@ -459,7 +461,7 @@ OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, l
   if (silu_mul) {
     OI_REQUIRE(tile_n == 256 && c_dtype == OI_BF16 && N % 256 == 0,
                "gemm_tcgen05: the fused activation needs tile_n 256, bfloat16 output and N %% 256 == 0 (N=%d)", N);
-    return launch<256, 4, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    return launch<256, 4, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s, act);
   }
   if (c_dtype == OI_BF16) {
     if (tile_n == 256) return launch<256, 4, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
@@ -474,7 +476,9 @@ OI_API int oi_gemm_tcgen05(void* C, int c_dtype, long long ldc, const void* A, l
 
 // The same product with 256 x 256 tiles computed by pairs of CTAs (tcgen05 cta_group::2).
 OI_API int oi_gemm_tcgen05_pair(void* C, int c_dtype, long long ldc, const void* A, long long lda, const void* W,
-                                long long ldw, int M, int N, int K, int silu_mul, void* stream) {
+                                long long ldw, int M, int N, int K, int act, void* stream) {
+  const int silu_mul = act;
+  OI_REQUIRE(act >= OI_ACT_NONE && act <= OI_ACT_GELU_TANH, "gemm_tcgen05_pair: unknown activation code %d", act);
   OI_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05_pair: bad sizes M=%d N=%d K=%d", M, N, K);
   OI_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05_pair: K and row strides must be multiples of 8");
   OI_REQUIRE((uintptr_t)A % 16 == 0 && (uintptr_t)W % 16 == 0, "gemm_tcgen05_pair: operands must be 16-byte aligned");
@@ -482,7 +486,7 @@ OI_API int oi_gemm_tcgen05_pair(void* C, int c_dtype, long long ldc, const void*
   if (silu_mul) {
     OI_REQUIRE(c_dtype == OI_BF16 && N % 256 == 0,
                "gemm_tcgen05_pair: the fused activation needs bfloat16 output and N %% 256 == 0 (N=%d)", N);
-    return launch_pair<kPairStages, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s);
+    return launch_pair<kPairStages, bf16, true>(C, ldc, A, lda, W, ldw, M, N, K, s, act);
   }
   if (c_dtype == OI_BF16) return launch_pair<kPairStages, bf16>(C, ldc, A, lda, W, ldw, M, N, K, s);
   if (c_dtype == OI_F32) return launch_pair<kPairStages, float>(C, ldc, A, lda, W, ldw, M, N, K, s);

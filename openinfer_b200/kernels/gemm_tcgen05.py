@@ -8,6 +8,7 @@ from ctypes import c_int, c_longlong, c_void_p
 import torch
 
 from . import lib as _lib
+from . import ops
 from .lib import KernelError
 
 
@@ -68,8 +69,9 @@ def _pair(L, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int)
     return out
 
 
-def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
-    """out[M, I] = silu(x Wg^T) * (x Wu^T) in one kernel. ``w_gate_up`` is [2 I, K] with rows in blocks
+def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor, tile_n: int = 256,
+                  act: str = "silu") -> torch.Tensor:
+    """out[M, I] = act(x Wg^T) * (x Wu^T) in one kernel (act: "silu" or "gelu_tanh"). ``w_gate_up`` is [2 I, K] with rows in blocks
     of 64 gate rows followed by the 64 up rows of the same indices (I a multiple of 128: a tile of the
     kernel holds two such pairs)."""
     M, K = x.shape
@@ -77,10 +79,11 @@ def gemm_silu_mul(out: torch.Tensor, x: torch.Tensor, w_gate_up: torch.Tensor, t
     if N % (2 * ACT_BLOCK) or out.shape != (M, N // 2) or out.dtype != torch.bfloat16 or not takes(out, x, w_gate_up):
         raise KernelError(f"gemm_silu_mul: operands not accepted: x={tuple(x.shape)} w={tuple(w_gate_up.shape)} out={tuple(out.shape)}")
     L = _lib.load()
+    code = ops.act_code(act)
     if tile_n == PAIR:
-        return _pair(L, out, x, w_gate_up, 1)
+        return _pair(L, out, x, w_gate_up, code)
     _lib.check(L.oi_gemm_tcgen05(out.data_ptr(), 1, out.stride(0), x.data_ptr(), x.stride(0), w_gate_up.data_ptr(),
-                                 w_gate_up.stride(0), M, N, K, tile_n, 1, _lib.current_stream()),
+                                 w_gate_up.stride(0), M, N, K, tile_n, code, _lib.current_stream()),
                "gemm_tcgen05 (fused activation)")
     return out
 

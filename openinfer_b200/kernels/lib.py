@@ -27,7 +27,8 @@ _SIGNATURES = {
     "oi_copy_words": [P, P, I, I, I, I, P, I, P],
     "oi_rmsnorm": [P, P, P, I, P, I, P, I, I, F, F, P],
     "oi_add_inplace": [P, P, I, L, P],
-    "oi_silu_mul": [P, P, I, I, I, I, P],
+    "oi_scale_cap": [P, I, L, F, F, P],
+    "oi_silu_mul": [P, P, I, I, I, I, I, P],
     "oi_qk_norm_rope_kv": [P, I, I, I, I, I, I, P, P, I, F, F, P, P, I, I, P, P, P, P, L, I, I, P],
     "oi_attention_generic": [P, I, P, I, I, P, P, L, I, P, I, P, P, I, I, I, I, F, I, P],
     "oi_gemm_generic": [P, I, P, I, P, I, I, I, I, L, L, L, P],
@@ -35,7 +36,7 @@ _SIGNATURES = {
     "oi_token_logprobs": [P, L, I, P, P, P, I, I, P, P, P, P],
     "oi_sample": [P, P, L, P, I, I, P, P, P, P, P, P],
     "oi_sample_use_clusters": [I],
-    "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, P],
+    "oi_gemm_skinny": [P, I, L, P, L, P, L, I, I, I, I, I, I, P],
     "oi_gemm_tcgen05": [P, I, L, P, L, P, L, I, I, I, I, I, P],
     "oi_gemm_tcgen05_pair": [P, I, L, P, L, P, L, I, I, I, I, P],
     "oi_gemm_tcgen05_status": [ctypes.POINTER(c_int)],

@@ -74,10 +74,11 @@ def _operands_ok(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
     return not (x.stride(0) % 8 or w.stride(0) % 8 or x.data_ptr() % 16 or w.data_ptr() % 16)
 
 
-def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool = False) -> bool:
-    """The tcgen05 weight-streaming kernel, when it takes the shape."""
+def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, act: int = 0) -> bool:
+    """The tcgen05 weight-streaming kernel, when it takes the shape. ``act``: 0, or the code of the gate
+    activation to form from gate and up rows (``ops.act_code``)."""
     M, N, K = x.shape[0], w.shape[0], w.shape[1]
-    if K % 8 or not _operands_ok(out, x, w) or (silu_mul and N % 128):
+    if K % 8 or not _operands_ok(out, x, w) or (act and N % 128):
         return False
     c = stream_cluster_size(N, K, _sm_count(x.device))
     if _FORCE_C:
@@ -87,13 +88,13 @@ def _stream(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: bool 
         c //= 2
     L = _lib.load()
     _lib.check(L.oi_gemm_stream(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c, 1 if silu_mul else 0,
+                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, c, int(act),
                                 _lib.current_stream()), "gemm_stream")
     return True
 
 
-def gate_up_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch.Tensor]:
-    """silu(x Wg^T) * (x Wu^T) for up to 32 rows of x in ONE weight-streaming kernel, or None when it
+def gate_up_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor, act: str = "silu") -> Optional[torch.Tensor]:
+    """act(x Wg^T) * (x Wu^T) for up to 32 rows of x in ONE weight-streaming kernel, or None when it
     does not take the operands. ``w_gate_up`` [2 I, K]: blocks of 64 gate rows followed by the 64 up
     rows of the same indices."""
     M = x.shape[0]
@@ -102,8 +103,8 @@ def gate_up_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> Optional[torch
     if (DECODE_GEMM != "stream" or not 0 < M <= DECODE_MAX_ROWS or x.dtype != torch.bfloat16
             or w_gate_up.dtype != torch.bfloat16):
         return None
-    act = torch.empty((M, w_gate_up.shape[0] // 2), dtype=x.dtype, device=x.device)
-    return act if _stream(act, x, w_gate_up, silu_mul=True) else None
+    out = torch.empty((M, w_gate_up.shape[0] // 2), dtype=x.dtype, device=x.device)
+    return out if _stream(out, x, w_gate_up, act=ops.act_code(act)) else None
 
 
 def stream_status() -> int:
@@ -127,7 +128,7 @@ def skinny_cluster_size(N: int, K: int, sm_count: int) -> int:
     return valid[-1]
 
 
-def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) -> bool:
+def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int, act: int = 1) -> bool:
     """The mma.sync weight-streaming kernel, when it takes the shape."""
     M, N, K = x.shape[0], w.shape[0], w.shape[1]
     if M > SKINNY_MAX_ROWS or not _operands_ok(out, x, w):
@@ -139,23 +140,23 @@ def _skinny(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, silu_mul: int) 
         c = _FORCE_C
     L = _lib.load()
     _lib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, int(silu_mul), c,
+                                x.stride(0), w.data_ptr(), w.stride(0), M, N, K, int(silu_mul), int(act), c,
                                 _lib.current_stream()), "gemm_skinny")
     return True
 
 
-def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
-    """(silu(gate) * up) W^T for a fused [M, 2K] gate|up buffer (blocks of ``block`` gates then
+def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, block: Optional[int] = None, act: str = "silu") -> torch.Tensor:
+    """(act(gate) * up) W^T for a fused [M, 2K] gate|up buffer (blocks of ``block`` gates then
     their ups; default all gates, then all ups) and w [N, K]."""
     M, K = gate_up.shape[0], w.shape[1]
     block = K if block is None else block
     if FUSE_SILU_MUL and gate_up.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < M <= SKINNY_MAX_ROWS:
         out = torch.empty((M, w.shape[0]), dtype=gate_up.dtype, device=gate_up.device)
-        if _skinny(out, gate_up, w, block):
+        if _skinny(out, gate_up, w, block, ops.act_code(act)):
             return out
-    act = torch.empty((M, K), dtype=gate_up.dtype, device=gate_up.device)
-    ops.silu_mul(act, gate_up, block)
-    return linear(act, w)
+    a = torch.empty((M, K), dtype=gate_up.dtype, device=gate_up.device)
+    ops.silu_mul(a, gate_up, block, act)
+    return linear(a, w)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,

@@ -123,8 +123,29 @@ def add_inplace(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, block: Optional[int] = None) -> torch.Tensor:
-    """out[r, i] = silu(gate_i) * up_i for a fused gate|up buffer [rows, 2 * inter] laid out in
+def scale_cap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place: x = x * scale, then, with cap > 0, x = cap * tanh(x / cap)."""
+    _cuda(x)
+    if not x.is_contiguous():
+        raise KernelError("scale_cap: the tensor must be contiguous")
+    L = _lib.load()
+    _lib.check(L.oi_scale_cap(x.data_ptr(), _code(x, "scale_cap"), x.numel(), float(scale), float(cap), _stream()), "scale_cap")
+    return x
+
+
+# gate activations of a gated feed-forward: name -> code of the C interface (common.cuh)
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
+
+
+def act_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation {name!r} has no kernel (known: {', '.join(sorted(ACTIVATIONS))})") from None
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, block: Optional[int] = None, act: str = "silu") -> torch.Tensor:
+    """out[r, i] = act(gate_i) * up_i for a fused gate|up buffer [rows, 2 * inter] laid out in
     blocks of ``block`` gate values followed by their up values (default: all gates, then all ups)."""
     _cuda(out, gate_up)
     rows, inter = out.shape
@@ -132,7 +153,8 @@ def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, block: Optional[int] = No
     if gate_up.shape != (rows, 2 * inter) or out.dtype != gate_up.dtype or not (out.is_contiguous() and gate_up.is_contiguous()):
         raise KernelError(f"silu_mul: shapes out={tuple(out.shape)} gate_up={tuple(gate_up.shape)}")
     L = _lib.load()
-    _lib.check(L.oi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _code(out, "silu_mul"), rows, inter, block, _stream()), "silu_mul")
+    _lib.check(L.oi_silu_mul(out.data_ptr(), gate_up.data_ptr(), _code(out, "silu_mul"), rows, inter, block, act_code(act),
+                             _stream()), "silu_mul")
     return out
 
 

@@ -1,4 +1,5 @@
-"""Gated feed-forward (SwiGLU): down( act(gate x) * (up x) ).
+"""Gated feed-forward: down( act(gate x) * (up x) ), act chosen by the spec ("silu": SwiGLU, the
+reference's; "gelu_tanh": the tanh form of GELU).
 
 gate and up are one fused [2*intermediate, hidden] matrix, as in the reference
 (pegainfer-qwen3/src/weights/load.rs:136-154), so one product feeds the activation kernel
@@ -10,22 +11,21 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import gemm_tcgen05, policy
+from ..kernels import gemm_tcgen05, ops, policy
 from ..kernels.linear import gate_up_silu_mul, linear, linear_silu_mul
-
-# rows from which the gate/up product with the activation in its epilogue is used (prompt portions)
-FUSED_MIN_ROWS = 128
 from .base import FeedForward
 from .registry import register_feed_forward
 from .spec import GatedMlpSpec, ParamInfo
+
+# rows from which the gate/up product with the activation in its epilogue is used (prompt portions)
+FUSED_MIN_ROWS = 128
 
 
 @register_feed_forward("gated_mlp")
 class GatedMlp(FeedForward):
     def __init__(self, spec: GatedMlpSpec) -> None:
         super().__init__(spec)
-        if spec.activation != "silu":
-            raise ValueError(f"activation {spec.activation!r} has no kernel (silu only)")
+        ops.act_code(spec.activation)      # refuses a name no kernel knows; the kernels take the code as an argument
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -57,11 +57,11 @@ class GatedMlp(FeedForward):
                 act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
                 if gemm_tcgen05.takes(act, x, self.w_gate_up):
                     tile = 256 if policy.batch_invariant() else gemm_tcgen05.portion_tile(x.shape[0], x.shape[1])
-                    gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up, tile)
+                    gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up, tile, self.spec.activation)
                     return linear(act, self.w_down)
             else:
-                act = gate_up_silu_mul(x, self.w_gate_up)     # decode: the weight stream forms the activation
+                act = gate_up_silu_mul(x, self.w_gate_up, self.spec.activation)     # decode: the weight stream forms the activation
                 if act is not None:
                     return linear(act, self.w_down)
         gate_up = linear(x, self.w_gate_up)
-        return linear_silu_mul(gate_up, self.w_down, self.block)
+        return linear_silu_mul(gate_up, self.w_down, self.block, self.spec.activation)

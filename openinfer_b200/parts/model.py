@@ -114,6 +114,8 @@ class Model:
         (h, pending): pending is the last branch output, not yet added."""
         h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=self.dtype, device=self.device)
         ops.embedding(h, self.embedding, ctx.token_ids)
+        if self.spec.embedding_scale != 1.0:
+            ops.scale_cap(h, scale=self.spec.embedding_scale)
         pending = None
         for call, binding in zip(self.calls, self.bindings):
             h, pending = self.blocks[call.layer].forward(h, pending, ctx, binding)
@@ -123,4 +125,7 @@ class Model:
         """Float32 logits [rows, vocab] of the wanted rows only: gather + final norm in one
         kernel, then the head (pegainfer-qwen3/src/prefill.rs:440-477)."""
         x = self.final_norm(h, delta=pending, row_idx=row_idx)
-        return linear(x, self.head, out_dtype=torch.float32)
+        out = linear(x, self.head, out_dtype=torch.float32)
+        if self.spec.logit_soft_cap > 0.0:
+            ops.scale_cap(out, cap=self.spec.logit_soft_cap)
+        return out

@@ -105,6 +105,8 @@ class ModelSpec:
     head_name: Optional[str] = "lm_head.weight"   # None: the head is the embedding table (tied)
     max_positions: int = 0
     stop_token_ids: Tuple[int, ...] = ()
+    embedding_scale: float = 1.0     # the embedded rows are multiplied by this (1: as stored, the reference's Qwen3)
+    logit_soft_cap: float = 0.0      # > 0: logits = cap * tanh(logits / cap)
 
     def calls(self) -> List[LayerCall]:
         return [c if isinstance(c, LayerCall) else LayerCall(int(c)) for c in self.order]

@@ -542,7 +542,7 @@ def test_gemm_skinny(M, N, K):
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
             klib.check(L.oi_gemm_skinny(out.data_ptr(), 1 if out_dtype == torch.bfloat16 else 0, out.stride(0), x.data_ptr(),
-                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, c,
+                                        x.stride(0), w.data_ptr(), w.stride(0), M, N, K, 0, 0, c,
                                         torch.cuda.current_stream().cuda_stream), "gemm_skinny")
             tol_ = 2e-2 * ref.abs().max().item() if out_dtype == torch.bfloat16 else 2e-4 * ref.abs().max().item()
             err = (out.double() - ref).abs().max().item()
@@ -613,6 +613,58 @@ def test_gemm_skinny_with_fused_activation(M, N, K):
         finally:
             lin.FUSE_SILU_MUL = False
         assert (out.double() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item(), f"fused={fused}"
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+def test_gate_activation_is_an_argument_of_every_kernel_that_forms_it(act):
+    """act(gate) * up against float64 from the formulas, in the four kernels that form it: the stand-alone
+    kernel (both dtypes, block layouts), the streaming product, the tcgen05 products (single CTAs and pairs)
+    and the skinny product's staging loop."""
+    from openinfer_b200.kernels import gemm_tcgen05 as g, linear as lin, ops
+
+    def activation(x):
+        if act == "silu":
+            return x / (1.0 + torch.exp(-x))
+        return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+
+    torch.manual_seed(3)
+    K, inter = 256, 512
+    for M in (5, 20, 300):
+        x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+        wg = (torch.randn(inter, K, device=DEV) * 0.1).to(torch.bfloat16)
+        wu = (torch.randn(inter, K, device=DEV) * 0.1).to(torch.bfloat16)
+        ref = activation(x.double() @ wg.double().t()) * (x.double() @ wu.double().t())
+        tol = 2e-2 * ref.abs().max().item()
+        w = torch.stack([wg.view(-1, 64, K), wu.view(-1, 64, K)], dim=1).reshape(2 * inter, K).contiguous()
+        if M <= 32:
+            out = lin.gate_up_silu_mul(x, w, act)
+            assert out is not None and (out.double() - ref).abs().max().item() <= tol, f"streaming product, {M} rows"
+        for tile in (256, g.PAIR):
+            out = torch.full((M, inter), float("nan"), device=DEV, dtype=torch.bfloat16)
+            g.gemm_silu_mul(out, x, w, tile, act)
+            assert (out.double() - ref).abs().max().item() <= tol, f"tcgen05 product, tile {tile}, {M} rows"
+        gu = (x.float() @ w.float().t())                      # [M, 2 inter] in blocks of 64
+        for dtype in (torch.float32, torch.bfloat16):
+            buf = gu.to(dtype)
+            gd = buf.double().view(M, -1, 2, 64)
+            want = (activation(gd[:, :, 0]) * gd[:, :, 1]).reshape(M, inter)
+            out = torch.full((M, inter), float("nan"), device=DEV, dtype=dtype)
+            ops.silu_mul(out, buf, 64, act)
+            bound = 1e-5 if dtype == torch.float32 else 1e-2
+            assert (out.double() - want).abs().max().item() <= bound * max(1.0, want.abs().max().item()), f"stand-alone {dtype}"
+        if M <= 16:
+            wd = (torch.randn(96, inter, device=DEV) * 0.05).to(torch.bfloat16)
+            buf = gu.to(torch.bfloat16)
+            gd = buf.double().view(M, -1, 2, 64)
+            a = (activation(gd[:, :, 0]) * gd[:, :, 1]).reshape(M, inter).to(torch.bfloat16)
+            want = a.double() @ wd.double().t()
+            lin.FUSE_SILU_MUL = True
+            try:
+                out = lin.linear_silu_mul(buf, wd, 64, act)
+            finally:
+                lin.FUSE_SILU_MUL = False
+            assert (out.double() - want).abs().max().item() <= 2e-2 * want.abs().max().item(), "skinny product"
+    assert g.status() == 0 and lin.stream_status() == 0
 
 
 @pytest.mark.parametrize("tile_n", [256, 128, 0])

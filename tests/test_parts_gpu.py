@@ -36,26 +36,38 @@ def _random_tensors(spec, seed):
 
 
 def _mini_spec(window=None, order=None, layers=2, nq=4, nkv=2, hd=16, hidden=40, inter=72, vocab=50,
-               rotary_dim=None, qk_norm=True, offset=0.0):
+               rotary_dim=None, qk_norm=True, offset=0.0, activation="silu", embedding_scale=1.0, logit_soft_cap=0.0):
     from openinfer_b200.parts.spec import (AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NormSpec, PositionSpec)
     norm = NormSpec("rms", hidden, 1e-5, offset)
     pos = PositionSpec("rope", rotary_dim or hd, 777.0, 256)
     mixer = AttentionSpec(hidden_size=hidden, num_heads=nq, num_kv_heads=nkv, head_dim=hd,
                           softmax_scale=1 / math.sqrt(hd), position=pos,
                           qk_norm=NormSpec("rms", hd, 1e-5, offset) if qk_norm else None, window=window)
-    blocks = tuple(BlockSpec(name=f"L{i}.", mixer=mixer, feed_forward=GatedMlpSpec(hidden_size=hidden, intermediate_size=inter),
+    blocks = tuple(BlockSpec(name=f"L{i}.", mixer=mixer, feed_forward=GatedMlpSpec(hidden_size=hidden, intermediate_size=inter, activation=activation),
                              input_norm=norm, post_norm=norm) for i in range(layers))
     return ModelSpec(vocab_size=vocab, hidden_size=hidden, blocks=blocks, order=tuple(order or range(layers)),
-                     final_norm=norm, embedding_name="emb", final_norm_name="fn.", head_name="head", max_positions=256)
+                     final_norm=norm, embedding_name="emb", final_norm_name="fn.", head_name="head", max_positions=256,
+                     embedding_scale=embedding_scale, logit_soft_cap=logit_soft_cap)
 
 
-def _plain_forward(spec, w, toks, window=None, order=None, cache_of=None, rotary_dim=None, qk_norm=True, offset=0.0):
+def _plain_gated_mlp(x, w, prefix, activation):
+    """down( act(gate x) * (up x) ); "gelu_tanh": act(g) = 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))."""
+    if activation == "silu":
+        return plain.swiglu(x, w, prefix)
+    g = plain.linear(x, w[prefix + "gate_proj.weight"])
+    u = plain.linear(x, w[prefix + "up_proj.weight"])
+    act = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
+    return plain.linear(act * u, w[prefix + "down_proj.weight"])
+
+
+def _plain_forward(spec, w, toks, window=None, order=None, cache_of=None, rotary_dim=None, qk_norm=True, offset=0.0,
+                   activation="silu", embedding_scale=1.0, logit_soft_cap=0.0):
     """Whole-sequence float32 forward of a mini spec, from the plain part functions."""
     w = {k: v.float() for k, v in w.items()}
     m = spec.blocks[0].mixer
     T = len(toks)
     positions = torch.arange(T)
-    h = plain.embedding(torch.tensor(toks), w["emb"])
+    h = plain.embedding(torch.tensor(toks), w["emb"]) * embedding_scale
     kv_of_call = {}
     calls = spec.calls()
     for ci, c in enumerate(calls):
@@ -80,9 +92,10 @@ def _plain_forward(spec, w, toks, window=None, order=None, cache_of=None, rotary
         o = plain.causal_attention(q, k, v, m.softmax_scale, window)
         h = h + plain.linear(o.reshape(T, -1), w[a + "o_proj.weight"])
         x = plain.rms_norm(h, offset + w[p + "post_attention_layernorm.weight"], 1e-5)
-        h = h + plain.swiglu(x, w, p + "mlp.")
+        h = h + _plain_gated_mlp(x, w, p + "mlp.", activation)
     h = plain.rms_norm(h, offset + w["fn.weight"], 1e-5)
-    return plain.linear(h, w["head"])
+    logits = plain.linear(h, w["head"])
+    return logit_soft_cap * torch.tanh(logits / logit_soft_cap) if logit_soft_cap > 0 else logits
 
 
 def _step_all(runner, toks, cuts):
@@ -213,6 +226,29 @@ def _register_toy():
             return out
 
     return RunningMean
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_activation_embedding_scale_and_logit_cap_are_spec_values(dtype):
+    """Another gate activation (tanh-GELU), a scale on the embedded rows and a soft cap on the logits are values
+    of the spec: the package's own feed-forward and model take them, its kernels get the activation as an argument.
+    Sizes at which the bfloat16 path forms the activation in all three places: the streaming product (steps of up
+    to 32 rows), the stand-alone kernel (33 to 127 rows) and the epilogue of the tcgen05 product (128 rows and more)."""
+    kw = dict(layers=2, nq=4, nkv=2, hd=64, hidden=256, inter=512, vocab=300)
+    extra = dict(activation="gelu_tanh", embedding_scale=3.5, logit_soft_cap=2.0)
+    spec = _mini_spec(**kw, **extra)
+    w = _random_tensors(spec, 21)
+    rng = random.Random(6)
+    toks = [rng.randrange(300) for _ in range(230)]
+    ref = _plain_forward(spec, w, toks, **extra)
+    assert float(ref.abs().max()) <= 2.0 and float(ref.abs().max()) > 1.0     # the cap bites
+    assert not torch.allclose(ref, _plain_forward(spec, w, toks, embedding_scale=3.5, logit_soft_cap=2.0), atol=1e-3)
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    runner = _runner(spec, dtype, w, page=16, pages=32)
+    got = _step_all(runner, toks, [130, 40, 7, 1, 1, 33, 18])
+    assert_close(got, ref, name, f"gelu_tanh / scaled embedding / capped logits {name}")
+    with pytest.raises(Exception, match="no kernel"):
+        _runner(_mini_spec(**kw, activation="relu_squared"), dtype, w)
 
 
 def test_toy_mixer_with_state_registers_builds_and_steps():
