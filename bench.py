@@ -229,7 +229,7 @@ class Bench:
         for _ in range(warmup):
             one()
         torch.cuda.synchronize()
-        l0 = klib.launches
+        l0 = klib.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
@@ -237,7 +237,7 @@ class Bench:
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
-        launches = klib.launches - l0
+        launches = klib.launch_count() - l0
         for rid in ids:
             runner.end(rid)
         return ms, launches

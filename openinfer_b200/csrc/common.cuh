@@ -70,6 +70,7 @@ typedef __nv_bfloat16 bf16;
 // instructions as no-ops.
 // ---------------------------------------------------------------------------------------------
 int oi_pdl_enabled();
+void oi_count_launch();   // every kernel launched through oi_launch is counted (oi_launches)
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_start() {
@@ -103,6 +104,7 @@ inline void oi_launch_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, 
   }
   cfg.attrs = na ? attr : nullptr;
   cfg.numAttrs = (unsigned)na;
+  oi_count_launch();
   (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);   // the error stays for cudaGetLastError
 }
 template <typename... Params, typename... Args>

@@ -21,6 +21,11 @@ OI_API int oi_abi_version() { return 1; }
 // Programmatic dependent launch of the library's kernels (see common.cuh): on unless switched off.
 static int g_pdl = 1;
 int oi_pdl_enabled() { return g_pdl; }
+// Kernels of this library launched so far (through oi_launch; a recorded graph's replays are not seen here).
+static unsigned long long g_launches = 0;
+void oi_count_launch() { ++g_launches; }
+OI_API unsigned long long oi_launches() { return g_launches; }
+
 OI_API int oi_set_pdl(int enabled) {
   g_pdl = enabled ? 1 : 0;
   return OI_OK;

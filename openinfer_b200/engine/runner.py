@@ -223,8 +223,7 @@ class ModelRunner:
                 logits = self._step_decode_graph(entries, starts)
             else:
                 ctx, row_idx = self._build_context(entries, starts)
-                h, pending = self.model.forward(ctx)
-                logits = self.model.logits(h, pending, row_idx) if row_idx is not None else None
+                logits = self.model.run(ctx, row_idx)
         except Exception:
             for rid in reserved:
                 cache.rollback(rid)
@@ -393,8 +392,7 @@ class ModelRunner:
         row_idx = meta[sections["want"]: sections["want"] + bucket]
 
         def run():
-            h, pending = self.model.forward(ctx)
-            return self.model.logits(h, pending, row_idx)
+            return self.model.run(ctx, row_idx)
 
         # warm-up on a side stream (plans and workspaces are made here, outside the recording)
         side = torch.cuda.Stream(device=self.device)
@@ -405,10 +403,11 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        before = kernel_lib.launches
+        before = kernel_lib.launch_count()
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = run()
-        recorded = kernel_lib.launches - before   # entry-point calls one replay stands for
+        recorded = kernel_lib.launch_count() - before   # kernels one replay stands for
+        kernel_lib.replayed -= recorded                 # the recording itself ran none of them
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
         entry = (graph, meta, sections, total, logits, (ctx, recorded))
@@ -431,7 +430,7 @@ class ModelRunner:
         host[sections["want"]: sections["want"] + bucket] = np.arange(bucket, dtype=np.int32)
         self._upload(meta, host, sections, bucket, entries)
         graph.replay()
-        kernel_lib.launches += recorded
+        kernel_lib.replayed += recorded
         if not want_rows:
             return None
         if want_rows == list(range(len(want_rows))):

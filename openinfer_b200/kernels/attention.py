@@ -20,15 +20,72 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     ``group.block_table`` lists for each request of the step. With ``rope`` (only after
     ``decode_takes_rope`` said yes) q is the RAW fused projection and the decode kernel does the
     q/k norm, the rotation and the cache write itself."""
+    if rope is None:
+        for impl in _TUNED:
+            if impl(q, out, k_cache, v_cache, page_stride, ctx, group, nq, nkv, hd, scale, window):
+                return out
+    step = attention_step(ctx, group, q, out, k_cache, page_stride, nq, nkv, hd, window,
+                          cos=rope.cos if rope is not None else None, q_norm_w=rope.q_norm_w if rope is not None else None)
     if rope is not None:
-        if not attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group, nq, nkv, hd, scale, window, rope=rope):
+        if not step.fuse_rope:
             raise ops.KernelError("paged_attention: the fused rotation was promised and then refused")
-        return out
-    for impl in _TUNED:
-        if impl(q, out, k_cache, v_cache, page_stride, ctx, group, nq, nkv, hd, scale, window):
-            return out
-    return ops.attention_generic(q, out, k_cache, v_cache, page_stride, ctx.cache.page_size,
-                                 group.block_table, ctx.token_req, ctx.positions, nq, nkv, hd, scale, window)
+        mine = native.AttnStep()          # the caller's own positions and slots, not the step's
+        ctypes.memmove(ctypes.byref(mine), ctypes.byref(step), ctypes.sizeof(native.AttnStep))
+        mine.positions, mine.slot_mapping = rope.positions.data_ptr(), rope.slots.data_ptr()
+        mine.keep = (step, rope)
+        step = mine
+    layer = attention_layer(q, out, k_cache, v_cache, nq, nkv, hd, scale, window,
+                            q_norm_w=rope.q_norm_w if rope else None, k_norm_w=rope.k_norm_w if rope else None,
+                            eps=rope.eps if rope else 0.0, weight_offset=rope.weight_offset if rope else 0.0,
+                            cos=rope.cos if rope else None, sin=rope.sin if rope else None,
+                            write_kv=bool(rope.write_kv) if rope else False, rope_mode=1 if rope else 0)
+    run_attention(step, layer)
+    return out
+
+
+def run_attention(step: "native.AttnStep", layer: "native.AttnLayer") -> None:
+    """One layer's attention in native code (``oi_attention_layer``): the norm + rotation + cache write kernel when the
+    layer asks for it and the decode kernel does not do that itself, then the kernel(s) that take the step's shape."""
+    _lib.check(_lib.load().oi_attention_layer(ctypes.byref(step), ctypes.byref(layer), _lib.current_stream()), "attention")
+
+
+def attention_layer(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nq: int, nkv: int,
+                    hd: int, scale: float, window: Optional[int], *, q_norm_w=None, k_norm_w=None, eps: float = 0.0,
+                    weight_offset: float = 0.0, cos=None, sin=None, write_kv: bool = True, rope_mode: int = 1) -> "native.AttnLayer":
+    """The description of one layer's attention call (csrc/oi_api.h, OiAttnLayer)."""
+    _check_layer_operands(qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, hd)
+    norm_dtype = 0
+    if q_norm_w is not None:
+        norm_dtype = 1 if q_norm_w.dtype == torch.bfloat16 else 0
+    return native.AttnLayer(
+        qkv=qkv.data_ptr(), out=out.data_ptr(), k_cache=k_cache.data_ptr(), v_cache=v_cache.data_ptr(),
+        q_norm_w=0 if q_norm_w is None else q_norm_w.data_ptr(), k_norm_w=0 if k_norm_w is None else k_norm_w.data_ptr(),
+        cos_tab=0 if cos is None else cos.data_ptr(), sin_tab=0 if sin is None else sin.data_ptr(),
+        q_row_stride=qkv.stride(0), out_row_stride=out.stride(0), dtype=native.DTYPE_CODE[qkv.dtype],
+        nq=nq, nkv=nkv, hd=hd, window=int(window) if window else 0, scale=float(scale), eps=float(eps),
+        w_offset=float(weight_offset), norm_dtype=norm_dtype, rot_half=0 if cos is None else cos.shape[1],
+        max_pos=0 if cos is None else cos.shape[0], write_kv=1 if write_kv else 0, rope_mode=rope_mode)
+
+
+def _check_layer_operands(qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, hd) -> None:
+    for t in (qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin):
+        if t is not None and not t.is_cuda:
+            raise ops.KernelError("a kernel was given a tensor that is not on a CUDA device; this package has no CPU path")
+    if qkv.dtype not in native.DTYPE_CODE or out.dtype != qkv.dtype or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+        raise ops.KernelError(f"attention: q, out and the cache must share one dtype (float32 or bfloat16), got "
+                              f"{qkv.dtype}, {out.dtype}, {k_cache.dtype}")
+    if qkv.stride(1) != 1 or out.stride(1) != 1:
+        raise ops.KernelError("attention: q and out must be contiguous along the head dimension")
+    if (q_norm_w is None) != (k_norm_w is None):
+        raise ops.KernelError("attention: q and k norm weights come together or not at all")
+    for w in (q_norm_w, k_norm_w):
+        if w is not None and (w.numel() != hd or not w.is_contiguous() or w.dtype not in native.DTYPE_CODE):
+            raise ops.KernelError("attention: a norm weight must have head_dim contiguous float32 or bfloat16 elements")
+    if q_norm_w is not None and q_norm_w.dtype != k_norm_w.dtype:
+        raise ops.KernelError("attention: q and k norm weights must share a dtype")
+    if cos is not None and (cos.dtype != torch.float32 or sin is None or sin.shape != cos.shape
+                            or not (cos.is_contiguous() and sin.is_contiguous())):
+        raise ops.KernelError("attention: cos/sin must be contiguous float32 tables of one shape")
 
 
 # tuned implementations: fn(...) -> bool, True when it ran
@@ -49,7 +106,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p  # noqa: E402
 import numpy as np  # noqa: E402
 
 from . import lib as _lib  # noqa: E402
-from . import policy  # noqa: E402
+from . import native, policy  # noqa: E402
 
 _P, _I, _L, _F = c_void_p, c_int, c_longlong, c_float
 
@@ -205,6 +262,9 @@ def plan_items_static_decode(num_requests: int, group: int, nkv: int, sm_count: 
     return items, empty, np.full(num_requests, ns, dtype=np.int32), ns, ns > 1
 
 
+_PLAN_RING = ops.UploadRing()
+
+
 def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, device) -> AttentionPlan:
     key = ("attention_mma_plan", id(group_step), group, nkv, window)
     plan = ctx.scratch.get(key)
@@ -221,8 +281,8 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
             t_items, d_items, row_splits, max_splits, tile_split = plan_items(
                 ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window, _sm_count(device), rows_per_cta=rows,
                 whole_tiles_kernel=whole)
-        packed = np.concatenate([t_items.reshape(-1), d_items.reshape(-1), row_splits])
-        dev = torch.from_numpy(packed).to(device, non_blocking=True)
+        packed = np.concatenate([t_items.reshape(-1), d_items.reshape(-1), row_splits]).astype(np.int32, copy=False)
+        dev = _PLAN_RING.upload(packed, device)   # pinned memory read by a kernel: the host does not wait for the stream
         nt, nd = t_items.shape[0], d_items.shape[0]
         part_o = part_lse = None
         # decode rows merge their slices inside the kernel when their CTAs fit a cluster; prompt tiles
@@ -280,54 +340,50 @@ def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd:
     return plan.num_tile_items == 0 and plan.num_decode_items > 0 and one_wave
 
 
-def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window, rope=None) -> bool:
-    """The tensor-core kernels, when they cover the shape: bfloat16, head_dim 32, 64 or 128."""
-    if q.dtype != torch.bfloat16 or hd not in (32, 64, 128) or nq // nkv > ROWS_PER_CTA_LARGE:
-        return False
-    if q.stride(0) % 2 or page_stride % 8:
-        return False
-    plan = _plan_for(ctx, group_step, nq // nkv, nq, nkv, hd, window, q.device)
-    if rope is not None and (plan.num_tile_items or not plan.num_decode_items):
-        return False
-    L = _lib.load()
-    stream = _lib.current_stream()
+def attention_step(ctx, group_step, qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, page_stride: int,
+                   nq: int, nkv: int, hd: int, window, cos=None, q_norm_w=None) -> "native.AttnStep":
+    """What every attention call of one geometry shares in this step (csrc/oi_api.h, OiAttnStep): the step's metadata
+    on the device, which kernels take it, and their work items. Made once per step and geometry."""
+    key = ("attention_step", id(group_step), nq, nkv, hd, window, qkv.dtype, qkv.stride(0), out.stride(0), cos is not None)
+    step = ctx.scratch.get(key)
+    if step is not None:
+        return step
+    group = nq // nkv
     bt = group_step.block_table
-    po = 0 if plan.part_o is None else plan.part_o.data_ptr()
-    pl = 0 if plan.part_lse is None else plan.part_lse.data_ptr()
-    win = int(window) if window else 0
-    if plan.num_tile_items and _tcgen05_takes(plan, q, out, k_cache, ctx.cache.page_size, nq, nkv, hd, page_stride):
-        _lib.check(L.oi_attention_tcgen05(
-            q.data_ptr(), q.stride(0), q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-            int(page_stride), ctx.cache.page_size, k_cache.shape[0], bt.data_ptr(), bt.stride(0),
-            ctx.cu_seqlens.data_ptr(), group_step.kv_lens.data_ptr(), plan.tile_items.data_ptr(), plan.num_tile_items,
-            nq, nkv, hd, float(scale), win, stream), "attention_tcgen05")
-    elif plan.num_tile_items:
-        _lib.check(L.oi_attention_mma(
-            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-            int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
-            group_step.kv_lens.data_ptr(), plan.tile_items.data_ptr(), plan.num_tile_items,
-            plan.row_splits.data_ptr(), out.shape[0], 1 if plan.tile_split else 0, nq, nkv, hd, float(scale), win,
-            po, pl, plan.max_splits, plan.rows_per_cta, stream), "attention_mma")
-    if plan.num_decode_items and rope is not None:
-        nw = rope.q_norm_w
-        _lib.check(L.oi_attention_decode_rope(
-            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-            int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
-            group_step.kv_lens.data_ptr(), plan.decode_items.data_ptr(), plan.num_decode_items,
-            plan.row_splits.data_ptr(), out.shape[0], nq, nkv, hd, float(scale), win, po, pl, plan.max_splits,
-            1 if plan.decode_merge_in_kernel else 0,
-            0 if nw is None else nw.data_ptr(), 0 if rope.k_norm_w is None else rope.k_norm_w.data_ptr(),
-            1 if (nw is not None and nw.dtype == torch.bfloat16) else 0, float(rope.eps), float(rope.weight_offset),
-            rope.cos.data_ptr(), rope.sin.data_ptr(), rope.cos.shape[1], rope.cos.shape[0], rope.positions.data_ptr(),
-            rope.slots.data_ptr(), 1 if rope.write_kv else 0, stream), "attention_decode_rope")
-    elif plan.num_decode_items:
-        _lib.check(L.oi_attention_decode(
-            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
-            int(page_stride), ctx.cache.page_size, bt.data_ptr(), bt.stride(0), ctx.cu_seqlens.data_ptr(),
-            group_step.kv_lens.data_ptr(), plan.decode_items.data_ptr(), plan.num_decode_items,
-            plan.row_splits.data_ptr(), out.shape[0], nq, nkv, hd, float(scale), win, po, pl, plan.max_splits,
-            1 if plan.decode_merge_in_kernel else 0, stream), "attention_decode")
+    # the tensor-core kernels: bfloat16, head_dim 32, 64 or 128
+    tensor_core = (qkv.dtype == torch.bfloat16 and hd in (32, 64, 128) and group <= ROWS_PER_CTA_LARGE
+                   and qkv.stride(0) % 2 == 0 and page_stride % 8 == 0)
+    def ptr(obj, name):     # a step that only runs kernels which do not read a tensor may leave it out
+        t = getattr(obj, name, None)
+        return 0 if t is None else t.data_ptr()
+
+    step = native.AttnStep(
+        slot_mapping=ptr(group_step, "slot_mapping"), block_table=bt.data_ptr(), kv_lens=group_step.kv_lens.data_ptr(),
+        cu_seqlens=ctx.cu_seqlens.data_ptr(), token_req=ptr(ctx, "token_req"), positions=ptr(ctx, "positions"),
+        bt_stride=bt.stride(0), tokens=ctx.num_tokens, page_size=ctx.cache.page_size, num_pages=k_cache.shape[0],
+        page_stride=int(page_stride), tensor_core=1 if tensor_core else 0)
+    if tensor_core:
+        plan = _plan_for(ctx, group_step, group, nq, nkv, hd, window, qkv.device)
+        step.keep = plan       # the plan's device tensors live as long as the description
+        step.tile_items, step.num_tile_items = plan.tile_items.data_ptr(), plan.num_tile_items
+        step.decode_items, step.num_decode_items = plan.decode_items.data_ptr(), plan.num_decode_items
+        step.row_splits = plan.row_splits.data_ptr()
+        step.rows_per_cta, step.tile_split, step.max_splits = plan.rows_per_cta, 1 if plan.tile_split else 0, plan.max_splits
+        step.merge_in_kernel = 1 if plan.decode_merge_in_kernel else 0
+        step.part_o = 0 if plan.part_o is None else plan.part_o.data_ptr()
+        step.part_lse = 0 if plan.part_lse is None else plan.part_lse.data_ptr()
+        step.use_tcgen05 = 1 if (plan.num_tile_items and _tcgen05_takes(plan, qkv, out, k_cache, ctx.cache.page_size, nq, nkv,
+                                                                       hd, page_stride)) else 0
+        step.fuse_rope = 1 if decode_takes_rope(qkv, ctx, group_step, nq, nkv, hd, window, cos, q_norm_w, page_stride) else 0
+    ctx.scratch[key] = step
+    return step
+
+
+def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window) -> bool:
+    """The tensor-core kernels alone, when they cover the shape (bfloat16, head_dim 32, 64 or 128): q is ready and the
+    cache is written. Returns whether they ran."""
+    step = attention_step(ctx, group_step, q, out, k_cache, page_stride, nq, nkv, hd, window)
+    if not step.tensor_core:
+        return False
+    run_attention(step, attention_layer(q, out, k_cache, v_cache, nq, nkv, hd, scale, window, write_kv=False, rope_mode=0))
     return True
-
-
-register_tuned(attention_mma)

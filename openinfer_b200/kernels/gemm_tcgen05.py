@@ -25,22 +25,18 @@ def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 PAIR = 0          # tile_n value that selects 256 x 256 tiles computed by pairs of CTAs (cta_group::2)
-PAIR_MIN_ROWS = int(os.environ.get("OI_PAIR_MIN_ROWS", "129"))   # from this many rows the pair's 256-row tiles are used for prompt portions
-# Which kernel takes the plain projections of prompt portions: "library" or "pair" (this file's).
-# Measured on B200 at 2,048 rows (us, library / pair / one CTA per tile): QKV 6144 x 4096: 72 / 76 / 84;
-# O 4096 x 4096: 49 / 51 / 51; down 4096 x 12288: 136 / 148 / 165; gate|up 24576 x 4096: 279 / 285 / 313
-# (and 285 includes the activation, which costs the library path a further 32 us kernel). The pair's
-# main loop runs at about 89 % of the library's rate per SM: its stage of 32 KB per 512 tensor-core
-# cycles keeps the shared memory busy with 64 + 64 bytes per cycle, where the library's 256 x 256 tile
-# per CTA needs 48 + 48.
-PREFILL_GEMM = os.environ.get("OI_PREFILL_GEMM", "library")
 
 
 def portion_tile(rows: int, K: int = 1 << 30) -> int:
-    """The tile a prompt portion of ``rows`` tokens is computed with. Short sums (K <= 2048) stay with single
-    CTAs: a tile's products are then no longer than its epilogue, which the pairs' larger tile does not
-    hide (fused gate/up at 2,048 rows, N 6144: K 1024 34.6 against 37.6 us, K 2048 44.2 against 45.5)."""
-    return PAIR if rows >= PAIR_MIN_ROWS and K > 2048 else 256
+    """The tile a prompt portion of ``rows`` tokens is computed with (what the native dispatch of the fused gate/up
+    product uses). Short sums (K <= 2048) stay with single CTAs: a tile's products are then no longer than its
+    epilogue, which the pairs' larger tile does not hide (fused gate/up at 2,048 rows, N 6144: K 1024 34.6 against
+    37.6 us, K 2048 44.2 against 45.5). Measured on B200 at 2,048 rows (us, library / pair / one CTA per tile):
+    QKV 6144 x 4096: 72 / 76 / 84; O 4096 x 4096: 49 / 51 / 51; down 4096 x 12288: 136 / 148 / 165;
+    gate|up 24576 x 4096: 279 / 285 / 313 (and 285 includes the activation, which costs the library path a further
+    32 us kernel): the plain products of prompt portions stay with the library unless OI_PREFILL_GEMM=pair."""
+    from . import native
+    return PAIR if rows >= _lib.load().oi_option(native.OPT_PAIR_MIN_ROWS) and K > 2048 else 256
 
 
 def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256) -> torch.Tensor:

@@ -81,6 +81,9 @@ def load(verbose: bool = True) -> ctypes.CDLL:
             fn.argtypes = args
             fn.restype = c_int
         _declare_optional(lib)
+        from . import native
+        native.declare(lib)
+        native.configure_from_environment(lib)
         _lib = lib
         return lib
 
@@ -105,8 +108,14 @@ def _declare_optional(lib) -> None:
             fn.restype = c_int
 
 
-# number of entry-point calls that launched work (read by the benchmark)
-launches = 0
+# kernels of recorded graphs that replays launched (the library counts the kernels it launches itself)
+replayed = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far: by its entry points, and by replays of recorded graphs."""
+    return int(load().oi_launches()) + replayed
+
 
 try:    # the raw handle of the current stream without building a Stream object (about ten times faster)
     from torch._C import _cuda_getCurrentRawStream as _raw_stream
@@ -124,8 +133,6 @@ def current_stream() -> int:
 
 
 def check(code: int, what: str) -> None:
-    global launches
-    launches += 1
     if code != 0:
         msg = load().oi_last_error().decode(errors="replace")
         raise KernelError(f"{what} failed (code {code}): {msg}")

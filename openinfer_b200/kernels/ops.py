@@ -87,6 +87,38 @@ def copy_words(dst: torch.Tensor, src: torch.Tensor, n: int, *, ids_off: int = -
                                _ptr(tokens), 0 if tokens is None else tokens.numel(), _stream()), "copy_words")
 
 
+class UploadRing:
+    """Small host arrays of int32 to the device without a copy-engine operation and without making the host wait
+    for the stream: a ring of pinned buffers that a kernel reads (``copy_words``), each guarded by the event of its
+    last use."""
+
+    def __init__(self, slots: int = 4) -> None:
+        self.slots = slots
+        self.buffers: list = []
+        self.events: list = []
+        self.turn = 0
+
+    def upload(self, host, device) -> torch.Tensor:
+        n = int(host.size)
+        if not self.buffers or self.buffers[0].numel() < n:
+            if self.buffers:
+                torch.cuda.current_stream().synchronize()   # kernels in flight may still read the old buffers
+            self.buffers = [torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True) for _ in range(self.slots)]
+            self.events = [None] * self.slots
+        self.turn = (self.turn + 1) % self.slots
+        if self.events[self.turn] is not None:
+            self.events[self.turn].synchronize()
+        buf = self.buffers[self.turn]
+        buf[:n].numpy()[:] = host
+        dev = torch.empty(max(n, 1), dtype=torch.int32, device=device)
+        if n:
+            copy_words(dev, buf, n)
+        event = torch.cuda.Event()
+        event.record()
+        self.events[self.turn] = event
+        return dev[:n]
+
+
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, *,
             delta: Optional[torch.Tensor] = None, row_idx: Optional[torch.Tensor] = None,
             weight_offset: float = 0.0) -> torch.Tensor:

@@ -21,8 +21,11 @@ INVARIANT_DECODE_SPLITS = 16
 
 
 def set_batch_invariant(on: bool) -> None:
+    """Process-wide; the native dispatch of the products is told as well."""
     global _BATCH_INVARIANT
     _BATCH_INVARIANT = bool(on)
+    from . import lib, native
+    lib.check(lib.load().oi_configure(native.OPT_BATCH_INVARIANT, 1 if _BATCH_INVARIANT else 0), "configure")
 
 
 def batch_invariant() -> bool:

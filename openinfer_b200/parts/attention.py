@@ -15,7 +15,6 @@ import torch
 
 from ..cache.manager import KvNeed
 from ..kernels import attention as attn_kernels
-from ..kernels import ops
 from ..kernels.linear import linear
 from .base import CacheBinding, Mixer
 from .registry import build_position_encoding, register_mixer
@@ -85,23 +84,13 @@ class Attention(Mixer):
         cos, sin = self.tables if self.tables is not None else (None, None)
         qn = s.qk_norm
         out = torch.empty((x.shape[0], self.q_dim), dtype=x.dtype, device=x.device)
-        if attn_kernels.decode_takes_rope(qkv, ctx, group, s.num_heads, s.num_kv_heads, s.head_dim, s.window, cos,
-                                          self.q_norm_w, page_stride):
-            # a step of single tokens: the decode kernel normalises and rotates q and k and stores k and v itself
-            fusion = attn_kernels.RopeFusion(
-                self.q_norm_w, self.k_norm_w, qn.eps if qn else 0.0, qn.weight_offset if qn else 0.0, cos, sin,
-                ctx.positions, group.slot_mapping, binding.owns_kv)
-            attn_kernels.paged_attention(qkv, out, k_cache, v_cache, page_stride, ctx, group, s.num_heads, s.num_kv_heads,
-                                         s.head_dim, s.softmax_scale, s.window, rope=fusion)
-            return linear(out, self.w_o)
-        ops.qk_norm_rope_kv(
-            qkv, s.num_heads, s.num_kv_heads, s.head_dim,
-            q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w,
-            eps=qn.eps if qn else 0.0, weight_offset=qn.weight_offset if qn else 0.0,
-            cos=cos, sin=sin, positions=ctx.positions, slots=group.slot_mapping,
-            k_cache=k_cache, v_cache=v_cache, page_stride=page_stride, page_size=ctx.cache.page_size,
-            write_kv=binding.owns_kv)
-        attn_kernels.paged_attention(
-            qkv[:, : self.q_dim], out, k_cache, v_cache, page_stride, ctx, group,
-            s.num_heads, s.num_kv_heads, s.head_dim, s.softmax_scale, s.window)
+        # One native call: the norm + rotation + cache write (in a kernel of its own, or inside the decode kernel when
+        # the step is single tokens in one wave), then the attention kernel(s) that take the step's shape.
+        step = attn_kernels.attention_step(ctx, group, qkv, out, k_cache, page_stride, s.num_heads, s.num_kv_heads,
+                                           s.head_dim, s.window, cos=cos, q_norm_w=self.q_norm_w)
+        layer = attn_kernels.attention_layer(
+            qkv, out, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim, s.softmax_scale, s.window,
+            q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=qn.eps if qn else 0.0,
+            weight_offset=qn.weight_offset if qn else 0.0, cos=cos, sin=sin, write_kv=binding.owns_kv, rope_mode=1)
+        attn_kernels.run_attention(step, layer)
         return linear(out, self.w_o)

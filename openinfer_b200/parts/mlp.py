@@ -11,21 +11,20 @@ from typing import Dict, Optional
 
 import torch
 
-from ..kernels import gemm_tcgen05, ops, policy
-from ..kernels.linear import gate_up_silu_mul, linear, linear_silu_mul
+from ..kernels import gemm_tcgen05, native, ops
+from ..kernels import lib as _lib
+from ..kernels.linear import ensure_library
 from .base import FeedForward
 from .registry import register_feed_forward
 from .spec import GatedMlpSpec, ParamInfo
 
-# rows from which the gate/up product with the activation in its epilogue is used (prompt portions)
-FUSED_MIN_ROWS = 128
 
 
 @register_feed_forward("gated_mlp")
 class GatedMlp(FeedForward):
     def __init__(self, spec: GatedMlpSpec) -> None:
         super().__init__(spec)
-        ops.act_code(spec.activation)      # refuses a name no kernel knows; the kernels take the code as an argument
+        self.act_code = ops.act_code(spec.activation)   # refuses a name no kernel knows; the kernels take the code
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -51,17 +50,24 @@ class GatedMlp(FeedForward):
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        inter = self.spec.intermediate_size
-        if self.block == gemm_tcgen05.ACT_BLOCK and x.dtype == torch.bfloat16:
-            if (x.shape[0] >= FUSED_MIN_ROWS or policy.batch_invariant()) and inter % (2 * gemm_tcgen05.ACT_BLOCK) == 0:
-                act = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
-                if gemm_tcgen05.takes(act, x, self.w_gate_up):
-                    tile = 256 if policy.batch_invariant() else gemm_tcgen05.portion_tile(x.shape[0], x.shape[1])
-                    gemm_tcgen05.gemm_silu_mul(act, x, self.w_gate_up, tile, self.spec.activation)
-                    return linear(act, self.w_down)
-            else:
-                act = gate_up_silu_mul(x, self.w_gate_up, self.spec.activation)     # decode: the weight stream forms the activation
-                if act is not None:
-                    return linear(act, self.w_down)
-        gate_up = linear(x, self.w_gate_up)
-        return linear_silu_mul(gate_up, self.w_down, self.block, self.spec.activation)
+        """One native call (``oi_gated_mlp``): it picks, by the step's rows, the product that forms the activation in
+        its epilogue (tcgen05 tiles from 128 rows, the weight stream up to 32) or the plain product and the
+        stand-alone activation kernel, then the down projection."""
+        s = self.spec
+        M, inter = x.shape[0], s.intermediate_size
+        L = _lib.load()
+        codes = native.DTYPE_CODE
+        if not x.is_contiguous():
+            x = x.contiguous()
+        if M > 32:
+            ensure_library(x.device)
+        out = torch.empty((M, s.hidden_size), dtype=x.dtype, device=x.device)
+        act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
+        gate_up = None
+        if L.oi_gated_mlp_needs_gate_up(codes[x.dtype], codes[self.w_gate_up.dtype], M, s.hidden_size, inter, self.block):
+            gate_up = torch.empty((M, 2 * inter), dtype=x.dtype, device=x.device)
+        _lib.check(L.oi_gated_mlp(out.data_ptr(), x.data_ptr(), codes[x.dtype], M, s.hidden_size, inter,
+                                  self.w_gate_up.data_ptr(), codes[self.w_gate_up.dtype], self.w_down.data_ptr(),
+                                  codes[self.w_down.dtype], self.act_code, self.block, act.data_ptr(), 0 if gate_up is None else gate_up.data_ptr(),
+                                  _lib.current_stream()), "gated_mlp")
+        return out

@@ -280,3 +280,24 @@ def test_head_sizes_in_steps_of_16(tmp_path, dtype, hd, nq, nkv, hidden):
     _check(replay_in_process(runner, steps), ref, dtype, f"head {hd}/{dtype}")
     runner.cache.check()
     assert runner.cache.min_free_pages() == runner.cache.num_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_native_step_and_part_by_part_step_give_the_same_bits(folders, workloads, name, dtype):
+    """A model made of the package's own parts runs every layer of a step in one native call; with that switched
+    off the parts are called one by one from Python (what a model with a registered part of its own does). Both
+    launch the same kernels with the same arguments: the logits are equal bit for bit, mixed steps and recorded
+    decode steps included, and equal to the plain implementation within the tolerance."""
+    cfg, reqs, ref = workloads[name]
+    max_tokens = max(round64(len(t)) for t in reqs.values()) + 192
+    steps = trace_mixed(reqs, max_tokens, seed=13)
+    outs = {}
+    for native_step in (True, False):
+        runner = _runner(folders[name], dtype, max_tokens, page_size=16, cuda_graph=True)
+        runner.model.native_step = native_step
+        outs[native_step] = replay_in_process(runner, steps)
+        assert (runner.model._native is not None) == native_step
+    for rid in ref:
+        assert torch.equal(outs[True][rid], outs[False][rid]), f"request {rid}: the two step paths differ"
+    _check(outs[True], ref, dtype, f"native step {name}/{dtype}")
