@@ -465,7 +465,7 @@ def main() -> int:
     for x in sizes:
         if x not in MODELS:
             ap.error(f"--sizes: unknown size {x!r}")
-    max_batch = B if args.skip_points else max(B, 64)
+    max_batch = max(B, 64) if (not args.skip_points or args.profile == "mixed") else B
     # Through the entry point the requests' prompts are computed one portion a step, and a request that has its
     # prompt decodes while the others' are still computed: it must not finish before all of them decode.
     e2e_prompt_steps = max(B, 8) * -(-CONTEXT // PREFILL_TOKENS)

@@ -9,7 +9,7 @@
 
 namespace {
 
-int g_opt[OI_OPT_COUNT] = {0, 0, 0, 0, 129};
+int g_opt[OI_OPT_COUNT] = {0, 0, 0, 0, 129, 0};
 constexpr int kDecodeMaxRows = 32;    // rows up to which the streaming product takes a product
 constexpr int kSkinnyMaxRows = 16;
 constexpr int kFusedMinRows = 128;    // rows from which gate/up forms the activation in the tcgen05 product's epilogue
@@ -206,6 +206,91 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
   return OI_OK;
 }
 
+namespace {
+// A decode-sized step without norm kernels inside the layer stack: the products that end a residual branch (O, down)
+// add the residual and leave the next norm's inputs behind, the products that follow (gate/up, QKV) scale their
+// rows (gemm_stream.cu). Taken, when switched on (OI_OPT_FUSE_NORM, off by default), for up to 32 rows of a bfloat16
+// model whose weights are all bfloat16 and TMA-readable.
+// Measured on B200, it is no gain: 5 instead of 7 kernels per layer, but Qwen3-8B sizes at batch 8 run 3.56 ms a step
+// against 3.50 ms with the norm kernels (batch 1: 3.22 against 3.19; Qwen3-0.6B sizes, batch 8: 1.19 against 1.11).
+// The norm kernel's 2-3 us are not idle time: under it the product behind it, already resident, fills its ring of
+// weight tiles, which it can only do once the product before has left the SMs; without the norm kernel that filling
+// stands in the open, and the products that end a branch are 1-3 us longer for the residual's round trip through L2.
+bool fused_norm_step(const OiModelDesc* m, const OiStepDesc* st) {
+  if (!g_opt[OI_OPT_FUSE_NORM] || g_opt[OI_OPT_BATCH_INVARIANT] || g_opt[OI_OPT_DECODE_GEMM] != 0) return false;
+  if (st->tokens > kDecodeMaxRows || m->dtype != OI_BF16 || !st->xs || !st->ssq || m->hidden % 8) return false;
+  if (st->ssq_stride % 4 || st->ssq_stride < 8 * ((m->hidden + 127) / 128)) return false;
+  for (int i = 0; i < m->num_layers; ++i) {
+    const OiLayerDesc& L = m->layers[i];
+    const int q_dim = L.attn.nq * L.attn.hd;
+    if (L.w_qkv_dtype != OI_BF16 || L.w_o_dtype != OI_BF16 || L.w_gate_up_dtype != OI_BF16 || L.w_down_dtype != OI_BF16) return false;
+    if (L.act_block != 64 || (2 * L.inter) % 128 || L.inter % 8 || q_dim % 8) return false;
+    if ((uintptr_t)L.w_qkv % 16 || (uintptr_t)L.w_o % 16 || (uintptr_t)L.w_gate_up % 16 || (uintptr_t)L.w_down % 16) return false;
+  }
+  return true;
+}
+
+int forward_fused_norm(const OiModelDesc* m, const OiStepDesc* st, void* stream) {
+  const int T = st->tokens, H = m->hidden;
+  __nv_bfloat16* h = (__nv_bfloat16*)st->h;
+  __nv_bfloat16* xs = (__nv_bfloat16*)st->xs;
+  const float inv_width = 1.f / (float)H;
+  int units = 0;   // partial sums of squares that the last residual product left per row
+  for (int i = 0; i < m->num_layers; ++i) {
+    const OiLayerDesc& L = m->layers[i];
+    OI_REQUIRE(L.attn_step >= 0 && L.attn_step < st->num_attn_steps, "forward: layer %d names attention step %d of %d", i,
+               L.attn_step, st->num_attn_steps);
+    const int q_dim = L.attn.nq * L.attn.hd;
+    // ---- input norm + QKV
+    if (i == 0) {
+      OI_TRY(oi_rmsnorm(st->x, st->h, nullptr, OI_BF16, L.input_norm_w, L.input_norm_dtype, nullptr, T, H, L.input_eps,
+                        L.input_offset, stream));
+      OI_TRY(oi_gemm_stream(st->qkv, OI_BF16, L.qkv_rows, st->x, H, L.w_qkv, H, T, L.qkv_rows, H, stream_slices(L.qkv_rows, H),
+                            OI_ACT_NONE, stream));
+    } else {
+      OiStreamEpilogue ep = {};
+      ep.ssq_in = st->ssq, ep.ssq_units = units, ep.ssq_stride = st->ssq_stride, ep.inv_width = inv_width, ep.eps = L.input_eps;
+      OI_TRY(oi_gemm_stream_fused(st->qkv, OI_BF16, L.qkv_rows, xs, H, L.w_qkv, H, T, L.qkv_rows, H,
+                                  stream_slices(L.qkv_rows, H), OI_ACT_NONE, &ep, stream));
+    }
+    // ---- attention
+    OiAttnLayer a = L.attn;
+    a.qkv = st->qkv, a.q_row_stride = L.qkv_rows, a.out = st->attn, a.out_row_stride = q_dim, a.dtype = OI_BF16;
+    OI_TRY(oi_attention_layer(&st->attn_steps[L.attn_step], &a, stream));
+    // ---- O + residual, and what the post norm needs
+    {
+      const int c = stream_slices(H, q_dim);
+      OiStreamEpilogue ep = {};
+      ep.residual = h, ep.ld_residual = H, ep.norm_w = L.post_norm_w, ep.norm_w_bf16 = L.post_norm_dtype == OI_BF16;
+      ep.w_offset = L.post_offset, ep.xs = xs, ep.ld_xs = H, ep.ssq_out = st->ssq, ep.ssq_stride = st->ssq_stride;
+      OI_TRY(oi_gemm_stream_fused(h, OI_BF16, H, st->attn, q_dim, L.w_o, q_dim, T, H, q_dim, c, OI_ACT_NONE, &ep, stream));
+      units = ((H + 127) / 128) * c;
+    }
+    // ---- post norm + gate/up with the activation
+    {
+      OiStreamEpilogue ep = {};
+      ep.ssq_in = st->ssq, ep.ssq_units = units, ep.ssq_stride = st->ssq_stride, ep.inv_width = inv_width, ep.eps = L.post_eps;
+      OI_TRY(oi_gemm_stream_fused(st->act, OI_BF16, L.inter, xs, H, L.w_gate_up, H, T, 2 * L.inter, H,
+                                  stream_slices(2 * L.inter, H), L.act, &ep, stream));
+    }
+    // ---- down + residual, and what the next layer's input norm needs (the last layer: only the residual)
+    {
+      const int c = stream_slices(H, L.inter);
+      OiStreamEpilogue ep = {};
+      ep.residual = h, ep.ld_residual = H;
+      if (i + 1 < m->num_layers) {
+        const OiLayerDesc& next = m->layers[i + 1];
+        ep.norm_w = next.input_norm_w, ep.norm_w_bf16 = next.input_norm_dtype == OI_BF16, ep.w_offset = next.input_offset;
+        ep.xs = xs, ep.ld_xs = H, ep.ssq_out = st->ssq, ep.ssq_stride = st->ssq_stride;
+      }
+      OI_TRY(oi_gemm_stream_fused(h, OI_BF16, H, st->act, L.inter, L.w_down, L.inter, T, H, L.inter, c, OI_ACT_NONE, &ep, stream));
+      units = ((H + 127) / 128) * c;
+    }
+  }
+  return OI_OK;
+}
+}  // namespace
+
 OI_API int oi_forward(const OiModelDesc* m, const OiStepDesc* st, void* stream) {
   OI_REQUIRE(m && st && m->layers && (st->num_attn_steps == 0 || st->attn_steps), "forward: null description");
   const int T = st->tokens, H = m->hidden, dt = m->dtype;
@@ -214,7 +299,9 @@ OI_API int oi_forward(const OiModelDesc* m, const OiStepDesc* st, void* stream) 
   OI_TRY(oi_embedding(st->h, dt, m->embedding, m->embedding_dtype, st->token_ids, T, H, m->vocab, stream));
   if (m->embedding_scale != 1.f) OI_TRY(oi_scale_cap(st->h, dt, (long long)T * H, m->embedding_scale, 0.f, stream));
   const void* pending = nullptr;   // the last branch output, added by the norm that reads the row next
-  for (int i = 0; i < m->num_layers; ++i) {
+  const bool fused = fused_norm_step(m, st);
+  if (fused) OI_TRY(forward_fused_norm(m, st, stream));
+  for (int i = 0; i < (fused ? 0 : m->num_layers); ++i) {
     const OiLayerDesc& L = m->layers[i];
     OI_REQUIRE(L.attn_step >= 0 && L.attn_step < st->num_attn_steps, "forward: layer %d names attention step %d of %d", i,
                L.attn_step, st->num_attn_steps);

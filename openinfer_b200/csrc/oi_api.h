@@ -7,6 +7,28 @@
 
 #include "common.cuh"
 
+// What the streaming product can do where it adds up its K slices, to take the norm kernels out of a decode layer
+// (gemm_stream.cu). All pointers are device pointers; a null `ssq_in` / `residual` switches the part off.
+typedef struct OiStreamEpilogue {
+  // the product FOLLOWS a norm whose weight is already in its input: row m of the sums is multiplied by
+  // rsqrt(sum_u ssq_in[m * ssq_stride + u] * inv_width + eps), u < ssq_units
+  const float* ssq_in;
+  int ssq_units;
+  int ssq_stride;              // floats between rows of the partial squares (both directions), a multiple of 4
+  float inv_width, eps;
+  // the product ENDS a residual branch: out[m, n] = round(residual[m, n] + sum) (out may be the residual itself), and
+  // for the norm that reads the row next (xs null: none): xs[m, n] = round(out[m, n] * (w_offset + norm_w[n])) and
+  // ssq_out[m * ssq_stride + tile * slices + slice] = the sum of out[m, n]^2 over the columns that slice of that tile owns
+  const __nv_bfloat16* residual;
+  long long ld_residual;
+  const void* norm_w;
+  int norm_w_bf16;
+  float w_offset;
+  __nv_bfloat16* xs;
+  long long ld_xs;
+  float* ssq_out;
+} OiStreamEpilogue;
+
 // argmax_noalloc.cu
 OI_API int oi_argmax_noalloc(int* out, const float* logits, int rows, int vocab, long long row_stride, void* stream);
 
@@ -66,6 +88,8 @@ OI_API int oi_gemm_skinny(void* out, int out_dtype, long long ldc, const void* x
 // gemm_stream.cu
 OI_API int oi_gemm_stream(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W, long
        long ldw, int M, int N, int K, int cluster_size, int act, void* stream);
+OI_API int oi_gemm_stream_fused(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W,
+       long long ldw, int M, int N, int K, int cluster_size, int act, const OiStreamEpilogue* epilogue, void* stream);
 OI_API int oi_gemm_stream_status(int* status);
 
 // gemm_tcgen05.cu
@@ -120,7 +144,9 @@ enum : int {
   OI_OPT_PREFILL_GEMM = 2,      // plain products of more rows: 0 library, 1 the pair kernel of gemm_tcgen05.cu
   OI_OPT_FORCE_SLICES = 3,      // > 0: K slices of the decode products, whatever the shape (measurements)
   OI_OPT_PAIR_MIN_ROWS = 4,     // rows from which the fused gate/up product uses pairs of CTAs
-  OI_OPT_COUNT = 5,
+  OI_OPT_FUSE_NORM = 5,         // 1: steps of up to 32 rows run without norm kernels inside the layer stack (oi_forward);
+                                // off by default: measured slower, see host_step.cu
+  OI_OPT_COUNT = 6,
 };
 OI_API int oi_configure(int option, int value);
 OI_API int oi_option(int option);
@@ -225,6 +251,9 @@ typedef struct OiStepDesc {
   void* gate_up;              // [tokens, 2 max_inter] or null (see oi_gated_mlp_needs_gate_up)
   void* wanted;               // [num_want, hidden] normed wanted rows
   float* logits;              // [num_want, vocab]
+  void* xs;                   // [tokens, hidden] rows times the next norm's weight (steps of up to 32 rows; or null)
+  float* ssq;                 // [32, ssq_stride] partial sums of squares (with xs); ssq_stride >= 8 * ceil(hidden / 128)
+  int ssq_stride;
   int tokens, num_attn_steps, num_want;
 } OiStepDesc;
 

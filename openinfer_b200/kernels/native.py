@@ -16,11 +16,19 @@ import torch
 from . import lib as _lib
 
 # options of oi_configure
-OPT_BATCH_INVARIANT, OPT_DECODE_GEMM, OPT_PREFILL_GEMM, OPT_FORCE_SLICES, OPT_PAIR_MIN_ROWS = range(5)
+OPT_BATCH_INVARIANT, OPT_DECODE_GEMM, OPT_PREFILL_GEMM, OPT_FORCE_SLICES, OPT_PAIR_MIN_ROWS, OPT_FUSE_NORM = range(6)
 DECODE_GEMM_CODES = {"stream": 0, "skinny": 1, "library": 2}
 PREFILL_GEMM_CODES = {"library": 0, "pair": 1}
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class StreamEpilogue(Structure):
+    _fields_ = [
+        ("ssq_in", c_void_p), ("ssq_units", c_int), ("ssq_stride", c_int), ("inv_width", c_float), ("eps", c_float),
+        ("residual", c_void_p), ("ld_residual", c_longlong), ("norm_w", c_void_p), ("norm_w_bf16", c_int),
+        ("w_offset", c_float), ("xs", c_void_p), ("ld_xs", c_longlong), ("ssq_out", c_void_p),
+    ]
 
 
 class AttnStep(Structure):
@@ -76,6 +84,7 @@ class StepDesc(Structure):
         ("token_ids", c_void_p), ("attn_steps", POINTER(AttnStep)), ("want_rows", c_void_p),
         ("h", c_void_p), ("x", c_void_p), ("qkv", c_void_p), ("attn", c_void_p), ("branch_a", c_void_p),
         ("branch_m", c_void_p), ("act", c_void_p), ("gate_up", c_void_p), ("wanted", c_void_p), ("logits", c_void_p),
+        ("xs", c_void_p), ("ssq", c_void_p), ("ssq_stride", c_int),
         ("tokens", c_int), ("num_attn_steps", c_int), ("num_want", c_int),
     ]
 
@@ -95,6 +104,8 @@ def declare(lib) -> None:
     lib.oi_attention_layer.argtypes, lib.oi_attention_layer.restype = [POINTER(AttnStep), POINTER(AttnLayer), P], c_int
     lib.oi_forward.argtypes, lib.oi_forward.restype = [POINTER(ModelDesc), POINTER(StepDesc), P], c_int
     lib.oi_launches.argtypes, lib.oi_launches.restype = [], ctypes.c_ulonglong
+    lib.oi_gemm_stream_fused.argtypes = [P, I, L, P, L, P, L, I, I, I, I, I, POINTER(StreamEpilogue), P]
+    lib.oi_gemm_stream_fused.restype = c_int
 
 
 def configure_from_environment(lib) -> None:
@@ -108,6 +119,8 @@ def configure_from_environment(lib) -> None:
         lib.oi_configure(OPT_PREFILL_GEMM, PREFILL_GEMM_CODES[env["OI_PREFILL_GEMM"]])
     if env.get("OI_GEMM_C"):
         lib.oi_configure(OPT_FORCE_SLICES, int(env["OI_GEMM_C"]))
+    if env.get("OI_FUSE_NORM"):
+        lib.oi_configure(OPT_FUSE_NORM, int(env["OI_FUSE_NORM"]))
     if env.get("OI_PAIR_MIN_ROWS"):
         lib.oi_configure(OPT_PAIR_MIN_ROWS, int(env["OI_PAIR_MIN_ROWS"]))
 

@@ -239,6 +239,10 @@ class Model:
                                             L.attn.nq, L.attn.nkv, L.attn.hd, at.spec.window, cos=cos, q_norm_w=at.q_norm_w)
             kept.append(s)
             ctypes.memmove(ctypes.byref(steps[j]), ctypes.byref(s), ctypes.sizeof(native.AttnStep))
+        xs = ssq = None
+        if T <= 32 and dt == torch.bfloat16:   # decode-sized steps may run without norm kernels inside the layer stack
+            xs = buf(H)
+            ssq = torch.empty((32, -(-H // 128) * 8), dtype=torch.float32, device=dev)   # [row][tile of 128 columns, K slice]
         n_want = 0 if row_idx is None else row_idx.numel()
         wanted = buf(H, rows=n_want) if n_want else None
         logits = buf(self.spec.vocab_size, dtype=torch.float32, rows=n_want) if n_want else None
@@ -247,7 +251,8 @@ class Model:
             h=h.data_ptr(), x=x.data_ptr(), qkv=qkv.data_ptr(), attn=attn.data_ptr(), branch_a=branch_a.data_ptr(),
             branch_m=branch_m.data_ptr(), act=act.data_ptr(), gate_up=0 if gate_up is None else gate_up.data_ptr(),
             wanted=wanted.data_ptr() if n_want else 0, logits=logits.data_ptr() if n_want else 0,
-            tokens=T, num_attn_steps=len(keys), num_want=n_want)
+            xs=0 if xs is None else xs.data_ptr(), ssq=0 if ssq is None else ssq.data_ptr(),
+            ssq_stride=0 if ssq is None else ssq.stride(0), tokens=T, num_attn_steps=len(keys), num_want=n_want)
         _lib.check(lib.oi_forward(ctypes.byref(desc), ctypes.byref(step), _lib.current_stream()), "forward")
         return logits
 

@@ -582,6 +582,61 @@ def test_gemm_stream(M, N, K):
         assert torch.equal(one[0], out[M - 1])
 
 
+@pytest.mark.parametrize("M", [1, 8, 20, 32])
+@pytest.mark.parametrize("H,K", [(320, 512), (1024, 2048), (4096, 1024)])
+def test_gemm_stream_takes_the_norms_of_a_decode_layer_into_itself(M, H, K):
+    """The streaming product's two additions against float64: a product that ends a residual branch adds the
+    residual and leaves the next norm's inputs (rows times the norm weight, partial sums of squares per tile and
+    K slice); the product behind it scales its rows by rsqrt(mean square + eps). Together: residual add, RMSNorm
+    and projection without a norm kernel. Every number of K slices the shape allows; a width that is no multiple
+    of the tile (320); gate/up with the activation as the second product."""
+    import ctypes
+    from openinfer_b200.kernels import lib as klib, linear as lin, native
+    L = klib.load()
+    torch.manual_seed(M + H)
+    eps, off, inter = 1e-5, 0.25, 256
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)                 # the branch's last activations
+    w1 = (torch.randn(H, K, device=DEV) * 0.05).to(torch.bfloat16)        # the branch's last projection
+    h = torch.randn(M, H, device=DEV).to(torch.bfloat16)                 # the residual stream
+    wn = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16)        # the next norm's weight
+    w2 = (torch.randn(2 * inter, H, device=DEV) * 0.05).to(torch.bfloat16)   # gate|up in blocks of 64
+    stream = torch.cuda.current_stream().cuda_stream
+    for c in (1, 2, 4, 8):
+        if (c - 1) * (-(-(K // 64) // c)) >= K // 64:
+            continue
+        h_new = h.clone()
+        xs = torch.full((M, H), float("nan"), device=DEV, dtype=torch.bfloat16)
+        units = -(-H // 128) * c
+        stride = -(-units // 4) * 4 + 4
+        ssq = torch.full((32, stride), float("nan"), device=DEV)          # whatever lies beyond the units is not read
+        ep = native.StreamEpilogue(residual=h_new.data_ptr(), ld_residual=H, norm_w=wn.data_ptr(), norm_w_bf16=1,
+                                   w_offset=off, xs=xs.data_ptr(), ld_xs=H, ssq_out=ssq.data_ptr(), ssq_stride=stride)
+        klib.check(L.oi_gemm_stream_fused(h_new.data_ptr(), 1, H, a.data_ptr(), K, w1.data_ptr(), K, M, H, K, c, 0,
+                                          ctypes.byref(ep), stream), "gemm_stream_fused")
+        want_h = h.double() + a.double() @ w1.double().t()
+        assert (h_new.double() - want_h).abs().max().item() <= 2e-2 * want_h.abs().max().item(), f"{c} slices: residual sum"
+        hr = h_new.double()                                              # what the kernel rounded is what it normalises
+        assert torch.equal(xs, (hr * (off + wn.double())).to(torch.bfloat16)), f"{c} slices: rows times the norm weight"
+        got_ssq = ssq[:M, :units].double().sum(1)
+        assert torch.allclose(got_ssq, (hr * hr).sum(-1), rtol=1e-5), f"{c} slices: sums of squares"
+        assert torch.isnan(ssq[M:]).all() and torch.isnan(ssq[:, units:]).all(), "written outside its rows and units"
+        # the product behind it: plain, and gate/up with the activation
+        rstd = torch.rsqrt((hr * hr).mean(-1, keepdim=True) + eps)
+        for act in (0, 1):
+            n_out = inter if act else 2 * inter
+            out = torch.full((M, n_out), float("nan"), device=DEV, dtype=torch.bfloat16)
+            ep2 = native.StreamEpilogue(ssq_in=ssq.data_ptr(), ssq_units=units, ssq_stride=stride, inv_width=1.0 / H, eps=eps)
+            klib.check(L.oi_gemm_stream_fused(out.data_ptr(), 1, n_out, xs.data_ptr(), H, w2.data_ptr(), H, M, 2 * inter, H,
+                                              L.oi_stream_slices(2 * inter, H), act, ctypes.byref(ep2), stream), "gemm_stream_fused")
+            y = (xs.double() @ w2.double().t()) * rstd
+            if act:
+                y = y.view(M, -1, 2, 64)
+                g, u = y[:, :, 0], y[:, :, 1]
+                y = (g / (1 + torch.exp(-g)) * u).reshape(M, inter)
+            assert (out.double() - y).abs().max().item() <= 2e-2 * y.abs().max().item(), f"{c} slices, act {act}: scaled product"
+    assert lin.stream_status() == 0
+
+
 def test_gemm_stream_refuses_bad_operands():
     from openinfer_b200.kernels import lib as klib
     L = klib.load()
