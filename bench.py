@@ -377,6 +377,13 @@ def measure_size(torch, mods, key, args, peaks, mixed: bool):
             flat[f"mixed_{key}"] = round(rows * 1000.0 / ms, 1)
             flat[f"mixed_{key}_ms"] = round(ms, 3)
             flat[f"mixed_{key}_frac"] = round(b.mixed_flops(nd, npor, por) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)
+            # the step is bound on both sides: the decoding requests' cache and the weights have to be read, the
+            # portions' products computed; the third figure is the time both would take one after the other at their
+            # measured peaks, divided by the step's time
+            mixed_bytes = b.runner.model.weight_bytes() + nd * CONTEXT * b.cache.bytes_per_token(b.esize)
+            t_floor = b.mixed_flops(nd, npor, por) / (peaks["bf16_tflops_sustained"] * 1e12) + mixed_bytes / (peaks["hbm_gbs"] * 1e9)
+            flat[f"mixed_{key}_hbm_frac"] = round(mixed_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            flat[f"mixed_{key}_frac_of_both"] = round(t_floor / (ms * 1e-3), 4)
             s_step, tok_step = b.mixed_e2e(nd, npor, por, steps, warm)
             flat[f"mixed_{key}_e2e"] = round(rows / s_step, 1)
             flat[f"mixed_{key}_e2e_ms"] = round(s_step * 1000, 3)

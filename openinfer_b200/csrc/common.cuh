@@ -64,12 +64,16 @@ typedef __nv_bfloat16 bf16;
 // in stream order; what overlaps is the launch latency, the prologues, and in the weight-streaming
 // products the first loads of the (never written) weights, which they request before waiting.
 // What a kernel may read before its wait must have been written before the step's kernels began: the
-// step's metadata is put in place by a kernel that does NOT trigger early (copy_words_kernel), so
-// everything behind it starts after it has finished; keys and values of earlier steps lie behind that fence too.
+// step's metadata is put in place by a kernel that does NOT trigger early (copy_words_kernel), and the
+// kernel launched after that one is launched WITHOUT the attribute (oi_fence_next_launch): it starts only
+// when the metadata kernel has completed and its writes are visible, and every later kernel of the chain
+// starts after that kernel has started. Keys and values of earlier steps lie behind that fence too.
 // A kernel launched without the attribute (oi_set_pdl(0), or after a library kernel) sees both
 // instructions as no-ops.
 // ---------------------------------------------------------------------------------------------
 int oi_pdl_enabled();
+void oi_fence_next_launch();   // the next kernel launched through oi_launch gets plain stream order (once)
+int oi_take_launch_fence();
 void oi_count_launch();   // every kernel launched through oi_launch is counted (oi_launches)
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
@@ -90,7 +94,8 @@ inline void oi_launch_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, 
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int na = 0;
-  if (oi_pdl_enabled()) {
+  const int fenced = oi_take_launch_fence();
+  if (oi_pdl_enabled() && !fenced) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;

@@ -60,13 +60,6 @@ OI_API int oi_embedding(void* out, int out_dtype, const void* table, int table_d
   return OI_OK;
 }
 
-// ---------------------------------------------------------------------------
-// RMSNorm. One block per output row.
-//   delta != null : x[row] <- round(x[row] + delta[row]) first (the residual sum, stored), and the
-//                   norm is taken of the ROUNDED sum (flashinfer_norm.cu:76-83, 107-124).
-//   row_idx != null : output row r reads x[row_idx[r]] (+ delta[row_idx[r]], not stored): the rows
-//                   whose logits are wanted.
-//   out[r] = round( x * rsqrt(mean(x^2) + eps) * (w_offset + w) )
 // ids[i] = from[src[i]] where src[i] >= 0: token ids that the previous step drew and the host has not
 // seen yet (indices outside `from` leave the id alone; the host checks them before the launch).
 __global__ void gather_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ from,
@@ -82,6 +75,7 @@ OI_API int oi_gather_tokens(int* ids, const int* src, const int* from, int n, in
   OI_REQUIRE(n >= 0 && n_from >= 0, "gather_tokens: bad sizes");
   if (n == 0) return OI_OK;
   oi_launch(gather_tokens_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, ids, src, from, n, n_from);
+  oi_fence_next_launch();
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -95,7 +89,8 @@ __global__ void copy_words_kernel(int* __restrict__ dst, const int* __restrict__
                                   int n_ids, const int* __restrict__ from, int n_from) {
   // No early trigger here: what this kernel writes (a step's lengths, block tables, positions) is read by
   // later kernels BEFORE their own wait, so nothing after it may start until it has finished. It is the
-  // fence between two steps.
+  // fence between two steps; the kernel launched next is launched without the programmatic attribute
+  // (oi_fence_next_launch below), so it starts only when this one has completed and its writes are visible.
   pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     int v = src[i];
@@ -115,11 +110,19 @@ OI_API int oi_copy_words(int* dst, const int* src, int n, int ids_off, int src_o
   if (n == 0) return OI_OK;
   const int blocks = (n + 255) / 256 > 64 ? 64 : (n + 255) / 256;
   oi_launch(copy_words_kernel, blocks, 256, 0, (cudaStream_t)stream, dst, src, n, ids_off, src_off, n_ids, from, n_from);
+  oi_fence_next_launch();
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
 
 // ---------------------------------------------------------------------------
+// ---------------------------------------------------------------------------
+// RMSNorm. One block per output row.
+//   delta != null : x[row] <- round(x[row] + delta[row]) first (the residual sum, stored), and the
+//                   norm is taken of the ROUNDED sum (flashinfer_norm.cu:76-83, 107-124).
+//   row_idx != null : output row r reads x[row_idx[r]] (+ delta[row_idx[r]], not stored): the rows
+//                   whose logits are wanted.
+//   out[r] = round( x * rsqrt(mean(x^2) + eps) * (w_offset + w) )
 template <typename T, bool kCache>
 __global__ void rmsnorm_kernel(T* __restrict__ out, T* __restrict__ x, const T* __restrict__ delta,
                                const void* __restrict__ w, int w_dtype, const int* __restrict__ row_idx,

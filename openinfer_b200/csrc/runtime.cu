@@ -21,6 +21,16 @@ OI_API int oi_abi_version() { return 1; }
 // Programmatic dependent launch of the library's kernels (see common.cuh): on unless switched off.
 static int g_pdl = 1;
 int oi_pdl_enabled() { return g_pdl; }
+// A kernel whose writes later kernels read BEFORE their own wait (the step's metadata) asks for the next launch to be
+// an ordinary one: that kernel then starts after the writer has completed, and the chain behind it after that.
+static int g_fence_next = 0;
+void oi_fence_next_launch() { g_fence_next = 1; }
+int oi_take_launch_fence() {
+  const int v = g_fence_next;
+  g_fence_next = 0;
+  return v;
+}
+
 // Kernels of this library launched so far (through oi_launch; a recorded graph's replays are not seen here).
 static unsigned long long g_launches = 0;
 void oi_count_launch() { ++g_launches; }

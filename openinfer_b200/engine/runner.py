@@ -188,6 +188,11 @@ class ModelRunner:
         the order of the entries and of each entry's ``want`` (None when nothing is wanted).
         ``device_tokens`` (int32, on the device): where entries with ``token_from`` take their token.
 
+        The returned tensor is valid until the next call of ``step``: a step that is replayed as a recorded
+        graph returns a view of that graph's output buffer, which the next replay overwrites (work queued on
+        the same stream before the next call, like the sampler's, reads it safely; keep ``logits.clone()``
+        to hold it longer).
+
         Raises ``OutOfPages`` with nothing changed if the cache cannot hold the new rows."""
         entries = list(entries)
         if not entries:

@@ -722,6 +722,25 @@ def test_gate_activation_is_an_argument_of_every_kernel_that_forms_it(act):
     assert g.status() == 0 and lin.stream_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 4096, 12288), (64, 1024, 25600), (33, 151, 72), (500, 3001, 1024)])
+def test_products_of_more_than_32_rows_add_up_in_float32(M, N, K):
+    """The dispatcher's product for steps of more than 32 rows (the vendor library called from native code, or the
+    package's own tcgen05 kernel where the library has nothing) against float64, with sums of up to 25,600 terms: the
+    bound is what float32 accumulation with ONE rounding of the result leaves (half a bfloat16 ulp of the result plus
+    a little); partial sums of a split K rounded to bfloat16 would break it. Output in bfloat16 and in float32."""
+    from openinfer_b200.kernels import linear as lin
+    torch.manual_seed(K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    out = lin.linear(x, w)
+    err = (out.double() - ref).abs()
+    assert (err <= ref.abs() * 2.0 ** -8 + 1e-3 * ref.abs().max()).all(), f"bfloat16 out: max err {err.max().item()}"
+    out32 = lin.linear(x, w, out_dtype=torch.float32)
+    err32 = (out32.double() - ref).abs().max().item()
+    assert err32 <= 2e-4 * ref.abs().max().item(), f"float32 out: max err {err32}"
+
+
 @pytest.mark.parametrize("tile_n", [256, 128, 0])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 4096), (300, 520, 1000), (2048, 1024, 512),
                                    (17, 100, 72), (129, 257, 8), (2048, 5120, 192), (600, 1100, 2048), (2048, 2560, 1536)])
