@@ -124,10 +124,12 @@ __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 #define OI_ACT_NONE 0
 #define OI_ACT_SILU 1        // g * sigmoid(g)
 #define OI_ACT_GELU_TANH 2   // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) = g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
-template <bool kFastExp>
+// kFast: exponential and division by the special-function unit's approximations (2 ulp each, far below the
+// rounding of a bfloat16 result), for the epilogues of the bfloat16 products.
+template <bool kFast>
 __device__ __forceinline__ float gate_act(float g, int act) {
   const float t = act == OI_ACT_GELU_TANH ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
-  return g / (1.f + (kFastExp ? __expf(-t) : expf(-t)));
+  return kFast ? __fdividef(g, 1.f + __expf(-t)) : g / (1.f + expf(-t));
 }
 
 template <typename T>

@@ -10,8 +10,12 @@
 //   warp 1     allocates tensor memory; one elected thread issues four tcgen05.mma (K = 16 each)
 //              per stage and commits them to the stage's "empty" barrier, and after the last k
 //              block to the "accumulator ready" barrier;
-//   warps 2-5  wait for the accumulator, read it back with tcgen05.ld (each warp its quarter of the
-//              128 lanes, 32 columns at a time), round once and store rows of C.
+//   warps 2-9  wait for the accumulator, read it back with tcgen05.ld (a warp reads the quarter of the 128 lanes
+//              that its number modulo four names, 32 columns at a time; the two warps of a quarter take half
+//              of the tile's columns each), round once and store rows of C. Eight warps, two per scheduler: one
+//              warp's chain of tensor-memory load, conversion (with the activation: two special-function
+//              operations per value) and store is latency-bound on its own, 26 k cycles for a 128 x 256 tile
+//              with four warps, which is more than the products of a tile take when K is 1,024 or 2,048.
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error word in global memory
 // and a flag in shared memory that ends all roles; the CTA then lets its copies land (bounded),
 // frees its tensor memory and returns. No load uses cluster multicast: every CTA fetches its own
@@ -25,7 +29,9 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;      // measured: 4 -> 8 warps 4.5 -> 4.1 ms for a 2,048-token prompt at Qwen3-0.6B sizes; 16: no further gain
+constexpr int kParts = kEpilogueWarps / 4;          // warps that share a lane quarter split the tile's columns
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;  // warps 0, 1: copies and products; the others: the epilogue
 constexpr int kPairStages = 6;        // 32 KB each in the kernel of CTA pairs
 
 __device__ int g_gemm_error = 0;       // set to a non-zero code when a bounded wait ran out
@@ -74,9 +80,10 @@ __device__ __forceinline__ void store_32(TOut* dst, const float (&a)[32], int va
   }
 }
 
+// `part` (0 or 1): which half of the tile's columns this warp takes.
 template <int BN, typename TOut, bool kSiluMul>
 __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __restrict__ C, long long ldc, int row, int n0,
-                                                  int M, int N, int act) {
+                                                  int M, int N, int act, int part) {
   auto load = [&](int col, float (&a)[32]) {
     unsigned v[32];
     tmem_ld32(tmem_acc + (unsigned)col, v);
@@ -88,7 +95,7 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
     // the tile's columns: [64 gate | their 64 up] twice; output columns n0 / 2 + 64 * half + c
     const int n_out = N / 2, o0 = n0 / 2;
 #pragma unroll 1
-    for (int cc = 0; cc < BN / 2; cc += 32) {
+    for (int cc = part * (BN / 2 / kParts); cc < (part + 1) * (BN / 2 / kParts); cc += 32) {
       const int half = cc / 64, c = cc % 64;
       float g[32], u[32];
       load(half * 128 + c, g);
@@ -101,7 +108,7 @@ __device__ __forceinline__ void store_accumulator(unsigned tmem_acc, TOut* __res
     }
   } else {
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
+    for (int c = part * (BN / kParts); c < (part + 1) * (BN / kParts); c += 32) {
       float a[32];
       load(c, a);
       if (row < M) store_32(C + (size_t)row * ldc + n0 + c, a, N - (n0 + c));
@@ -144,7 +151,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), 4);      // one arrival per epilogue warp
+      mbar_init(acc_empty_bar(a), kEpilogueWarps);      // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -209,8 +216,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;            // a warp may only touch lanes [32 * (warp % 4), +32)
+    const int part = (warp - 2) >> 2;        // the two warps of a quarter take half of the columns each
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int a = local & 1;
@@ -219,7 +227,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
-      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act);
+      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act, part);
       // this warp has read its part of the accumulator: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -253,8 +261,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //   warp 1     of the even CTA alone issues the products (M = 256, N = 256, K = 16) and commits
 //              them to the "empty" barrier of the stage in both CTAs, and each tile's last ones to
 //              "accumulator ready" in both; warp 1 of both CTAs allocates and frees tensor memory;
-//   warps 2-5  of both CTAs drain their own tensor memory and arrive on the even CTA's
-//              "accumulator drained" barrier (8 arrivals).
+//   warps 2-9  of both CTAs drain their own tensor memory and arrive on the even CTA's
+//              "accumulator drained" barrier (16 arrivals).
 // Loads carry no cluster multicast: each CTA fetches what it holds. Every wait is bounded as above;
 // the two CTAs meet at the cluster's barrier before the tensor memory is freed.
 template <int kStages, typename TOut, bool kSiluMul>
@@ -289,7 +297,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
-      mbar_init(acc_empty_bar(a), 8);      // one arrival per epilogue warp of both CTAs
+      mbar_init(acc_empty_bar(a), 2 * kEpilogueWarps);      // one arrival per epilogue warp of both CTAs
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -355,6 +363,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
     int local = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
       const int a = local & 1;
@@ -363,7 +372,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int m0 = (tile % m_tiles) * kPairM + (int)rank * 128, n0 = (tile / m_tiles) * BN;
       const int row = m0 + quarter * 32 + lane;
       const unsigned tmem_acc = tmem_base + (unsigned)(a * BN) + ((unsigned)(quarter * 32) << 16);
-      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act);
+      store_accumulator<BN, TOut, kSiluMul>(tmem_acc, C, ldc, row, n0, M, N, act, part);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty_bar(a), 0));
