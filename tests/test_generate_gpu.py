@@ -323,3 +323,52 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
                 judged += 1
             seq.append(tok)
     assert judged >= 40
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_cancel_leaves_the_others_alone_and_frees_its_pages(folders, ahead):
+    """Requests are taken back in the middle of a prompt that is computed in portions and in the middle of
+    decoding (one step ahead: with a row in flight): nothing more of them is reported, the other requests' tokens
+    are what they are without any cancelling, and every page and state slot is back at the end."""
+    from openinfer_b200 import LLM
+    cfg, w = plain.read_model_folder(folders["B"])
+    rng = random.Random(21)
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (9, 70, 33, 5, 60)]
+    keep = [0, 2, 3]
+    want = {i: plain.greedy_generate(cfg, w, prompts[i], 10) for i in keep}
+    llm = LLM(folders["B"], dtype="float32", max_cache_tokens=1024, max_prefill_tokens=13, lookahead=ahead)
+    ids = [llm.submit(p, max_tokens=10) for p in prompts]
+    tokens = {rid: [] for rid in ids}
+    finished = {}
+    cancelled_at = {}
+
+    def take(events):
+        for ev in events:
+            assert ev.request_id not in cancelled_at, f"request {ev.request_id} reported {ev.kind} after it was cancelled"
+            if ev.kind == "token":
+                tokens[ev.request_id].append(ev.token)
+            elif ev.kind == "finished":
+                finished[ev.request_id] = ev.reason
+            else:
+                raise AssertionError(f"unexpected event {ev}")
+
+    steps = 0
+    while llm.has_work():
+        take(llm.step())
+        steps += 1
+        # request 1 (70 tokens, portions of 13): taken back while its prompt is half computed
+        if ids[1] not in cancelled_at and any(p.req.request_id == ids[1] and p.done >= 13 for p in llm.scheduler.prefilling):
+            assert llm.cancel(ids[1])
+            cancelled_at[ids[1]] = steps
+        # request 4: taken back after its third token
+        if ids[4] not in cancelled_at and len(tokens[ids[4]]) >= 3:
+            assert llm.cancel(ids[4])
+            cancelled_at[ids[4]] = steps
+            assert not llm.cancel(ids[4])
+        assert steps < 500
+    assert set(cancelled_at) == {ids[1], ids[4]} and tokens[ids[1]] == [] and 3 <= len(tokens[ids[4]]) <= 4
+    for i in keep:
+        assert tokens[ids[i]] == want[i] and finished[ids[i]] == "length"
+    cache = llm.runner.cache
+    cache.check()
+    assert cache.min_free_pages() == cache.num_pages and cache.slot_pool.used_count == 0
