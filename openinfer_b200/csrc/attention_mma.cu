@@ -16,7 +16,7 @@
 // S = Q K^T and O = P V run as mma.sync m16n8k16 with float32 accumulators.
 #include <cooperative_groups.h>
 
-#include "common.cuh"
+#include "oi_api.h"
 
 namespace cg = cooperative_groups;
 
@@ -931,6 +931,16 @@ int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens
 }
 
 template <int HD>
+int launch_merge(void* out, int out_row_stride, const float* part_o, const float* part_lse, const int* row_splits, int nq,
+                 int max_splits, int tokens, cudaStream_t s) {
+  const long long warps = (long long)tokens * nq;
+  oi_launch(attention_merge_kernel<HD>, (unsigned)((warps + 3) / 4), 128, 0, s, (bf16*)out, out_row_stride, part_o, part_lse,
+            row_splits, nq, max_splits, tokens);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+template <int HD>
 int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
   // the warps' rings, room for the rotated query heads of one kv head (fuse_rope), and the receive buffer
   // of the merge by deposit
@@ -1095,4 +1105,18 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
   if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
   if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
   return launch<128>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
+}
+
+// Merge the slices that another attention kernel left in scratch (the layout of oi_attention_mma's part_o and
+// part_lse): rows whose row_splits entry is above one get out = sum_s w_s o_s / sum_s w_s.
+OI_API int oi_attention_merge_slices(void* out, int out_row_stride, const float* part_o, const float* part_lse,
+                                     const int* row_splits, int nq, int max_splits, int tokens, int hd, void* stream) {
+  OI_REQUIRE(out && part_o && part_lse && row_splits && tokens >= 0 && nq > 0 && max_splits >= 1 && max_splits <= 64,
+             "attention_merge: bad arguments");
+  if (tokens == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 128) return launch_merge<128>(out, out_row_stride, part_o, part_lse, row_splits, nq, max_splits, tokens, s);
+  if (hd == 64) return launch_merge<64>(out, out_row_stride, part_o, part_lse, row_splits, nq, max_splits, tokens, s);
+  if (hd == 32) return launch_merge<32>(out, out_row_stride, part_o, part_lse, row_splits, nq, max_splits, tokens, s);
+  OI_REQUIRE(false, "attention_merge: head_dim %d not covered (32, 64, 128)", hd);
 }

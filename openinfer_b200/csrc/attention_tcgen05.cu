@@ -32,6 +32,7 @@
 // Math as the other attention kernels: s = (q . k) / sqrt(hd) for keys j <= pos (and j > pos - window),
 // softmax in float32 with exp2 and the scale folded in, o = sum p v
 // (pegainfer-kernels/csrc/shared/paged_attention.cu:439-567).
+#include "oi_api.h"
 #include "tcgen05.cuh"
 
 namespace {
@@ -45,7 +46,7 @@ constexpr int kThreads = 192;
 __device__ int g_attn_error = 0;
 
 struct Params {
-  const int4* items;        // (request, first token of the tile, -, -)
+  const int4* items;        // (request, first token of the tile, slice of its keys, slices)
   const int* cu_seqlens;
   const int* kv_lens;
   const int* block_table;
@@ -57,6 +58,9 @@ struct Params {
   int window;
   bf16* out;
   int out_row_stride;
+  float* part_o;            // partial results of tiles whose keys are cut into slices (see oi_attention_mma)
+  float* part_lse;
+  int max_splits;
 };
 
 using namespace tc;
@@ -129,7 +133,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   if (p.window > 0) lo = max(0, pos0 - p.window + 1);
   lo &= ~(kKeys - 1);
   const int hi = pos0 + tile_toks;
-  const int num_tiles = (hi - lo + kKeys - 1) / kKeys;
+  // An item may cover a slice of the tile's keys (when whole tiles would leave SMs idle): key tiles
+  // [t_begin, t_end) of the span, cut as in the mma.sync kernel; its result goes to scratch, normalised and with
+  // its log-sum-exp, and a second kernel merges the slices.
+  const int split = item.z, nsplits = item.w > 1 ? item.w : 1;
+  const int span_tiles = (hi - lo + kKeys - 1) / kKeys;
+  const int tiles_per_split = (span_tiles + nsplits - 1) / nsplits;
+  const int t_begin = min(span_tiles, split * tiles_per_split);
+  const int num_tiles = min(span_tiles, t_begin + tiles_per_split) - t_begin;
+  lo += t_begin * kKeys;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -352,7 +364,35 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    if (ok && num_tiles > 0) {
+    if (nsplits > 1) {
+      // a slice: the normalised partial result in float32 and the base-2 log-sum-exp of its keys
+      bool have = ok && num_tiles > 0;
+      if (have) {
+        have = mbar_wait(o_full, (unsigned)(num_tiles - 1) & 1, abort_flag, 8);
+        tc_fence_after();
+      }
+      const float inv = (have && l > 0.f) ? 1.f / l : 0.f;
+      const size_t slot = ((size_t)(q_start + tok0 + t_row) * p.nq + (size_t)(kvh * group + r % group)) * p.max_splits + split;
+      float* dst = p.part_o + slot * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        unsigned v[32];
+        if (have) {                    // uniform in the warp: the waits above are the same for all its lanes
+          tmem_ld32(lane_base + 128u + (unsigned)c, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            reinterpret_cast<float4*>(dst + c)[q4] = make_float4(__uint_as_float(v[q4 * 4]) * inv, __uint_as_float(v[q4 * 4 + 1]) * inv,
+                                                               __uint_as_float(v[q4 * 4 + 2]) * inv, __uint_as_float(v[q4 * 4 + 3]) * inv);
+        }
+      }
+      if (row_ok) p.part_lse[slot] = (have && l > 0.f) ? m_ref * p.scale_log2 + log2f(l) : -INFINITY;
+    } else if (ok && num_tiles > 0) {
       ok = mbar_wait(o_full, (unsigned)(num_tiles - 1) & 1, abort_flag, 8);
       if (ok) {
         tc_fence_after();
@@ -394,8 +434,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
 }  // namespace
 
-// Prompt tiles of 128 query rows; items as for oi_attention_mma with rows_per_cta 128 and no key
-// slices. Requirements (else the caller uses the mma.sync kernel): head_dim 128, 128 % group == 0,
+// Prompt tiles of 128 query rows; items as for oi_attention_mma with rows_per_cta 128, key slices included
+// (any_split != 0: some item covers a slice; part_o float32 [tokens * nq * max_splits * 128] and part_lse
+// [tokens * nq * max_splits] take the slices' results and a second kernel merges them by row_splits). Requirements (else the caller uses the mma.sync kernel): head_dim 128, 128 % group == 0,
 // page_size a power of two >= 16 (64 % page_size == 0 or page_size % 64 == 0), 16-byte aligned
 // buffers with row strides that are multiples of 8 elements. q: [tokens, q_row_stride] (heads of
 // 128 from column 0); cache: [num_pages, page_size, nkv, 128] with page_stride elements per page.
@@ -403,8 +444,11 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
                                 const void* k_cache, const void* v_cache, long long page_stride, int page_size,
                                 int num_pages, const int* block_table, int bt_stride, const int* cu_seqlens,
                                 const int* kv_lens, const int* items, int num_items, int nq, int nkv, int hd,
-                                float scale, int window, void* stream) {
+                                float scale, int window, const int* row_splits, int any_split, float* part_o,
+                                float* part_lse, int max_splits, void* stream) {
   OI_REQUIRE(hd == HD, "attention_tcgen05: head_dim %d not covered (128)", hd);
+  OI_REQUIRE(!any_split || (part_o && part_lse && row_splits && max_splits >= 2 && max_splits <= 64 && (uintptr_t)part_o % 16 == 0),
+             "attention_tcgen05: key slices need 16-byte aligned scratch, the rows' slice counts and 2..64 slices");
   OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && kRows % (nq / nkv) == 0, "attention_tcgen05: group %d/%d not covered", nq, nkv);
   OI_REQUIRE(page_size >= 16 && (page_size & (page_size - 1)) == 0, "attention_tcgen05: page size %d not covered", page_size);
   OI_REQUIRE(q_row_stride % 8 == 0 && page_stride % 8 == 0 && out_row_stride % 8 == 0 && (uintptr_t)q % 16 == 0 &&
@@ -444,6 +488,7 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   p.out = (bf16*)out; p.out_row_stride = out_row_stride;
+  p.part_o = part_o; p.part_lse = part_lse; p.max_splits = any_split ? max_splits : 1;
   static bool configured = false;
   if (!configured) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
@@ -451,6 +496,7 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
   }
   oi_launch(attention_tcgen05_kernel, (unsigned)((long long)num_items * nkv), kThreads, kSmemTotal, (cudaStream_t)stream, mq, mk, mv, p);
   OI_CHECK_LAUNCH();
+  if (any_split) return oi_attention_merge_slices(out, out_row_stride, part_o, part_lse, row_splits, nq, max_splits, tokens, hd, stream);
   return OI_OK;
 }
 

@@ -192,7 +192,8 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
   if (s->num_tile_items && s->use_tcgen05)
     OI_TRY(oi_attention_tcgen05(l->qkv, l->q_row_stride, tokens, l->out, l->out_row_stride, l->k_cache, l->v_cache,
                                 s->page_stride, s->page_size, s->num_pages, s->block_table, s->bt_stride, s->cu_seqlens,
-                                s->kv_lens, s->tile_items, s->num_tile_items, l->nq, l->nkv, l->hd, l->scale, l->window, stream));
+                                s->kv_lens, s->tile_items, s->num_tile_items, l->nq, l->nkv, l->hd, l->scale, l->window,
+                                s->row_splits, s->tile_split, s->part_o, s->part_lse, s->max_splits, stream));
   else if (s->num_tile_items)
     OI_TRY(oi_attention_mma(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->k_cache, l->v_cache, s->page_stride,
                             s->page_size, s->block_table, s->bt_stride, s->cu_seqlens, s->kv_lens, s->tile_items,

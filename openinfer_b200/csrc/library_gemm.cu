@@ -8,7 +8,7 @@
 // cuBLASLt is looked up at run time (dlopen / dlsym): the copy that the process has loaded already
 // (torch's) if there is one, else the path given to oi_library_gemm_init. Nothing is linked at build
 // time, so the package builds and loads on a machine without the library; a product that needs it
-// then fails with a message, and the dispatcher (linear.cu) uses the hand-written tcgen05 kernel instead.
+// then fails with a message, and the dispatcher (host_step.cu) uses the hand-written tcgen05 kernel instead.
 // A plan (operation and layout descriptors, the algorithm the library's heuristic ranks first) is made
 // once per shape and kept, so a call costs one cublasLtMatmul. Partial sums of a split K are never
 // rounded to the output type: reduction schemes that do so are excluded from the search.
@@ -49,14 +49,16 @@ struct Plan {
 struct Key {
   int M, N, K, out_dtype;
   long long ldx, ldw, ldc;
+  int align;   // bytes to which x, W and out are all aligned (16 ... 256): an algorithm is chosen for what it may assume
   bool operator==(const Key& o) const {
-    return M == o.M && N == o.N && K == o.K && out_dtype == o.out_dtype && ldx == o.ldx && ldw == o.ldw && ldc == o.ldc;
+    return M == o.M && N == o.N && K == o.K && out_dtype == o.out_dtype && ldx == o.ldx && ldw == o.ldw && ldc == o.ldc &&
+           align == o.align;
   }
 };
 struct KeyHash {
   size_t operator()(const Key& k) const {
     size_t h = 1469598103934665603ull;
-    for (long long v : {(long long)k.M, (long long)k.N, (long long)k.K, (long long)k.out_dtype, k.ldx, k.ldw, k.ldc})
+    for (long long v : {(long long)k.M, (long long)k.N, (long long)k.K, (long long)k.out_dtype, k.ldx, k.ldw, k.ldc, (long long)k.align})
       h = (h ^ (size_t)v) * 1099511628211ull;
     return h;
   }
@@ -133,6 +135,11 @@ static int make_plan(const Key& k, Plan* plan) {
   OI_REQUIRE(st == CUBLAS_STATUS_SUCCESS, "library_gemm: preference (%d)", (int)st);
   const uint64_t ws = g_workspace_bytes;
   a.pref_set(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws, sizeof(ws));
+  const uint32_t align = (uint32_t)k.align;
+  a.pref_set(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_A_BYTES, &align, sizeof(align));
+  a.pref_set(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_B_BYTES, &align, sizeof(align));
+  a.pref_set(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_C_BYTES, &align, sizeof(align));
+  a.pref_set(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_D_BYTES, &align, sizeof(align));
   // partial sums of a split K stay in the compute type (float32), never in the output type
   const uint32_t schemes = CUBLASLT_REDUCTION_SCHEME_NONE | CUBLASLT_REDUCTION_SCHEME_INPLACE | CUBLASLT_REDUCTION_SCHEME_COMPUTE_TYPE;
   a.pref_set(pref, CUBLASLT_MATMUL_PREF_REDUCTION_SCHEME_MASK, &schemes, sizeof(schemes));
@@ -155,7 +162,11 @@ OI_API int oi_library_gemm(void* out, int out_dtype, long long ldc, const void* 
   OI_REQUIRE(g_lt != nullptr, "library_gemm: not initialised (oi_library_gemm_init)");
   OI_REQUIRE(M >= 1 && N >= 1 && K >= 1 && ldx >= K && ldw >= K && ldc >= N, "library_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   OI_REQUIRE(out_dtype == OI_BF16 || out_dtype == OI_F32, "library_gemm: unknown output dtype code %d", out_dtype);
-  const Key key{M, N, K, out_dtype, ldx, ldw, ldc};
+  int align = 256;
+  for (const void* ptr : {x, W, (const void*)out})
+    while (align > 1 && ((uintptr_t)ptr & (uintptr_t)(align - 1))) align >>= 1;
+  OI_REQUIRE(align >= 2, "library_gemm: operands must be aligned to their element size");
+  const Key key{M, N, K, out_dtype, ldx, ldw, ldc, align};
   Plan plan;
   {
     std::lock_guard<std::mutex> lock(g_mutex);

@@ -61,7 +61,10 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
 OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int tokens, void* out, int out_row_stride,
        const void* k_cache, const void* v_cache, long long page_stride, int page_size, int num_pages, const int*
        block_table, int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items, int num_items, int nq,
-       int nkv, int hd, float scale, int window, void* stream);
+       int nkv, int hd, float scale, int window, const int* row_splits, int any_split, float* part_o, float* part_lse,
+       int max_splits, void* stream);
+OI_API int oi_attention_merge_slices(void* out, int out_row_stride, const float* part_o, const float* part_lse,
+       const int* row_splits, int nq, int max_splits, int tokens, int hd, void* stream);
 OI_API int oi_attention_tcgen05_status(int* status);
 
 // elementwise.cu

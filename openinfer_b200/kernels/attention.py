@@ -197,10 +197,9 @@ def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_
     each row's keys are cut into ``decode_splits`` slices, four per CTA. The others are cut
     into query tiles (``rows_per_cta`` rows = rows // group tokens times `group` heads) for the tile kernel;
     when that grid would leave SMs idle and there are no decode rows, a tile's keys are cut
-    into slices too (``whole_tiles_kernel``: the tcgen05 kernel, which takes whole tiles only and is
-    2.7 times as fast per tile as the one that takes slices, stands ready for this shape: tiles are then
-    cut only when they would not even fill half of the SMs). Returns (tile_items [n, 4], decode_items [n, 4], row_splits [tokens],
-    max_splits, tile_split)."""
+    into slices too, merged by a second kernel (``whole_tiles_kernel``: keep tiles whole unless they would not even
+    fill half of the SMs; for the fast tile kernel).
+    Returns (tile_items [n, 4], decode_items [n, 4], row_splits [tokens], max_splits, tile_split)."""
     rows_per_cta = rows_per_cta or tile_rows(q_lens, group, decode_kernel)
     tpt = rows_per_cta // group
     starts = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int64)
@@ -276,11 +275,14 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
         else:
             rows = tile_rows(ctx.q_lens_host, group)
             page = ctx.cache.page_size
-            whole = (USE_TCGEN05 and hd == 128 and rows == ROWS_PER_CTA_LARGE and ROWS_PER_CTA_LARGE % group == 0
-                     and page >= 16 and page & (page - 1) == 0)
+            # the tcgen05 kernel takes slices too, but is fast enough per tile that cutting its tiles only pays when
+            # they would not even fill half of the SMs (measured: a 2,048-token prompt at Qwen3-0.6B sizes, 256 tiles,
+            # 4.1 ms whole against 4.6 ms cut in two with their partial results merged by a second kernel)
+            fast_tiles = (USE_TCGEN05 and hd == 128 and rows == ROWS_PER_CTA_LARGE and ROWS_PER_CTA_LARGE % group == 0
+                          and page >= 16 and page & (page - 1) == 0)
             t_items, d_items, row_splits, max_splits, tile_split = plan_items(
                 ctx.q_lens_host, ctx.kv_lens_host, group, nkv, window, _sm_count(device), rows_per_cta=rows,
-                whole_tiles_kernel=whole)
+                whole_tiles_kernel=fast_tiles)
         packed = np.concatenate([t_items.reshape(-1), d_items.reshape(-1), row_splits]).astype(np.int32, copy=False)
         dev = _PLAN_RING.upload(packed, device)   # pinned memory read by a kernel: the host does not wait for the stream
         nt, nd = t_items.shape[0], d_items.shape[0]
@@ -299,7 +301,7 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
 
 def _tcgen05_takes(plan, q, out, k_cache, page_size, nq, nkv, hd, page_stride) -> bool:
     group = nq // nkv
-    return (USE_TCGEN05 and hd == 128 and plan.rows_per_cta == ROWS_PER_CTA_LARGE and not plan.tile_split
+    return (USE_TCGEN05 and hd == 128 and plan.rows_per_cta == ROWS_PER_CTA_LARGE
             and ROWS_PER_CTA_LARGE % group == 0 and page_size >= 16 and page_size & (page_size - 1) == 0
             and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and page_stride % 8 == 0
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and k_cache.data_ptr() % 16 == 0)

@@ -47,7 +47,8 @@ _SIGNATURES = {
     "oi_attention_decode": [P, I, P, I, P, P, L, I, P, I, P, P, P, I, P, I, I, I, I, F, I, P, P, I, I, P],
     "oi_attention_decode_rope": [P, I, P, I, P, P, L, I, P, I, P, P, P, I, P, I, I, I, I, F, I, P, P, I, I,
                                  P, P, I, F, F, P, P, I, I, P, P, I, P],
-    "oi_attention_tcgen05": [P, L, I, P, I, P, P, L, I, I, P, I, P, P, P, I, I, I, I, F, I, P],
+    "oi_attention_tcgen05": [P, L, I, P, I, P, P, L, I, I, P, I, P, P, P, I, I, I, I, F, I, P, I, P, P, I, P],
+    "oi_attention_merge_slices": [P, I, P, P, P, I, I, I, I, P],
     "oi_attention_tcgen05_status": [ctypes.POINTER(c_int)],
     "oi_argmax_noalloc": [P, P, I, I, L, P],
 }

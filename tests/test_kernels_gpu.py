@@ -436,6 +436,10 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
     assert ran
     assert A.tcgen05_status() == 0, "a bounded wait ran out in the tcgen05 attention kernel"
     plan = next(iter(ctx.scratch.values()))
+    step = [v for k, v in ctx.scratch.items() if k[0] == "attention_step"][0]
+    if (A.USE_TCGEN05 and hd == 128 and plan.rows_per_cta == 128 and 128 % (nq // nkv) == 0 and P >= 16 and P & (P - 1) == 0
+            and plan.num_tile_items):
+        assert step.use_tcgen05, "the tcgen05 kernel covers this shape and did not run"
     scale = 1.0 / math.sqrt(hd)
     row = 0
     for b, (n, kv) in enumerate(zip(q_lens, kv_lens)):
@@ -501,9 +505,21 @@ def test_attention_mma_split_prompt_portion():
     assert not plan.tile_split and plan.num_decode_items
 
 
+@pytest.mark.parametrize("nq,nkv,P,window", [(32, 8, 16, None), (8, 4, 64, None), (4, 2, 16, 200), (16, 1, 32, None)])
+def test_attention_tcgen05_with_key_slices(nq, nkv, P, window):
+    """Prompt tiles whose keys are cut into slices (a grid that would leave SMs idle) through the tcgen05 kernel:
+    every slice leaves its normalised partial result and log-sum-exp in scratch, a second kernel merges them.
+    Portions over long prefixes, slices that come out empty, a window."""
+    from openinfer_b200.kernels import attention as A
+    for q_lens, kv_lens in (([260, 70], [900, 330]), ([33], [1200]), ([150, 40, 129], [150, 1000, 640])):
+        plan = _mma_case(nq, nkv, 128, P, window, q_lens, kv_lens, force_splits="max")
+        assert plan.tile_split and plan.max_splits > 1     # _mma_case checks that the tcgen05 kernel ran where it covers the shape
+        assert A.tcgen05_status() == 0
+
+
 def test_attention_mma_plan():
     from openinfer_b200.kernels.attention import plan_items
-    # a kernel that takes whole tiles only stands ready: 32 tiles x 8 kv heads (less than two CTAs per SM) stay
+    # for the fast tile kernel: 32 tiles x 8 kv heads (less than two CTAs per SM) stay
     # whole; two tiles over a long prefix (a quarter of the SMs at most) are still cut
     _, _, _, mx, cut = plan_items([1024], [1024], group=4, nkv=8, window=None, sm_count=148, rows_per_cta=128,
                                   whole_tiles_kernel=True)
