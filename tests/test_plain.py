@@ -106,3 +106,29 @@ def test_sampling_distribution_semantics():
     assert plain.inverse_cdf_pick(torch.tensor([0.0, 0.25, 0.0, 0.75]), 0.2) == 1
     assert plain.inverse_cdf_pick(torch.tensor([0.0, 0.25, 0.0, 0.75]), 0.25) == 3
     assert plain.inverse_cdf_pick(torch.tensor([0.0, 0.25, 0.0, 0.75]), 0.999) == 3
+
+
+def test_bfloat16_twin_with_the_reference_rounding_points(tmp_path):
+    """The twin restates WHERE the reference rounds (q/k norm twice, every product of the rotation, SiLU before the
+    multiply, each residual sum, bfloat16 tables and logits). Its logits are bfloat16 values, stay within the
+    bfloat16 tolerance of the float32 plain implementation on all five tiny configurations, and its rounding
+    points are live: each differs from the single rounding somewhere."""
+    import plain_qwen3_bf16 as twin
+    from helpers import BF16_MAX_REL, BF16_MEAN_REL
+    for name, (cfg, seed) in TINY.items():
+        f = make_model_folder(str(tmp_path / name), cfg, seed)
+        c, w = plain.read_model_folder(f)
+        toks = random_tokens(random.Random(3), 90, cfg["vocab_size"])
+        a, b = plain.forward_logits(c, w, toks), twin.forward_logits(c, w, toks)
+        assert torch.equal(b, b.to(torch.bfloat16).float()), "the twin's logits are not bfloat16 values"
+        scale = a.abs().max().item()
+        err = (a - b).abs()
+        assert err.max().item() / scale <= BF16_MAX_REL and err.mean().item() / scale <= BF16_MEAN_REL, name
+        assert err.max().item() > 0
+    torch.manual_seed(0)
+    u, wn = torch.randn(50, 3, 32), 1 + 0.1 * torch.randn(32)
+    once = twin.bf(plain.rms_norm(u, wn, 1e-6))
+    assert not torch.equal(twin.head_norm(u, wn, 1e-6), once), "two roundings never differ from one"
+    pos = torch.arange(50)
+    cos, sin = plain.rope_tables(32, 1e4, pos)
+    assert not torch.equal(twin.apply_rope(twin.bf(u), pos, 1e4), twin.bf(plain.apply_rope(twin.bf(u), cos, sin)))

@@ -310,3 +310,24 @@ def test_native_step_and_part_by_part_step_give_the_same_bits(folders, workloads
         assert torch.equal(outs["native"][rid], outs["parts"][rid]), f"request {rid}: the two step paths differ"
     _check(outs["native_fused_norms"], ref, dtype, f"native step without norm kernels {name}/{dtype}")
     _check(outs["parts"], ref, dtype, f"part by part {name}/{dtype}")
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_bfloat16_engine_against_the_twin_with_the_reference_rounding(folders, workloads, name):
+    """The engine rounds once per kernel output where the reference rounds more often (tests/plain_qwen3_bf16.py
+    restates where). Against the float32 plain implementation the engine's bfloat16 logits are at least about as
+    exact as that scheme of rounding would be (mean error at most 1.25 times the twin's), and the two bfloat16
+    computations agree with each other within the bfloat16 tolerance."""
+    import plain_qwen3_bf16 as twin
+    cfg, reqs, ref = workloads[name]
+    pcfg, w = plain.read_model_folder(folders[name])
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    toks = reqs[rid]
+    runner = _runner(folders[name], "bfloat16", round64(len(toks)), page_size=16)
+    got = replay_in_process(runner, trace_whole({rid: toks}))[rid]
+    tw = twin.forward_logits(pcfg, w, toks)
+    scale = ref[rid].abs().max().item()
+    err_engine = (got - ref[rid]).abs().mean().item() / scale
+    err_twin = (tw - ref[rid]).abs().mean().item() / scale
+    assert err_engine <= 1.25 * err_twin, f"engine {err_engine:.5f} against the reference's rounding {err_twin:.5f}"
+    assert_close(got, tw, "bfloat16", f"engine against the bfloat16 twin, {name}")
