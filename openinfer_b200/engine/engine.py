@@ -24,8 +24,8 @@ from .scheduler import (DEFAULT_ENGINE_SEED, DEFAULT_MAX_DECODE_BATCH, DEFAULT_M
 DEFAULT_GPU_MEMORY_UTILIZATION = 0.90   # pegainfer-qwen3/src/weights.rs:31-36
 DEFAULT_KV_MARGIN_MIB = 150
 DEFAULT_KV_PAGE_SIZE = 16
-# rows of a mixed step are made a multiple of the widest row tile of the prompt products (256: a pair of CTAs)
-DEFAULT_ROW_ALIGNMENT = 256
+# rows of a mixed step are made a multiple of the widest row tile of the prompt products: the kernels say how wide
+from ..kernels.gemm_tcgen05 import ROW_TILE as DEFAULT_ROW_ALIGNMENT  # noqa: E402
 
 
 class RunnerExecutor(Executor):

@@ -25,6 +25,7 @@ def takes(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 PAIR = 0          # tile_n value that selects 256 x 256 tiles computed by pairs of CTAs (cta_group::2)
+ROW_TILE = 256    # rows of the widest row tile of the prompt products (a pair of CTAs): steps whose rows are a multiple fill every tile
 
 
 def portion_tile(rows: int, K: int = 1 << 30) -> int:
