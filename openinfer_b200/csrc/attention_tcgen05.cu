@@ -80,6 +80,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// the largest of three values in one instruction (sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // shared memory map (bytes from a 1024-aligned base)
 constexpr int kQBytes = kRows * HD * 2;            // 32 KB: two halves [128 rows][64 dims]
 constexpr int kKBytes = kKeys * HD * 2;            // 16 KB: two halves [64 keys][64 dims]
@@ -301,13 +308,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           sv[e] = vis ? sv[e] : -INFINITY;
         }
       }
+      // The softmax warps are bound by the instructions they issue (a cubic exponential on the multiply-add pipe beside
+      // the special-function unit's made long prompts 6 % slower), so the row's arithmetic uses the instructions that
+      // do two things at once: three-input maxima, and multiply-adds and additions on PAIRS of float32.
       // row maximum with eight independent chains (a single chain of 64 would be pure latency)
       float mx[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) mx[e] = sv[e];
 #pragma unroll
-      for (int e = 8; e < kKeys; ++e) mx[e & 7] = fmaxf(mx[e & 7], sv[e]);
-      const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      for (int e = 8; e < kKeys - 8; e += 16)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mx[c] = max3(mx[c], sv[e + c], sv[e + 8 + c]);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) mx[c] = fmaxf(mx[c], sv[kKeys - 8 + c]);
+      const float m_tile = fmaxf(max3(mx[0], mx[1], mx[2]), max3(max3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
       // move the reference only when the maximum has outgrown it by 2^8 (or there is none yet)
       const bool move = m_tile > m_ref && (m_ref == -INFINITY || (m_tile - m_ref) * p.scale_log2 > kRescaleThreshold);
       // P(t) = 2^(s * scale - m_ref * scale), rounded to bfloat16, kept in registers: the second product
@@ -316,20 +330,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const float f = rescale ? fast_exp2((m_ref - m_tile) * p.scale_log2) : 1.f;
       if (move) m_ref = m_tile;
       const float base = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
-      float lsum[4] = {0.f, 0.f, 0.f, 0.f};
+      float2 lsum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), nbase2 = make_float2(-base, -base);
       uint4 chunks[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&chunks[c]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(sv[c * 8 + 2 * e], p.scale_log2, -base));
-          const float p1 = fast_exp2(fmaf(sv[c * 8 + 2 * e + 1], p.scale_log2, -base));
-          lsum[e] += p0 + p1;
-          h[e] = __floats2bfloat162_rn(p0, p1);
+          const float2 x = __ffma2_rn(make_float2(sv[c * 8 + 2 * e], sv[c * 8 + 2 * e + 1]), scale2, nbase2);
+          const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          lsum[e] = __fadd2_rn(lsum[e], pp);
+          h[e] = __floats2bfloat162_rn(pp.x, pp.y);
         }
       }
-      l = l * f + ((lsum[0] + lsum[1]) + (lsum[2] + lsum[3]));
+      const float2 lsum_all = __fadd2_rn(__fadd2_rn(lsum[0], lsum[1]), __fadd2_rn(lsum[2], lsum[3]));
+      l = l * f + (lsum_all.x + lsum_all.y);
       // the second product of the previous tile reads the P tile and updates O until o_full(t - 1)
       if (t > 0) {
         ok = mbar_wait(o_full, (unsigned)(t - 1) & 1, abort_flag, 7);
