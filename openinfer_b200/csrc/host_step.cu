@@ -165,7 +165,7 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
   OI_REQUIRE(s && l, "attention_layer: null description");
   const int tokens = s->tokens;
   if (tokens == 0) return OI_OK;
-  const bool fused = l->rope_mode == 1 && s->tensor_core && s->fuse_rope;
+  const bool fused = l->rope_mode == 1 && s->tensor_core && s->fuse_rope && !l->interleaved;
   OI_REQUIRE(l->qkv && l->out && l->k_cache && l->v_cache && s->block_table && s->kv_lens && s->cu_seqlens,
              "attention_layer: a tensor of the step or of the layer is missing");
   OI_REQUIRE(l->rope_mode == 0 || ((!l->write_kv || s->slot_mapping) && (!l->cos_tab || s->positions)),
@@ -175,7 +175,7 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
     OI_TRY(oi_qk_norm_rope_kv(l->qkv, l->dtype, l->q_row_stride, tokens, l->nq, l->nkv, l->hd, l->q_norm_w, l->k_norm_w,
                               l->norm_dtype, l->eps, l->w_offset, l->cos_tab, l->sin_tab, l->cos_tab ? l->rot_half : 0,
                               l->cos_tab ? l->max_pos : 0, s->positions, s->slot_mapping, l->k_cache, l->v_cache,
-                              s->page_stride, s->page_size, l->write_kv, stream));
+                              s->page_stride, s->page_size, l->write_kv, l->interleaved, stream));
   if (!s->tensor_core)
     return oi_attention_generic(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->dtype, l->k_cache, l->v_cache,
                                 s->page_stride, s->page_size, s->block_table, s->bt_stride, s->token_req, s->positions,

@@ -106,7 +106,7 @@ OI_API int oi_gemm_tcgen05_status(int* status);
 OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, int nq, int nkv, int hd, const void*
        q_norm_w, const void* k_norm_w, int norm_dtype, float eps, float w_offset, const float* cos_tab, const float*
        sin_tab, int rot_half, int max_pos, const int* positions, const int* slots, void* k_cache, void* v_cache, long
-       long page_stride, int page_size, int write_kv, void* stream);
+       long page_stride, int page_size, int write_kv, int interleaved, void* stream);
 
 // runtime.cu
 OI_API const char* oi_last_error();
@@ -205,6 +205,7 @@ typedef struct OiAttnLayer {
   int nq, nkv, hd, window;   // window 0: every key
   float scale, eps, w_offset;
   int norm_dtype, rot_half, max_pos;
+  int interleaved;           // the rotation turns neighbours (2 d, 2 d + 1) instead of (d, d + half)
   int write_kv;              // the call owns its cache: keys and values of the step's rows are stored
   int rope_mode;             // 0: q is ready and the cache is written; 1: norm + rotation + cache write first (in its own
                              // kernel, or inside the decode kernel when the step says fuse_rope)

@@ -1,4 +1,6 @@
-// Fused per-head q/k norm + rotate-half position rotation + write of K and V into the paged cache.
+// Fused per-head q/k norm + position rotation + write of K and V into the paged cache. The rotation turns the
+// pair (d, d + half) by angle d ("rotate half", the reference's) or, with `interleaved`, the neighbours (2 d, 2 d + 1);
+// the tuned bfloat16 kernels below cover the first, the general kernel both.
 //
 // One warp per (token, head) over the fused projection output [tokens, (nq + 2*nkv) * hd]:
 //   q heads: norm, rotate, written back in place (attention reads q from this buffer);
@@ -20,7 +22,7 @@ __global__ void qk_norm_rope_kv_kernel(
     float w_offset, const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
     int rot_half, int max_pos, const int* __restrict__ positions, const int* __restrict__ slots,
     T* __restrict__ k_cache, T* __restrict__ v_cache, long long page_stride, int page_size,
-    int heads_total, int tokens) {
+    int heads_total, int tokens, int interleaved) {
   pdl_start();
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -57,15 +59,17 @@ __global__ void qk_norm_rope_kv_kernel(
   int pos = positions[token];
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // admission bounds positions
   for (int i = lane; i < rot_half; i += 32) {
-    float a = to_f32(src[i]), b = to_f32(src[i + rot_half]);
+    // the pair that angle i turns: (i, i + half) ("rotate half"), or the neighbours (2 i, 2 i + 1) when interleaved
+    const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + rot_half;
+    float a = to_f32(src[ia]), b = to_f32(src[ib]);
     if (w) {
-      a = a * inv * (w_offset + load_as_f32(w, norm_dtype, i));
-      b = b * inv * (w_offset + load_as_f32(w, norm_dtype, i + rot_half));
+      a = a * inv * (w_offset + load_as_f32(w, norm_dtype, ia));
+      b = b * inv * (w_offset + load_as_f32(w, norm_dtype, ib));
     }
     const float c = cos_tab[(size_t)pos * rot_half + i];
     const float s = sin_tab[(size_t)pos * rot_half + i];
-    dst[i] = from_f32<T>(a * c - b * s);
-    dst[i + rot_half] = from_f32<T>(a * s + b * c);
+    dst[ia] = from_f32<T>(a * c - b * s);
+    dst[ib] = from_f32<T>(a * s + b * c);
   }
   for (int d = 2 * rot_half + lane; d < hd; d += 32) {  // dims beyond the rotary part
     float a = to_f32(src[d]);
@@ -285,7 +289,7 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
                               float w_offset, const float* cos_tab, const float* sin_tab, int rot_half,
                               int max_pos, const int* positions, const int* slots, void* k_cache,
                               void* v_cache, long long page_stride, int page_size, int write_kv,
-                              void* stream) {
+                              int interleaved, void* stream) {
   OI_REQUIRE(tokens >= 0 && nq > 0 && nkv >= 0 && hd > 0, "qk_norm_rope_kv: bad sizes");
   OI_REQUIRE(rot_half >= 0 && 2 * rot_half <= hd, "qk_norm_rope_kv: rotary_dim %d exceeds head_dim %d",
              2 * rot_half, hd);
@@ -300,8 +304,8 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
     oi_launch(qk_norm_rope_kv_kernel<float>, blocks, 128, 0, s, 
         (float*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
         sin_tab, rot_half, max_pos, positions, slots, (float*)k_cache, (float*)v_cache, page_stride,
-        page_size, heads_total, tokens);
-  } else if (dtype == OI_BF16 && 2 * rot_half == hd && (hd == 32 || hd == 64 || hd == 128) && row_stride % 8 == 0 &&
+        page_size, heads_total, tokens, interleaved);
+  } else if (dtype == OI_BF16 && !interleaved && 2 * rot_half == hd && (hd == 32 || hd == 64 || hd == 128) && row_stride % 8 == 0 &&
              (uintptr_t)qkv % 16 == 0 && page_stride % 8 == 0 && (uintptr_t)cos_tab % 16 == 0 && (uintptr_t)sin_tab % 16 == 0 &&
              (!write_kv || ((uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0)) &&
              ((!q_norm_w && !k_norm_w) || norm_dtype == OI_BF16 || norm_dtype == OI_F32)) {
@@ -318,7 +322,7 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
       if (hd == 128) OI_ROPE_VEC(128, float); else if (hd == 64) OI_ROPE_VEC(64, float); else OI_ROPE_VEC(32, float);
     }
 #undef OI_ROPE_VEC
-  } else if (dtype == OI_BF16 && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 && tokens <= 2147483647 &&
+  } else if (dtype == OI_BF16 && !interleaved && rot_half > 0 && rot_half % 2 == 0 && hd % 2 == 0 && hd <= 256 && row_stride % 2 == 0 && tokens <= 2147483647 &&
              (uintptr_t)qkv % 4 == 0 && page_stride % 2 == 0 && (!write_kv || ((uintptr_t)k_cache % 4 == 0 && (uintptr_t)v_cache % 4 == 0)) &&
              (uintptr_t)cos_tab % 8 == 0 && (uintptr_t)sin_tab % 8 == 0) {
     // few tokens (decode): one head per warp for parallelism; many tokens: a warp walks over 2 heads
@@ -340,7 +344,7 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
     oi_launch(qk_norm_rope_kv_kernel<bf16>, blocks, 128, 0, s, 
         (bf16*)qkv, row_stride, nq, nkv, hd, q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab,
         sin_tab, rot_half, max_pos, positions, slots, (bf16*)k_cache, (bf16*)v_cache, page_stride,
-        page_size, heads_total, tokens);
+        page_size, heads_total, tokens, interleaved);
   } else {
     OI_REQUIRE(false, "qk_norm_rope_kv: unknown dtype code %d", dtype);
   }

@@ -51,7 +51,8 @@ def run_attention(step: "native.AttnStep", layer: "native.AttnLayer") -> None:
 
 def attention_layer(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nq: int, nkv: int,
                     hd: int, scale: float, window: Optional[int], *, q_norm_w=None, k_norm_w=None, eps: float = 0.0,
-                    weight_offset: float = 0.0, cos=None, sin=None, write_kv: bool = True, rope_mode: int = 1) -> "native.AttnLayer":
+                    weight_offset: float = 0.0, cos=None, sin=None, write_kv: bool = True, rope_mode: int = 1,
+                    interleaved: bool = False) -> "native.AttnLayer":
     """The description of one layer's attention call (csrc/oi_api.h, OiAttnLayer)."""
     _check_layer_operands(qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, hd)
     norm_dtype = 0
@@ -64,7 +65,8 @@ def attention_layer(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         q_row_stride=qkv.stride(0), out_row_stride=out.stride(0), dtype=native.DTYPE_CODE[qkv.dtype],
         nq=nq, nkv=nkv, hd=hd, window=int(window) if window else 0, scale=float(scale), eps=float(eps),
         w_offset=float(weight_offset), norm_dtype=norm_dtype, rot_half=0 if cos is None else cos.shape[1],
-        max_pos=0 if cos is None else cos.shape[0], write_kv=1 if write_kv else 0, rope_mode=rope_mode)
+        max_pos=0 if cos is None else cos.shape[0], interleaved=1 if interleaved else 0, write_kv=1 if write_kv else 0,
+        rope_mode=rope_mode)
 
 
 def _check_layer_operands(qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, hd) -> None:

@@ -29,7 +29,7 @@ _SIGNATURES = {
     "oi_add_inplace": [P, P, I, L, P],
     "oi_scale_cap": [P, I, L, F, F, P],
     "oi_silu_mul": [P, P, I, I, I, I, I, P],
-    "oi_qk_norm_rope_kv": [P, I, I, I, I, I, I, P, P, I, F, F, P, P, I, I, P, P, P, P, L, I, I, P],
+    "oi_qk_norm_rope_kv": [P, I, I, I, I, I, I, P, P, I, F, F, P, P, I, I, P, P, P, P, L, I, I, I, P],
     "oi_attention_generic": [P, I, P, I, I, P, P, L, I, P, I, P, P, I, I, I, I, F, I, P],
     "oi_gemm_generic": [P, I, P, I, P, I, I, I, I, L, L, L, P],
     "oi_argmax": [P, P, I, I, L, P, P, P],

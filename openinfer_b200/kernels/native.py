@@ -53,7 +53,7 @@ class AttnLayer(Structure):
         ("nq", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int),
         ("scale", c_float), ("eps", c_float), ("w_offset", c_float),
         ("norm_dtype", c_int), ("rot_half", c_int), ("max_pos", c_int),
-        ("write_kv", c_int), ("rope_mode", c_int),
+        ("interleaved", c_int), ("write_kv", c_int), ("rope_mode", c_int),
     ]
 
 

@@ -195,10 +195,11 @@ def qk_norm_rope_kv(qkv: torch.Tensor, nq: int, nkv: int, hd: int, *, q_norm_w: 
                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
                     slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
                     v_cache: Optional[torch.Tensor], page_stride: int, page_size: int,
-                    write_kv: bool = True) -> None:
+                    write_kv: bool = True, interleaved: bool = False) -> None:
     """Per-head norm and rotation of q (in place) and k, and the write of k and v into
     their pages. ``qkv`` is [tokens, >= (nq + 2 nkv) * hd] (or [tokens, >= nq * hd] when
-    write_kv is false); ``cos``/``sin`` are float32 [max_pos, rotary_dim / 2]."""
+    write_kv is false); ``cos``/``sin`` are float32 [max_pos, rotary_dim / 2]; ``interleaved``: angle d turns the
+    neighbours (2 d, 2 d + 1) instead of (d, d + rotary_dim / 2)."""
     _cuda(qkv, q_norm_w, k_norm_w, cos, sin, positions, slots, k_cache, v_cache)
     _i32(positions, "positions")
     _i32(slots, "slots")
@@ -229,7 +230,7 @@ def qk_norm_rope_kv(qkv: torch.Tensor, nq: int, nkv: int, hd: int, *, q_norm_w: 
         qkv.data_ptr(), _code(qkv, "qk_norm_rope_kv"), qkv.stride(0), tokens, nq, nkv, hd, _ptr(q_norm_w),
         _ptr(k_norm_w), norm_code, float(eps), float(weight_offset), _ptr(cos), _ptr(sin), rot_half, max_pos,
         positions.data_ptr(), _ptr(slots), _ptr(k_cache), _ptr(v_cache), int(page_stride), int(page_size),
-        1 if write_kv else 0, _stream()), "qk_norm_rope_kv")
+        1 if write_kv else 0, 1 if interleaved else 0, _stream()), "qk_norm_rope_kv")
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -91,6 +91,7 @@ class Attention(Mixer):
         layer = attn_kernels.attention_layer(
             qkv, out, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim, s.softmax_scale, s.window,
             q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=qn.eps if qn else 0.0,
-            weight_offset=qn.weight_offset if qn else 0.0, cos=cos, sin=sin, write_kv=binding.owns_kv, rope_mode=1)
+            weight_offset=qn.weight_offset if qn else 0.0, cos=cos, sin=sin, write_kv=binding.owns_kv, rope_mode=1,
+            interleaved=bool(getattr(s.position, "interleaved", False)))
         attn_kernels.run_attention(step, layer)
         return linear(out, self.w_o)

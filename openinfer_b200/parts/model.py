@@ -199,6 +199,7 @@ class Model:
             a.nq, a.nkv, a.hd, a.window = s.num_heads, s.num_kv_heads, s.head_dim, int(s.window) if s.window else 0
             a.scale, a.eps, a.w_offset = s.softmax_scale, (qn.eps if qn else 0.0), (qn.weight_offset if qn else 0.0)
             a.write_kv, a.rope_mode = (1 if binding.owns_kv else 0), 1
+            a.interleaved = 1 if getattr(s.position, "interleaved", False) else 0
         sp = self.spec
         desc = native.ModelDesc(
             layers=layers, embedding=self.embedding.data_ptr(), final_norm_w=self.final_norm.weight.data_ptr(),

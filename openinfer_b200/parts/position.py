@@ -2,7 +2,8 @@
 
 A position encoding is anything that can be given as a rotation table per position:
 ``rotation_tables`` returns float32 cos/sin [max_positions, rotary_dim/2], and the
-fused kernel rotates the pair (d, d + rotary_dim/2) of each head with them. Scaled or
+fused kernel rotates the pair (d, d + rotary_dim/2) of each head with them (or, with the spec's
+``interleaved``, the neighbours (2 d, 2 d + 1)). Scaled or
 partial rotary variants only change the table; "none" returns no table.
 
 "rope" is the reference's rotate-half encoding over the full head:

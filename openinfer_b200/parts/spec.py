@@ -38,10 +38,11 @@ class NormSpec:
 class PositionSpec:
     """Position encoding applied to queries and keys inside a mixer."""
 
-    kind: str = "rope"          # "rope" (rotate-half) or "none"
+    kind: str = "rope"          # "rope" or "none"
     rotary_dim: int = 0         # leading dims of each head that rotate (<= head_dim, even)
     theta: float = 10000.0
     max_positions: int = 0
+    interleaved: bool = False   # angle d turns the neighbours (2 d, 2 d + 1) instead of (d, d + rotary_dim / 2)
 
 
 @dataclasses.dataclass(frozen=True)

@@ -36,10 +36,11 @@ def _random_tensors(spec, seed):
 
 
 def _mini_spec(window=None, order=None, layers=2, nq=4, nkv=2, hd=16, hidden=40, inter=72, vocab=50,
-               rotary_dim=None, qk_norm=True, offset=0.0, activation="silu", embedding_scale=1.0, logit_soft_cap=0.0):
+               rotary_dim=None, qk_norm=True, offset=0.0, activation="silu", embedding_scale=1.0, logit_soft_cap=0.0,
+               interleaved=False):
     from openinfer_b200.parts.spec import (AttentionSpec, BlockSpec, GatedMlpSpec, ModelSpec, NormSpec, PositionSpec)
     norm = NormSpec("rms", hidden, 1e-5, offset)
-    pos = PositionSpec("rope", rotary_dim or hd, 777.0, 256)
+    pos = PositionSpec("rope", rotary_dim or hd, 777.0, 256, interleaved)
     mixer = AttentionSpec(hidden_size=hidden, num_heads=nq, num_kv_heads=nkv, head_dim=hd,
                           softmax_scale=1 / math.sqrt(hd), position=pos,
                           qk_norm=NormSpec("rms", hd, 1e-5, offset) if qk_norm else None, window=window)
@@ -60,8 +61,18 @@ def _plain_gated_mlp(x, w, prefix, activation):
     return plain.linear(act * u, w[prefix + "down_proj.weight"])
 
 
+def _plain_rope(x, cos, sin, interleaved):
+    """Rotate-half (the plain implementation's), or the neighbours (2 d, 2 d + 1) by angle d:
+    out[2d] = x[2d] cos_d - x[2d+1] sin_d, out[2d+1] = x[2d] sin_d + x[2d+1] cos_d."""
+    if not interleaved:
+        return plain.apply_rope(x, cos, sin)
+    a, b = x[..., 0::2], x[..., 1::2]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.stack([a * c - b * s, a * s + b * c], dim=-1).flatten(-2)
+
+
 def _plain_forward(spec, w, toks, window=None, order=None, cache_of=None, rotary_dim=None, qk_norm=True, offset=0.0,
-                   activation="silu", embedding_scale=1.0, logit_soft_cap=0.0):
+                   activation="silu", embedding_scale=1.0, logit_soft_cap=0.0, interleaved=False):
     """Whole-sequence float32 forward of a mini spec, from the plain part functions."""
     w = {k: v.float() for k, v in w.items()}
     m = spec.blocks[0].mixer
@@ -79,12 +90,12 @@ def _plain_forward(spec, w, toks, window=None, order=None, cache_of=None, rotary
             q = plain.rms_norm(q, offset + w[a + "q_norm.weight"], 1e-5)
         rot = rotary_dim or m.head_dim
         cos, sin = plain.rope_tables(rot, 777.0, positions)
-        q = torch.cat([plain.apply_rope(q[..., :rot], cos, sin), q[..., rot:]], -1)
+        q = torch.cat([_plain_rope(q[..., :rot], cos, sin, interleaved), q[..., rot:]], -1)
         if c.read_cache_of is None:
             k = plain.linear(x, w[a + "k_proj.weight"]).view(T, m.num_kv_heads, m.head_dim)
             if qk_norm:
                 k = plain.rms_norm(k, offset + w[a + "k_norm.weight"], 1e-5)
-            k = torch.cat([plain.apply_rope(k[..., :rot], cos, sin), k[..., rot:]], -1)
+            k = torch.cat([_plain_rope(k[..., :rot], cos, sin, interleaved), k[..., rot:]], -1)
             v = plain.linear(x, w[a + "v_proj.weight"]).view(T, m.num_kv_heads, m.head_dim)
             kv_of_call[ci] = (k, v)
         else:
@@ -120,7 +131,7 @@ def _cuts(n, rng):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("case", ["plain", "window", "partial_rotary", "no_qk_norm", "one_plus_w",
-                                  "shared_cache", "layer_twice"])
+                                  "shared_cache", "layer_twice", "interleaved_rotary", "interleaved_partial_rotary"])
 def test_assemblies(dtype, case):
     from openinfer_b200.parts.spec import LayerCall
     kw, pkw = {}, {}
@@ -136,6 +147,12 @@ def test_assemblies(dtype, case):
     elif case == "one_plus_w":
         kw = dict(offset=1.0)
         pkw = dict(offset=1.0)
+    elif case == "interleaved_rotary":    # the rotation turns neighbouring pairs (2 d, 2 d + 1)
+        kw = dict(interleaved=True)
+        pkw = dict(interleaved=True)
+    elif case == "interleaved_partial_rotary":
+        kw = dict(interleaved=True, rotary_dim=8)
+        pkw = dict(interleaved=True, rotary_dim=8)
     elif case == "shared_cache":      # the second call reads the keys and values of the first
         kw = dict(order=(0, LayerCall(1, read_cache_of=0)))
     elif case == "layer_twice":       # layer 0 runs twice (with a cache of its own each time), then layer 1
