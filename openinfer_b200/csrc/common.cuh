@@ -65,7 +65,7 @@ typedef __nv_bfloat16 bf16;
 // products the first loads of the (never written) weights, which they request before waiting.
 // What a kernel may read before its wait must have been written before the step's kernels began: the
 // step's metadata is put in place by a kernel that does NOT trigger early (copy_words_kernel), and the
-// kernel launched after that one is launched WITHOUT the attribute (oi_fence_next_launch): it starts only
+// kernel launched after that one is launched WITHOUT the attribute (oi_launch_fence, called by whoever uploads it): it starts only
 // when the metadata kernel has completed and its writes are visible, and every later kernel of the chain
 // starts after that kernel has started. Keys and values of earlier steps lie behind that fence too.
 // A kernel launched without the attribute (oi_set_pdl(0), or after a library kernel) sees both

@@ -75,7 +75,6 @@ OI_API int oi_gather_tokens(int* ids, const int* src, const int* from, int n, in
   OI_REQUIRE(n >= 0 && n_from >= 0, "gather_tokens: bad sizes");
   if (n == 0) return OI_OK;
   oi_launch(gather_tokens_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, ids, src, from, n, n_from);
-  oi_fence_next_launch();
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -89,8 +88,9 @@ __global__ void copy_words_kernel(int* __restrict__ dst, const int* __restrict__
                                   int n_ids, const int* __restrict__ from, int n_from) {
   // No early trigger here: what this kernel writes (a step's lengths, block tables, positions) is read by
   // later kernels BEFORE their own wait, so nothing after it may start until it has finished. It is the
-  // fence between two steps; the kernel launched next is launched without the programmatic attribute
-  // (oi_fence_next_launch below), so it starts only when this one has completed and its writes are visible.
+  // fence between two steps: whoever copies such data asks for the kernel launched next to be launched without
+  // the programmatic attribute (oi_launch_fence), so that it starts only when this one has completed and its
+  // writes are visible.
   pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     int v = src[i];
@@ -110,7 +110,6 @@ OI_API int oi_copy_words(int* dst, const int* src, int n, int ids_off, int src_o
   if (n == 0) return OI_OK;
   const int blocks = (n + 255) / 256 > 64 ? 64 : (n + 255) / 256;
   oi_launch(copy_words_kernel, blocks, 256, 0, (cudaStream_t)stream, dst, src, n, ids_off, src_off, n_ids, from, n_from);
-  oi_fence_next_launch();
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

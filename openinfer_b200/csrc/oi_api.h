@@ -112,6 +112,7 @@ OI_API int oi_qk_norm_rope_kv(void* qkv, int dtype, int row_stride, int tokens, 
 OI_API const char* oi_last_error();
 OI_API int oi_abi_version();
 OI_API unsigned long long oi_launches();
+OI_API int oi_launch_fence();   // the next kernel launched by this library gets plain stream order (once)
 OI_API int oi_set_pdl(int enabled);
 OI_API int oi_device_info(int device, int* sm_major, int* sm_minor, int* sm_count, long long* l2_bytes);
 

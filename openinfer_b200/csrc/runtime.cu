@@ -25,6 +25,10 @@ int oi_pdl_enabled() { return g_pdl; }
 // an ordinary one: that kernel then starts after the writer has completed, and the chain behind it after that.
 static int g_fence_next = 0;
 void oi_fence_next_launch() { g_fence_next = 1; }
+OI_API int oi_launch_fence() {
+  g_fence_next = 1;
+  return OI_OK;
+}
 int oi_take_launch_fence() {
   const int v = g_fence_next;
   g_fence_next = 0;

@@ -149,13 +149,15 @@ class ModelRunner:
         self._staging_last_bytes = n * 4
         return buf
 
-    def _upload(self, dev: torch.Tensor, host: np.ndarray, sections: Dict[str, int], T: int, entries) -> None:
+    def _upload(self, dev: torch.Tensor, host: np.ndarray, sections: Dict[str, int], T: int, entries, fence: bool = True) -> None:
         """Metadata to the device by a KERNEL that reads the pinned buffer (no copy-engine operation between
-        the steps' kernels); the same kernel puts in the token ids that the host does not know yet."""
+        the steps' kernels); the same kernel puts in the token ids that the host does not know yet. ``fence``:
+        the step's kernels are launched one by one behind it and read the metadata before their own wait, so the
+        first of them gets plain stream order (a recorded graph is ordered behind the copy as a whole)."""
         buf = self._pinned(host)
         feed = any(e.token_from is not None for e in entries)
         ops.copy_words(dev, buf, host.size, ids_off=sections["token_ids"] if feed else -1, src_off=sections["token_src"],
-                       n_ids=T if feed else 0, tokens=self._device_tokens if feed else None)
+                       n_ids=T if feed else 0, tokens=self._device_tokens if feed else None, fence=fence)
         event = torch.cuda.Event()
         event.record()
         self._staging_events[self._staging_turn] = event
@@ -433,7 +435,7 @@ class ModelRunner:
         host = np.zeros(total, dtype=np.int32)
         want_rows = self._fill(host, sections, entries, starts, bucket, bucket, cap)
         host[sections["want"]: sections["want"] + bucket] = np.arange(bucket, dtype=np.int32)
-        self._upload(meta, host, sections, bucket, entries)
+        self._upload(meta, host, sections, bucket, entries, fence=False)
         graph.replay()
         kernel_lib.replayed += recorded
         if not want_rows:

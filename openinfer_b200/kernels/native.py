@@ -104,6 +104,7 @@ def declare(lib) -> None:
     lib.oi_attention_layer.argtypes, lib.oi_attention_layer.restype = [POINTER(AttnStep), POINTER(AttnLayer), P], c_int
     lib.oi_forward.argtypes, lib.oi_forward.restype = [POINTER(ModelDesc), POINTER(StepDesc), P], c_int
     lib.oi_launches.argtypes, lib.oi_launches.restype = [], ctypes.c_ulonglong
+    lib.oi_launch_fence.argtypes, lib.oi_launch_fence.restype = [], c_int
     lib.oi_gemm_stream_fused.argtypes = [P, I, L, P, L, P, L, I, I, I, I, I, POINTER(StreamEpilogue), P]
     lib.oi_gemm_stream_fused.restype = c_int
 

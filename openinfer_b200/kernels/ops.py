@@ -72,10 +72,12 @@ def gather_tokens(ids: torch.Tensor, src: torch.Tensor, tokens: torch.Tensor) ->
 
 
 def copy_words(dst: torch.Tensor, src: torch.Tensor, n: int, *, ids_off: int = -1, src_off: int = 0, n_ids: int = 0,
-               tokens: Optional[torch.Tensor] = None) -> None:
+               tokens: Optional[torch.Tensor] = None, fence: bool = False) -> None:
     """dst[:n] = src[:n] (int32) by a kernel; one of the two may be pinned host memory, which the device
     reads or writes directly. With ``ids_off >= 0`` the words [ids_off, ids_off + n_ids) are token ids:
-    where the source index at ``src_off`` is >= 0 the id comes from ``tokens`` (int32, on the device)."""
+    where the source index at ``src_off`` is >= 0 the id comes from ``tokens`` (int32, on the device).
+    ``fence``: what is copied is read by later kernels before their own wait for their predecessor (a step's
+    lengths, block tables, positions, work items): the kernel launched next then gets plain stream order."""
     for t, what in ((dst, "dst"), (src, "src")):
         if t.dtype != torch.int32 or not t.is_contiguous() or t.numel() < n or not (t.is_cuda or t.is_pinned()):
             raise KernelError(f"copy_words: {what} must be contiguous int32 of at least {n} words, on the device or pinned")
@@ -85,6 +87,8 @@ def copy_words(dst: torch.Tensor, src: torch.Tensor, n: int, *, ids_off: int = -
     L = _lib.load()
     _lib.check(L.oi_copy_words(dst.data_ptr(), src.data_ptr(), int(n), int(ids_off), int(src_off), int(n_ids),
                                _ptr(tokens), 0 if tokens is None else tokens.numel(), _stream()), "copy_words")
+    if fence:
+        L.oi_launch_fence()
 
 
 class UploadRing:
@@ -112,7 +116,7 @@ class UploadRing:
         buf[:n].numpy()[:] = host
         dev = torch.empty(max(n, 1), dtype=torch.int32, device=device)
         if n:
-            copy_words(dev, buf, n)
+            copy_words(dev, buf, n, fence=True)
         event = torch.cuda.Event()
         event.record()
         self.events[self.turn] = event

@@ -274,7 +274,7 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
     number that belongs to the draw: SplitMix64(the request's seed, its own count of tokens so far) for a seeded
     request; for an unseeded one SplitMix64(SplitMix64(the step's seed, its row among the step's sampled rows),
     its own count), the step's seed being the next 64 bits of Random(engine seed). A draw whose uniform number lies
-    within 1e-4 of an edge of the cumulative distribution is not judged."""
+    within 1e-4 of an edge of the cumulative distribution is not checked."""
     from openinfer_b200 import LLM, SamplingParams
     cfg, w = plain.read_model_folder(folders["B"])
     rng = random.Random(8)
@@ -305,7 +305,7 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
             where[(rid, drawn[rid])] = (step_seed, row)
             drawn[rid] += 1
     ids = sorted(drawn)
-    judged = 0
+    checked = 0
     for i, rid in enumerate(ids):
         assert len(got[i]) == n_new
         sp, seq = params[i], list(prompts[i])
@@ -320,9 +320,9 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
             edges = torch.cumsum(dist, 0)
             if float((edges - u).abs().min()) > 1e-4:
                 assert tok == plain.inverse_cdf_pick(dist, u), f"request {i}, token {k}: not the plain draw"
-                judged += 1
+                checked += 1
             seq.append(tok)
-    assert judged >= 40
+    assert checked >= 40
 
 
 @pytest.mark.parametrize("ahead", [False, True])
