@@ -393,7 +393,9 @@ attention_mma_kernel(const AttnParams p) {
 // memory and attention_merge_kernel combines them. The tiles of earlier steps' keys are requested
 // before the kernel waits for its predecessor on the stream (programmatic dependent launch), and on
 // request the kernel also does the per-head q/k norm, the rotation and the write of the step's key
-// and value (fuse_rope), which otherwise take a kernel of their own in front of it.
+// and value (fuse_rope), which otherwise take a kernel of their own in front of it; the new key and value
+// reach the scores through shared memory (put into the row's last tile by the warp that owns it), so no
+// warp waits for a store to come back from global memory.
 // ---------------------------------------------------------------------------
 constexpr int kDecWarps = 4;
 constexpr int kDecKeys = 16;     // keys per tile
@@ -469,18 +471,26 @@ __device__ __forceinline__ void load_kv_tile16(bf16* k_smem, bf16* v_smem, const
 // A lane owns the element pair (2 lane, 2 lane + 1) of the first rotary half and its partner pair in the
 // second (head_dim <= 128: at most 32 such pairs); its cos/sin values and norm weights (wa, wb, with the
 // offset added) are fetched by the caller ahead of time.
-__device__ __forceinline__ void warp_norm_rope_head(const bf16* __restrict__ src, bf16* __restrict__ dst, int hd,
-                                                    const void* w, int norm_dtype, float eps, float w_offset, float2 wa,
-                                                    float2 wb, float2 c, float2 sn, int rot_half, int lane) {
+struct HeadIn { float2 x, y; };
+__device__ __forceinline__ HeadIn head_load(const bf16* __restrict__ src, int rot_half, int lane) {
+  const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
+  const int rot_pairs = rot_half / 2;
+  HeadIn in;
+  in.x = in.y = make_float2(0.f, 0.f);
+  if (lane < rot_pairs) {
+    in.x = __bfloat1622float2(src2[lane]);
+    in.y = __bfloat1622float2(src2[lane + rot_pairs]);
+  }
+  return in;
+}
+__device__ __forceinline__ void head_finish(HeadIn in, const bf16* __restrict__ src, bf16* __restrict__ dst, int hd,
+                                            const void* w, int norm_dtype, float eps, float w_offset, float2 wa,
+                                            float2 wb, float2 c, float2 sn, int rot_half, int lane) {
   const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
   __nv_bfloat162* dst2 = reinterpret_cast<__nv_bfloat162*>(dst);
   const int npairs = hd / 2, rot_pairs = rot_half / 2;
   const bool mine = lane < rot_pairs;
-  float2 x = make_float2(0.f, 0.f), y = x;
-  if (mine) {
-    x = __bfloat1622float2(src2[lane]);
-    y = __bfloat1622float2(src2[lane + rot_pairs]);
-  }
+  float2 x = in.x, y = in.y;
   float inv = 1.f;
   if (w) {
     float ss = x.x * x.x + x.y * x.y + y.x * y.x + y.y * y.y;
@@ -505,6 +515,11 @@ __device__ __forceinline__ void warp_norm_rope_head(const bf16* __restrict__ src
     }
     dst2[pr] = __floats2bfloat162_rn(t.x, t.y);
   }
+}
+__device__ __forceinline__ void warp_norm_rope_head(const bf16* __restrict__ src, bf16* __restrict__ dst, int hd,
+                                                    const void* w, int norm_dtype, float eps, float w_offset, float2 wa,
+                                                    float2 wb, float2 c, float2 sn, int rot_half, int lane) {
+  head_finish(head_load(src, rot_half, lane), src, dst, hd, w, norm_dtype, eps, w_offset, wa, wb, c, sn, rot_half, lane);
 }
 
 template <int HD>
@@ -569,13 +584,16 @@ attention_decode_kernel(const AttnParams p) {
     }
     cp_async_commit();
   };
-  // Prologue: kDecStages - 1 tiles in flight. Keys of earlier steps do not change any more, so their
-  // tiles are requested BEFORE waiting for the kernels ahead on the stream; the row's last tile holds
-  // the key this step has just written and is requested, like q, only after the wait. (The lengths,
-  // the block table and the items were copied to the device before the step's first kernel.)
+  // Prologue: the ring is filled (kDecStages tiles in flight). Keys of earlier steps do not change any more, so
+  // their tiles are requested BEFORE waiting for the kernels ahead on the stream. The row's last tile holds the
+  // key and value of this step: when another kernel has stored them it is requested, like q, only after the wait;
+  // when this kernel stores them itself (fuse_rope with write_kv) the tile is requested early as well, and the
+  // warp that owns it puts the new row into the tile in shared memory once the copy has landed. (The lengths, the
+  // block table and the items were copied to the device before the step's first kernel.)
+  const bool inserts_row = p.fuse_rope && p.write_kv;
   int primed = 0;
   if (split_ok) {
-    for (; primed < kDecStages - 1 && ld_t != span_tiles - 1; ++primed) issue_next();
+    for (; primed < kDecStages && (inserts_row || ld_t != span_tiles - 1); ++primed) issue_next();
   }
   // fuse_rope: this lane's cos/sin values and norm weights do not depend on the step's kernels either
   float2 rc = make_float2(1.f, 1.f), rs = make_float2(0.f, 0.f);
@@ -602,11 +620,38 @@ attention_decode_kernel(const AttnParams p) {
   // the row does its own copy), and the warp that owns the row's last tile normalises and rotates the step's
   // key and stores it, and the value, into their page before it requests that tile
   const bf16* q_src = p.q + (size_t)row_q * p.q_row_stride + (size_t)(kvh * group) * HD;   // [group][HD]
+  bool insert = false;   // this warp puts the step's key and value into the row's last tile
+  bf16* const q_s = reinterpret_cast<bf16*>(smem_raw + (size_t)kDecWarps * kDecStages * 2 * kDecKeys * HD * sizeof(bf16));
+  bf16* const new_k = q_s + 16 * HD;   // the step's key (normalised, rotated) and value of this kv head
+  bf16* const new_v = new_k + HD;
   if (p.fuse_rope) {
-    bf16* q_s = reinterpret_cast<bf16*>(smem_raw + (size_t)kDecWarps * kDecStages * 2 * kDecKeys * HD * sizeof(bf16));
+    // the owner of the last tile asks for the raw key and value together with the query heads
+    const bf16* row = p.q + (size_t)row_q * p.q_row_stride;
+    const bf16* k_raw = row + (size_t)(p.nq + kvh) * HD;
+    int slot = -1;
+    HeadIn kin;
+    uint4 vin = make_uint4(0u, 0u, 0u, 0u);
+    if (inserts_row && owns_last_tile) {
+      slot = p.slots[row_q];   // a padding row (slot < 0) stores nothing
+      insert = slot >= 0;
+    }
+    if (insert) {
+      kin = head_load(k_raw, p.rot_half, lane);
+      if (lane < HD / 8) vin = reinterpret_cast<const uint4*>(row + (size_t)(p.nq + p.nkv + kvh) * HD)[lane];
+    }
     for (int r = warp; r < group; r += kDecWarps)
       warp_norm_rope_head(q_src + (size_t)r * HD, q_s + r * HD, HD, p.q_norm_w, p.norm_dtype, p.eps, p.w_offset, wqa, wqb,
                           rc, rs, p.rot_half, lane);
+    if (insert) {
+      head_finish(kin, k_raw, new_k, HD, p.k_norm_w, p.norm_dtype, p.eps, p.w_offset, wka, wkb, rc, rs, p.rot_half, lane);
+      __syncwarp();
+      const size_t off = (size_t)(slot / p.page_size) * p.page_stride + (size_t)(slot % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
+      if (lane < HD / 8) {
+        reinterpret_cast<uint4*>(new_v)[lane] = vin;
+        reinterpret_cast<uint4*>(const_cast<bf16*>(p.v_cache) + off)[lane] = vin;
+        reinterpret_cast<uint4*>(const_cast<bf16*>(p.k_cache) + off)[lane] = reinterpret_cast<const uint4*>(new_k)[lane];
+      }
+    }
     __syncthreads();
     q_src = q_s;
   }
@@ -632,28 +677,22 @@ attention_decode_kernel(const AttnParams p) {
       }
     }
   }
-  if (p.fuse_rope && p.write_kv && owns_last_tile) {
-    const int slot = p.slots[row_q];
-    if (slot >= 0) {    // a padding row stores nothing
-      const size_t off = (size_t)(slot / p.page_size) * p.page_stride + (size_t)(slot % p.page_size) * p.nkv * HD + (size_t)kvh * HD;
-      const bf16* row = p.q + (size_t)row_q * p.q_row_stride;
-      warp_norm_rope_head(row + (size_t)(p.nq + kvh) * HD, const_cast<bf16*>(p.k_cache) + off, HD, p.k_norm_w, p.norm_dtype,
-                          p.eps, p.w_offset, wka, wkb, rc, rs, p.rot_half, lane);
-      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(row + (size_t)(p.nq + p.nkv + kvh) * HD);
-      __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(const_cast<bf16*>(p.v_cache) + off);
-      for (int pr = lane; pr < HD / 2; pr += 32) d2[pr] = v2[pr];
-      __threadfence();   // the tile copy below reads these rows back from global memory
-    }
-    __syncwarp();
-  }
   if (split_ok) {
-    for (; primed < kDecStages - 1; ++primed) issue_next();
+    for (; primed < kDecStages; ++primed) issue_next();
     int stage = 0;
     for (int t = t_begin; t < t_end; ++t) {
-      issue_next();   // keeps the ring full: goes into the stage freed last iteration
       cp_async_wait<kDecStages - 1>();   // tile t (this thread's part) has landed ...
       __syncwarp();                      // ... and so have the other lanes' parts
       const int key0 = lo + t * kDecKeys;
+      if (insert && t == span_tiles - 1) {
+        // what the copy brought for the step's own row is whatever the page held: the new key and value replace it
+        const int r = pos - key0;
+        if (lane < HD / 8)
+          *reinterpret_cast<uint4*>(k_tile(stage) + tile_offset<HD>(r, lane)) = reinterpret_cast<const uint4*>(new_k)[lane];
+        else if (lane >= 16 && lane - 16 < HD / 8)
+          *reinterpret_cast<uint4*>(v_tile(stage) + tile_offset<HD>(r, lane - 16)) = reinterpret_cast<const uint4*>(new_v)[lane - 16];
+        __syncwarp();
+      }
 
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       {
@@ -731,6 +770,7 @@ attention_decode_kernel(const AttnParams p) {
         }
       }
       __syncwarp();   // all lanes are done reading this stage before it is refilled
+      issue_next();   // keeps the ring full: goes into the stage just read
       stage = stage + 1 == kDecStages ? 0 : stage + 1;
     }
     cp_async_wait<0>();
@@ -751,7 +791,7 @@ attention_decode_kernel(const AttnParams p) {
     // given, in slice order (the formula of attention_merge_kernel), and nobody touches remote memory again.
     cg::cluster_group cluster = cg::this_cluster();
     const int csize = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
-    float* const recv_o = reinterpret_cast<float*>(smem_raw + (size_t)(kDecWarps * kDecStages * 2 * kDecKeys + 16) * HD * sizeof(bf16));
+    float* const recv_o = reinterpret_cast<float*>(smem_raw + (size_t)(kDecWarps * kDecStages * 2 * kDecKeys + 18) * HD * sizeof(bf16));
     const int passes = (group * HD + 128 * csize - 1) / (128 * csize);
     float* const recv_lse = recv_o + (size_t)passes * nsplits * 128;    // [slice][16]
     asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");   // phase 0: every CTA of the cluster runs
@@ -942,10 +982,10 @@ int launch_merge(void* out, int out_row_stride, const float* part_o, const float
 
 template <int HD>
 int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
-  // the warps' rings, room for the rotated query heads of one kv head (fuse_rope), and the receive buffer
-  // of the merge by deposit
+  // the warps' rings, room for the rotated query heads of one kv head and the step's key and value
+  // (fuse_rope), and the receive buffer of the merge by deposit
   constexpr int kRecvMax = 12 * 1024;
-  constexpr int smem = (kDecWarps * kDecStages * 2 * kDecKeys + 16) * HD * (int)sizeof(bf16) + kRecvMax;
+  constexpr int smem = (kDecWarps * kDecStages * 2 * kDecKeys + 18) * HD * (int)sizeof(bf16) + kRecvMax;
   static bool configured = false;
   if (!configured) {
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -1018,6 +1058,7 @@ int decode_entry(const void* q, int q_row_stride, void* out, int out_row_stride,
                    rope->max_pos > 0 && rope->positions,
                "attention_decode: rotation tables, positions and an even rotary half <= head_dim / 2 are needed (half %d)", rope->rot_half);
     OI_REQUIRE(!rope->write_kv || rope->slots, "attention_decode: cache write without slots");
+    OI_REQUIRE(q_row_stride % 8 == 0 && (uintptr_t)q % 16 == 0, "attention_decode: the fused projection's rows must be 16-byte aligned");
     OI_REQUIRE((rope->q_norm_w == nullptr) == (rope->k_norm_w == nullptr) || !rope->write_kv,
                "attention_decode: q and k norm weights come together");
     p.fuse_rope = 1; p.write_kv = rope->write_kv ? 1 : 0;
