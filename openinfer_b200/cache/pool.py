@@ -22,7 +22,10 @@ class IdPool:
     """Ids 0..n-1; each is either free or held by exactly one owner.
 
     Freed ids are handed out again first (last freed, first reused), so reuse of a
-    page shows up in tests as soon as possible.
+    page shows up in tests as soon as possible. Ids that are given back together come
+    out again in ascending order, as a fresh pool's do: pages with consecutive ids lie
+    side by side in the cache, and the prompt attention kernel fetches such a run with
+    one copy.
     """
 
     def __init__(self, count: int, what: str = "page") -> None:
@@ -59,7 +62,7 @@ class IdPool:
             if not (0 <= i < self.count) or not self._held[i] or i in seen:
                 raise DoubleFree(f"{self.what} {i} is not held")
             seen.add(i)
-        for i in ids:
+        for i in sorted(ids, reverse=True):   # pop() takes from the end: the smallest of these first
             self._held[i] = False
             self._free.append(i)
 

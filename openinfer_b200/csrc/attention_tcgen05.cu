@@ -6,7 +6,8 @@
 // as in the mma.sync kernels. Roles:
 //   warp 0      producer: the Q tile once (two 128 x 64 boxes out of the projection buffer, rows
 //               ordered token-major by a 3-D box), then per 64-key tile the K and V boxes of the pages
-//               the block table names (4-D maps over the layer's cache). Each box is issued by a lane
+//               the block table names (4-D maps over the layer's cache; one box for the whole tile when
+//               the tile's pages have consecutive ids). Each box is issued by a lane
 //               of its own (a box of one 16-key page costs about 90 cycles of issue, one after the
 //               other from a single thread), page ids are read 32 at a time one round ahead, and K
 //               and V have barriers of their own: a K stage is free as soon as S has been computed
@@ -53,6 +54,7 @@ struct Params {
   int bt_stride;
   int page_size, box_keys;  // keys per TMA box = min(page_size, 64)
   int num_pages;
+  int run_boxes;            // maps over runs of 64 / page_size neighbouring pages exist (pages of fewer than 64 keys)
   int nq, nkv, group;
   float scale_log2;
   int window;
@@ -104,7 +106,8 @@ constexpr unsigned kTmemCols = 256;                // S0 [0,64) S1 [64,128) O_ti
 
 __global__ void __launch_bounds__(kThreads)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                         const __grid_constant__ CUtensorMap map_v, const Params p) {
+                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k_run,
+                         const __grid_constant__ CUtensorMap map_v_run, const Params p) {
   pdl_start();
   // the swizzled tiles need a 1024-byte aligned base; no slack is added for it (two CTAs must fit on an SM)
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -205,8 +208,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           my_page[b] = __shfl_sync(0xffffffffu, pages_now, g & 31);
         }
       }
+      // Pages whose ids follow one another (as a fresh pool hands them out) lie side by side in the cache: the
+      // tile's keys are then ONE box over `boxes` pages, and one copy per half of the head dims does what otherwise
+      // takes a copy per page. With pages of 16 keys the copy unit is otherwise the bound: 16 boxes per tile and CTA.
+      bool run = p.run_boxes != 0;
+#pragma unroll
+      for (int b = 1; b < 4; ++b)
+        if (b < boxes) run = run && my_page[b] == my_page[0] + b;
       // every lane below 2 * boxes issues one copy of K and one of V: (box, half of the head dims)
-      const int my_box = lane >> 1, my_half = lane & 1;
+      const int my_box = run ? 0 : lane >> 1, my_half = lane & 1;
+      const int copies = run ? 2 : 2 * boxes;
       int page = 0;
 #pragma unroll
       for (int b = 0; b < 4; ++b) page = my_box == b ? my_page[b] : page;
@@ -217,12 +228,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!ok) break;
       if (lane == 0) mbar_expect_tx(k_full(s), kKBytes);
       __syncwarp();
-      if (lane < 2 * boxes) tma_load_4d(k_dst, &map_k, my_half * 64, kvh, in_page, page, k_full(s));
+      if (lane < copies) tma_load_4d(k_dst, run ? &map_k_run : &map_k, my_half * 64, kvh, in_page, page, k_full(s));
       if (t >= kStages) ok = mbar_wait(v_empty(s), (unsigned)((t / kStages) - 1) & 1, abort_flag, 5);
       if (!ok) break;
       if (lane == 0) mbar_expect_tx(v_full(s), kVBytes);
       __syncwarp();
-      if (lane < 2 * boxes) tma_load_4d(v_dst, &map_v, my_half * 64, kvh, in_page, page, v_full(s));
+      if (lane < copies) tma_load_4d(v_dst, run ? &map_v_run : &map_v, my_half * 64, kvh, in_page, page, v_full(s));
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
@@ -475,7 +486,9 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
   OI_REQUIRE(enc != nullptr, "attention_tcgen05: cuTensorMapEncodeTiled is not available from this driver");
   const int group = nq / nkv;
   const int box_keys = page_size < kKeys ? page_size : kKeys;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mk_run, mv_run;
+  const int boxes = kKeys / box_keys;
+  const int run_boxes = (boxes > 1 && num_pages >= boxes) ? 1 : 0;
   {
     cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nq, (cuuint64_t)tokens};
     cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_row_stride * 2};
@@ -486,12 +499,18 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     OI_REQUIRE(r == CUDA_SUCCESS, "attention_tcgen05: tensor map for q failed (%d)", (int)r);
   }
-  for (int which = 0; which < 2; ++which) {
+  for (int which = 0; which < 4; ++which) {   // K, V; then K, V with a box over a run of pages
+    const bool v = (which & 1) != 0, wide = which >= 2;
+    CUtensorMap* m = wide ? (v ? &mv_run : &mk_run) : (v ? &mv : &mk);
+    if (wide && !run_boxes) {
+      *m = v ? mv : mk;   // never used
+      continue;
+    }
     cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)nkv, (cuuint64_t)page_size, (cuuint64_t)num_pages};
     cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)nkv * HD * 2, (cuuint64_t)page_stride * 2};
-    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_keys, 1};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_keys, (cuuint32_t)(wide ? boxes : 1)};
     cuuint32_t es[4] = {1, 1, 1, 1};
-    CUresult r = enc(which ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(which ? v_cache : k_cache),
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(v ? v_cache : k_cache),
                      dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     OI_REQUIRE(r == CUDA_SUCCESS, "attention_tcgen05: tensor map for the cache failed (%d)", (int)r);
@@ -499,7 +518,7 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
   Params p;
   p.items = (const int4*)items; p.cu_seqlens = cu_seqlens; p.kv_lens = kv_lens;
   p.block_table = block_table; p.bt_stride = bt_stride;
-  p.page_size = page_size; p.box_keys = box_keys; p.num_pages = num_pages;
+  p.page_size = page_size; p.box_keys = box_keys; p.num_pages = num_pages; p.run_boxes = run_boxes;
   p.nq = nq; p.nkv = nkv; p.group = group;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
@@ -510,7 +529,7 @@ OI_API int oi_attention_tcgen05(const void* q, long long q_row_stride, int token
     OI_CHECK_CUDA(cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
     configured = true;
   }
-  oi_launch(attention_tcgen05_kernel, (unsigned)((long long)num_items * nkv), kThreads, kSmemTotal, (cudaStream_t)stream, mq, mk, mv, p);
+  oi_launch(attention_tcgen05_kernel, (unsigned)((long long)num_items * nkv), kThreads, kSmemTotal, (cudaStream_t)stream, mq, mk, mv, mk_run, mv_run, p);
   OI_CHECK_LAUNCH();
   if (any_split) return oi_attention_merge_slices(out, out_row_stride, part_o, part_lse, row_splits, nq, max_splits, tokens, hd, stream);
   return OI_OK;

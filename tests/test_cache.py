@@ -32,6 +32,20 @@ def test_pool_basics():
     assert p.allocate(1) == [a[0]]  # last freed, first reused
 
 
+def test_pool_hands_out_ascending_runs():
+    """A fresh pool gives consecutive ids in ascending order, and ids that come back together come out ascending
+    again (before older free ones): neighbouring table entries then name neighbouring pages."""
+    p = IdPool(12)
+    assert p.allocate(5) == [0, 1, 2, 3, 4]
+    b = p.allocate(4)
+    assert b == [5, 6, 7, 8]
+    p.release([7, 5, 8, 6])
+    assert p.allocate(3) == [5, 6, 7]
+    p.release([2, 0, 1])
+    assert p.allocate(5) == [0, 1, 2, 8, 9]
+    p.check()
+
+
 def test_layers_with_same_need_share_a_group():
     cm, h = make(two_groups=True, window=6)
     assert h[0].group == h[1].group == 0 and (h[0].layer, h[1].layer) == (0, 1)

@@ -1,6 +1,7 @@
 """Each CUDA kernel alone against a plain float32 statement of the same operation, at sizes
 other than the engine's (widths that are no power of two, odd row counts, every head size)."""
 import math
+import random
 
 import pytest
 import torch
@@ -387,14 +388,27 @@ class _FakeGroup:
         self.kv_lens = torch.tensor(kv_lens, dtype=torch.int32, device=DEV)
 
 
-def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None):
+def _pages_in_runs(total_pages, seed):
+    """All page ids, in runs of 1 to 9 consecutive ids that come in random order: some groups of neighbouring
+    table entries are consecutive pages, some are not, some runs end in the middle of a tile."""
+    rng = random.Random(seed)
+    runs, at = [], 0
+    while at < total_pages:
+        n = min(total_pages - at, rng.randint(1, 9))
+        runs.append(list(range(at, at + n)))
+        at += n
+    rng.shuffle(runs)
+    return [p for run in runs for p in run]
+
+
+def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None, page_runs=False):
     from openinfer_b200.kernels import attention as A
     torch.manual_seed(seed)
     dtype = torch.bfloat16
     n_req = len(q_lens)
     pages_needed = [-(-kv // P) for kv in kv_lens]
     total_pages = sum(pages_needed) + 5
-    perm = torch.randperm(total_pages).tolist()
+    perm = _pages_in_runs(total_pages, seed) if page_runs else torch.randperm(total_pages).tolist()
     cache = torch.zeros(total_pages, 2, 2, P, nkv, hd, dtype=dtype)   # two layers per page; layer 1 is used
     bt = torch.zeros(n_req, max(pages_needed), dtype=torch.int32)
     ks, vs, at = [], [], 0
@@ -515,6 +529,18 @@ def test_attention_tcgen05_with_key_slices(nq, nkv, P, window):
         plan = _mma_case(nq, nkv, 128, P, window, q_lens, kv_lens, force_splits="max")
         assert plan.tile_split and plan.max_splits > 1     # _mma_case checks that the tcgen05 kernel ran where it covers the shape
         assert A.tcgen05_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nq,nkv,P,window", [(8, 2, 16, None), (4, 4, 32, None), (16, 2, 16, 100), (8, 8, 64, None)])
+def test_attention_tcgen05_with_runs_of_consecutive_pages(nq, nkv, P, window):
+    """Pages whose ids follow one another are fetched with ONE box per 64-key tile, the others page by page; tables
+    that mix both (runs of 1 to 9 pages in random order, so runs begin and end inside tiles), and the identity table
+    of a fresh pool."""
+    for seed, (q_lens, kv_lens) in enumerate((([300, 77], [300, 333]), ([129], [1100]), ([64, 200, 5], [640, 200, 390]))):
+        _mma_case(nq, nkv, 128, P, window, q_lens, kv_lens, seed=seed, page_runs=True)
+    from openinfer_b200.kernels import attention as A
+    assert A.tcgen05_status() == 0
 
 
 def test_attention_mma_plan():
