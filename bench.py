@@ -9,7 +9,8 @@ engine's step function plus on-device argmax); ``e2e`` is the same through the P
 entry point ``LLM.step()`` with host token ids in and out every step. The line also
 reports a 2,048-token prefill, the decode step's fraction of the HBM roofline, and decode
 at batch 1 and 64; then, as flat entries of ``points`` (and once more, grouped, under
-``sizes``), prefills of 8,192 and 32,768 tokens at the headline sizes and the other two
+``sizes``), prefills of 8,192 and 32,768 tokens and decoding at longer contexts (batch 8 at
+16,384 tokens, batch 1 at 32,768) at the headline sizes, and the other two
 sizes of the reference's benchmarks, each built, measured and freed in turn: Qwen3-0.6B
 sizes (decode at batch 1/8/64, prefill, and the mixed step of 8 prompt portions of 512
 tokens beside 56 decoding requests, device-timed and through ``LLM.step()``) and Qwen3-32B
@@ -418,6 +419,9 @@ def main() -> int:
     ap.add_argument("--long-prefill", default=None,
                     help="further prefill lengths at the headline sizes, comma separated (default 8192,32768 with the "
                          "full model; 'none' to skip)")
+    ap.add_argument("--long-decode", default=None,
+                    help="further decode points at the headline sizes as BATCHxCONTEXT, comma separated (default 8x16384,1x32768 "
+                         "with the full model; 'none' to skip)")
     ap.add_argument("--batch-invariant", action="store_true",
                     help="measure under the batch-invariant numeric policy (one product kernel, fixed key slices)")
     ap.add_argument("--timeline", default=None, metavar="FILE",
@@ -466,6 +470,8 @@ def main() -> int:
     long_prefill = [] if args.skip_points else \
         ([8192, 32768] if headline_full else []) if args.long_prefill is None else \
         [int(x) for x in args.long_prefill.split(",") if x and x != "none"]
+    long_decode = ([(8, 16384), (1, 32768)] if headline_full else []) if args.long_decode is None else \
+        [tuple(int(v) for v in x.split("x")) for x in args.long_decode.split(",") if x and x != "none"]
     sizes = [] if args.skip_points else \
         (["0.6b", "32b"] if headline_full else []) if args.sizes is None else \
         [x for x in args.sizes.split(",") if x and x != "none"]
@@ -647,6 +653,19 @@ def main() -> int:
             points[f"prefill_{T}_frac"] = round(bench.prefill_flops(T) / (ms_t * 1e-3) / (peak_tf * 1e12), 4)
     runner = cache = None
     bench.close()
+    if long_decode and not args.skip_points:
+        # decoding at longer contexts, where the cache outweighs the weights: (batch, context) pairs at the headline sizes
+        for b, ctx in long_decode:
+            steps = max(16, K // 4)
+            lb = Bench(torch, mods, model_cfg, args.dtype, b, 2 * steps + 32, ctx, layers=args.layers)
+            try:
+                warm = max(3, W // 2)
+                ms_b, _ = lb.decode_run(b, steps, warm)
+                gbs = lb.decode_bytes(b, steps, warm) / (ms_b * 1e-3) / 1e9
+                out["points"][f"decode_b{b}_ctx{ctx}"] = round(b * 1000.0 / ms_b, 1)
+                out["points"][f"decode_b{b}_ctx{ctx}_hbm_frac"] = round(gbs / peaks["hbm_gbs"], 4)
+            finally:
+                lb.close()
     if sizes:
         out["sizes"] = {}
         for key in sizes:

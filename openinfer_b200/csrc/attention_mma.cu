@@ -893,8 +893,9 @@ attention_decode_kernel(const AttnParams p) {
 }
 
 // out[token, head] = sum_s w_s o_s / sum_s w_s with w_s = 2^(lse_s - max lse). One warp per
-// (token, head): the lanes fetch the slices' log-sum-exps side by side (up to 64 slices), and the
+// (token, head): the lanes fetch the slices' log-sum-exps side by side (up to kMaxMergeSlices), and the
 // partial outputs are read eight slices at a time so that the loads overlap.
+constexpr int kMaxMergeSlices = 128;
 template <int HD>
 __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_stride, const float* __restrict__ part_o,
                                        const float* __restrict__ part_lse, const int* __restrict__ row_splits,
@@ -908,15 +909,26 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_strid
   if (ns <= 1) return;  // written directly by the attention kernel
   const size_t base = ((size_t)token * nq + head) * max_splits;
   constexpr int kPer = HD / 32;
+  constexpr int kLaneSlices = kMaxMergeSlices / 32;
   float acc[kPer];
 #pragma unroll
   for (int e = 0; e < kPer; ++e) acc[e] = 0.f;
-  // ns <= 64 (checked by the entry points): lane i holds slices i and i + 32
-  const float l0 = lane < ns ? part_lse[base + lane] : -INFINITY;
-  const float l1 = 32 + lane < ns ? part_lse[base + 32 + lane] : -INFINITY;
-  const float mx = warp_max(fmaxf(l0, l1));
-  const float w0 = l0 == -INFINITY ? 0.f : exp2f(l0 - mx), w1 = l1 == -INFINITY ? 0.f : exp2f(l1 - mx);
-  const float wsum = warp_sum(w0 + w1);
+  // ns <= kMaxMergeSlices (checked by the entry points): lane i holds slices i, i + 32, i + 64, i + 96
+  float lse[kLaneSlices], w[kLaneSlices];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kLaneSlices; ++j) {
+    lse[j] = 32 * j + lane < ns ? part_lse[base + 32 * j + lane] : -INFINITY;
+    mx = fmaxf(mx, lse[j]);
+  }
+  mx = warp_max(mx);
+  float wsum = 0.f;
+#pragma unroll
+  for (int j = 0; j < kLaneSlices; ++j) {
+    w[j] = lse[j] == -INFINITY ? 0.f : exp2f(lse[j] - mx);
+    wsum += w[j];
+  }
+  wsum = warp_sum(wsum);
   for (int s = 0; s < ns; s += 8) {
     float v[8][kPer];
 #pragma unroll
@@ -927,13 +939,17 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_strid
         for (int e = 0; e < kPer; ++e) v[u][e] = op[e];
       }
     }
+    // the eight slices of a round lie in one block of 32: the same register of every lane holds their weights
+    float wj = w[0];
+#pragma unroll
+    for (int j = 1; j < kLaneSlices; ++j) wj = (s >> 5) == j ? w[j] : wj;
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int idx = s + u;
-      const float w = __shfl_sync(0xffffffffu, idx < 32 ? w0 : w1, idx & 31);
+      const float ws = __shfl_sync(0xffffffffu, wj, idx & 31);
       if (idx < ns) {
 #pragma unroll
-        for (int e = 0; e < kPer; ++e) acc[e] += w * v[u][e];
+        for (int e = 0; e < kPer; ++e) acc[e] += ws * v[u][e];
       }
     }
   }
@@ -1036,8 +1052,8 @@ int decode_entry(const void* q, int q_row_stride, void* out, int out_row_stride,
                "attention_decode: %d slices cannot be merged in the kernel (a multiple of 4 up to 32)", max_splits);
     OI_REQUIRE((uintptr_t)out % 2 == 0, "attention_decode: misaligned output");
   } else {
-    OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2 && max_splits <= 64,
-               "attention_decode: scratch missing, or slices outside 2..64");
+    OI_REQUIRE(part_o && part_lse && row_splits && max_splits >= 2 && max_splits <= kMaxMergeSlices,
+               "attention_decode: scratch missing, or slices outside 2..%d", kMaxMergeSlices);
   }
   if (num_items == 0 || tokens == 0) return OI_OK;
   AttnParams p;
@@ -1152,7 +1168,7 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
 // part_lse): rows whose row_splits entry is above one get out = sum_s w_s o_s / sum_s w_s.
 OI_API int oi_attention_merge_slices(void* out, int out_row_stride, const float* part_o, const float* part_lse,
                                      const int* row_splits, int nq, int max_splits, int tokens, int hd, void* stream) {
-  OI_REQUIRE(out && part_o && part_lse && row_splits && tokens >= 0 && nq > 0 && max_splits >= 1 && max_splits <= 64,
+  OI_REQUIRE(out && part_o && part_lse && row_splits && tokens >= 0 && nq > 0 && max_splits >= 1 && max_splits <= kMaxMergeSlices,
              "attention_merge: bad arguments");
   if (tokens == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;

@@ -127,6 +127,13 @@ DECODE_CTAS_PER_SM = 2
 DECODE_MAX_SPLITS = 32     # 8 CTAs of 4 slices: what a cluster merges in the kernel (batch 1 at context 2048: 313 tok/s
                            # against 299 with 64 slices and the second kernel)
 DECODE_MERGE_IN_KERNEL_MAX_SPLITS = 32   # up to 8 CTAs of a row form a cluster and merge their slices themselves
+DECODE_LONG_SPLITS = 64     # rows of DECODE_LONG_CONTEXT keys and more get up to this many slices (the most the merge kernel
+                            # takes) when 32 a row leave SMs without a CTA; their partial results go through global memory
+                            # and the second kernel. Qwen3-8B sizes, batch 1: context 8,192 280 tok/s against 284 with 32
+                            # slices, 16,384 261 against 251, 32,768 230 against 204; batch 2 at 16,384 496 against 481
+DECODE_LONG_CONTEXT = 12288
+DECODE_VERY_LONG_CONTEXT = 24576   # and from here up to 128: batch 1 at 32,768 keys 240 against 229, at 65,536 206 against 188
+DECODE_VERY_LONG_SPLITS = 128
 DECODE_MIN_KEYS_PER_SPLIT = 32
 DECODE_MAX_GROUP = 16
 _SM_COUNT = None
@@ -168,14 +175,22 @@ class AttentionPlan:
     decode_merge_in_kernel: bool = False
 
 
-def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int]) -> int:
+def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int], capacity: Optional[int] = None) -> int:
     """Slices per decode row: as many as fill the GPU once (two CTAs of four slices per SM), a
-    multiple of four, each at least 32 keys long when the lengths are known."""
+    multiple of four, each at least 32 keys long when the lengths are known. ``capacity``: the keys a row
+    may hold when the lengths are not known (a recorded step: the width of its block table)."""
     if policy.batch_invariant():
         return policy.INVARIANT_DECODE_SPLITS      # the same cutting whatever else is in the step
     pairs = max(1, num_rows * nkv)
     ns = DECODE_WARPS * max(1, (DECODE_CTAS_PER_SM * sm_count) // pairs)
-    ns = min(ns, DECODE_MAX_SPLITS)
+    # a recorded step serves the lengths in the upper half of its table's capacity
+    longest = max_kv_len if max_kv_len is not None else (capacity // 2 if capacity is not None else None)
+    limit = DECODE_MAX_SPLITS
+    if longest is not None and longest >= DECODE_LONG_CONTEXT:
+        limit = DECODE_VERY_LONG_SPLITS if longest >= DECODE_VERY_LONG_CONTEXT else DECODE_LONG_SPLITS
+    ns = min(ns, limit)
+    if ns > DECODE_MAX_SPLITS:
+        ns = 1 << (ns.bit_length() - 1)    # beyond what a cluster merges: 64 or 128 (72 slices measured slower than 64)
     if max_kv_len is not None:
         ns = min(ns, max(DECODE_WARPS, (max_kv_len // DECODE_MIN_KEYS_PER_SPLIT) // DECODE_WARPS * DECODE_WARPS))
     return ns
@@ -246,13 +261,13 @@ def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_
             row_splits, max_splits, tile_split)
 
 
-def plan_items_static_decode(num_requests: int, group: int, nkv: int, sm_count: int):
+def plan_items_static_decode(num_requests: int, group: int, nkv: int, sm_count: int, capacity: Optional[int] = None):
     """Items of a decode step whose launch is recorded once and replayed (a CUDA graph): one
     query token per request, and a number of key slices that depends on the batch size only;
     the kernels find each slice's bounds from the request's current length."""
     empty = np.zeros((0, 4), dtype=np.int32)
     if group <= DECODE_MAX_GROUP:
-        ns = decode_splits(num_requests, nkv, sm_count, None)
+        ns = decode_splits(num_requests, nkv, sm_count, None, capacity)
         items = np.asarray([(b, 0, s0, ns) for b in range(num_requests) for s0 in range(0, ns, DECODE_WARPS)],
                            dtype=np.int32).reshape(-1, 4)
         return empty, items, np.full(num_requests, ns, dtype=np.int32), ns, False
@@ -272,8 +287,10 @@ def _plan_for(ctx, group_step, group: int, nq: int, nkv: int, hd: int, window, d
     if plan is None:
         if getattr(ctx, "static_decode", False):
             rows = ROWS_PER_CTA if (group <= ROWS_PER_CTA and not policy.batch_invariant()) else ROWS_PER_CTA_LARGE
+            table = getattr(group_step, "block_table", None)
+            capacity = int(table.shape[1]) * ctx.cache.page_size if table is not None and table.dim() == 2 else None
             t_items, d_items, row_splits, max_splits, tile_split = plan_items_static_decode(
-                ctx.num_requests, group, nkv, _sm_count(device))
+                ctx.num_requests, group, nkv, _sm_count(device), capacity)
         else:
             rows = tile_rows(ctx.q_lens_host, group)
             page = ctx.cache.page_size
@@ -328,7 +345,7 @@ def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd:
         return False
     if policy.batch_invariant():
         return False
-    if nq // nkv > DECODE_MAX_GROUP or qkv.stride(0) % 2 or page_stride % 8 or qkv.data_ptr() % 4:
+    if nq // nkv > DECODE_MAX_GROUP or qkv.stride(0) % 8 or page_stride % 8 or qkv.data_ptr() % 16:
         return False
     rot_half = cos.shape[1]
     if rot_half == 0 or rot_half % 2 or 2 * rot_half > hd:

@@ -74,6 +74,37 @@ def random_tokens(rng: random.Random, n: int, vocab: int) -> List[int]:
     return [rng.randrange(vocab) for _ in range(n)]
 
 
+_ORACLE_F64 = {}
+ORACLE_SELF_TOL = 8e-6   # float32 against float64 evaluation of the plain implementation: 2.5e-6 at most on the tiny models
+
+
+def oracle_logits(cfg: dict, w, token_ids) -> torch.Tensor:
+    """The plain implementation's logits for one whole sequence, checked against itself: evaluated in float32
+    (tensors as read) and in float64, the two must agree to float32 rounding; the float64 result, rounded once,
+    is returned (an oracle without rounding of its own). Why the check: on a many-core host the CPU library
+    behind ``plain_qwen3`` was seen to return, in a few per cent of the processes, logits of a 300-token sequence
+    that are off by 2e-5 to 9e-5 (the same wrong values every time within that process, in one precision only),
+    which made exact float32 comparisons fail for no fault of the engine. On disagreement both are evaluated
+    again on one thread; if they still disagree the ORACLE is reported as broken, not the engine."""
+    import plain_qwen3 as plain
+    key = id(w)
+    if key not in _ORACLE_F64:
+        _ORACLE_F64[key] = (w, {k: v.to(torch.float64) for k, v in w.items()})   # w is kept so that its id stays its own
+    w64 = _ORACLE_F64[key][1]
+    threads = torch.get_num_threads()
+    try:
+        for attempt in range(2):
+            a = plain.forward_logits(cfg, w, token_ids)
+            b = plain.forward_logits(cfg, w64, token_ids)
+            if (a.double() - b).abs().max().item() <= ORACLE_SELF_TOL * max(1.0, b.abs().max().item()):
+                return b.to(torch.float32)
+            torch.set_num_threads(1)
+    finally:
+        torch.set_num_threads(threads)
+    raise AssertionError("the plain implementation disagrees with itself between float32 and float64 "
+                         f"(max difference {(a.double() - b).abs().max().item():.3e}): the CPU oracle is broken here")
+
+
 def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "") -> None:
     got = got.detach().float().cpu()
     ref = ref.detach().float().cpu()

@@ -10,7 +10,7 @@ import torch
 
 import plain_qwen3 as plain
 from helpers import (TINY_C, TINY_E, TINY_F, assert_close, count_page_handouts, make_model_folder,
-                     random_tokens)
+                     random_tokens, oracle_logits)
 
 pytestmark = pytest.mark.gpu
 
@@ -70,7 +70,7 @@ def workloads(tmp_path_factory):
         folder = make_model_folder(str(tmp_path_factory.mktemp(f"big{name}")), cfg, seed)
         pcfg, w = plain.read_model_folder(folder)
         seqs, steps, num_pages, need1, need2 = _plan(cfg["vocab_size"], 40 + seed)
-        ref = {rid: plain.forward_logits(pcfg, w, toks) for rid, toks in seqs.items()}
+        ref = {rid: oracle_logits(pcfg, w, toks) for rid, toks in seqs.items()}
         out[name] = (folder, pcfg, w, seqs, steps, num_pages, ref)
     return out
 
@@ -133,7 +133,7 @@ def test_a_hundred_requests_through_the_scheduler_one_step_ahead(workloads, name
         assert len(g) == new
         seq = list(p)
         for tok in g:
-            logits = plain.forward_logits(pcfg, w, seq)[-1]
+            logits = oracle_logits(pcfg, w, seq)[-1]
             if dtype == "float32":
                 assert tok == int(logits.argmax()), f"prompt of {len(p)} tokens: token {len(seq) - len(p)} differs"
             else:

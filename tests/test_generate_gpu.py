@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import ROOT, TINY, make_model_folder, random_tokens
+from helpers import ROOT, TINY, make_model_folder, random_tokens, oracle_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -46,7 +46,7 @@ def test_bf16_greedy_follows_plain_where_the_margin_is_clear(folders):
     for p, g in zip(prompts, got):
         seq = list(p)
         for tok in g:
-            logits = plain.forward_logits(cfg, w, seq)[-1]
+            logits = oracle_logits(cfg, w, seq)[-1]
             top2 = torch.topk(logits, 2).values
             if float(top2[0] - top2[1]) > 0.05 * float(logits.abs().max()):
                 assert tok == int(logits.argmax())
@@ -185,7 +185,7 @@ def test_logprobs_and_echo(folders, lookahead):
     plain_tokens = llm.generate(prompts, max_tokens=5)
     for p, r, toks in zip(prompts, res, plain_tokens):
         assert r.token_ids == toks and r.finish_reason == "length"
-        full = torch.log_softmax(plain.forward_logits(cfg, w, p + r.token_ids).double(), dim=-1)
+        full = torch.log_softmax(oracle_logits(cfg, w, p + r.token_ids).double(), dim=-1)
         assert len(r.logprobs) == 5 and len(r.prompt_logprobs) == len(p) and r.prompt_logprobs[0] is None
         for t in range(1, len(p)):          # the prompt: token t under the distribution after t - 1
             e = r.prompt_logprobs[t]
@@ -310,7 +310,7 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
         assert len(got[i]) == n_new
         sp, seq = params[i], list(prompts[i])
         for k, tok in enumerate(got[i]):
-            logits = plain.forward_logits(cfg, w, seq)[-1]
+            logits = oracle_logits(cfg, w, seq)[-1]
             dist = plain.sampling_distribution(logits, sp.temperature, sp.top_k, sp.top_p, sp.min_p)
             if sp.seed is not None:
                 u = _uniform(sp.seed, k)

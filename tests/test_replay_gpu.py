@@ -7,7 +7,7 @@ import torch
 
 import plain_qwen3 as plain
 from helpers import (TINY, assert_close, count_page_handouts, make_model_folder, random_tokens, replay_in_process,
-                     replay_trace_run, round64, trace_mixed, trace_portions, trace_tail, trace_whole)
+                     replay_trace_run, round64, trace_mixed, trace_portions, trace_tail, trace_whole, oracle_logits)
 
 pytestmark = pytest.mark.gpu
 
@@ -31,7 +31,7 @@ def workloads(folders):
         cfg, w = plain.read_model_folder(folder)
         rng = random.Random(100 + len(name))
         reqs = {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(LENGTHS[name])}
-        ref = {rid: plain.forward_logits(cfg, w, toks) for rid, toks in reqs.items()}
+        ref = {rid: oracle_logits(cfg, w, toks) for rid, toks in reqs.items()}
         out[name] = (cfg, reqs, ref)
     return out
 
@@ -97,7 +97,7 @@ def test_first_tokens_and_long_decode(folders, workloads):
     cfg, w = plain.read_model_folder(folders[name])
     rng = random.Random(5)
     toks = random_tokens(rng, 300, cfg["vocab_size"])
-    ref = plain.forward_logits(cfg, w, toks)
+    ref = oracle_logits(cfg, w, toks)
     for dtype in ("float32", "bfloat16"):
         runner = _runner(folders[name], dtype, round64(len(toks)), page_size=8)
         steps = [{"step": i, "entries": [{"id": "x", "tokens": [t], "want": [0]}], "end": []}
@@ -273,7 +273,7 @@ def test_head_sizes_in_steps_of_16(tmp_path, dtype, hd, nq, nkv, hidden):
     pcfg, w = plain.read_model_folder(folder)
     rng = random.Random(hd)
     reqs = {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate((70, 45, 100))}
-    ref = {rid: plain.forward_logits(pcfg, w, toks) for rid, toks in reqs.items()}
+    ref = {rid: oracle_logits(pcfg, w, toks) for rid, toks in reqs.items()}
     max_tokens = 128 + 128
     steps = trace_mixed(reqs, max_tokens, seed=hd)
     runner = _runner(folder, dtype, max_tokens, page_size=16)
