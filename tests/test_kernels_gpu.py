@@ -543,6 +543,64 @@ def test_attention_tcgen05_with_runs_of_consecutive_pages(nq, nkv, P, window):
     assert A.tcgen05_status() == 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 2, 128), (4, 4, 64)])
+def test_attention_decode_with_64_and_128_key_slices_at_long_contexts(nq, nkv, hd):
+    """Decode rows over 13,000 and 25,000 keys: when 32 slices a row leave SMs idle such rows are cut into 64 or
+    128 slices, whose partial results go through global memory and the merge kernel (128 is the most it takes).
+    One far key is made to stand out (its k aligned with q), so a slice that is lost or merged with a wrong
+    weight shows. Reference: the row's softmax over all keys in float64."""
+    from openinfer_b200.kernels import attention as A
+    P = 16
+    for kv_lens, want_splits in (([13000], 64), ([13000, 12500], 64), ([25000, 13000], 128)):
+        torch.manual_seed(len(kv_lens) + want_splits)
+        pages_needed = [-(-kv // P) for kv in kv_lens]
+        total_pages = sum(pages_needed) + 3
+        perm = torch.randperm(total_pages)
+        cache = torch.zeros(total_pages, 2, P, nkv, hd, dtype=torch.bfloat16)
+        bt = torch.zeros(len(kv_lens), max(pages_needed), dtype=torch.int32)
+        q = torch.randn(len(kv_lens), nq, hd).to(torch.bfloat16)
+        ks, vs, at = [], [], 0
+        for b, kv in enumerate(kv_lens):
+            order = perm[at: at + pages_needed[b]]
+            at += pages_needed[b]
+            bt[b, : len(order)] = order.to(torch.int32)
+            k, v = torch.randn(kv, nkv, hd).to(torch.bfloat16), torch.randn(kv, nkv, hd).to(torch.bfloat16)
+            far = 37 + 1000 * b        # a key in an early slice that outweighs the others for head 0
+            k[far, 0] = (q[b, 0].float() * 2.0).to(torch.bfloat16)
+            pad = pages_needed[b] * P - kv
+            kp = torch.cat([k, torch.zeros(pad, nkv, hd, dtype=torch.bfloat16)]).view(-1, P, nkv, hd)
+            vp = torch.cat([v, torch.zeros(pad, nkv, hd, dtype=torch.bfloat16)]).view(-1, P, nkv, hd)
+            cache[order, 0] = kp
+            cache[order, 1] = vp
+            ks.append(k.double())
+            vs.append(v.double())
+        cache = cache.to(DEV)
+        ctx = _FakeCtx([1] * len(kv_lens), kv_lens, P)
+        grp = _FakeGroup(bt.to(DEV), kv_lens)
+        out = torch.full((len(kv_lens), nq * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+        old = A._sm_count
+        A._sm_count = lambda device: 10 ** 6      # as on a GPU that 32 slices a row never fill
+        try:
+            assert A.attention_mma(q.view(len(kv_lens), -1).to(DEV), out, cache[:, 0], cache[:, 1], cache.stride(0), ctx, grp,
+                                   nq, nkv, hd, 1.0 / math.sqrt(hd), None)
+        finally:
+            A._sm_count = old
+        plan = next(iter(ctx.scratch.values()))
+        assert plan.max_splits == want_splits and not plan.decode_merge_in_kernel
+        group = nq // nkv
+        for b, kv in enumerate(kv_lens):
+            for h in range(nq):
+                s = (ks[b][:, h // group] @ q[b, h].double()) / math.sqrt(hd)
+                ref = torch.softmax(s, dim=0) @ vs[b][:, h // group]
+                got = out[b].float().cpu().view(nq, hd)[h].double()
+                err = (got - ref).abs().max().item()
+                assert err <= 2e-2 * max(1.0, ref.abs().max().item()), f"kv {kv} head {h}: {err}"
+            # the far key carries most of head 0's weight: its value dominates the output
+            far = 37 + 1000 * b
+            assert (out[b].float().cpu().view(nq, hd)[0] - vs[b][far, 0].float()).abs().max().item() < 0.35
+
+
 def test_attention_mma_plan():
     from openinfer_b200.kernels.attention import plan_items
     # for the fast tile kernel: 32 tiles x 8 kv heads (less than two CTAs per SM) stay
