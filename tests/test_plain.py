@@ -132,3 +132,34 @@ def test_bfloat16_twin_with_the_reference_rounding_points(tmp_path):
     pos = torch.arange(50)
     cos, sin = plain.rope_tables(32, 1e4, pos)
     assert not torch.equal(twin.apply_rope(twin.bf(u), pos, 1e4), twin.bf(plain.apply_rope(twin.bf(u), cos, sin)))
+
+
+def test_oracle_checks_itself_and_survives_one_wrong_evaluation(tmp_path, monkeypatch):
+    """``oracle_logits`` evaluates the plain implementation in float32 and float64 and wants them to agree; when one
+    evaluation is off (simulated here: the float32 one, by 5e-5 at one place) a third evaluation with other shapes
+    decides, and the exact result comes back; when nothing agrees it reports the oracle, not the engine."""
+    from helpers import oracle_logits
+    f = make_model_folder(str(tmp_path / "m"), TINY["A"][0], TINY["A"][1])
+    c, w = plain.read_model_folder(f)
+    toks = random_tokens(random.Random(5), 60, c["vocab_size"])
+    good = oracle_logits(c, w, toks)
+    assert (good - plain.forward_logits(c, w, toks)).abs().max().item() < 5e-6
+    real = plain.forward_logits
+
+    def off_in_float32(cfg, ww, t):
+        out = real(cfg, ww, t).clone()
+        if next(iter(ww.values())).dtype == torch.float32:
+            out[5, 7] += 5e-5
+        return out
+
+    monkeypatch.setattr(plain, "forward_logits", off_in_float32)
+    assert torch.equal(oracle_logits(c, w, toks), good)
+
+    def off_everywhere(cfg, ww, t):
+        out = real(cfg, ww, t).clone()
+        out[5, 7] += 5e-5 * (1 + len(t) % 3) * (2.0 if out.dtype == torch.float64 else 1.0)
+        return out
+
+    monkeypatch.setattr(plain, "forward_logits", off_everywhere)
+    with pytest.raises(AssertionError, match="oracle"):
+        oracle_logits(c, w, toks)
