@@ -75,44 +75,53 @@ def random_tokens(rng: random.Random, n: int, vocab: int) -> List[int]:
 
 
 _ORACLE_F64 = {}
-ORACLE_SELF_TOL = 8e-6   # float32 against float64 evaluation of the plain implementation: 2.5e-6 at most on the tiny models
+ORACLE_SELF_TOL = 8e-6    # float32 against float64 evaluation of the plain implementation: 2.5e-6 at most on the tiny models
+ORACLE_F64_TOL = 1e-9     # two float64 evaluations with different shapes
 
 
 def oracle_logits(cfg: dict, w, token_ids) -> torch.Tensor:
-    """The plain implementation's logits for one whole sequence, checked against itself: evaluated in float32
-    (tensors as read) and in float64, the two must agree to float32 rounding; the float64 result, rounded once,
-    is returned (an oracle without rounding of its own). Why the check: on a many-core host the CPU library
-    behind ``plain_qwen3`` was seen to return, in a few per cent of the processes, logits of a 300-token sequence
-    that are off by 2e-5 to 9e-5 (the same wrong values every time within that process, in one precision only),
-    which made exact float32 comparisons fail for no fault of the engine. On disagreement both are evaluated
-    again on one thread; if they still disagree the ORACLE is reported as broken, not the engine."""
+    """The plain implementation's logits for one whole sequence, checked against itself, as float32 values of a
+    float64 evaluation (an oracle without rounding of its own). Two evaluations must agree: in float64 and in
+    float32 (tensors as read), to float32 rounding; or, when the tensors are float64 already, in float64 with
+    other shapes (one token more: causal, so the rows in front are the same function of the same tokens). On
+    disagreement a third evaluation, on one thread and with yet other shapes, decides which to believe; when
+    nothing agrees the ORACLE is reported as broken, not the engine.
+    Why: on a many-core host the CPU library behind ``plain_qwen3`` was seen to return, in a few per cent of the
+    processes, logits of a 300-token sequence that are off by 2e-5 to 9e-5 (the same wrong values every time within
+    that process, in one precision only), which made exact float32 comparisons fail for no fault of the engine."""
     import plain_qwen3 as plain
-    key = id(w)
-    if key not in _ORACLE_F64:
-        _ORACLE_F64[key] = (w, {k: v.to(torch.float64) for k, v in w.items()})   # w is kept so that its id stays its own
-    w64 = _ORACLE_F64[key][1]
-    def agree(x, y):
-        return (x.double() - y.double()).abs().max().item() <= ORACLE_SELF_TOL * max(1.0, y.abs().max().item())
+    toks = [int(t) for t in token_ids]
+    n = len(toks)
+    if next(iter(w.values())).dtype == torch.float64:
+        w64, second_tol = w, ORACLE_F64_TOL
+        second = lambda: plain.forward_logits(cfg, w64, toks + toks[:1])[:n]
+    else:
+        key = id(w)
+        if key not in _ORACLE_F64:
+            _ORACLE_F64[key] = (w, {k: v.to(torch.float64) for k, v in w.items()})   # w is kept so that its id stays its own
+        w64, second_tol = _ORACLE_F64[key][1], ORACLE_SELF_TOL
+        second = lambda: plain.forward_logits(cfg, w, toks)
 
+    def agree(x, y, tol):
+        return (x.double() - y.double()).abs().max().item() <= tol * max(1.0, y.abs().max().item())
+
+    a = plain.forward_logits(cfg, w64, toks)
+    b = second()
+    if agree(a, b, second_tol):
+        return a.to(torch.float32)
     threads = torch.get_num_threads()
     try:
-        for attempt in range(2):
-            a = plain.forward_logits(cfg, w, token_ids)
-            b = plain.forward_logits(cfg, w64, token_ids)
-            if agree(a, b):
-                return b.to(torch.float32)
-            torch.set_num_threads(1)
-        # a third evaluation with other shapes (one token more; causal, so the rows in front are the same function
-        # of the same tokens): whichever of the two it agrees with is taken
-        n = len(token_ids)
-        c = plain.forward_logits(cfg, w64, list(token_ids) + [int(token_ids[0])])[:n]
-        for x in (b, a):
-            if agree(x, c):
-                return c.to(torch.float32)
+        torch.set_num_threads(1)
+        c = plain.forward_logits(cfg, w64, toks + toks[:2])[:n]
     finally:
         torch.set_num_threads(threads)
-    raise AssertionError("the plain implementation disagrees with itself between float32 and float64 "
-                         f"(max difference {(a.double() - b).abs().max().item():.3e}): the CPU oracle is broken here")
+    if agree(a, c, ORACLE_F64_TOL):
+        return a.to(torch.float32)
+    if agree(b, c, second_tol):
+        return c.to(torch.float32)
+    raise AssertionError("the plain implementation disagrees with itself "
+                         f"(max difference between two evaluations {(a.double() - b.double()).abs().max().item():.3e}): "
+                         "the CPU oracle is broken here")
 
 
 def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = "") -> None:

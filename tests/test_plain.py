@@ -163,3 +163,20 @@ def test_oracle_checks_itself_and_survives_one_wrong_evaluation(tmp_path, monkey
     monkeypatch.setattr(plain, "forward_logits", off_everywhere)
     with pytest.raises(AssertionError, match="oracle"):
         oracle_logits(c, w, toks)
+
+    # float64 tensors: the second evaluation has other shapes; one wrong evaluation is outvoted
+    monkeypatch.setattr(plain, "forward_logits", real)
+    _, w64 = plain.read_model_folder(f, torch.float64)
+    good64 = oracle_logits(c, w64, toks)
+    assert (good64 - good).abs().max().item() < 1e-6
+    calls = {"n": 0}
+
+    def first_call_off(cfg, ww, t):
+        out = real(cfg, ww, t).clone()
+        calls["n"] += 1
+        if calls["n"] == 1:
+            out[3, 2] += 1e-4
+        return out
+
+    monkeypatch.setattr(plain, "forward_logits", first_call_off)
+    assert torch.equal(oracle_logits(c, w64, toks), good64) and calls["n"] == 3

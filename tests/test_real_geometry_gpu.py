@@ -13,7 +13,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import assert_close, count_page_handouts, make_model_folder, random_tokens, replay_in_process, trace_mixed
+from helpers import assert_close, count_page_handouts, make_model_folder, random_tokens, replay_in_process, trace_mixed, oracle_logits
 
 pytestmark = pytest.mark.gpu
 
@@ -37,7 +37,7 @@ def workload(request, tmp_path_factory):
     cfg, w = plain.read_model_folder(folder, dtype=torch.float64)
     rng = random.Random(17)
     reqs = {f"r{i}": random_tokens(rng, n, cfg["vocab_size"]) for i, n in enumerate(LENGTHS)}
-    ref = {rid: plain.forward_logits(cfg, w, toks).float() for rid, toks in reqs.items()}
+    ref = {rid: oracle_logits(cfg, w, toks) for rid, toks in reqs.items()}
     del w
     return name, folder, reqs, ref
 
