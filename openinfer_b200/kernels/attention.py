@@ -175,10 +175,13 @@ class AttentionPlan:
     decode_merge_in_kernel: bool = False
 
 
-def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int], capacity: Optional[int] = None) -> int:
+def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[int], capacity: Optional[int] = None,
+                  long_ok: bool = True) -> int:
     """Slices per decode row: as many as fill the GPU once (two CTAs of four slices per SM), a
     multiple of four, each at least 32 keys long when the lengths are known. ``capacity``: the keys a row
-    may hold when the lengths are not known (a recorded step: the width of its block table)."""
+    may hold when the lengths are not known (a recorded step: the width of its block table). ``long_ok`` False: no
+    more slices than a cluster merges, whatever the lengths (steps that also bring prompt portions: the scratch of
+    slices merged by the second kernel is indexed by the step's rows, and the GPU is busy anyway)."""
     if policy.batch_invariant():
         return policy.INVARIANT_DECODE_SPLITS      # the same cutting whatever else is in the step
     pairs = max(1, num_rows * nkv)
@@ -186,7 +189,7 @@ def decode_splits(num_rows: int, nkv: int, sm_count: int, max_kv_len: Optional[i
     # a recorded step serves the lengths in the upper half of its table's capacity
     longest = max_kv_len if max_kv_len is not None else (capacity // 2 if capacity is not None else None)
     limit = DECODE_MAX_SPLITS
-    if longest is not None and longest >= DECODE_LONG_CONTEXT:
+    if long_ok and longest is not None and longest >= DECODE_LONG_CONTEXT:
         limit = DECODE_VERY_LONG_SPLITS if longest >= DECODE_VERY_LONG_CONTEXT else DECODE_LONG_SPLITS
     ns = min(ns, limit)
     if ns > DECODE_MAX_SPLITS:
@@ -237,7 +240,7 @@ def plan_items(q_lens, kv_lens, group: int, nkv: int, window: Optional[int], sm_
     max_splits = 1
     decode_items = []
     if decode_reqs:
-        ns = decode_splits(len(decode_reqs), nkv, sm_count, max(kv_lens[b] for b in decode_reqs))
+        ns = decode_splits(len(decode_reqs), nkv, sm_count, max(kv_lens[b] for b in decode_reqs), long_ok=not tiles)
         max_splits = ns
         for b in decode_reqs:
             row_splits[starts[b]] = ns

@@ -602,7 +602,16 @@ def test_attention_decode_with_64_and_128_key_slices_at_long_contexts(nq, nkv, h
 
 
 def test_attention_mma_plan():
-    from openinfer_b200.kernels.attention import plan_items
+    from openinfer_b200.kernels.attention import decode_splits, plan_items
+    # decode rows: 32 slices at most (what a cluster merges), 64 and 128 for long rows that leave SMs idle otherwise,
+    # never in a step that also brings prompt portions (the merge scratch is indexed by the step's rows)
+    assert decode_splits(1, 8, 148, 2048) == 32 and decode_splits(1, 8, 148, 13000) == 64
+    assert decode_splits(1, 8, 148, 30000) == 128 and decode_splits(2, 8, 148, 30000) == 64
+    assert decode_splits(8, 8, 148, 30000) == 16 and decode_splits(1, 8, 148, None, capacity=65536) == 128
+    assert decode_splits(1, 8, 148, None, capacity=16384) == 32
+    _, _, _, mx, _ = plan_items([1, 300], [30000, 300], group=4, nkv=8, window=None, sm_count=148, rows_per_cta=128,
+                                whole_tiles_kernel=True)
+    assert mx == 32
     # for the fast tile kernel: 32 tiles x 8 kv heads (less than two CTAs per SM) stay
     # whole; two tiles over a long prefix (a quarter of the SMs at most) are still cut
     _, _, _, mx, cut = plan_items([1024], [1024], group=4, nkv=8, window=None, sm_count=148, rows_per_cta=128,
