@@ -207,6 +207,57 @@ def test_batch_invariant_mode_is_bitwise(folders, workloads, name):
     _check({r: together[r] for r in ids}, {r: ref[r] for r in ids}, "bfloat16", "batch-invariant policy")
 
 
+def test_long_context_decode_rows_in_64_and_128_slices_through_the_engine(tmp_path):
+    """Two requests with 13,000 and 25,000 tokens of context decode alone: such rows are cut into 64 and 128 key
+    slices whose partial results a second kernel merges (recorded graphs and launched steps). The bfloat16 engine's
+    logits are compared with the float32 engine's (its general attention kernel visits every key in order) on the
+    same weights: whole prompts in portions of 4,096 tokens, then four tokens one by one. (The kernel itself is
+    compared with float64 in test_kernels_gpu; the plain implementation cannot hold 25,000 x 25,000 scores.)"""
+    from openinfer_b200.engine.runner import ModelRunner, StepEntry
+    from openinfer_b200.kernels import attention as A
+    cfg = dict(TINY["E"][0], max_position_embeddings=32768)
+    folder = make_model_folder(str(tmp_path / "m"), cfg, 11)
+    rng = random.Random(2)
+    prompts = {"long": random_tokens(rng, 25000, cfg["vocab_size"]), "mid": random_tokens(rng, 13000, cfg["vocab_size"])}
+    seen = []
+    old = A.decode_splits
+
+    def recording(*a, **k):
+        ns = old(*a, **k)
+        seen.append(ns)
+        return ns
+
+    outs, feed = {}, {}
+    for dtype, graphs in (("float32", False), ("bfloat16", True), ("bfloat16", False)):
+        runner = ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", page_size=16, max_tokens=40000, max_requests=4)
+        runner.cuda_graph = graphs
+        rows = {r: [] for r in prompts}
+        for r, p in prompts.items():
+            for at in range(0, len(p), 4096):
+                toks = p[at: at + 4096]
+                logits = runner.step([StepEntry(r, toks, [len(toks) - 1])])
+            rows[r].append(logits[0].float().cpu())
+        A.decode_splits = recording
+        try:
+            for step in range(4):
+                for r in prompts:                    # each alone: one row a step leaves SMs idle with 32 slices
+                    if dtype == "float32":
+                        feed[(step, r)] = int(rows[r][-1].argmax())
+                    logits = runner.step([StepEntry(r, [feed[(step, r)]], [0])])
+                    rows[r].append(logits[0].float().cpu())
+        finally:
+            A.decode_splits = old
+        outs[(dtype, graphs)] = {r: torch.stack(v) for r, v in rows.items()}
+        if graphs:
+            assert runner._graphs, "the single-token steps did not go through a graph"
+        del runner
+        torch.cuda.empty_cache()
+    assert 64 in seen and 128 in seen, seen
+    for key in (("bfloat16", True), ("bfloat16", False)):
+        for r in prompts:
+            assert_close(outs[key][r], outs[("float32", False)][r], "bfloat16", f"long context, {r}, graphs {key[1]}")
+
+
 def test_real_layer_sizes_and_vocabulary(tmp_path):
     """Qwen3-8B layer sizes (hidden 4096, 32/8 heads of 128, intermediate 12288) with the REAL vocabulary
     of 151,936 entries, two layers, random weights written to a folder: the bfloat16 engine (streaming
