@@ -106,7 +106,7 @@ class Sampler:
             if k == n:
                 out = picked
             else:
-                out.index_copy_(0, idx, picked)
+                out.index_copy_(0, idx.to(torch.int64), picked)   # greedy rows keep their argmax
         host = self._host_buffer(n)
         ops.copy_words(host, out, n)     # a kernel writes the ids into pinned host memory: no copy-engine operation
         event = torch.cuda.Event()

@@ -272,15 +272,17 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
     temperature 0.8 (one request also with top-k and top-p), seeded and unseeded requests mixed, in float32.
     Every token must be the plain implementation's inverse-CDF pick from the plain distribution at the uniform
     number that belongs to the draw: SplitMix64(the request's seed, its own count of tokens so far) for a seeded
-    request; for an unseeded one SplitMix64(SplitMix64(the step's seed, its row among the step's sampled rows),
-    its own count), the step's seed being the next 64 bits of Random(engine seed). A draw whose uniform number lies
-    within 1e-4 of an edge of the cumulative distribution is not checked."""
+    request; for an unseeded one SplitMix64(SplitMix64(the step's seed, its row among the rows the step hands to
+    the sampler), its own count), the step's seed being the next 64 bits of Random(engine seed). A draw whose uniform
+    number lies within 1e-4 of an edge of the cumulative distribution is not checked. A fifth request is greedy and
+    runs in the same steps: its rows keep the argmax while the others' are drawn."""
     from openinfer_b200 import LLM, SamplingParams
     cfg, w = plain.read_model_folder(folders["B"])
     rng = random.Random(8)
-    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 9, 33, 70)]
+    prompts = [random_tokens(rng, n, cfg["vocab_size"]) for n in (1, 9, 33, 70, 20)]
     params = [SamplingParams(temperature=0.8, seed=1234), SamplingParams(temperature=0.8),
-              SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=77), SamplingParams(temperature=0.8)]
+              SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=77), SamplingParams(temperature=0.8),
+              SamplingParams()]      # and a greedy request in the same steps: its rows keep the argmax
     n_new = 12
     engine_seed = 4242
     llm = LLM(folders["B"], dtype="float32", max_cache_tokens=1024, max_prefill_tokens=13, lookahead=ahead,
@@ -297,7 +299,7 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
     llm.executor.launch = launch
     got = llm.generate(prompts, params, max_tokens=n_new)
     seeds = random.Random(engine_seed)
-    drawn = {i: 0 for i in range(4)}
+    drawn = {i: 0 for i in range(5)}
     where = {}                           # (request, its k-th token) -> (step seed, row)
     for step_seed, rows in batches:
         assert step_seed == seeds.getrandbits(64)
@@ -311,6 +313,13 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
         sp, seq = params[i], list(prompts[i])
         for k, tok in enumerate(got[i]):
             logits = oracle_logits(cfg, w, seq)[-1]
+            if sp.temperature == 0:
+                top = torch.topk(logits, 2).values
+                if float(top[0] - top[1]) > 1e-4:
+                    assert tok == int(logits.argmax()), f"request {i}, token {k}: not the argmax"
+                    checked += 1
+                seq.append(tok)
+                continue
             dist = plain.sampling_distribution(logits, sp.temperature, sp.top_k, sp.top_p, sp.min_p)
             if sp.seed is not None:
                 u = _uniform(sp.seed, k)
@@ -322,7 +331,7 @@ def test_sampled_tokens_are_the_plain_draws(folders, ahead):
                 assert tok == plain.inverse_cdf_pick(dist, u), f"request {i}, token {k}: not the plain draw"
                 checked += 1
             seq.append(tok)
-    assert checked >= 40
+    assert checked >= 50
 
 
 @pytest.mark.parametrize("ahead", [False, True])
