@@ -99,6 +99,11 @@ def main(argv: Optional[List[str]] = None) -> int:
         print("no prompts: give --prompt-ids or --prompt-file", file=sys.stderr)
         return 2
 
+    if args.batch_invariant and not args.no_prefix_cache:
+        print("--batch-invariant requires --no-prefix-cache: prefix-cache hits move a prompt's portions off the "
+              "request's own grid, so bit-identical results cannot be promised", file=sys.stderr)
+        return 2
+
     from .engine.engine import LLM
     from .sampling.params import SamplingParams
 

@@ -167,13 +167,22 @@ class LLM:
                  kv_cache_memory_margin_mib: int = DEFAULT_KV_MARGIN_MIB,
                  max_prefill_tokens: int = DEFAULT_MAX_PREFILL_TOKENS,
                  max_decode_batch: int = DEFAULT_MAX_DECODE_BATCH, engine_seed: int = DEFAULT_ENGINE_SEED,
-                 cuda_graph: bool = True, lookahead: bool = True, prefix_cache: bool = True,
+                 cuda_graph: bool = True, lookahead: bool = True, prefix_cache: Optional[bool] = None,
                  batch_invariant: Optional[bool] = None, runner: Optional[ModelRunner] = None,
                  row_alignment: int = DEFAULT_ROW_ALIGNMENT, strict_weights: bool = False) -> None:
         from ..kernels import policy
         if batch_invariant is not None:
             policy.set_batch_invariant(batch_invariant)   # process-wide: which kernels take which step shapes
         batch_invariant = policy.batch_invariant()
+        # A hit in the prefix cache moves a prompt's portions off the request's own grid (they then start where
+        # the cached pages end), and a position's bits depend on the portion it is computed in: the two do not go
+        # together, as in the reference (pegainfer-qwen3/src/lib.rs:549-554: --batch-invariant requires
+        # --no-prefix-cache). Left open, the prefix cache is on unless the policy is.
+        if prefix_cache is None:
+            prefix_cache = not batch_invariant
+        if batch_invariant and (prefix_cache or (runner is not None and runner.cache.prefix_cache)):
+            raise ValueError("batch_invariant requires prefix_cache=False: a prefix-cache hit moves a prompt's portions "
+                             "off the request's own grid, so bit-identical results cannot be promised")
         device = f"cuda:{device_ordinal}"
         weights_seed = None
         if runner is not None:

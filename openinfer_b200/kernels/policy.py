@@ -12,7 +12,11 @@ the request alone: all bfloat16 products go through ONE kernel (gemm_tcgen05: a 
 in the same order whatever else is in the step), decode rows always get 16 key slices, prompt tiles are
 never cut and always hold 128 query rows, the rotation kernel always runs on its own. Together with
 request-local portions in the scheduler a request's logits are then the same BIT FOR BIT whatever it is batched
-with. It costs speed, mostly in decode (the product kernel is built for prompt-sized steps).
+with. It costs speed, mostly in decode (the product kernel is built for prompt-sized steps). The prefix cache
+must be off, as in the reference (pegainfer-qwen3/src/lib.rs:549-554): a hit moves a prompt's portions off the
+request's own grid, and a position's bits depend on the portion it is computed in (a portion of one token goes
+to the decode kernel, for one); ``LLM`` and the command line refuse the combination. Two engines give the same
+bits when they cut prompts alike (the same ``max_prefill_tokens``).
 """
 from __future__ import annotations
 

@@ -449,3 +449,27 @@ def test_state_slots_are_a_limit_of_admission_not_an_error():
     toks, fin = collect(first + s.run())
     assert all(fin[i] == ("finished", "length") and len(toks[i]) == 3 for i in range(5))
     assert max(len(p) + len(d) for p, d in ex.batches) <= 2
+
+
+def test_batch_invariant_and_prefix_cache_do_not_go_together(tmp_path):
+    """As in the reference (pegainfer-qwen3/src/lib.rs:549-554): a prefix-cache hit moves a prompt's portions off the
+    request's own grid, so the command line refuses --batch-invariant without --no-prefix-cache (before anything is
+    built), and so does the Python entry point when both are asked for."""
+    import json
+    import subprocess
+    import sys
+
+    from helpers import ROOT, TINY
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(TINY["A"][0]))
+    out = subprocess.run([sys.executable, "-m", "openinfer_b200", "--random-config", str(cfg_file), "--prompt-ids", "1,2,3",
+                          "--batch-invariant"], cwd=ROOT, capture_output=True, text=True)
+    assert out.returncode == 2 and "--no-prefix-cache" in out.stderr, (out.returncode, out.stderr[-300:])
+
+    from openinfer_b200.engine.engine import LLM
+    from openinfer_b200.kernels import policy
+    try:
+        with pytest.raises(ValueError, match="prefix_cache"):
+            LLM(str(tmp_path), batch_invariant=True, prefix_cache=True)
+    finally:
+        policy.set_batch_invariant(False)
