@@ -468,3 +468,49 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(dtype_name):
         assert (err < 0.05).float().mean() >= 0.8, f"rows within 5 %: {(err < 0.05).float().mean():.2f}"
     runner.end("a"); runner.end("b")
     runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,nq,nkv,hidden,inter,window", [(128, 8, 2, 256, 384, 40), (64, 6, 3, 192, 320, 100),
+                                                           (128, 4, 4, 128, 256, 17)])
+def test_windows_through_the_tuned_kernels(dtype, hd, nq, nkv, hidden, inter, window):
+    """A mixer with a window at head sizes 64 and 128 and pages of 16 keys, where the tensor-core kernels run (prompt
+    tiles, decode rows in recorded graphs): five requests together in portions of changing size and then token by
+    token, in a pool smaller than their total length, so that pages behind the window go back while a request lives
+    and are used again; against the plain implementation with the same window."""
+    from openinfer_b200.engine.runner import StepEntry
+    spec = _mini_spec(window=window, nq=nq, nkv=nkv, hd=hd, hidden=hidden, inter=inter, vocab=120)
+    w = _random_tensors(spec, 3)
+    rng = random.Random(window + hd)
+    seqs = {f"q{i}": [rng.randrange(120) for _ in range(n)] for i, n in enumerate((250, 131, 64, 199, 33))}
+    refs = {r: _plain_forward(spec, w, t, window=window) for r, t in seqs.items()}
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    runner = _runner(spec, dtype, w, page=16, pages=40)      # 640 tokens of room for requests of 677 tokens
+    runner.cuda_graph = True
+    at = {r: 0 for r in seqs}
+    got = {r: [] for r in seqs}
+    live = list(seqs)
+    while live:
+        entries = []
+        for r in list(live):
+            left = len(seqs[r]) - at[r]
+            n = 1 if left <= 30 else min(left - 30, rng.choice([1, 2, 9, 31, 64, 100]))
+            if rng.random() < 0.2 and len(live) > 1:
+                continue
+            entries.append((r, n))
+        if not entries:
+            continue
+        logits = runner.step([StepEntry(r, seqs[r][at[r]: at[r] + n], list(range(n))) for r, n in entries]).float().cpu()
+        row = 0
+        for r, n in entries:
+            got[r].append(logits[row: row + n])
+            row += n
+            at[r] += n
+            if at[r] == len(seqs[r]):
+                runner.end(r)
+                live.remove(r)
+    for r in seqs:
+        assert_close(torch.cat(got[r]), refs[r], name, f"head {hd}, window {window}, {name}, request {r}")
+    assert runner._graphs, "the single-token steps did not go through a graph"
+    runner.cache.check()
+    assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
