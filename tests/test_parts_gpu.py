@@ -470,23 +470,10 @@ def test_toy_routed_feed_forward_and_toy_position_encoding(dtype_name):
     runner.cache.check()
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hd,nq,nkv,hidden,inter,window", [(128, 8, 2, 256, 384, 40), (64, 6, 3, 192, 320, 100),
-                                                           (128, 4, 4, 128, 256, 17)])
-def test_windows_through_the_tuned_kernels(dtype, hd, nq, nkv, hidden, inter, window):
-    """A mixer with a window at head sizes 64 and 128 and pages of 16 keys, where the tensor-core kernels run (prompt
-    tiles, decode rows in recorded graphs): five requests together in portions of changing size and then token by
-    token, in a pool smaller than their total length, so that pages behind the window go back while a request lives
-    and are used again; against the plain implementation with the same window."""
+def _drive_together(runner, seqs, rng):
+    """All requests at once through the step function: portions of changing size (a request may sit a step out),
+    then the last 30 tokens of each one by one; returns the logits of every position, per request."""
     from openinfer_b200.engine.runner import StepEntry
-    spec = _mini_spec(window=window, nq=nq, nkv=nkv, hd=hd, hidden=hidden, inter=inter, vocab=120)
-    w = _random_tensors(spec, 3)
-    rng = random.Random(window + hd)
-    seqs = {f"q{i}": [rng.randrange(120) for _ in range(n)] for i, n in enumerate((250, 131, 64, 199, 33))}
-    refs = {r: _plain_forward(spec, w, t, window=window) for r, t in seqs.items()}
-    name = "float32" if dtype == torch.float32 else "bfloat16"
-    runner = _runner(spec, dtype, w, page=16, pages=40)      # 640 tokens of room for requests of 677 tokens
-    runner.cuda_graph = True
     at = {r: 0 for r in seqs}
     got = {r: [] for r in seqs}
     live = list(seqs)
@@ -509,8 +496,64 @@ def test_windows_through_the_tuned_kernels(dtype, hd, nq, nkv, hidden, inter, wi
             if at[r] == len(seqs[r]):
                 runner.end(r)
                 live.remove(r)
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,nq,nkv,hidden,inter,window", [(128, 8, 2, 256, 384, 40), (64, 6, 3, 192, 320, 100),
+                                                           (128, 4, 4, 128, 256, 17)])
+def test_windows_through_the_tuned_kernels(dtype, hd, nq, nkv, hidden, inter, window):
+    """A mixer with a window at head sizes 64 and 128 and pages of 16 keys, where the tensor-core kernels run (prompt
+    tiles, decode rows in recorded graphs): five requests together in portions of changing size and then token by
+    token, in a pool smaller than their total length, so that pages behind the window go back while a request lives
+    and are used again; against the plain implementation with the same window."""
+    spec = _mini_spec(window=window, nq=nq, nkv=nkv, hd=hd, hidden=hidden, inter=inter, vocab=120)
+    w = _random_tensors(spec, 3)
+    rng = random.Random(window + hd)
+    seqs = {f"q{i}": [rng.randrange(120) for _ in range(n)] for i, n in enumerate((250, 131, 64, 199, 33))}
+    refs = {r: _plain_forward(spec, w, t, window=window) for r, t in seqs.items()}
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    runner = _runner(spec, dtype, w, page=16, pages=40)      # 640 tokens of room for requests of 677 tokens
+    runner.cuda_graph = True
+    got = _drive_together(runner, seqs, rng)
     for r in seqs:
-        assert_close(torch.cat(got[r]), refs[r], name, f"head {hd}, window {window}, {name}, request {r}")
+        assert_close(got[r], refs[r], name, f"head {hd}, window {window}, {name}, request {r}")
     assert runner._graphs, "the single-token steps did not go through a graph"
+    runner.cache.check()
+    assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ["partial_rotary", "partial_rotary_16", "no_qk_norm", "one_plus_w", "interleaved_rotary",
+                                  "shared_cache", "layer_twice", "gelu_tanh", "window_and_shared_cache"])
+def test_assemblies_through_the_tensor_core_kernels(dtype, case):
+    """The assemblies of test_assemblies once more at a head size of 128 and pages of 16 keys, where the bfloat16 model
+    runs the tensor-core attention kernels, the decode kernel with the rotation inside, the streaming products and
+    recorded graphs (the float32 model the general ones): five requests together, portions and single tokens."""
+    from openinfer_b200.parts.spec import LayerCall
+    kw, pkw = {
+        "partial_rotary": (dict(rotary_dim=64), dict(rotary_dim=64)),
+        "partial_rotary_16": (dict(rotary_dim=16), dict(rotary_dim=16)),
+        "no_qk_norm": (dict(qk_norm=False), dict(qk_norm=False)),
+        "one_plus_w": (dict(offset=1.0), dict(offset=1.0)),
+        "interleaved_rotary": (dict(interleaved=True), dict(interleaved=True)),
+        "shared_cache": (dict(order=(0, LayerCall(1, read_cache_of=0))), {}),
+        "layer_twice": (dict(order=(0, 0, 1)), {}),
+        "gelu_tanh": (dict(activation="gelu_tanh"), dict(activation="gelu_tanh")),
+        "window_and_shared_cache": (dict(window=50, order=(0, LayerCall(1, read_cache_of=0))), dict(window=50)),
+    }[case]
+    spec = _mini_spec(nq=8, nkv=2, hd=128, hidden=256, inter=384, vocab=120, **kw)
+    w = _random_tensors(spec, 3)
+    if case == "one_plus_w":     # stored around zero, as such models store them: 1 + w is around one
+        w = {k: (v - 1.0 if (k.endswith("norm.weight") or k == "fn.weight") else v) for k, v in w.items()}
+    rng = random.Random(len(case))
+    seqs = {f"q{i}": [rng.randrange(120) for _ in range(n)] for i, n in enumerate((250, 131, 64, 199, 33))}
+    refs = {r: _plain_forward(spec, w, t, **pkw) for r, t in seqs.items()}
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    runner = _runner(spec, dtype, w, page=16, pages=64)
+    runner.cuda_graph = True
+    got = _drive_together(runner, seqs, rng)
+    for r in seqs:
+        assert_close(got[r], refs[r], name, f"{case}, {name}, request {r}")
     runner.cache.check()
     assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
