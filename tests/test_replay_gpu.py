@@ -1,5 +1,6 @@
 """The engine against the plain implementation under every way of cutting the work,
 in float32 and in bfloat16, for both tiny configurations."""
+import os
 import random
 
 import pytest
@@ -89,6 +90,27 @@ def test_trace_run_program(folders, workloads, tmp_path, dtype):
     steps = trace_mixed(reqs, max_tokens, seed=3)
     got = replay_trace_run(folders[name], dtype, steps, str(tmp_path / "out"), max_tokens, cfg["vocab_size"])
     _check(got, ref, dtype, f"trace_run/{dtype}")
+
+
+def test_trace_run_writes_no_file_for_a_step_in_which_nothing_is_wanted(folders, tmp_path):
+    """Steps may bring tokens whose logits nobody asks for (``want`` empty, or absent): the tokens still go through the
+    model and into the cache, ``done`` is printed, and no file is written; later steps' logits are right."""
+    name = "A"
+    cfg, w = plain.read_model_folder(folders[name])
+    rng = random.Random(9)
+    a, b = random_tokens(rng, 9, cfg["vocab_size"]), random_tokens(rng, 5, cfg["vocab_size"])
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:6], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[6:7], "want": [0]}, {"id": "b", "tokens": b[:3], "want": []}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[3:4], "want": []}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[7:], "want": [1]}, {"id": "b", "tokens": b[4:], "want": [0]}], "end": ["a", "b"]},
+    ]
+    out = str(tmp_path / "out")
+    got = replay_trace_run(folders[name], "float32", steps, out, 256, cfg["vocab_size"])   # asserts which files exist
+    assert sorted(os.listdir(out)) == ["1.f32", "3.f32"]
+    ra, rb = oracle_logits(cfg, w, a), oracle_logits(cfg, w, b)
+    assert_close(got["a"], ra[[6, 8]], "float32", "request a")
+    assert_close(got["b"], rb[[4]], "float32", "request b")
 
 
 def test_first_tokens_and_long_decode(folders, workloads):
