@@ -143,9 +143,10 @@ OI_API int oi_gated_mlp(void* out, const void* x, int dtype, int M, int hidden, 
   if (M == 0) return OI_OK;
   const int fusion = gated_mlp_fusion(dtype, w_dtype, M, hidden, inter, act_block, x, w_gate_up);
   if (fusion == 2) {
-    // Short sums (K <= 2048) stay with single CTAs: a tile's products are then no longer than its epilogue, which
-    // the pairs' larger tile does not hide.
-    const int tile = g_opt[OI_OPT_BATCH_INVARIANT] ? 256 : (M >= g_opt[OI_OPT_PAIR_MIN_ROWS] && hidden > 2048 ? kPair : 256);
+    // Short sums (K <= 2048) of fewer than 2,048 rows stay with single CTAs: a tile's products are then no longer than
+    // its epilogue, which the pairs' larger tile does not hide, and there are too few of the larger tiles to go round.
+    const bool pairs = M >= g_opt[OI_OPT_PAIR_MIN_ROWS] && (hidden > 2048 || M >= 2048);
+    const int tile = g_opt[OI_OPT_BATCH_INVARIANT] ? 256 : (pairs ? kPair : 256);
     if (tile == kPair)
       OI_TRY(oi_gemm_tcgen05_pair(act_buf, OI_BF16, inter, x, hidden, w_gate_up, hidden, M, 2 * inter, hidden, act, stream));
     else

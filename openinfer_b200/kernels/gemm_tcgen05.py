@@ -30,14 +30,15 @@ ROW_TILE = 256    # rows of the widest row tile of the prompt products (a pair o
 
 def portion_tile(rows: int, K: int = 1 << 30) -> int:
     """The tile a prompt portion of ``rows`` tokens is computed with (what the native dispatch of the fused gate/up
-    product uses). Short sums (K <= 2048) stay with single CTAs: a tile's products are then no longer than its
-    epilogue, which the pairs' larger tile does not hide (fused gate/up at 2,048 rows, N 6144: K 1024 34.6 against
-    37.6 us, K 2048 44.2 against 45.5). Measured on B200 at 2,048 rows (us, library / pair / one CTA per tile):
+    product uses). Short sums (K <= 2048) of fewer than 2,048 rows stay with single CTAs: a tile's products are then
+    no longer than its epilogue, which the pairs' larger tile does not hide (fused gate/up, N 6144, K 1024, single
+    against pair, us: 512 rows 11.3 / 13.1; 1,024 rows 17.6 / 18.8; 2,048 rows 25.7 / 25.3; 4,152 rows 46.0 / 43.8;
+    K 2048 at 2,048 rows 43.1 / 41.4). Measured on B200 at 2,048 rows (us, library / pair / one CTA per tile):
     QKV 6144 x 4096: 72 / 76 / 84; O 4096 x 4096: 49 / 51 / 51; down 4096 x 12288: 136 / 148 / 165;
     gate|up 24576 x 4096: 279 / 285 / 313 (and 285 includes the activation, which costs the library path a further
     32 us kernel): the plain products of prompt portions stay with the library unless OI_PREFILL_GEMM=pair."""
     from . import native
-    return PAIR if rows >= _lib.load().oi_option(native.OPT_PAIR_MIN_ROWS) and K > 2048 else 256
+    return PAIR if rows >= _lib.load().oi_option(native.OPT_PAIR_MIN_ROWS) and (K > 2048 or rows >= 2048) else 256
 
 
 def gemm(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_n: int = 256) -> torch.Tensor:
